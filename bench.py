@@ -1,0 +1,323 @@
+#!/usr/bin/env python
+"""Benchmark of the xLSTM hot path on B200.
+
+Default workload: the mLSTM layer kernel, forward + backward, at B=16 H=8 S=2048
+d_qk=d_v=128 chunk 64, q/k/v bf16 ~N(0,1) (k pre-scaled by 1/sqrt(d_qk), the contract of the
+op), gate logits fp32 (input N(0,1), forget N(3,1)), zero initial state, upstream grad N(0,1).
+One "step" is one forward + backward over that batch. With N GPUs every rank runs the same
+per-GPU batch (the path shards over batch with no data-path collective): weak scaling.
+
+Prints ONE JSON line (rank 0). `value` is device-timed with inputs resident in HBM; `e2e` is
+the same step through the public op API starting from pinned HOST buffers, host<->device
+copies inside the timed region. `--impl reference` times the CPU restatement of the
+reference's layer math (the reference itself is a Rust crate that cannot be built here) on
+the host cores, on a bounded sample of the same workload.
+"""
+import argparse
+import ctypes
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(B=16, H=8, T=2048, dqk=128, dhv=128, L=64)
+
+
+def flops_fwd_bwd(B, H, T, dqk, dhv, L):
+    """Causal-exact contraction FLOPs of one forward + backward (L^2 terms counted as L(L+1)/2)."""
+    nchunks = B * H * (T // L)
+    fwd = L * (L + 1) * (dqk + dhv) + 4 * L * dqk * dhv
+    bwd = L * (L + 1) * (3 * dqk + 2 * dhv) + 8 * L * dqk * dhv
+    return nchunks * fwd, nchunks * bwd
+
+
+def algorithmic_bytes(B, H, T, dqk, dhv, gbytes):
+    """Compulsory HBM traffic of the op: inputs once, outputs once; chunk states excluded."""
+    n = B * T * H
+    qkv = n * (2 * dqk + dhv) * 2
+    gates = n * 2 * 4
+    ytil = n * dhv * 2
+    scal = n * 2 * 4  # m, psi
+    fwd = qkv + gates + ytil + scal
+    bwd = qkv + gates + ytil + scal + n * dhv * gbytes + n * (2 * dqk + dhv) * gbytes + gates
+    return fwd, bwd
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=d["hbm_gbs"], tensor=d["bf16_tflops"], src="measured")
+    return dict(hbm=6650.0, tensor=1590.0, src="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks while the timed region runs."""
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def make_inputs(cfg, seed):
+    """Seeded synthetic inputs of the workload on the host (numpy)."""
+    r = np.random.default_rng(seed)
+    B, H, T, dqk, dhv = cfg["B"], cfg["H"], cfg["T"], cfg["dqk"], cfg["dhv"]
+    n = B * T
+    q = r.standard_normal((n, H * dqk), dtype=np.float32)
+    k = r.standard_normal((n, H * dqk), dtype=np.float32) / np.float32(np.sqrt(dqk))
+    v = r.standard_normal((n, H * dhv), dtype=np.float32)
+    ig = r.standard_normal((n, H), dtype=np.float32)
+    fg = r.standard_normal((n, H), dtype=np.float32) + np.float32(3.0)
+    dy = r.standard_normal((n, H * dhv), dtype=np.float32)
+    return q, k, v, ig, fg, dy
+
+
+def cpu_sample(seconds_target=15.0, threads=None):
+    """Times the CPU restatement (f32) on a slice of the workload: Bs sequences of the full length."""
+    from oracle import oracle as O
+    cfg = dict(CFG)
+    ncores = os.cpu_count() or 1
+    threads = threads or min(ncores, 64)  # each worker holds ~134 MB of per-step records
+    os.environ["OMP_NUM_THREADS"] = str(threads)
+    Bs = max(1, min(cfg["B"], (4 * threads + cfg["H"] - 1) // cfg["H"]))
+    cfg["B"] = Bs
+    q, k, v, ig, fg, dy = make_inputs(cfg, 0)
+    args = (cfg["B"], cfg["H"], cfg["T"], cfg["dqk"], cfg["dhv"])
+    t0 = time.perf_counter()
+    O.mlstm_core_fw(q, k, v, ig, fg, *args, dtype=np.float32)
+    O.mlstm_core_bw(q, k, v, ig, fg, dy, *args, dtype=np.float32)
+    dt = time.perf_counter() - t0
+    f, b = flops_fwd_bwd(**cfg)
+    return dict(seconds=dt, flops=f + b, tokens=Bs * cfg["T"], Bs=Bs, threads=threads)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    times = []
+    for i in range(args.warmup + args.steps):
+        s = cpu_sample()
+        if i >= args.warmup:
+            times.append(s["seconds"])
+    t = float(np.mean(times))
+    val = s["flops"] / t / 1e12
+    line = {
+        "impl": "reference", "metric": "mlstm_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "mlstm_layer_fwd_bwd B16 H8 S2048 dqk128 dv128 chunk64 (configs[1])",
+                   "sample": "B=%d of 16 sequences, full length" % s["Bs"]},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": s["threads"], "kind": "port",
+                         "sample": "%d of 16 sequences x 2048 positions x 8 heads, recurrent f32 oracle, OpenMP over (batch, head)" % s["Bs"]},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "tokens_per_s": s["tokens"] / t,
+    }
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    xl = importlib.import_module("neural-networks_b200")
+    ops = xl.ops
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cfg = dict(CFG)
+    gd = torch.bfloat16 if args.grad_dtype == "bf16" else torch.float32
+    st = ops.MlstmShape(cfg["B"], cfg["H"], cfg["T"], cfg["dqk"], cfg["dhv"], cfg["L"], torch.bfloat16, gd, 0)
+    hq, hk, hv, hig, hfg, hdy = make_inputs(cfg, 1000 + rank)
+    pin = lambda a, dt: torch.from_numpy(a).to(dt).pin_memory()
+    host_in = [pin(hq, torch.bfloat16), pin(hk, torch.bfloat16), pin(hv, torch.bfloat16), pin(hig, torch.float32),
+               pin(hfg, torch.float32), pin(hdy, gd)]
+    dev_in = [t.cuda(non_blocking=True) for t in host_in]
+    torch.cuda.synchronize()
+    q, k, v, ig, fg, dy = dev_in
+
+    def step():
+        fused = ops.mlstm_fused_fw(q, k, v, ig, fg, st, save_states=not args.recompute, want_state=False)
+        return fused, ops.mlstm_fused_bw(fused, q, k, v, ig, fg, dy, st, want_dstate=False)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    # ---- device-timed steps (inputs resident) -------------------------------------------
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = xl._lib.lib.xlstm_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = xl._lib.lib.xlstm_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+
+    # ---- per-kernel timing for the roofline (forward and backward separately) -----------
+    fw_ms, bw_ms = [], []
+    for _ in range(max(3, min(args.steps, 10))):
+        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        a.record()
+        fused = ops.mlstm_fused_fw(q, k, v, ig, fg, st, save_states=not args.recompute, want_state=False)
+        b.record()
+        ops.mlstm_fused_bw(fused, q, k, v, ig, fg, dy, st, want_dstate=False)
+        c.record()
+        torch.cuda.synchronize()
+        fw_ms.append(a.elapsed_time(b)); bw_ms.append(b.elapsed_time(c))
+    fw_t, bw_t = float(np.mean(fw_ms)), float(np.mean(bw_ms))
+
+    # ---- end to end from pinned host buffers ----------------------------------------------
+    outs_host = None
+
+    def e2e_step():
+        nonlocal outs_host
+        d = [t.cuda(non_blocking=True) for t in host_in]
+        fused = ops.mlstm_fused_fw(d[0], d[1], d[2], d[3], d[4], st, save_states=not args.recompute, want_state=False)
+        g = ops.mlstm_fused_bw(fused, d[0], d[1], d[2], d[3], d[4], d[5], st, want_dstate=False)
+        res = [fused.ytil, g[0], g[1], g[2], g[3], g[4]]
+        if outs_host is None:
+            outs_host = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
+        for h, r in zip(outs_host, res):
+            h.copy_(r, non_blocking=True)
+        return res
+
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_ms /= e2e_steps
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    d2h = sum(t.numel() * t.element_size() for t in outs_host)
+
+    if rank == 0:
+        ff, fb = flops_fwd_bwd(**cfg)
+        gb = 2 if gd == torch.bfloat16 else 4
+        bf, bb = algorithmic_bytes(cfg["B"], cfg["H"], cfg["T"], cfg["dqk"], cfg["dhv"], gb)
+        pk = peaks()
+        tokens = cfg["B"] * cfg["T"]
+        value = (ff + fb) * world / (ms_per_step * 1e-3) / 1e12
+        achieved = bb / (bw_t * 1e-3) / 1e9
+        cpu = cpu_sample() if world == 1 and not args.no_cpu else None
+        line = {
+            "metric": "mlstm_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "mlstm_layer_fwd_bwd B16 H8 S2048 dqk128 dv128 chunk64 (configs[1])",
+                       "per_gpu_batch": cfg["B"], "grad_dtype": args.grad_dtype,
+                       "chunk_states": "recomputed in backward" if args.recompute else "saved by forward",
+                       "l2": "inputs (%.0f MB) larger than L2" % ((bf + bb) / 1e6), "parallelism": "dp%d (batch shards, no collective)" % world},
+            "tokens_per_s": tokens * world / (ms_per_step * 1e-3),
+            "frac_of_bf16_peak": value / world / pk["tensor"],
+            "roofline": {"kernel": "mlstm backward", "bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
+                         "frac": achieved / pk["hbm"], "traffic": None, "peak_source": pk["src"],
+                         "algorithmic_bytes": bb, "launch_ms": bw_t,
+                         "forward": {"achieved": bf / (fw_t * 1e-3) / 1e9, "frac": bf / (fw_t * 1e-3) / 1e9 / pk["hbm"],
+                                     "algorithmic_bytes": bf, "launch_ms": fw_t}},
+            "e2e": {"value": (ff + fb) * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = {"value": cpu["flops"] / cpu["seconds"] / 1e12, "unit": "TFLOP/s", "cores": cpu["threads"],
+                                    "kind": "port", "seconds": cpu["seconds"],
+                                    "sample": "%d of 16 sequences x 2048 positions x 8 heads, recurrent f32 oracle, OpenMP over (batch, head)" % cpu["Bs"]}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--grad-dtype", default="f32", choices=["f32", "bf16"])
+    ap.add_argument("--recompute", action="store_true", help="backward recomputes chunk-boundary states")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

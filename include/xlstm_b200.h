@@ -1,0 +1,165 @@
+/*
+ * xlstm_b200 — C ABI of the B200 (sm_100a) engine for the xLSTM training hot path.
+ *
+ * Every entry point is an op-level replacement for one function of the reference's
+ * `gpu::ops` seam (Rust, paths below are inside the reference project): the body of the
+ * Rust function calls the C function instead of launching its NVRTC kernels.
+ *
+ * Conventions (the reference's own, src/gpu/buf.rs:24-30, src/gpu/mod.rs:128-148):
+ *   - all data pointers are DEVICE pointers; the caller allocates every input, output,
+ *     saved buffer and workspace; the callee writes every element of its outputs;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*) in program order; no
+ *     call synchronises the stream or the device;
+ *   - tensors are contiguous row-major; q/k/v and gate logits are position-major
+ *     [B*T, H*W]: element (b,h,t,c) at ((b*T+t)*H+h)*W+c (src/gpu/ops.rs:4357-4366);
+ *   - a NULL carry means "zero state", materialised by the kernel, not by a memset
+ *     (src/gpu/cuda/mlstm_fused.cu:455-465);
+ *   - the storage width of the narrow ("slab") tensors is explicit in every call
+ *     (XLSTM_F32 / XLSTM_BF16) instead of a process-wide switch (src/gpu/kernels.rs:208-215);
+ *   - there is no CPU fallback: without a CUDA device every compute call returns
+ *     XLSTM_ERR_CUDA.
+ *
+ * Return value: XLSTM_OK, XLSTM_DECLINED (shape not supported by this engine — nothing
+ * was launched; mirrors the reference's `bool` "declined" fast paths, src/gpu/ops.rs:
+ * 2712-2777), or a negative error. xlstm_last_error() gives the text of the last failure
+ * on the calling thread.
+ */
+#ifndef XLSTM_B200_H
+#define XLSTM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XLSTM_OK 0
+#define XLSTM_DECLINED 1
+#define XLSTM_ERR_ARG (-1)
+#define XLSTM_ERR_CUDA (-2)
+#define XLSTM_ERR_TIMEOUT (-3)
+#define XLSTM_ERR_WORKSPACE (-4)
+
+#define XLSTM_F32 0
+#define XLSTM_BF16 1
+
+/* flags */
+#define XLSTM_FORCE_SIMT 1u /* use the CUDA-core kernels even where a tensor-core kernel exists */
+
+int xlstm_version(void);
+const char* xlstm_last_error(void);
+/* Number of kernels this library has launched from the calling process so far. */
+uint64_t xlstm_launch_count(void);
+
+/* ---- chunkwise mLSTM core -------------------------------------------------------------
+ * Replaces ops::mlstm_fused_fw / ops::mlstm_fused_bw (src/gpu/ops.rs:4380-4537,
+ * 4546-4707) and their kernels (src/gpu/cuda/mlstm_fused.cu:136,224,271,415,514,747,859).
+ */
+typedef struct {
+    int B, H, T, dqk, dhv;
+    int L;          /* chunk length (blocking only: results do not depend on it) */
+    int dtype;      /* storage of q, k, v, ytil                (MlstmShape + SlabBuf width) */
+    int gdtype;     /* storage of d_ytil, dq, dk, dv            (reference: always f32) */
+    unsigned flags;
+} xlstm_mlstm_shape;
+
+/* Bytes of the opaque chunk-state record the forward can leave for the backward
+ * (the reference's cst/nst arrays, src/gpu/ops.rs:3955-3967). Passing saved=NULL to
+ * both calls makes the backward recompute the chunk-boundary states instead. */
+size_t xlstm_mlstm_saved_bytes(const xlstm_mlstm_shape* s);
+size_t xlstm_mlstm_fw_workspace_bytes(const xlstm_mlstm_shape* s);
+size_t xlstm_mlstm_bw_workspace_bytes(const xlstm_mlstm_shape* s, int have_saved);
+
+/* q,k [B*T,H*dqk] (k pre-scaled by 1/sqrt(dqk), src/gpu/mlstm.rs:241-252), v [B*T,H*dhv]
+ * at `dtype`; ig,fg [B*T,H] f32 gate logits; carry_* the state the call continues from
+ * (C [BH,dhv,dqk], n [BH,dqk], m [BH], f32; all three NULL = start at zero).
+ * Outputs: ytil [B*T,H*dhv] at `dtype`; msv (stabiliser m_t), psiv (normaliser psi_t),
+ * qnv (q·n before the floor), each [BH,T] f32; saved (optional); out_* the state after
+ * the last position (optional, f32). */
+int xlstm_mlstm_fw(void* stream, const xlstm_mlstm_shape* s, const void* q, const void* k,
+                   const void* v, const float* ig, const float* fg, const float* carry_C,
+                   const float* carry_n, const float* carry_m, void* ytil, float* msv,
+                   float* psiv, float* qnv, void* saved, float* out_C, float* out_n,
+                   float* out_m, void* workspace, size_t workspace_bytes);
+
+/* Backward with the stabiliser held constant. d_ytil [B*T,H*dhv] at `gdtype`;
+ * carry_dC [BH,dhv,dqk], carry_dn [BH,dqk] f32: gradient w.r.t. the state this call left
+ * (NULL = zero), out_dC/out_dn: gradient w.r.t. the state it entered with (optional).
+ * dq,dk [B*T,H*dqk], dv [B*T,H*dhv] at `gdtype`; dig,dfg [B*T,H] f32. */
+int xlstm_mlstm_bw(void* stream, const xlstm_mlstm_shape* s, const void* q, const void* k,
+                   const void* v, const float* ig, const float* fg, const float* carry_C,
+                   const float* carry_n, const float* carry_m, const void* ytil,
+                   const float* msv, const float* psiv, const float* qnv, const void* saved,
+                   const void* d_ytil, const float* carry_dC, const float* carry_dn, void* dq,
+                   void* dk, void* dv, float* dig, float* dfg, float* out_dC, float* out_dn,
+                   void* workspace, size_t workspace_bytes);
+
+/* ---- sLSTM recurrent loop ---------------------------------------------------------------
+ * Replaces ops::slstm_fused_time / slstm_fused_time_bwd (src/gpu/ops.rs:2787-2880,
+ * src/gpu/cuda/slstm_coop.cu:103,374). All tensors f32.
+ *   wh: NH==1: dense [H,4H] (gate blocks z,i,f,o);  NH>1: block-diagonal [NH,dh,4*dh],
+ *       dh=H/NH, row = source unit inside the head, column = gate*dh + unit in the head.
+ *   g [B,T,4H]: x·Wx on entry; forward overwrites its f block with the biased
+ *       pre-activation, backward overwrites all of it with the four gate deltas.
+ *   state c,n,m,h [B,H]: read when carry!=0 (else zero), always written.
+ *   slabs: nine [B,T,H] records in this order:
+ *       c_prev, n_prev, i', f', c, n, z, o, h_prev   (src/gpu/ops.rs:2206-2256).
+ */
+typedef struct {
+    float *c_prev, *n_prev, *ipr, *fpr, *c, *n, *zt, *ot, *h_prev;
+} xlstm_slstm_slabs;
+
+int xlstm_slstm_fw(void* stream, const float* wh, float* g, const float* bcat, float* c,
+                   float* n, float* m, float* h, float* out, const xlstm_slstm_slabs* slabs,
+                   int B, int H, int NH, int T, int carry, unsigned flags);
+/* dh,dc,dn [B,H]: BPTT state, read when carry!=0 (else zero), always written. */
+int xlstm_slstm_bw(void* stream, const float* wh, const float* dy, float* g, float* dh,
+                   float* dc, float* dn, const xlstm_slstm_slabs* slabs, int B, int H, int NH,
+                   int T, int carry, unsigned flags);
+
+/* ---- grouped RMSNorm -----------------------------------------------------------------------
+ * Replaces ops::rms_norm_forward_into / rms_norm_backward_into (src/gpu/ops.rs:1601-1685).
+ * x,y [rows,F] f32; gamma [F]; inv_rms [rows*F/group]. x_hat may be NULL (the backward
+ * rebuilds it from x and inv_rms). */
+int xlstm_rmsnorm_fw(void* stream, const float* x, const float* gamma, float* y,
+                     float* inv_rms, float* x_hat, int rows, int F, int group, float eps);
+size_t xlstm_rmsnorm_bw_workspace_bytes(int rows, int F);
+/* dgamma [F] is ACCUMULATED into (+=), by a fixed-order two-stage column sum. */
+int xlstm_rmsnorm_bw(void* stream, const float* dy, const float* x, const float* inv_rms,
+                     const float* gamma, float* dx, float* dgamma, int rows, int F, int group,
+                     void* workspace, size_t workspace_bytes);
+
+/* ---- softmax cross-entropy, forward + backward in one pass ---------------------------------
+ * Replaces ops::softmax_cross_entropy and masked_softmax_ce_u32_into (src/gpu/ops.rs:
+ * 1689-1714, 3567-3618). logits [rows,C] f32; targets u32 [rows]; mask u32 [rows] or NULL;
+ * dlogits = (p - onehot)*inv (may alias logits); *loss_accum += inv * sum of row losses,
+ * added on the device (no host read-back). */
+size_t xlstm_ce_workspace_bytes(int rows);
+int xlstm_ce_fw_bw(void* stream, const float* logits, const uint32_t* targets,
+                   const uint32_t* mask, float* dlogits, float* loss_accum, int rows, int C,
+                   float inv, void* workspace, size_t workspace_bytes);
+
+/* ---- AdamW over many tensors ----------------------------------------------------------------
+ * Replaces ops::adamw and AdamwQueue::flush (src/gpu/ops.rs:1775-1933, src/gpu/cuda/
+ * common.cu:323-361). `descs` is a HOST array. bc1 = 1-beta1^t, bc2 = 1-beta2^t are
+ * computed by the caller as the reference does. p_bf16 (optional) receives the bf16 copy
+ * of the updated parameter in the same pass; zero_grad!=0 clears g after use. */
+typedef struct {
+    float* p;
+    float* g;
+    float* m;
+    float* v;
+    void* p_bf16;
+    uint64_t len;
+    float wd; /* this tensor's decoupled weight decay (0 for biases and norm scales) */
+    float _pad;
+} xlstm_adamw_desc;
+
+int xlstm_adamw_multi(void* stream, const xlstm_adamw_desc* descs, int n, float lr,
+                      float beta1, float beta2, float eps, float bc1, float bc2, int zero_grad);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,134 @@
+// C-ABI layer: argument checking, workspace carving and dispatch for the mLSTM entry points,
+// plus the library-wide helpers (error text, launch counter, device properties).
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "mlstm.cuh"
+
+namespace xl {
+
+static thread_local char g_err[512] = "";
+std::atomic<uint64_t> g_launches{0};
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+static int check_shape(const char* who, const xlstm_mlstm_shape* s) {
+    XL_CHECK_ARG(s, "%s: null shape", who);
+    XL_CHECK_ARG(s->B > 0 && s->H > 0 && s->T > 0 && s->dqk > 0 && s->dhv > 0 && s->L > 0,
+                 "%s: bad shape B=%d H=%d T=%d dqk=%d dhv=%d L=%d", who, s->B, s->H, s->T, s->dqk, s->dhv, s->L);
+    XL_CHECK_ARG((s->dtype == XLSTM_F32 || s->dtype == XLSTM_BF16) && (s->gdtype == XLSTM_F32 || s->gdtype == XLSTM_BF16),
+                 "%s: unknown storage type", who);
+    return XLSTM_OK;
+}
+
+static inline int eff_L(const xlstm_mlstm_shape* s) { return s->L < s->T ? s->L : s->T; }
+static inline int num_chunks(const xlstm_mlstm_shape* s) { int L = eff_L(s); return (s->T + L - 1) / L; }
+
+// Chunk-state record: C then n, each the state ENTERING a chunk, f32.
+static size_t saved_C_bytes(const xlstm_mlstm_shape* s) {
+    return align_up((size_t)s->B * s->H * num_chunks(s) * s->dhv * s->dqk * sizeof(float), 256);
+}
+static size_t saved_n_bytes(const xlstm_mlstm_shape* s) {
+    return align_up((size_t)s->B * s->H * num_chunks(s) * s->dqk * sizeof(float), 256);
+}
+
+}  // namespace xl
+
+using namespace xl;
+
+extern "C" int xlstm_version(void) { return 1; }
+extern "C" const char* xlstm_last_error(void) { return g_err; }
+extern "C" uint64_t xlstm_launch_count(void) { return g_launches.load(); }
+
+extern "C" size_t xlstm_mlstm_saved_bytes(const xlstm_mlstm_shape* s) {
+    if (!s || s->B <= 0 || s->H <= 0 || s->T <= 0 || s->dqk <= 0 || s->dhv <= 0 || s->L <= 0) return 0;
+    return saved_C_bytes(s) + saved_n_bytes(s);
+}
+extern "C" size_t xlstm_mlstm_fw_workspace_bytes(const xlstm_mlstm_shape* s) {
+    (void)s;
+    return 0;
+}
+extern "C" size_t xlstm_mlstm_bw_workspace_bytes(const xlstm_mlstm_shape* s, int have_saved) {
+    return have_saved ? 0 : xlstm_mlstm_saved_bytes(s);
+}
+
+extern "C" int xlstm_mlstm_fw(void* stream, const xlstm_mlstm_shape* s, const void* q, const void* k, const void* v,
+                              const float* ig, const float* fg, const float* carry_C, const float* carry_n,
+                              const float* carry_m, void* ytil, float* msv, float* psiv, float* qnv, void* saved,
+                              float* out_C, float* out_n, float* out_m, void* workspace, size_t workspace_bytes) {
+    (void)workspace; (void)workspace_bytes;
+    int rc = check_shape("mlstm_fw", s);
+    if (rc) return rc;
+    XL_CHECK_ARG(q && k && v && ig && fg && ytil && msv && psiv && qnv, "mlstm_fw: null pointer");
+    XL_CHECK_ARG((carry_C != nullptr) == (carry_n != nullptr) && (carry_C != nullptr) == (carry_m != nullptr),
+                 "mlstm_fw: carry C, n, m must be given together");
+    MlstmFwArgs a = {};
+    a.q = q; a.k = k; a.v = v; a.ig = ig; a.fg = fg; a.cC = carry_C; a.cn = carry_n; a.cm = carry_m;
+    a.ytil = ytil; a.msv = msv; a.psiv = psiv; a.qnv = qnv;
+    if (saved) { a.savedC = (float*)saved; a.savedn = (float*)((char*)saved + saved_C_bytes(s)); }
+    a.oC = out_C; a.on = out_n; a.om = out_m;
+    a.B = s->B; a.H = s->H; a.T = s->T; a.dqk = s->dqk; a.dhv = s->dhv; a.L = eff_L(s); a.NC = num_chunks(s);
+    a.states_only = 0;
+    return mlstm_fw_simt_launch((cudaStream_t)stream, a, s->dtype);
+}
+
+extern "C" int xlstm_mlstm_bw(void* stream, const xlstm_mlstm_shape* s, const void* q, const void* k, const void* v,
+                              const float* ig, const float* fg, const float* carry_C, const float* carry_n,
+                              const float* carry_m, const void* ytil, const float* msv, const float* psiv,
+                              const float* qnv, const void* saved, const void* d_ytil, const float* carry_dC,
+                              const float* carry_dn, void* dq, void* dk, void* dv, float* dig, float* dfg,
+                              float* out_dC, float* out_dn, void* workspace, size_t workspace_bytes) {
+    int rc = check_shape("mlstm_bw", s);
+    if (rc) return rc;
+    XL_CHECK_ARG(q && k && v && ig && fg && ytil && msv && psiv && qnv && d_ytil && dq && dk && dv && dig && dfg,
+                 "mlstm_bw: null pointer");
+    XL_CHECK_ARG((carry_C != nullptr) == (carry_n != nullptr) && (carry_C != nullptr) == (carry_m != nullptr),
+                 "mlstm_bw: carry C, n, m must be given together");
+    XL_CHECK_ARG((carry_dC != nullptr) == (carry_dn != nullptr), "mlstm_bw: carry dC, dn must be given together");
+    cudaStream_t st = (cudaStream_t)stream;
+    const float *sC, *sn;
+    if (saved) {
+        sC = (const float*)saved;
+        sn = (const float*)((const char*)saved + saved_C_bytes(s));
+    } else {
+        // recompute the chunk-boundary states into the workspace
+        size_t need = xlstm_mlstm_bw_workspace_bytes(s, 0);
+        if (!workspace || workspace_bytes < need) {
+            set_error("mlstm_bw: workspace of %zu B is smaller than the %zu B needed to recompute chunk states",
+                      workspace_bytes, need);
+            return XLSTM_ERR_WORKSPACE;
+        }
+        MlstmFwArgs f = {};
+        f.q = q; f.k = k; f.v = v; f.ig = ig; f.fg = fg; f.cC = carry_C; f.cn = carry_n; f.cm = carry_m;
+        f.savedC = (float*)workspace; f.savedn = (float*)((char*)workspace + saved_C_bytes(s));
+        f.B = s->B; f.H = s->H; f.T = s->T; f.dqk = s->dqk; f.dhv = s->dhv; f.L = eff_L(s); f.NC = num_chunks(s);
+        f.states_only = 1;
+        rc = mlstm_fw_simt_launch(st, f, s->dtype);
+        if (rc) return rc;
+        sC = f.savedC; sn = f.savedn;
+    }
+    MlstmBwArgs a = {};
+    a.q = q; a.k = k; a.v = v; a.ig = ig; a.fg = fg; a.cm = carry_m; a.ytil = ytil; a.msv = msv; a.psiv = psiv;
+    a.qnv = qnv; a.savedC = sC; a.savedn = sn; a.dytil = d_ytil; a.cdC = carry_dC; a.cdn = carry_dn;
+    a.dq = dq; a.dk = dk; a.dv = dv; a.dig = dig; a.dfg = dfg; a.odC = out_dC; a.odn = out_dn;
+    a.B = s->B; a.H = s->H; a.T = s->T; a.dqk = s->dqk; a.dhv = s->dhv; a.L = eff_L(s); a.NC = num_chunks(s);
+    return mlstm_bw_simt_launch(st, a, s->dtype, s->gdtype);
+}

@@ -1,0 +1,196 @@
+// Softmax cross-entropy, forward and backward in one pass over the logits.
+//
+// One CTA (wide rows) or one warp (narrow rows) owns a row: it streams the logits once
+// from HBM while keeping them in shared memory / registers, reduces max and sum-exp, then
+// writes dlogits = (softmax - onehot) * inv from the on-chip copy: 8*C bytes per row. Row
+// losses go to a scratch vector and are summed on the device in a fixed order into
+// *loss_accum, so no host read-back sits on the step's critical path.
+//
+// Math: src/nn2/loss.rs:10-53 (p_t floored at 1e-30); masked form: src/gpu/cuda/
+// mlstm_ops.cu:332-370. Kernels replaced: src/gpu/cuda/common.cu:270-289.
+#include "common.cuh"
+
+namespace xl {
+
+// ---- wide rows: one CTA per row, row cached in shared memory ---------------------------------
+template <bool CACHE>
+__global__ void __launch_bounds__(1024) ce_row_cta(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
+                                                   const uint32_t* __restrict__ mask, float* __restrict__ dlogits,
+                                                   float* __restrict__ row_loss, int rows, int C, float inv) {
+    extern __shared__ __align__(16) float srow[];  // [C] when CACHE
+    __shared__ float red[32];
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float* z = logits + (size_t)r * C;
+        float* d = dlogits + (size_t)r * C;
+        if (mask && !mask[r]) {
+            for (int j = threadIdx.x; j < C; j += blockDim.x) d[j] = 0.f;
+            if (threadIdx.x == 0) row_loss[r] = 0.f;
+            continue;
+        }
+        // pass 1: load + running max / sum-exp per thread (online softmax)
+        float mx = -INFINITY, sum = 0.f;
+        const bool v4 = (C % 4 == 0) && (((uintptr_t)z & 15) == 0) && (((uintptr_t)d & 15) == 0);
+        if (v4) {
+            const float4* z4 = reinterpret_cast<const float4*>(z);
+            for (int j = threadIdx.x; j < C / 4; j += blockDim.x) {
+                float4 t = __ldcs(z4 + j);
+                if (CACHE) reinterpret_cast<float4*>(srow)[j] = t;
+                float m4 = fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w));
+                if (m4 > mx) { sum *= expf(mx - m4); mx = m4; }
+                sum += expf(t.x - mx) + expf(t.y - mx) + expf(t.z - mx) + expf(t.w - mx);
+            }
+        } else {
+            for (int j = threadIdx.x; j < C; j += blockDim.x) {
+                float t = z[j];
+                if (CACHE) srow[j] = t;
+                if (t > mx) { sum *= expf(mx - t); mx = t; }
+                sum += expf(t - mx);
+            }
+        }
+        float gmx = block_max(mx, red);
+        sum = (mx == -INFINITY) ? 0.f : sum * expf(mx - gmx);
+        float gsum = block_sum(sum, red);
+        const float is = 1.f / gsum;
+        const uint32_t tg = targets[r];
+        if (threadIdx.x == 0) {
+            float zt = CACHE ? srow[tg] : z[tg];
+            float pt = expf(zt - gmx) * is;
+            row_loss[r] = -logf(fmaxf(pt, 1e-30f));
+        }
+        if (!CACHE) __syncthreads();  // dlogits may alias logits: read z[target] before anyone overwrites it
+        // pass 2: gradient from the on-chip copy
+        if (v4) {
+            float4* d4 = reinterpret_cast<float4*>(d);
+            for (int j = threadIdx.x; j < C / 4; j += blockDim.x) {
+                float4 t = CACHE ? reinterpret_cast<float4*>(srow)[j] : reinterpret_cast<const float4*>(z)[j];
+                float4 o;
+                o.x = expf(t.x - gmx) * is; o.y = expf(t.y - gmx) * is;
+                o.z = expf(t.z - gmx) * is; o.w = expf(t.w - gmx) * is;
+                uint32_t base = 4u * j;
+                if (tg == base) o.x -= 1.f;
+                else if (tg == base + 1u) o.y -= 1.f;
+                else if (tg == base + 2u) o.z -= 1.f;
+                else if (tg == base + 3u) o.w -= 1.f;
+                o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
+                __stcs(d4 + j, o);
+            }
+        } else {
+            for (int j = threadIdx.x; j < C; j += blockDim.x) {
+                float t = CACHE ? srow[j] : z[j];
+                float o = expf(t - gmx) * is;
+                if ((uint32_t)j == tg) o -= 1.f;
+                d[j] = o * inv;
+            }
+        }
+        __syncthreads();  // srow is reused by the next row
+    }
+}
+
+// ---- narrow rows (C <= 1024): one warp per row, row in registers -----------------------------
+template <int VPL>
+__global__ void __launch_bounds__(256) ce_row_warp(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
+                                                   const uint32_t* __restrict__ mask, float* __restrict__ dlogits,
+                                                   float* __restrict__ row_loss, int rows, int C, float inv) {
+    const int lane = threadIdx.x & 31;
+    const int wglobal = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int wstride = gridDim.x * (blockDim.x >> 5);
+    for (int r = wglobal; r < rows; r += wstride) {
+        const float* z = logits + (size_t)r * C;
+        float* d = dlogits + (size_t)r * C;
+        if (mask && !mask[r]) {
+            for (int j = lane; j < C; j += 32) d[j] = 0.f;
+            if (lane == 0) row_loss[r] = 0.f;
+            continue;
+        }
+        float v[VPL];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            int j = i * 32 + lane;
+            v[i] = j < C ? z[j] : -INFINITY;
+            mx = fmaxf(mx, v[i]);
+        }
+        mx = warp_max(mx);
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            v[i] = expf(v[i] - mx);  // exp(-inf) = 0 for the padding
+            sum += v[i];
+        }
+        sum = warp_sum(sum);
+        const float is = 1.f / sum;
+        const uint32_t tg = targets[r];
+        float pt = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            int j = i * 32 + lane;
+            float p = v[i] * is;
+            if ((uint32_t)j == tg) { pt = p; p -= 1.f; }
+            if (j < C) d[j] = p * inv;
+        }
+        pt = warp_sum(pt);
+        if (lane == 0) row_loss[r] = -logf(fmaxf(pt, 1e-30f));
+    }
+}
+
+// *loss_accum += inv * sum(row_loss), one CTA, fixed order.
+__global__ void __launch_bounds__(1024) ce_loss_reduce(const float* __restrict__ row_loss, float* loss_accum, int rows, float inv) {
+    __shared__ float red[32];
+    float s = 0.f;
+    for (int r = threadIdx.x; r < rows; r += blockDim.x) s += row_loss[r];
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) *loss_accum += s * inv;
+}
+
+}  // namespace xl
+
+using namespace xl;
+
+extern "C" size_t xlstm_ce_workspace_bytes(int rows) { return rows > 0 ? (size_t)rows * sizeof(float) : 0; }
+
+extern "C" int xlstm_ce_fw_bw(void* stream, const float* logits, const uint32_t* targets, const uint32_t* mask,
+                              float* dlogits, float* loss_accum, int rows, int C, float inv, void* workspace,
+                              size_t workspace_bytes) {
+    XL_CHECK_ARG(logits && targets && dlogits && loss_accum, "ce_fw_bw: null pointer");
+    XL_CHECK_ARG(rows >= 0 && C > 0, "ce_fw_bw: bad shape rows=%d C=%d", rows, C);
+    if (rows == 0) return XLSTM_OK;
+    if (!workspace || workspace_bytes < xlstm_ce_workspace_bytes(rows)) {
+        set_error("ce_fw_bw: workspace of %zu B is smaller than the %zu B required", workspace_bytes,
+                  xlstm_ce_workspace_bytes(rows));
+        return XLSTM_ERR_WORKSPACE;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    float* row_loss = (float*)workspace;
+    if (C <= 1024) {
+        int wpb = 8;
+        int nb = (rows + wpb - 1) / wpb, maxb = sm_count() * 8;
+        int grid = nb < maxb ? nb : maxb;
+#define RUN(V) ce_row_warp<V><<<grid, 256, 0, st>>>(logits, targets, mask, dlogits, row_loss, rows, C, inv)
+        if (C <= 32) RUN(1);
+        else if (C <= 64) RUN(2);
+        else if (C <= 128) RUN(4);
+        else if (C <= 256) RUN(8);
+        else if (C <= 512) RUN(16);
+        else RUN(32);
+#undef RUN
+        XL_LAUNCH_OK("ce_row_warp");
+    } else {
+        size_t smem = (size_t)C * sizeof(float);
+        int threads = C >= 8192 ? 1024 : 256;
+        if (smem <= 200 * 1024) {
+            XL_CUDA(cudaFuncSetAttribute(ce_row_cta<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            int per_sm = (int)((220 * 1024) / (smem + 1024));
+            if (per_sm < 1) per_sm = 1;
+            if (per_sm > 2048 / threads) per_sm = 2048 / threads;
+            int maxb = sm_count() * per_sm;
+            ce_row_cta<true><<<rows < maxb ? rows : maxb, threads, smem, st>>>(logits, targets, mask, dlogits, row_loss, rows, C, inv);
+        } else {
+            int maxb = sm_count() * 2;
+            ce_row_cta<false><<<rows < maxb ? rows : maxb, 1024, 0, st>>>(logits, targets, mask, dlogits, row_loss, rows, C, inv);
+        }
+        XL_LAUNCH_OK("ce_row_cta");
+    }
+    ce_loss_reduce<<<1, 1024, 0, st>>>(row_loss, loss_accum, rows, inv);
+    XL_LAUNCH_OK("ce_loss_reduce");
+    return XLSTM_OK;
+}

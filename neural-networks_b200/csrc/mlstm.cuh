@@ -1,0 +1,38 @@
+// Argument blocks shared by the mLSTM kernels and the C-ABI layer.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace xl {
+
+struct MlstmFwArgs {
+    const void *q, *k, *v;
+    const float *ig, *fg;
+    const float *cC, *cn, *cm;  // carry in (may be null)
+    void* ytil;
+    float *msv, *psiv, *qnv;
+    float *savedC, *savedn;     // [BH, NC, dhv*dqk], [BH, NC, dqk]: state entering each chunk (may be null)
+    float *oC, *on, *om;        // state after the last position (may be null)
+    int B, H, T, dqk, dhv, L, NC;
+    int states_only;            // 1: walk the state recurrence only (recompute pass of the backward)
+};
+
+struct MlstmBwArgs {
+    const void *q, *k, *v;
+    const float *ig, *fg;
+    const float* cm;            // m the forward call entered with (may be null = 0)
+    const void* ytil;
+    const float *msv, *psiv, *qnv;
+    const float *savedC, *savedn;
+    const void* dytil;
+    const float *cdC, *cdn;     // BPTT carry in (may be null)
+    void *dq, *dk, *dv;
+    float *dig, *dfg;
+    float *odC, *odn;
+    int B, H, T, dqk, dhv, L, NC;
+};
+
+int mlstm_fw_simt_launch(cudaStream_t st, const MlstmFwArgs& a, int dtype);
+int mlstm_bw_simt_launch(cudaStream_t st, const MlstmBwArgs& a, int dtype, int gdtype);
+bool mlstm_simt_supported(int L, int dqk, int dhv, int dtype);
+
+}  // namespace xl

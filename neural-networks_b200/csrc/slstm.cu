@@ -1,0 +1,522 @@
+// sLSTM recurrent loop, forward and backward, as persistent thread-block-cluster kernels.
+//
+// The T-loop is a chain of dependent small mat-vecs, so it is latency-bound: the design
+// keeps everything a step needs on chip. A cluster of CS CTAs owns one (head, batch group);
+// each CTA keeps its slice of the recurrent matrix in shared memory for the whole call
+// (fp32, so results track the fp32 reference), computes its units' gate pre-activations
+// from the head's previous h, applies the pointwise cell, and broadcasts its new h to the
+// other CTAs of the cluster through distributed shared memory. One hardware cluster barrier
+// per timestep is the only inter-CTA synchronisation; there is no grid-wide barrier and no
+// spin-wait. Heads (block-diagonal recurrence) and batch groups are independent clusters.
+//
+// The backward runs the same structure on the transposed slice: a CTA owns the rows of Wh
+// belonging to its units, the gate deltas of the whole head are what is broadcast, and
+// dh_{t-1} for its own units is what the mat-vec produces.
+//
+// Math: src/nn2/slstm.rs:286-325, 399-423 with the GPU kernels' gate clamps
+// (src/gpu/cuda/slstm_fused.cu:132-142). Kernels replaced: src/gpu/cuda/slstm_coop.cu:103-515.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace xl {
+
+static constexpr int kThreads = 256;
+static constexpr int kPF = 2;  // pointwise items per thread whose global operands are prefetched
+
+struct SlstmArgs {
+    const float* wh;
+    float* g;
+    const float* bcat;
+    float *c, *n, *m, *h;      // forward state [B,H]
+    float* out;
+    xlstm_slstm_slabs s;
+    const float* dy;
+    float *dh, *dc, *dn;       // backward state [B,H]
+    int B, H, NH, T, carry;
+    int dhd;                   // units per head
+    int CS, UPC;               // cluster size, units per CTA
+    int KS;                    // k-slices of the mat-vec
+};
+
+struct SlstmSmem {
+    size_t ws, xin, part, stage, state, total;
+};
+
+static SlstmSmem smem_layout(int K, int NOUT, int BG, int KS, int UPC, int nstate) {
+    SlstmSmem l;
+    int NOUTp = (NOUT + 1) & ~1;
+    auto a16 = [](size_t x) { return (x + 15) / 16 * 16; };
+    l.ws = 0;
+    l.xin = l.ws + a16((size_t)K * NOUTp * 4);
+    l.part = l.xin + a16((size_t)2 * K * BG * 4);
+    l.stage = l.part + a16((size_t)KS * BG * NOUTp * 4);
+    l.state = l.stage + a16((size_t)BG * 4 * UPC * 4);
+    l.total = l.state + a16((size_t)nstate * BG * UPC * 4);
+    return l;
+}
+
+// out[b][j] partial sums over a k-slice: part[(ks*BG + b)*NOUTp + j] = sum_{k in slice} xin[k*BG+b] * Ws[k*NOUTp+j]
+template <int BG>
+__device__ __forceinline__ void matvec(const float* __restrict__ Ws, const float* __restrict__ xin,
+                                       float* __restrict__ part, int K, int NOUTp, int KS) {
+    const int npairs = NOUTp >> 1;
+    const int rows_per = (K + KS - 1) / KS;
+    for (int item = threadIdx.x; item < npairs * KS; item += kThreads) {
+        const int cp = item % npairs, ks = item / npairs;
+        const int r0 = ks * rows_per, r1 = min(K, r0 + rows_per);
+        float a0[BG], a1[BG];
+#pragma unroll
+        for (int b = 0; b < BG; ++b) a0[b] = a1[b] = 0.f;
+        const float* wp = Ws + (size_t)r0 * NOUTp + 2 * cp;
+        const float* xp = xin + (size_t)r0 * BG;
+#pragma unroll 4
+        for (int r = r0; r < r1; ++r) {
+            const float2 w = *reinterpret_cast<const float2*>(wp);
+            if (BG % 4 == 0) {
+#pragma unroll
+                for (int b4 = 0; b4 < BG / 4; ++b4) {
+                    const float4 x = *reinterpret_cast<const float4*>(xp + 4 * b4);
+                    a0[4 * b4 + 0] += x.x * w.x; a1[4 * b4 + 0] += x.x * w.y;
+                    a0[4 * b4 + 1] += x.y * w.x; a1[4 * b4 + 1] += x.y * w.y;
+                    a0[4 * b4 + 2] += x.z * w.x; a1[4 * b4 + 2] += x.z * w.y;
+                    a0[4 * b4 + 3] += x.w * w.x; a1[4 * b4 + 3] += x.w * w.y;
+                }
+            } else {
+#pragma unroll
+                for (int b = 0; b < BG; ++b) {
+                    const float x = xp[b];
+                    a0[b] += x * w.x;
+                    a1[b] += x * w.y;
+                }
+            }
+            wp += NOUTp;
+            xp += BG;
+        }
+#pragma unroll
+        for (int b = 0; b < BG; ++b) {
+            float* o = part + ((size_t)ks * BG + b) * NOUTp + 2 * cp;
+            o[0] = a0[b];
+            o[1] = a1[b];
+        }
+    }
+}
+
+// Copies stage[b][col_local] (ncol local columns per gate block layout given by the caller) into
+// every cluster peer's exchange buffer xin_next[(col_global)*BG + b].
+template <int BG>
+__device__ __forceinline__ void broadcast(cg::cluster_group& cluster, const float* stage, float* xin_next, int CS,
+                                          int nloc, int nblocks, int block_stride_loc, int block_stride_glob,
+                                          int glob_off) {
+    // local column index lc in [0, nblocks*nloc): block = lc / nloc (gate), within = lc % nloc
+    const int total = nblocks * nloc * BG;
+    for (int e = threadIdx.x; e < total; e += kThreads) {
+        const int lc = e / BG, b = e % BG;
+        const int blk = lc / nloc, w = lc % nloc;
+        const float v = stage[(size_t)b * block_stride_loc * nblocks + blk * block_stride_loc + w];
+        const size_t dst = (size_t)(blk * block_stride_glob + glob_off + w) * BG + b;
+        for (int p = 0; p < CS; ++p) {
+            float* remote = cluster.map_shared_rank(xin_next, p);
+            remote[dst] = v;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Forward
+// ---------------------------------------------------------------------------------------------
+template <int BG>
+__global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmSmem lay) {
+    cg::cluster_group cluster = cg::this_cluster();
+    const int CS = a.CS, UPC = a.UPC, dhd = a.dhd, H = a.H, T = a.T;
+    const int cr = (int)cluster.block_rank();
+    const int cid = blockIdx.x / CS;
+    const int nbg = (a.B + BG - 1) / BG;
+    const int hd = cid / nbg, b0 = (cid % nbg) * BG;
+    const int K = dhd, NOUT = 4 * UPC, NOUTp = NOUT;  // 4*UPC is even
+    const int tid = threadIdx.x;
+
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* Ws = (float*)(smem + lay.ws);
+    float* xin = (float*)(smem + lay.xin);      // [2][K][BG]
+    float* part = (float*)(smem + lay.part);    // [KS][BG][NOUTp]
+    float* stage = (float*)(smem + lay.stage);  // [BG][UPC]
+    float* st = (float*)(smem + lay.state);     // c,n,m: [3][BG*UPC]
+    const int NI = BG * UPC;
+
+    // recurrent slice: Ws[r][gate*UPC + ul] = wh[hd][r][gate*dhd + cr*UPC + ul]
+    for (int i = tid; i < K * NOUT; i += kThreads) {
+        int r = i / NOUT, col = i % NOUT, gate = col / UPC, ul = col % UPC;
+        Ws[(size_t)r * NOUTp + col] = a.wh[((size_t)hd * dhd + r) * 4 * dhd + gate * dhd + cr * UPC + ul];
+    }
+    // initial h of the whole head, and this CTA's c,n,m
+    for (int i = tid; i < K * BG; i += kThreads) {
+        int r = i / BG, b = i % BG;
+        float v = 0.f;
+        if (a.carry && b0 + b < a.B) v = a.h[(size_t)(b0 + b) * H + hd * dhd + r];
+        xin[i] = v;
+    }
+    for (int it = tid; it < NI; it += kThreads) {
+        int b = it / UPC, ul = it % UPC;
+        size_t si = (size_t)(b0 + b) * H + hd * dhd + cr * UPC + ul;
+        bool live = a.carry && b0 + b < a.B;
+        st[it] = live ? a.c[si] : 0.f;
+        st[NI + it] = live ? a.n[si] : 0.f;
+        st[2 * NI + it] = live ? a.m[si] : 0.f;
+    }
+    cluster.sync();  // every CTA's buffers exist before any remote write
+
+    int cur = 0;
+    for (int t = 0; t < T; ++t) {
+        // issue this step's global reads early; they land while the mat-vec runs
+        float gpre[kPF][4];
+#pragma unroll
+        for (int p = 0; p < kPF; ++p) {
+            int it = tid + p * kThreads;
+            if (it < NI) {
+                int b = it / UPC, ul = it % UPC;
+                if (b0 + b < a.B) {
+                    const float* gt = a.g + ((size_t)(b0 + b) * T + t) * 4 * H + hd * dhd + cr * UPC + ul;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) gpre[p][q] = __ldcs(gt + (size_t)q * H);
+                }
+            }
+        }
+        matvec<BG>(Ws, xin + (size_t)cur * K * BG, part, K, NOUTp, a.KS);
+        __syncthreads();
+        auto cell = [&](int it, const float* gin) {
+            const int b = it / UPC, ul = it % UPC;
+            float hh = 0.f;
+            if (b0 + b < a.B) {
+                const int j = hd * dhd + cr * UPC + ul;
+                float gh[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int ks = 0; ks < a.KS; ++ks) {
+                    const float* pp = part + ((size_t)ks * BG + b) * NOUTp + ul;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) gh[q] += pp[q * UPC];
+                }
+                float* gt = a.g + ((size_t)(b0 + b) * T + t) * 4 * H + j;
+                const float z_pre = gin[0] + gh[0] + a.bcat[j];
+                const float i_pre = gin[1] + gh[1] + a.bcat[H + j];
+                const float f_pre = gin[2] + gh[2] + a.bcat[2 * H + j];
+                const float o_pre = gin[3] + gh[3] + a.bcat[3 * H + j];
+                const size_t s = ((size_t)(b0 + b) * T + t) * H + j;
+                const float hp = xin[(size_t)cur * K * BG + (size_t)(cr * UPC + ul) * BG + b];
+                const float cp = st[it], np = st[NI + it], mp = st[2 * NI + it];
+                const float z = tanhf(z_pre);
+                const float o = stable_sigmoid(o_pre);
+                const float fm = log_sigmoid(f_pre) + mp;
+                const float m = (np == 0.f) ? i_pre : fmaxf(fm, i_pre);
+                const float ip = fminf(1.f, expf(i_pre - m));
+                const float fp = fminf(1.f, expf(fm - m));
+                const float c = fp * cp + ip * z;
+                const float n = fp * np + ip;
+                hh = o * c / n;
+                st[it] = c; st[NI + it] = n; st[2 * NI + it] = m;
+                __stcs(gt + (size_t)2 * H, f_pre);
+                __stcs(a.s.h_prev + s, hp);
+                __stcs(a.s.c_prev + s, cp);
+                __stcs(a.s.n_prev + s, np);
+                __stcs(a.s.zt + s, z);
+                __stcs(a.s.ot + s, o);
+                __stcs(a.s.ipr + s, ip);
+                __stcs(a.s.fpr + s, fp);
+                __stcs(a.s.c + s, c);
+                __stcs(a.s.n + s, n);
+                __stcs(a.out + s, hh);
+            }
+            stage[(size_t)b * UPC + ul] = hh;
+        };
+#pragma unroll
+        for (int p = 0; p < kPF; ++p) {
+            const int it = tid + p * kThreads;
+            if (it < NI) cell(it, gpre[p]);
+        }
+        for (int it = tid + kPF * kThreads; it < NI; it += kThreads) {
+            const int b = it / UPC, ul = it % UPC;
+            float gin[4] = {0.f, 0.f, 0.f, 0.f};
+            if (b0 + b < a.B) {
+                const float* gt = a.g + ((size_t)(b0 + b) * T + t) * 4 * H + hd * dhd + cr * UPC + ul;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) gin[q] = gt[(size_t)q * H];
+            }
+            cell(it, gin);
+        }
+        __syncthreads();
+        broadcast<BG>(cluster, stage, xin + (size_t)(cur ^ 1) * K * BG, CS, UPC, 1, UPC, 0, cr * UPC);
+        cluster.sync();
+        cur ^= 1;
+    }
+    // final state
+    for (int it = tid; it < NI; it += kThreads) {
+        int b = it / UPC, ul = it % UPC;
+        if (b0 + b >= a.B) continue;
+        size_t si = (size_t)(b0 + b) * H + hd * dhd + cr * UPC + ul;
+        a.c[si] = st[it];
+        a.n[si] = st[NI + it];
+        a.m[si] = st[2 * NI + it];
+        a.h[si] = xin[(size_t)cur * K * BG + (size_t)(cr * UPC + ul) * BG + b];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward
+// ---------------------------------------------------------------------------------------------
+template <int BG>
+__global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmSmem lay) {
+    cg::cluster_group cluster = cg::this_cluster();
+    const int CS = a.CS, UPC = a.UPC, dhd = a.dhd, H = a.H, T = a.T;
+    const int cr = (int)cluster.block_rank();
+    const int cid = blockIdx.x / CS;
+    const int nbg = (a.B + BG - 1) / BG;
+    const int hd = cid / nbg, b0 = (cid % nbg) * BG;
+    const int K = 4 * dhd, NOUT = UPC, NOUTp = (NOUT + 1) & ~1;
+    const int tid = threadIdx.x;
+
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* Ws = (float*)(smem + lay.ws);        // [K = gate*dhd+u][NOUTp = own rows]
+    float* xin = (float*)(smem + lay.xin);      // [2][K][BG]: gate deltas of the head
+    float* part = (float*)(smem + lay.part);    // [KS][BG][NOUTp]: dh partials for own units
+    float* stage = (float*)(smem + lay.stage);  // [BG][4][UPC]
+    float* st = (float*)(smem + lay.state);     // dc, dn: [2][BG*UPC]
+    const int NI = BG * UPC;
+
+    // transposed slice: Ws[gate*dhd + u][rl] = wh[hd][cr*UPC + rl][gate*dhd + u]
+    for (int i = tid; i < K * NOUTp; i += kThreads) {
+        int col = i / NOUTp, rl = i % NOUTp;
+        Ws[i] = rl < NOUT ? a.wh[((size_t)hd * dhd + cr * UPC + rl) * 4 * dhd + col] : 0.f;
+    }
+    // dh carry goes into k-slice 0 of the partial buffer, the other slices start at zero
+    for (int i = tid; i < a.KS * BG * NOUTp; i += kThreads) {
+        int ks = i / (BG * NOUTp), b = (i / NOUTp) % BG, rl = i % NOUTp;
+        float v = 0.f;
+        if (ks == 0 && rl < NOUT && a.carry && b0 + b < a.B) v = a.dh[(size_t)(b0 + b) * H + hd * dhd + cr * UPC + rl];
+        part[i] = v;
+    }
+    for (int it = tid; it < NI; it += kThreads) {
+        int b = it / UPC, ul = it % UPC;
+        size_t si = (size_t)(b0 + b) * H + hd * dhd + cr * UPC + ul;
+        bool live = a.carry && b0 + b < a.B;
+        st[it] = live ? a.dc[si] : 0.f;
+        st[NI + it] = live ? a.dn[si] : 0.f;
+    }
+    cluster.sync();
+
+    int cur = 0;
+    // operands of the first processed step
+    float pre[kPF][10];
+    auto prefetch = [&](int t) {
+#pragma unroll
+        for (int p = 0; p < kPF; ++p) {
+            int it = tid + p * kThreads;
+            if (it < NI && t >= 0) {
+                int b = it / UPC, ul = it % UPC;
+                if (b0 + b < a.B) {
+                    const int j = hd * dhd + cr * UPC + ul;
+                    const size_t s = ((size_t)(b0 + b) * T + t) * H + j;
+                    pre[p][0] = __ldcs(a.dy + s);
+                    pre[p][1] = __ldcs(a.s.ot + s);
+                    pre[p][2] = __ldcs(a.s.c + s);
+                    pre[p][3] = __ldcs(a.s.n + s);
+                    pre[p][4] = __ldcs(a.s.fpr + s);
+                    pre[p][5] = __ldcs(a.s.ipr + s);
+                    pre[p][6] = __ldcs(a.s.zt + s);
+                    pre[p][7] = __ldcs(a.s.c_prev + s);
+                    pre[p][8] = __ldcs(a.s.n_prev + s);
+                    pre[p][9] = __ldcs(a.g + ((size_t)(b0 + b) * T + t) * 4 * H + 2 * H + j);
+                }
+            }
+        }
+    };
+    prefetch(T - 1);
+    for (int t = T - 1; t >= 0; --t) {
+        auto cell = [&](int it, const float* op) {
+            const int b = it / UPC, ul = it % UPC;
+            float dz = 0.f, di = 0.f, df = 0.f, dob = 0.f;
+            if (b0 + b < a.B) {
+                const int j = hd * dhd + cr * UPC + ul;
+                float* gt = a.g + ((size_t)(b0 + b) * T + t) * 4 * H + j;
+                float dhr = 0.f;
+                for (int ks = 0; ks < a.KS; ++ks) dhr += part[((size_t)ks * BG + b) * NOUTp + ul];
+                const float d_h = op[0] + dhr;
+                const float o = op[1], c = op[2], n = op[3], f = op[4], i = op[5], z = op[6];
+                dob = d_h * (c / n) * o * (1.f - o);
+                const float d_c = d_h * o / n + st[it];
+                const float d_n = d_h * o * (-c) / (n * n) + st[NI + it];
+                const float d_f_gate = d_c * op[7] + d_n * op[8];
+                const float d_i_gate = d_c * z + d_n;
+                dz = d_c * i * (1.f - z * z);
+                di = d_i_gate * i;
+                df = d_f_gate * f * (1.f - stable_sigmoid(op[9]));
+                st[it] = d_c * f;
+                st[NI + it] = d_n * f;
+                __stcs(gt, dz);
+                __stcs(gt + (size_t)H, di);
+                __stcs(gt + (size_t)2 * H, df);
+                __stcs(gt + (size_t)3 * H, dob);
+            }
+            float* sg = stage + (size_t)b * 4 * UPC + ul;
+            sg[0] = dz; sg[UPC] = di; sg[2 * UPC] = df; sg[3 * UPC] = dob;
+        };
+#pragma unroll
+        for (int p = 0; p < kPF; ++p) {
+            const int it = tid + p * kThreads;
+            if (it < NI) cell(it, pre[p]);
+        }
+        for (int it = tid + kPF * kThreads; it < NI; it += kThreads) {
+            const int b = it / UPC, ul = it % UPC;
+            float op[10] = {0.f, 0.f, 0.f, 1.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (b0 + b < a.B) {
+                const int j = hd * dhd + cr * UPC + ul;
+                const size_t s = ((size_t)(b0 + b) * T + t) * H + j;
+                op[0] = a.dy[s]; op[1] = a.s.ot[s]; op[2] = a.s.c[s]; op[3] = a.s.n[s]; op[4] = a.s.fpr[s];
+                op[5] = a.s.ipr[s]; op[6] = a.s.zt[s]; op[7] = a.s.c_prev[s]; op[8] = a.s.n_prev[s];
+                op[9] = a.g[((size_t)(b0 + b) * T + t) * 4 * H + 2 * H + j];
+            }
+            cell(it, op);
+        }
+        __syncthreads();
+        broadcast<BG>(cluster, stage, xin + (size_t)(cur ^ 1) * K * BG, CS, UPC, 4, UPC, dhd, cr * UPC);
+        prefetch(t - 1);
+        cluster.sync();
+        cur ^= 1;
+        matvec<BG>(Ws, xin + (size_t)cur * K * BG, part, K, NOUTp, a.KS);
+        __syncthreads();
+    }
+    for (int it = tid; it < NI; it += kThreads) {
+        int b = it / UPC, ul = it % UPC;
+        if (b0 + b >= a.B) continue;
+        size_t si = (size_t)(b0 + b) * H + hd * dhd + cr * UPC + ul;
+        float dhr = 0.f;
+        for (int ks = 0; ks < a.KS; ++ks) dhr += part[((size_t)ks * BG + b) * NOUTp + ul];
+        a.dh[si] = dhr;
+        a.dc[si] = st[it];
+        a.dn[si] = st[NI + it];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side: geometry and launch
+// ---------------------------------------------------------------------------------------------
+struct Geo {
+    int BG, CS, UPC, KS;
+    SlstmSmem lay;
+};
+
+static const size_t kSmemCap = 220 * 1024;
+
+static bool fits(int BG, int CS, int dhd, bool bwd, Geo* out) {
+    if (dhd % CS) return false;
+    int UPC = dhd / CS;
+    int K = bwd ? 4 * dhd : dhd, NOUT = bwd ? UPC : 4 * UPC;
+    int NOUTp = (NOUT + 1) & ~1, npairs = NOUTp / 2;
+    int KS = kThreads / npairs;
+    if (KS < 1) KS = 1;
+    if (KS > 16) KS = 16;
+    if (KS > K) KS = K;
+    SlstmSmem l = smem_layout(K, NOUT, BG, KS, UPC, bwd ? 2 : 3);
+    if (l.total > kSmemCap) return false;
+    out->BG = BG; out->CS = CS; out->UPC = UPC; out->KS = KS; out->lay = l;
+    return true;
+}
+
+// Batch group: the largest of 8/4/2/1 that does not pad the batch by 2x or more. Cluster size:
+// the widest (<= 8, the portable limit) that keeps >= 8 units per CTA and the whole grid within
+// one wave of SMs; failing that, the narrowest whose slice fits shared memory.
+static bool pick_geometry(int B, int NH, int dhd, bool bwd, Geo* out) {
+    const int bgs[4] = {8, 4, 2, 1};
+    for (int bi = 0; bi < 4; ++bi) {
+        int BG = bgs[bi];
+        if (BG > 1 && BG / 2 >= B) continue;
+        int nbg = (B + BG - 1) / BG;
+        for (int CS = 8; CS >= 1; CS /= 2)
+            if ((dhd / CS >= 8 || CS == 1) && NH * nbg * CS <= sm_count() && fits(BG, CS, dhd, bwd, out)) return true;
+        for (int CS = 1; CS <= 8; CS *= 2)
+            if (fits(BG, CS, dhd, bwd, out)) return true;
+    }
+    return false;
+}
+
+template <int BG>
+static int launch(cudaStream_t st, bool bwd, const SlstmArgs& a, const Geo& g) {
+    auto kern = bwd ? slstm_bw_cluster<BG> : slstm_fw_cluster<BG>;
+    XL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.lay.total));
+    int nbg = (a.B + BG - 1) / BG;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(a.NH * nbg * g.CS));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = g.lay.total;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)g.CS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int nclusters = 0;
+    XL_CUDA(cudaOccupancyMaxActiveClusters(&nclusters, kern, &cfg));
+    if (nclusters < 1) {
+        set_error("slstm: a cluster of %d CTAs with %zu B shared memory cannot be resident", g.CS, g.lay.total);
+        return XLSTM_DECLINED;
+    }
+    XL_CUDA(cudaLaunchKernelEx(&cfg, kern, a, g.lay));
+    count_launch();
+    return XLSTM_OK;
+}
+
+static int run(cudaStream_t st, bool bwd, SlstmArgs a) {
+    Geo g;
+    if (!pick_geometry(a.B, a.NH, a.dhd, bwd, &g)) {
+        set_error("slstm: recurrent slice for %d units per head does not fit a cluster's shared memory", a.dhd);
+        return XLSTM_DECLINED;
+    }
+    a.CS = g.CS; a.UPC = g.UPC; a.KS = g.KS;
+    switch (g.BG) {
+        case 8: return launch<8>(st, bwd, a, g);
+        case 4: return launch<4>(st, bwd, a, g);
+        case 2: return launch<2>(st, bwd, a, g);
+        default: return launch<1>(st, bwd, a, g);
+    }
+}
+
+}  // namespace xl
+
+using namespace xl;
+
+static int check_common(const char* who, const float* wh, const float* g, const xlstm_slstm_slabs* s, int B, int H,
+                        int NH, int T) {
+    XL_CHECK_ARG(wh && g && s, "%s: null pointer", who);
+    XL_CHECK_ARG(B > 0 && H > 0 && NH > 0 && T >= 0 && H % NH == 0, "%s: bad shape B=%d H=%d NH=%d T=%d", who, B, H, NH, T);
+    XL_CHECK_ARG(s->c_prev && s->n_prev && s->ipr && s->fpr && s->c && s->n && s->zt && s->ot && s->h_prev,
+                 "%s: null slab pointer", who);
+    return XLSTM_OK;
+}
+
+extern "C" int xlstm_slstm_fw(void* stream, const float* wh, float* g, const float* bcat, float* c, float* n,
+                              float* m, float* h, float* out, const xlstm_slstm_slabs* slabs, int B, int H, int NH,
+                              int T, int carry, unsigned flags) {
+    (void)flags;
+    int rc = check_common("slstm_fw", wh, g, slabs, B, H, NH, T);
+    if (rc) return rc;
+    XL_CHECK_ARG(bcat && c && n && m && h && out, "slstm_fw: null pointer");
+    SlstmArgs a = {};
+    a.wh = wh; a.g = g; a.bcat = bcat; a.c = c; a.n = n; a.m = m; a.h = h; a.out = out; a.s = *slabs;
+    a.B = B; a.H = H; a.NH = NH; a.T = T; a.carry = carry; a.dhd = H / NH;
+    return run((cudaStream_t)stream, false, a);
+}
+
+extern "C" int xlstm_slstm_bw(void* stream, const float* wh, const float* dy, float* g, float* dh, float* dc,
+                              float* dn, const xlstm_slstm_slabs* slabs, int B, int H, int NH, int T, int carry,
+                              unsigned flags) {
+    (void)flags;
+    int rc = check_common("slstm_bw", wh, g, slabs, B, H, NH, T);
+    if (rc) return rc;
+    XL_CHECK_ARG(dy && dh && dc && dn, "slstm_bw: null pointer");
+    SlstmArgs a = {};
+    a.wh = wh; a.g = g; a.dy = dy; a.dh = dh; a.dc = dc; a.dn = dn; a.s = *slabs;
+    a.B = B; a.H = H; a.NH = NH; a.T = T; a.carry = carry; a.dhd = H / NH;
+    return run((cudaStream_t)stream, true, a);
+}

@@ -1,0 +1,199 @@
+"""Host-side mirror of the reference's op seam (`gpu::ops`, src/gpu/ops.rs) over the C ABI.
+
+Each function takes torch CUDA tensors the caller owns, passes their device pointers and the
+current torch stream to libxlstm_b200.so, and returns. Names and argument meaning follow the
+reference functions they stand in for; nothing here computes on the host.
+"""
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from ._lib import lib, check
+
+_DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise _lib.XlstmError("xlstm_b200 ops take CUDA tensors only (there is no CPU path)")
+    if not t.is_contiguous():
+        raise _lib.XlstmError("xlstm_b200 ops take contiguous tensors")
+    return t.data_ptr()
+
+
+def _stream():
+    if not torch.cuda.is_available():
+        raise _lib.XlstmError("no CUDA device: xlstm_b200 has no CPU path")
+    return torch.cuda.current_stream().cuda_stream
+
+
+class MlstmShape:
+    """The logical shape of one fused mLSTM call (reference: MlstmShape, src/gpu/ops.rs:4368-4378)."""
+
+    def __init__(self, b, h, t, dqk, dhv, l=64, dtype=torch.bfloat16, gdtype=torch.float32, flags=0):
+        self.b, self.h, self.t, self.dqk, self.dhv, self.l = b, h, t, dqk, dhv, l
+        self.dtype, self.gdtype, self.flags = dtype, gdtype, flags
+        self.c = _lib.MlstmShape(b, h, t, dqk, dhv, l, _DT[dtype], _DT[gdtype], flags)
+
+    def bh(self):
+        return self.b * self.h
+
+
+class MlstmFused:
+    """What the fused forward leaves for the backward (reference: MlstmFused, src/gpu/ops.rs:3955-3967)."""
+
+    def __init__(self, ytil, msv, psiv, qnv, saved, state):
+        self.ytil, self.msv, self.psiv, self.qnv, self.saved, self.state = ytil, msv, psiv, qnv, saved, state
+
+
+def mlstm_fused_fw(qh, kh, vh, igh, fgh, st, carry_in=None, save_states=True, want_state=True):
+    """ops::mlstm_fused_fw (src/gpu/ops.rs:4380-4537). carry_in = (C [BH,dhv,dqk], n [BH,dqk], m [BH])."""
+    dev = qh.device
+    bh, n = st.bh(), st.b * st.t
+    ytil = torch.empty((n, st.h * st.dhv), dtype=st.dtype, device=dev)
+    msv, psiv, qnv = (torch.empty((bh, st.t), dtype=torch.float32, device=dev) for _ in range(3))
+    saved = None
+    if save_states:
+        saved = torch.empty((lib.xlstm_mlstm_saved_bytes(ctypes.byref(st.c)),), dtype=torch.uint8, device=dev)
+    state = None
+    if want_state:
+        state = (torch.empty((bh, st.dhv, st.dqk), dtype=torch.float32, device=dev),
+                 torch.empty((bh, st.dqk), dtype=torch.float32, device=dev),
+                 torch.empty((bh,), dtype=torch.float32, device=dev))
+    wsb = lib.xlstm_mlstm_fw_workspace_bytes(ctypes.byref(st.c))
+    ws = torch.empty((max(wsb, 1),), dtype=torch.uint8, device=dev)
+    cC, cn, cm = carry_in if carry_in is not None else (None, None, None)
+    oC, on, om = state if state is not None else (None, None, None)
+    check(lib.xlstm_mlstm_fw(_stream(), ctypes.byref(st.c), _ptr(qh), _ptr(kh), _ptr(vh), _ptr(igh), _ptr(fgh),
+                             _ptr(cC), _ptr(cn), _ptr(cm), _ptr(ytil), _ptr(msv), _ptr(psiv), _ptr(qnv),
+                             _ptr(saved), _ptr(oC), _ptr(on), _ptr(om), _ptr(ws), wsb), "mlstm_fused_fw")
+    return MlstmFused(ytil, msv, psiv, qnv, saved, state)
+
+
+def mlstm_fused_bw(fused, qh, kh, vh, igh, fgh, d_ytil, st, carry_in=None, dstate_in=None, want_dstate=True):
+    """ops::mlstm_fused_bw (src/gpu/ops.rs:4546-4707). dstate_in = (dC, dn) from the call to the right.
+    Returns (dq, dk, dv, dig, dfg, (dC, dn))."""
+    dev = qh.device
+    bh, n = st.bh(), st.b * st.t
+    dq = torch.empty((n, st.h * st.dqk), dtype=st.gdtype, device=dev)
+    dk = torch.empty_like(dq)
+    dv = torch.empty((n, st.h * st.dhv), dtype=st.gdtype, device=dev)
+    dig = torch.empty((n, st.h), dtype=torch.float32, device=dev)
+    dfg = torch.empty_like(dig)
+    dstate = None
+    if want_dstate:
+        dstate = (torch.empty((bh, st.dhv, st.dqk), dtype=torch.float32, device=dev),
+                  torch.empty((bh, st.dqk), dtype=torch.float32, device=dev))
+    wsb = lib.xlstm_mlstm_bw_workspace_bytes(ctypes.byref(st.c), int(fused.saved is not None))
+    ws = torch.empty((max(wsb, 1),), dtype=torch.uint8, device=dev)
+    cC, cn, cm = carry_in if carry_in is not None else (None, None, None)
+    dC, dn = dstate_in if dstate_in is not None else (None, None)
+    oC, on = dstate if dstate is not None else (None, None)
+    check(lib.xlstm_mlstm_bw(_stream(), ctypes.byref(st.c), _ptr(qh), _ptr(kh), _ptr(vh), _ptr(igh), _ptr(fgh),
+                             _ptr(cC), _ptr(cn), _ptr(cm), _ptr(fused.ytil), _ptr(fused.msv), _ptr(fused.psiv),
+                             _ptr(fused.qnv), _ptr(fused.saved), _ptr(d_ytil), _ptr(dC), _ptr(dn), _ptr(dq), _ptr(dk),
+                             _ptr(dv), _ptr(dig), _ptr(dfg), _ptr(oC), _ptr(on), _ptr(ws), wsb), "mlstm_fused_bw")
+    return dq, dk, dv, dig, dfg, dstate
+
+
+SLSTM_SLAB_NAMES = ("c_prev", "n_prev", "ipr", "fpr", "c", "n", "zt", "ot", "h_prev")
+
+
+class SlstmSlabs:
+    """The nine [B,T,H] records of the fused sLSTM loop (reference: SlstmSlabs, src/gpu/ops.rs:2206-2256)."""
+
+    def __init__(self, b, t, h, device):
+        self.t = {n: torch.empty((b, t, h), dtype=torch.float32, device=device) for n in SLSTM_SLAB_NAMES}
+        self.c = _lib.SlstmSlabs(*[self.t[n].data_ptr() for n in SLSTM_SLAB_NAMES])
+
+
+def slstm_fused_time(wh, g, bcat, state, out, slabs, nh=1, carry=False):
+    """ops::slstm_fused_time (src/gpu/ops.rs:2787-2880). state = (c, n, m, h), each [B,H], updated in place.
+    Raises Declined (nothing launched) where the reference would return false."""
+    b, t, h4 = g.shape
+    h = h4 // 4
+    c, n, m, hh = state
+    check(lib.xlstm_slstm_fw(_stream(), _ptr(wh), _ptr(g), _ptr(bcat), _ptr(c), _ptr(n), _ptr(m), _ptr(hh), _ptr(out),
+                             ctypes.byref(slabs.c), b, h, nh, t, int(carry), 0), "slstm_fused_time")
+
+
+def slstm_fused_time_bwd(wh, dy, g, dstate, slabs, nh=1, carry=False):
+    """ops::slstm_fused_time_bwd (src/gpu/ops.rs:2712-2777). dstate = (dh, dc, dn), each [B,H], updated in place."""
+    b, t, h4 = g.shape
+    h = h4 // 4
+    dh, dc, dn = dstate
+    check(lib.xlstm_slstm_bw(_stream(), _ptr(wh), _ptr(dy), _ptr(g), _ptr(dh), _ptr(dc), _ptr(dn),
+                             ctypes.byref(slabs.c), b, h, nh, t, int(carry), 0), "slstm_fused_time_bwd")
+
+
+def rms_norm_forward_into(x, gamma, group, out, inv_rms, x_hat=None, eps=1e-6):
+    """ops::rms_norm_forward_into (src/gpu/ops.rs:1601-1640)."""
+    rows, f = x.shape
+    check(lib.xlstm_rmsnorm_fw(_stream(), _ptr(x), _ptr(gamma), _ptr(out), _ptr(inv_rms), _ptr(x_hat), rows, f, group,
+                               eps), "rms_norm_forward_into")
+
+
+def rms_norm_backward_into(dy, x, inv_rms, gamma, group, dx, dgamma):
+    """ops::rms_norm_backward_into + the dgamma column sum (src/gpu/ops.rs:1642-1685). dgamma is accumulated."""
+    rows, f = dy.shape
+    wsb = lib.xlstm_rmsnorm_bw_workspace_bytes(rows, f)
+    ws = torch.empty((max(wsb, 1),), dtype=torch.uint8, device=dy.device)
+    check(lib.xlstm_rmsnorm_bw(_stream(), _ptr(dy), _ptr(x), _ptr(inv_rms), _ptr(gamma), _ptr(dx), _ptr(dgamma), rows, f,
+                               group, _ptr(ws), wsb), "rms_norm_backward_into")
+
+
+def softmax_cross_entropy(logits, targets, dlogits, loss_accum, mask=None, inv=None):
+    """ops::softmax_cross_entropy / masked_softmax_ce_u32_into (src/gpu/ops.rs:1689-1714, 3567-3618).
+    targets/mask are int32 tensors holding u32 values; loss_accum is a 1-element f32 device tensor (+=)."""
+    rows, c = logits.shape
+    if inv is None:
+        inv = 1.0 / rows
+    wsb = lib.xlstm_ce_workspace_bytes(rows)
+    ws = torch.empty((max(wsb, 1),), dtype=torch.uint8, device=logits.device)
+    check(lib.xlstm_ce_fw_bw(_stream(), _ptr(logits), _ptr(targets), _ptr(mask), _ptr(dlogits), _ptr(loss_accum), rows, c,
+                             inv, _ptr(ws), wsb), "softmax_cross_entropy")
+
+
+class AdamCfg:
+    """reference: AdamCfg, src/nn2/optim.rs:12-33."""
+
+    def __init__(self, lr, weight_decay, beta1=0.9, beta2=0.999, eps=1e-8, t=0):
+        self.lr, self.weight_decay, self.beta1, self.beta2, self.eps, self.t = lr, weight_decay, beta1, beta2, eps, t
+
+
+class AdamwQueue:
+    """Collects (param, grad, m, v, decay) and applies them in one batched pass
+    (reference: AdamwQueue::{push,flush}, src/gpu/ops.rs:1816-1933). flush clears the grads."""
+
+    def __init__(self):
+        self.items = []
+
+    def push(self, p, g, m, v, decay, p_bf16=None):
+        self.items.append((p, g, m, v, decay, p_bf16))
+
+    def flush(self, cfg, zero_grad=True):
+        if not self.items:
+            return
+        n = len(self.items)
+        arr = (_lib.AdamwDesc * n)()
+        for i, (p, g, m, v, decay, pb) in enumerate(self.items):
+            arr[i] = _lib.AdamwDesc(_ptr(p), _ptr(g), _ptr(m), _ptr(v), _ptr(pb), p.numel(),
+                                    cfg.weight_decay if decay else 0.0, 0.0)
+        # bias corrections in f32, as the reference computes them on the host (powi)
+        import numpy as np
+        bc1 = float(np.float32(1.0) - np.float32(cfg.beta1) ** np.int32(cfg.t))
+        bc2 = float(np.float32(1.0) - np.float32(cfg.beta2) ** np.int32(cfg.t))
+        check(lib.xlstm_adamw_multi(_stream(), arr, n, cfg.lr, cfg.beta1, cfg.beta2, cfg.eps, bc1, bc2, int(zero_grad)),
+              "adamw_multi")
+        self.items = []
+
+
+def adamw(p, g, m, v, cfg, decay, p_bf16=None, zero_grad=False):
+    """ops::adamw (src/gpu/ops.rs:1775-1814): one tensor."""
+    q = AdamwQueue()
+    q.push(p, g, m, v, decay, p_bf16)
+    q.flush(cfg, zero_grad=zero_grad)

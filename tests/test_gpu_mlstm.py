@@ -1,0 +1,112 @@
+"""GPU parity of the chunkwise mLSTM core against the CPU oracle (recurrent form, float64),
+through the C ABI. Shapes and invariants follow the reference's own GPU tests:
+mlstm_matches_cpu, mlstm_fused_tiled_matches_cpu, mlstm_fused_ragged_chunk_matches_cpu,
+mlstm_chunking_matches_single_chunk, mlstm_chunked_carry_matches_whole,
+mlstm_chunked_backward_matches_whole (src/gpu/mlstm.rs:1004-1533).
+
+Bars: rel-to-max 1e-4 for fp32 storage, 2e-2 for bf16 storage."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2}
+
+
+def _run(shape, L, dtype, gdtype, seed=0, flags=0, save_states=True, carry=None, dstate=None):
+    from gpu_util import ops, dev, host, mlstm_inputs, bf16_round
+    B, H, T, dqk, dhv = shape
+    bf = dtype == torch.bfloat16
+    q, k, v, ig, fg, dy = mlstm_inputs(*shape, seed=seed, bf16=bf)
+    if gdtype == torch.bfloat16:
+        dy = bf16_round(dy)
+    st = ops.MlstmShape(B, H, T, dqk, dhv, L, dtype, gdtype, flags)
+    dq_, dk_, dv_ = dev(q, dtype), dev(k, dtype), dev(v, dtype)
+    di_, df_ = dev(ig), dev(fg)
+    cin = None if carry is None else tuple(dev(a) for a in carry)
+    fused = ops.mlstm_fused_fw(dq_, dk_, dv_, di_, df_, st, carry_in=cin, save_states=save_states)
+    din = None if dstate is None else tuple(dev(a) for a in dstate)
+    grads = ops.mlstm_fused_bw(fused, dq_, dk_, dv_, di_, df_, dev(dy, gdtype), st, carry_in=cin, dstate_in=din)
+    torch.cuda.synchronize()
+    c0 = dict(C0=None, n0=None, m0=None) if carry is None else dict(C0=carry[0], n0=carry[1], m0=carry[2])
+    d0 = dict(dC_in=None, dn_in=None) if dstate is None else dict(dC_in=dstate[0], dn_in=dstate[1])
+    ofw = O.mlstm_core_fw(q, k, v, ig, fg, B, H, T, dqk, dhv, **c0)
+    obw = O.mlstm_core_bw(q, k, v, ig, fg, dy, B, H, T, dqk, dhv, **c0, **d0)
+    got = dict(ytil=host(fused.ytil), m=host(fused.msv), psi=host(fused.psiv), nq=host(fused.qnv),
+               C=host(fused.state[0]), n=host(fused.state[1]), mlast=host(fused.state[2]),
+               dq=host(grads[0]), dk=host(grads[1]), dv=host(grads[2]), dig=host(grads[3]), dfg=host(grads[4]),
+               dC=host(grads[5][0]), dn=host(grads[5][1]))
+    ref = dict(ofw)
+    ref.update(obw)
+    return got, ref
+
+
+def _assert_close(got, ref, tol, names):
+    from gpu_util import rel_to_max
+    for n in names:
+        e = rel_to_max(got[n], ref[n])
+        assert e <= tol, "%s: rel-to-max error %.3e > %.1e" % (n, e, tol)
+
+
+FW = ("ytil", "m", "psi", "C", "n", "mlast")
+BW = ("dq", "dk", "dv", "dig", "dfg", "dC", "dn")
+
+
+@pytest.mark.parametrize("shape,L", [((2, 2, 6, 4, 4), 64), ((2, 2, 20, 4, 4), 8), ((2, 8, 70, 96, 96), 32),
+                                     ((2, 8, 200, 64, 64), 32), ((1, 2, 130, 32, 48), 64)])
+def test_fp32_matches_oracle(shape, L):
+    got, ref = _run(shape, L, torch.float32, torch.float32)
+    _assert_close(got, ref, 1e-4, FW + BW)
+
+
+@pytest.mark.parametrize("L", [1, 3, 8, 16, 32, 64, 200])
+def test_chunk_length_does_not_change_results(L):
+    got, ref = _run((2, 2, 70, 8, 12), L, torch.float32, torch.float32, seed=5)
+    _assert_close(got, ref, 1e-4, FW + BW)
+
+
+@pytest.mark.parametrize("shape,L", [((2, 2, 20, 4, 4), 8), ((2, 4, 200, 64, 64), 64), ((1, 2, 256, 128, 128), 64)])
+@pytest.mark.parametrize("gdtype", [torch.float32, torch.bfloat16])
+def test_bf16_storage_matches_oracle(shape, L, gdtype):
+    got, ref = _run(shape, L, torch.bfloat16, gdtype, flags=1)
+    _assert_close(got, ref, 2e-2, FW + BW)
+
+
+def test_carry_in_and_bptt_state_in():
+    """A call that continues a recurrence (state in) and receives BPTT state from its right."""
+    B, H, T, dqk, dhv = 2, 2, 40, 8, 8
+    r = np.random.default_rng(11)
+    carry = (r.standard_normal((B * H, dhv, dqk)), r.standard_normal((B * H, dqk)), r.standard_normal((B * H,)))
+    dstate = (r.standard_normal((B * H, dhv, dqk)) * 0.1, r.standard_normal((B * H, dqk)) * 0.1)
+    carry = tuple(a.astype(np.float32).astype(np.float64) for a in carry)
+    dstate = tuple(a.astype(np.float32).astype(np.float64) for a in dstate)
+    got, ref = _run((B, H, T, dqk, dhv), 16, torch.float32, torch.float32, carry=carry, dstate=dstate)
+    _assert_close(got, ref, 1e-4, FW + BW)
+
+
+def test_recomputed_states_equal_saved_states():
+    a, _ = _run((2, 2, 100, 16, 16), 32, torch.float32, torch.float32, save_states=True)
+    b, _ = _run((2, 2, 100, 16, 16), 32, torch.float32, torch.float32, save_states=False)
+    for n in BW:
+        assert np.array_equal(a[n], b[n]), n
+
+
+def test_bit_repeatable():
+    a, _ = _run((2, 4, 130, 32, 32), 64, torch.bfloat16, torch.float32, flags=1)
+    b, _ = _run((2, 4, 130, 32, 32), 64, torch.bfloat16, torch.float32, flags=1)
+    for n in FW + BW:
+        assert np.array_equal(a[n], b[n]), n
+
+
+def test_declines_oversized_tile_without_launching():
+    from gpu_util import ops, xl
+    st = ops.MlstmShape(1, 1, 64, 512, 512, 64, torch.float32, torch.float32, flags=1)
+    z = torch.zeros((64, 512), device="cuda")
+    g = torch.zeros((64, 1), device="cuda")
+    before = xl._lib.lib.xlstm_launch_count()
+    with pytest.raises(xl._lib.Declined):
+        ops.mlstm_fused_fw(z, z, z, g, g, st)
+    assert xl._lib.lib.xlstm_launch_count() == before
