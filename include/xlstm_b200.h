@@ -51,6 +51,10 @@ int xlstm_version(void);
 const char* xlstm_last_error(void);
 /* Number of kernels this library has launched from the calling process so far. */
 uint64_t xlstm_launch_count(void);
+/* Synchronising health check: XLSTM_OK, or XLSTM_ERR_TIMEOUT if a kernel launched earlier gave up
+ * on a bounded device-side wait (it then unwound cleanly and its outputs are invalid). Clears the
+ * flag. Copies one word from the device, so it waits for work already enqueued. */
+int xlstm_device_status(void);
 
 /* ---- chunkwise mLSTM core -------------------------------------------------------------
  * Replaces ops::mlstm_fused_fw / ops::mlstm_fused_bw (src/gpu/ops.rs:4380-4537,

@@ -40,6 +40,7 @@ SIGNATURES = {
     "xlstm_version": (ctypes.c_int, []),
     "xlstm_last_error": (ctypes.c_char_p, []),
     "xlstm_launch_count": (ctypes.c_uint64, []),
+    "xlstm_device_status": (ctypes.c_int, []),
     "xlstm_mlstm_saved_bytes": (_sz, [_shape_p]),
     "xlstm_mlstm_fw_workspace_bytes": (_sz, [_shape_p]),
     "xlstm_mlstm_bw_workspace_bytes": (_sz, [_shape_p, _i]),

@@ -42,7 +42,11 @@ static int check_shape(const char* who, const xlstm_mlstm_shape* s) {
 static inline int eff_L(const xlstm_mlstm_shape* s) { return s->L < s->T ? s->L : s->T; }
 static inline int num_chunks(const xlstm_mlstm_shape* s) { int L = eff_L(s); return (s->T + L - 1) / L; }
 
-// Chunk-state record: C then n, each the state ENTERING a chunk, f32.
+static inline bool use_tc(const xlstm_mlstm_shape* s) {
+    return !(s->flags & XLSTM_FORCE_SIMT) && mlstm_tc_supported(eff_L(s), s->dqk, s->dhv, s->dtype) && s->T >= 1;
+}
+
+// Chunk-state record of the CUDA-core path: C then n, each the state ENTERING a chunk, f32.
 static size_t saved_C_bytes(const xlstm_mlstm_shape* s) {
     return align_up((size_t)s->B * s->H * num_chunks(s) * s->dhv * s->dqk * sizeof(float), 256);
 }
@@ -57,9 +61,20 @@ using namespace xl;
 extern "C" int xlstm_version(void) { return 1; }
 extern "C" const char* xlstm_last_error(void) { return g_err; }
 extern "C" uint64_t xlstm_launch_count(void) { return g_launches.load(); }
+extern "C" int xlstm_device_status(void) {
+    int v = 0;
+    int rc = tc_status_read_and_clear(&v);
+    if (rc) return rc;
+    if (v != 0) {
+        set_error("a device-side wait ran out of its budget (code %d); the kernel unwound without completing", v);
+        return XLSTM_ERR_TIMEOUT;
+    }
+    return XLSTM_OK;
+}
 
 extern "C" size_t xlstm_mlstm_saved_bytes(const xlstm_mlstm_shape* s) {
     if (!s || s->B <= 0 || s->H <= 0 || s->T <= 0 || s->dqk <= 0 || s->dhv <= 0 || s->L <= 0) return 0;
+    if (use_tc(s)) return mlstm_tc_saved_C_bytes(s->B * s->H, num_chunks(s)) + mlstm_tc_saved_n_bytes(s->B * s->H, num_chunks(s));
     return saved_C_bytes(s) + saved_n_bytes(s);
 }
 extern "C" size_t xlstm_mlstm_fw_workspace_bytes(const xlstm_mlstm_shape* s) {
@@ -67,7 +82,9 @@ extern "C" size_t xlstm_mlstm_fw_workspace_bytes(const xlstm_mlstm_shape* s) {
     return 0;
 }
 extern "C" size_t xlstm_mlstm_bw_workspace_bytes(const xlstm_mlstm_shape* s, int have_saved) {
-    return have_saved ? 0 : xlstm_mlstm_saved_bytes(s);
+    if (!s || s->B <= 0 || s->H <= 0 || s->T <= 0 || s->dqk <= 0 || s->dhv <= 0 || s->L <= 0) return 0;
+    if (use_tc(s)) return saved_C_bytes(s) + saved_n_bytes(s);  // backward of this shape recomputes chunk states (f32)
+    return have_saved ? 0 : saved_C_bytes(s) + saved_n_bytes(s);
 }
 
 extern "C" int xlstm_mlstm_fw(void* stream, const xlstm_mlstm_shape* s, const void* q, const void* k, const void* v,
@@ -87,6 +104,7 @@ extern "C" int xlstm_mlstm_fw(void* stream, const xlstm_mlstm_shape* s, const vo
     a.oC = out_C; a.on = out_n; a.om = out_m;
     a.B = s->B; a.H = s->H; a.T = s->T; a.dqk = s->dqk; a.dhv = s->dhv; a.L = eff_L(s); a.NC = num_chunks(s);
     a.states_only = 0;
+    if (use_tc(s)) return mlstm_fw_tc_launch((cudaStream_t)stream, a, saved);
     return mlstm_fw_simt_launch((cudaStream_t)stream, a, s->dtype);
 }
 
@@ -105,7 +123,7 @@ extern "C" int xlstm_mlstm_bw(void* stream, const xlstm_mlstm_shape* s, const vo
     XL_CHECK_ARG((carry_dC != nullptr) == (carry_dn != nullptr), "mlstm_bw: carry dC, dn must be given together");
     cudaStream_t st = (cudaStream_t)stream;
     const float *sC, *sn;
-    if (saved) {
+    if (saved && !use_tc(s)) {
         sC = (const float*)saved;
         sn = (const float*)((const char*)saved + saved_C_bytes(s));
     } else {

@@ -35,4 +35,11 @@ int mlstm_fw_simt_launch(cudaStream_t st, const MlstmFwArgs& a, int dtype);
 int mlstm_bw_simt_launch(cudaStream_t st, const MlstmBwArgs& a, int dtype, int gdtype);
 bool mlstm_simt_supported(int L, int dqk, int dhv, int dtype);
 
+// Tensor-core (tcgen05) path
+bool mlstm_tc_supported(int L, int dqk, int dhv, int dtype);
+size_t mlstm_tc_saved_C_bytes(int BH, int NC);
+size_t mlstm_tc_saved_n_bytes(int BH, int NC);
+int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved);
+int tc_status_read_and_clear(int* out);
+
 }  // namespace xl

@@ -110,3 +110,38 @@ def test_declines_oversized_tile_without_launching():
     with pytest.raises(xl._lib.Declined):
         ops.mlstm_fused_fw(z, z, z, g, g, st)
     assert xl._lib.lib.xlstm_launch_count() == before
+
+
+# ---- tensor-core path (dqk = dhv = 128, L = 64, bf16 storage; flags = 0 selects it) -----------
+@pytest.mark.parametrize("shape", [(1, 2, 64, 128, 128), (1, 2, 256, 128, 128), (2, 3, 200, 128, 128), (2, 2, 40, 128, 128)])
+@pytest.mark.parametrize("gdtype", [torch.float32, torch.bfloat16])
+def test_tensor_core_path_matches_oracle(shape, gdtype):
+    from gpu_util import xl
+    got, ref = _run(shape, 64, torch.bfloat16, gdtype, seed=21)
+    assert xl._lib.lib.xlstm_device_status() == 0, xl._lib.lib.xlstm_last_error()
+    _assert_close(got, ref, 2e-2, FW + BW)
+
+
+def test_tensor_core_path_with_carry():
+    from gpu_util import xl
+    B, H, T, d = 2, 2, 150, 128
+    r = np.random.default_rng(12)
+    f32 = lambda a: a.astype(np.float32).astype(np.float64)
+    carry = (f32(r.standard_normal((B * H, d, d))), f32(r.standard_normal((B * H, d))), f32(r.standard_normal((B * H,))))
+    dstate = (f32(r.standard_normal((B * H, d, d)) * 0.1), f32(r.standard_normal((B * H, d)) * 0.1))
+    got, ref = _run((B, H, T, d, d), 64, torch.bfloat16, torch.float32, carry=carry, dstate=dstate)
+    assert xl._lib.lib.xlstm_device_status() == 0, xl._lib.lib.xlstm_last_error()
+    _assert_close(got, ref, 2e-2, FW + BW)
+
+
+def test_tensor_core_path_agrees_with_cuda_core_path():
+    a, _ = _run((2, 4, 256, 128, 128), 64, torch.bfloat16, torch.float32, seed=22, flags=0)
+    b, _ = _run((2, 4, 256, 128, 128), 64, torch.bfloat16, torch.float32, seed=22, flags=1)
+    _assert_close(a, b, 2e-2, FW + BW)
+
+
+def test_tensor_core_path_bit_repeatable():
+    a, _ = _run((2, 2, 200, 128, 128), 64, torch.bfloat16, torch.float32, seed=23)
+    b, _ = _run((2, 2, 200, 128, 128), 64, torch.bfloat16, torch.float32, seed=23)
+    for n in FW + BW:
+        assert np.array_equal(a[n], b[n]), n
