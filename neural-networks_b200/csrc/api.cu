@@ -83,7 +83,6 @@ extern "C" size_t xlstm_mlstm_fw_workspace_bytes(const xlstm_mlstm_shape* s) {
 }
 extern "C" size_t xlstm_mlstm_bw_workspace_bytes(const xlstm_mlstm_shape* s, int have_saved) {
     if (!s || s->B <= 0 || s->H <= 0 || s->T <= 0 || s->dqk <= 0 || s->dhv <= 0 || s->L <= 0) return 0;
-    if (use_tc(s)) return saved_C_bytes(s) + saved_n_bytes(s);  // backward of this shape recomputes chunk states (f32)
     return have_saved ? 0 : saved_C_bytes(s) + saved_n_bytes(s);
 }
 
@@ -122,8 +121,16 @@ extern "C" int xlstm_mlstm_bw(void* stream, const xlstm_mlstm_shape* s, const vo
                  "mlstm_bw: carry C, n, m must be given together");
     XL_CHECK_ARG((carry_dC != nullptr) == (carry_dn != nullptr), "mlstm_bw: carry dC, dn must be given together");
     cudaStream_t st = (cudaStream_t)stream;
+    if (saved && use_tc(s)) {
+        MlstmBwArgs a = {};
+        a.q = q; a.k = k; a.v = v; a.ig = ig; a.fg = fg; a.cm = carry_m; a.ytil = ytil; a.msv = msv; a.psiv = psiv;
+        a.qnv = qnv; a.dytil = d_ytil; a.cdC = carry_dC; a.cdn = carry_dn;
+        a.dq = dq; a.dk = dk; a.dv = dv; a.dig = dig; a.dfg = dfg; a.odC = out_dC; a.odn = out_dn;
+        a.B = s->B; a.H = s->H; a.T = s->T; a.dqk = s->dqk; a.dhv = s->dhv; a.L = eff_L(s); a.NC = num_chunks(s);
+        return mlstm_bw_tc_launch(st, a, saved, s->gdtype);
+    }
     const float *sC, *sn;
-    if (saved && !use_tc(s)) {
+    if (saved) {
         sC = (const float*)saved;
         sn = (const float*)((const char*)saved + saved_C_bytes(s));
     } else {

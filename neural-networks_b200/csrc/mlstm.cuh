@@ -40,6 +40,7 @@ bool mlstm_tc_supported(int L, int dqk, int dhv, int dtype);
 size_t mlstm_tc_saved_C_bytes(int BH, int NC);
 size_t mlstm_tc_saved_n_bytes(int BH, int NC);
 int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved);
+int mlstm_bw_tc_launch(cudaStream_t st, const MlstmBwArgs& a, const void* saved, int gdtype);
 int tc_status_read_and_clear(int* out);
 
 }  // namespace xl

@@ -101,6 +101,7 @@ struct TcFwParams {
     float* savedn;  // [BH][NC+1][128]
     float *oC, *on, *om;
     int B, H, T, NC;
+    long long* prof;  // optional: per-phase cycle counts of CTA 0 (development aid; null in production)
 };
 
 struct FwSmem {
@@ -224,6 +225,13 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
     constexpr uint32_t idC = instr_desc(128, 128, 1, 1);
 
     bool ok = true;
+    long long tprev = clock64();
+#define PROF(i)                                              \
+    if (p.prof && bh == 0 && tid == 0) {                     \
+        long long tn = clock64();                            \
+        p.prof[i] += tn - tprev;                             \
+        tprev = tn;                                          \
+    }
     for (int ch = 0; ch < p.NC; ++ch) {
         const int st = ch & 1;
         const int t0 = ch * L, Lc = min(L, p.T - t0);
@@ -235,7 +243,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
         unsigned char* sCb = sm + FwSmem::cb;
         unsigned char* sP = sm + FwSmem::p;
 
+        PROF(0)
         if (!mbar_wait(&bars[st], (ch >> 1) & 1)) { *abort_flag = 1; }
+        PROF(1)
         // ---- Va = a (.) V, chunk-for-chunk in the tile's physical order
         for (int i = 0; i < 8; ++i) {
             uint32_t off = (uint32_t)(tid + kThreads * i) * 16;
@@ -250,6 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
         fence_async_smem();
         __syncthreads();
         if (*abort_flag) { ok = false; break; }
+        PROF(2)
 
         if (tid == 0) {
             tc_fence_after();
@@ -275,8 +286,10 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
                 mma_ss(tC, smem_desc(aV + ks * 2048, kBoxBytes, 1024), smem_desc(aK + ks * 2048, kBoxBytes, 1024), idC, 1);
             mma_commit(&bars[2]);
         }
+        PROF(3)
         if (!mbar_wait(&bars[2], ch & 1)) { *abort_flag = 2; }
         tc_fence_after();
+        PROF(4)
 
         // ---- S epilogue: decay mask, P (bf16, K-major tile), row sums, q.n, psi
         float ipsi, bt = Gc->b[row];
@@ -324,6 +337,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
         tc_fence_before();
         __syncthreads();
         if (*abort_flag) { ok = false; break; }
+        PROF(5)
 
         if (tid == 0) {
             tc_fence_after();
@@ -336,6 +350,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
             mma_commit(&bars[3]);
         }
 
+        PROF(6)
         // ---- while P V runs: record and advance n, gates of the next chunk, C pass
         {
             const float g = Gc->g;
@@ -351,9 +366,11 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
             nvec[tid] = nn;
             if (p.savedn) p.savedn[((size_t)bh * (p.NC + 1) + ch + 1) * D + tid] = nn;
         }
+        PROF(7)
         m_prev = Gc->mlast;
         const bool last = (ch + 1 == p.NC);
         if (!last) fw_gates(p, b, h, ch + 1, m_prev, &G[st ^ 1], xchg);
+        PROF(8)
         {
             const float gn = last ? 1.f : G[st ^ 1].g;
             bf16* rec = p.savedC ? p.savedC + ((size_t)bh * (p.NC + 1) + ch + 1) * D * D + (size_t)tid * D : nullptr;
@@ -385,8 +402,10 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
             tmem_st_wait();
         }
 
+        PROF(9)
         if (!mbar_wait(&bars[3], ch & 1)) { *abort_flag = 3; }
         tc_fence_after();
+        PROF(10)
         // ---- H epilogue: y = (Hi + b_t He) / psi_t, this thread's 64 columns of its row
         {
             bf16* yrow = p.ytil + (((size_t)b * p.T + t0 + row) * p.H + h) * D + 64 * hf;
@@ -413,7 +432,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
         tc_fence_before();
         __syncthreads();
         if (*abort_flag) { ok = false; break; }
+        PROF(11)
     }
+#undef PROF
 
     if (ok) {
         if (p.on) p.on[(size_t)bh * D + tid] = nvec[tid];
@@ -449,7 +470,7 @@ static EncodeTiledFn encode_fn() {
 }
 
 // [B][T][W] bf16 row-major viewed as a 3-D tensor (W inner); box = {64 cols, 64 rows, 1}, 128-byte swizzle.
-static bool make_map3(CUtensorMap* m, const void* base, int B, int T, int W) {
+bool tc_make_map3(CUtensorMap* m, const void* base, int B, int T, int W) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[3] = {(cuuint64_t)W, (cuuint64_t)T, (cuuint64_t)B};
@@ -457,6 +478,22 @@ static bool make_map3(CUtensorMap* m, const void* base, int B, int T, int W) {
     cuuint32_t box[3] = {64, 64, 1};
     cuuint32_t es[3] = {1, 1, 1};
     return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, es,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static long long* g_prof = nullptr;
+extern "C" void xlstm_debug_set_prof(void* p) { g_prof = (long long*)p; }
+
+// [rows][W] bf16 row-major, box = {64 cols, box_rows}, 128-byte swizzle.
+bool tc_make_map2(CUtensorMap* m, const void* base, uint64_t rows, int W, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)W, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)W * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t es[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -474,8 +511,8 @@ int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved) {
         return XLSTM_ERR_ARG;
     }
     TcFwParams p = {};
-    if (!make_map3(&p.tmq, a.q, a.B, a.T, a.H * D) || !make_map3(&p.tmk, a.k, a.B, a.T, a.H * D) ||
-        !make_map3(&p.tmv, a.v, a.B, a.T, a.H * D)) {
+    if (!tc_make_map3(&p.tmq, a.q, a.B, a.T, a.H * D) || !tc_make_map3(&p.tmk, a.k, a.B, a.T, a.H * D) ||
+        !tc_make_map3(&p.tmv, a.v, a.B, a.T, a.H * D)) {
         set_error("mlstm_fw: cuTensorMapEncodeTiled failed");
         return XLSTM_ERR_CUDA;
     }
@@ -487,6 +524,7 @@ int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved) {
     }
     p.oC = a.oC; p.on = a.on; p.om = a.om;
     p.B = a.B; p.H = a.H; p.T = a.T; p.NC = a.NC;
+    p.prof = g_prof;
     size_t smem = FwSmem::total + 1024;
     XL_CUDA(cudaFuncSetAttribute(mlstm_fw_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     mlstm_fw_tc<<<a.B * a.H, kThreads, smem, st>>>(p);

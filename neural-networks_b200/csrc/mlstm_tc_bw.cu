@@ -1,0 +1,602 @@
+// Backward of the chunkwise mLSTM core on the Blackwell tensor cores (tcgen05 + TMEM + TMA).
+//
+// Same shape contract as the forward (dqk = dhv = 128, L = 64, bf16 storage). One CTA owns one
+// (batch, head) pair and walks its chunks right to left with dC resident in tensor memory as a
+// 128 x 128 fp32 accumulator. Eight math warps own the epilogues (thread = one row-half-quarter
+// of a position-indexed accumulator, or one row-half of dC); a ninth control warp issues every
+// TMA load and tcgen05.mma and computes the gate vectors one chunk ahead.
+//
+// Per chunk, with entering state (C, n), leaving-state gradient (dC+, dn+), dN = dy/psi:
+//   S = Q K^T, dds = dN V^T + dqn            ->  DS = Dbar.S, dS = Dbar.dds
+//   dV = DS^T dN + a (K dC+^T)                   dQ = dS K + (b.dN) C + b dqn n
+//   dK = dS^T Q + a (V dC+ + dn+)                dC = g dC+ + (b.dN)^T Q
+//   d(i)_r = dK_r.K_r,  dF_r = dQ_r.Q_r - dK_r.K_r,  d(f)_j = (sum_{r>=j} dF_r)(1 - sigmoid(f_j))
+// (src/gpu/cuda/mlstm_fused.cu:830-858 with the stabiliser held constant; the gate-gradient
+// identity replaces the reference's row/column sums and is checked against the CPU oracle.)
+#include <cuda.h>
+
+#include "common.cuh"
+#include "mlstm.cuh"
+#include "tc.cuh"
+
+namespace xl {
+
+using namespace tc;
+
+extern __device__ int g_tc_status;
+
+namespace bw {
+
+static constexpr int D = 128;
+static constexpr int L = 64;
+static constexpr int kMathThreads = 256;
+static constexpr int kThreads = 288;  // 8 math warps + 1 control warp
+static constexpr uint32_t kTileBytes = L * D * 2;
+static constexpr uint32_t kBoxBytes = L * 128;
+static constexpr uint32_t kStateBox = D * 128;
+
+struct Gates {
+    float rowt[L];  // fc_t - m_t
+    float colt[L];  // i_j - fc_j  (-inf past a ragged end)
+    float b[L];
+    float a[L];
+    float fg[L];
+    float emm[L];   // exp(-m_t), the floor of psi
+    float g;
+    float pad[3];
+};
+
+struct Params {
+    CUtensorMap tmq, tmk, tmv;  // [B][T][H*128] bf16, box {64, 64, 1}
+    CUtensorMap tmc;            // saved C: [BH*(NC+1)*128][128] bf16, box {64, 128}
+    const float *ig, *fg;
+    const float* cm;
+    const bf16* ytil;
+    const float *msv, *psiv, *qnv;
+    const bf16* savedC;
+    const float* savedn;
+    const void* dy;
+    const float *cdC, *cdn;
+    void *dq, *dk, *dv;
+    float *dig, *dfg;
+    float *odC, *odn;
+    int B, H, T, NC;
+    int gbf16;
+};
+
+struct Smem {
+    static constexpr uint32_t q = 0;
+    static constexpr uint32_t k = q + kTileBytes;
+    static constexpr uint32_t v = k + kTileBytes;
+    static constexpr uint32_t ck = v + kTileBytes;       // [128 x 128] entering state, bf16
+    static constexpr uint32_t dn_ = ck + 2 * kStateBox;  // dN  = dy/psi
+    static constexpr uint32_t dnb = dn_ + kTileBytes;    // dNb = b . dN
+    static constexpr uint32_t dcb = dnb + kTileBytes;    // bf16 dC+
+    static constexpr uint32_t ds_ = dcb + 2 * kStateBox; // DS  [64 x 64]
+    static constexpr uint32_t dS = ds_ + kBoxBytes;      // dS  [64 x 64]
+    static constexpr uint32_t gates = dS + kBoxBytes;    // 2 x Gates
+    static constexpr uint32_t nk = gates + 2 * sizeof(Gates);  // n entering the chunk [128]
+    static constexpr uint32_t dnv = nk + D * 4;          // dn, double buffered [2][128]
+    static constexpr uint32_t part = dnv + 2 * D * 4;    // partial sums [6][64]: dot(2), u(2), w(2)
+    static constexpr uint32_t dqn = part + 6 * L * 4;    // [64]
+    static constexpr uint32_t misc = dqn + L * 4;
+    static constexpr uint32_t total = misc + 256;
+};
+
+template <typename G>
+__device__ __forceinline__ void load32(const G* p, float* v);
+template <>
+__device__ __forceinline__ void load32<float>(const float* p, float* v) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float4 t = __ldcs(reinterpret_cast<const float4*>(p) + i);
+        v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+    }
+}
+template <>
+__device__ __forceinline__ void load32<bf16>(const bf16* p, float* v) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint4 t = __ldcs(reinterpret_cast<const uint4*>(p) + i);
+        float2 a = unpack_bf16(t.x), b = unpack_bf16(t.y), c = unpack_bf16(t.z), d = unpack_bf16(t.w);
+        v[8 * i] = a.x; v[8 * i + 1] = a.y; v[8 * i + 2] = b.x; v[8 * i + 3] = b.y;
+        v[8 * i + 4] = c.x; v[8 * i + 5] = c.y; v[8 * i + 6] = d.x; v[8 * i + 7] = d.y;
+    }
+}
+template <typename G>
+__device__ __forceinline__ void store32(G* p, const float* v);
+template <>
+__device__ __forceinline__ void store32<float>(float* p, const float* v) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        __stcs(reinterpret_cast<float4*>(p) + i, make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
+}
+template <>
+__device__ __forceinline__ void store32<bf16>(bf16* p, const float* v) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint4 t;
+        t.x = pack_bf16(v[8 * i], v[8 * i + 1]); t.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
+        t.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]); t.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
+        __stcs(reinterpret_cast<uint4*>(p) + i, t);
+    }
+}
+
+// 32 floats -> 4 swizzled 16-byte chunks of row `row`, starting at logical chunk `chunk0`.
+__device__ __forceinline__ void put_row32(unsigned char* tile, uint32_t row, uint32_t chunk0, const float* v) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        uint4 pk;
+        pk.x = pack_bf16(v[8 * q + 0], v[8 * q + 1]); pk.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
+        pk.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]); pk.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
+        *reinterpret_cast<uint4*>(tile + swz(row, chunk0 + q)) = pk;
+    }
+}
+// dot of 32 floats with 32 bf16 of row `row` (chunks chunk0..chunk0+3) of a swizzled tile
+__device__ __forceinline__ float dot_row32(const unsigned char* tile, uint32_t row, uint32_t chunk0, const float* v) {
+    float acc = 0.f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        uint4 x = *reinterpret_cast<const uint4*>(tile + swz(row, chunk0 + q));
+        float2 f0 = unpack_bf16(x.x), f1 = unpack_bf16(x.y), f2 = unpack_bf16(x.z), f3 = unpack_bf16(x.w);
+        acc += v[8 * q] * f0.x + v[8 * q + 1] * f0.y + v[8 * q + 2] * f1.x + v[8 * q + 3] * f1.y + v[8 * q + 4] * f2.x +
+               v[8 * q + 5] * f2.y + v[8 * q + 6] * f3.x + v[8 * q + 7] * f3.y;
+    }
+    return acc;
+}
+
+// Control warp: gate vectors of chunk `ch` (two positions per lane).
+__device__ __forceinline__ void gates_warp(const Params& p, int b, int h, int bh, int ch, Gates* G) {
+    const int lane = threadIdx.x & 31;
+    const int t0 = ch * L, Lc = min(L, p.T - t0);
+    float lf[2], iv[2], fr[2], mt[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        int t = lane + 32 * e;
+        lf[e] = 0.f; iv[e] = -INFINITY; fr[e] = 0.f;
+        if (t < Lc) {
+            size_t gi = ((size_t)b * p.T + t0 + t) * p.H + h;
+            fr[e] = p.fg[gi];
+            lf[e] = log_sigmoid(fr[e]);
+            iv[e] = p.ig[gi];
+        }
+        mt[e] = p.msv[(size_t)bh * p.T + t0 + min(t, Lc - 1)];
+    }
+    const float m_prev = (ch == 0) ? (p.cm ? p.cm[bh] : 0.f) : p.msv[(size_t)bh * p.T + t0 - 1];
+    float fc0 = lf[0], fc1 = lf[1];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        float y0 = __shfl_up_sync(0xffffffffu, fc0, o), y1 = __shfl_up_sync(0xffffffffu, fc1, o);
+        if (lane >= o) { fc0 += y0; fc1 += y1; }
+    }
+    fc1 += __shfl_sync(0xffffffffu, fc0, 31);
+    const float fcL = __shfl_sync(0xffffffffu, fc1, 31);
+    const float mL = __shfl_sync(0xffffffffu, mt[1], 31);
+    float fc[2] = {fc0, fc1};
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        int t = lane + 32 * e;
+        G->rowt[t] = fc[e] - mt[e];
+        G->colt[t] = iv[e] - fc[e];
+        G->b[t] = expf(fc[e] + m_prev - mt[e]);
+        G->a[t] = expf(fcL - fc[e] + iv[e] - mL);
+        G->fg[t] = fr[e];
+        G->emm[t] = expf(-mt[e]);
+    }
+    if (lane == 0) G->g = expf(fcL + m_prev - mL);
+}
+
+template <typename GT>
+__global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant__ Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool is_ctrl = warp == 8;
+    const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+    const int qd = warp & 3, cs = (warp >> 2) & 1;
+    const int row = 16 * qd + (lane & 15), hf = lane >> 4;
+    const uint32_t lane_base = (uint32_t)(32 * qd) << 16;
+
+    Gates* G = (Gates*)(sm + Smem::gates);
+    float* nk = (float*)(sm + Smem::nk);
+    float* sdn = (float*)(sm + Smem::dnv);
+    float* part = (float*)(sm + Smem::part);
+    float* sdqn = (float*)(sm + Smem::dqn);
+    uint64_t* bars = (uint64_t*)(sm + Smem::misc);  // [0] tiles, [1] group A, [2] group B
+    uint32_t* tmem_slot = (uint32_t*)(sm + Smem::misc + 64);
+    int* abort_flag = (int*)(sm + Smem::misc + 72);
+    float* srun = (float*)(sm + Smem::misc + 80);
+    float* sred = (float*)(sm + Smem::misc + 96);  // 16 floats
+
+    unsigned char* sQ = sm + Smem::q;
+    unsigned char* sK = sm + Smem::k;
+    unsigned char* sV = sm + Smem::v;
+    unsigned char* sCk = sm + Smem::ck;
+    unsigned char* sdN = sm + Smem::dn_;
+    unsigned char* sdNb = sm + Smem::dnb;
+    unsigned char* sdCb = sm + Smem::dcb;
+    unsigned char* sDS = sm + Smem::ds_;
+    unsigned char* sdS = sm + Smem::dS;
+
+    if (tid == 0) {
+        mbar_init(&bars[0], 1); mbar_init(&bars[1], 1); mbar_init(&bars[2], 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (is_ctrl) tmem_alloc(tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tS = tmem + 0, tDds = tmem + 32, tVi = tmem + 64, tVe = tmem + 128, tQ = tmem + 192, tKi = tmem + 256,
+                   tKe = tmem + 320, tC = tmem + 384;
+
+    auto issue_tiles = [&](int ch) {
+        mbar_expect_tx(&bars[0], 3 * kTileBytes + 2 * kStateBox);
+        for (int cbx = 0; cbx < 2; ++cbx) {
+            tma_load_3d(sQ + cbx * kBoxBytes, &p.tmq, &bars[0], h * D + 64 * cbx, ch * L, b);
+            tma_load_3d(sK + cbx * kBoxBytes, &p.tmk, &bars[0], h * D + 64 * cbx, ch * L, b);
+            tma_load_3d(sV + cbx * kBoxBytes, &p.tmv, &bars[0], h * D + 64 * cbx, ch * L, b);
+            tma_load_2d(sCk + cbx * kStateBox, &p.tmc, &bars[0], 64 * cbx, (bh * (p.NC + 1) + ch) * D);
+        }
+    };
+
+    // ---- prologue -------------------------------------------------------------------------------
+    if (is_ctrl) {
+        if (lane == 0) issue_tiles(p.NC - 1);
+        gates_warp(p, b, h, bh, p.NC - 1, &G[(p.NC - 1) & 1]);
+    } else {
+        // carry term of the forget-gate gradient: <dC_in, C_end> + dn_in . n_end
+        float acc = 0.f;
+        if (p.cdC) {
+            const bf16* Ce = p.savedC + ((size_t)bh * (p.NC + 1) + p.NC) * D * D;
+            const float* dCi = p.cdC + (size_t)bh * D * D;
+            for (int i = tid; i < D * D; i += kMathThreads) acc += dCi[i] * __bfloat162float(Ce[i]);
+            if (tid < D) acc += p.cdn[(size_t)bh * D + tid] * p.savedn[((size_t)bh * (p.NC + 1) + p.NC) * D + tid];
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) sred[warp] = acc;
+        if (tid < D) sdn[tid] = p.cdn ? p.cdn[(size_t)bh * D + tid] : 0.f;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float r = 0.f;
+        for (int w = 0; w < 8; ++w) r += sred[w];
+        *srun = r;
+    }
+    if (!is_ctrl) {
+        // dC+ into TMEM (pre-scaled by g of the last chunk) and as bf16 into dCb
+        const float g0 = G[(p.NC - 1) & 1].g;
+        const int vrow = 32 * qd + lane;
+        for (int c0 = 64 * cs; c0 < 64 * cs + 64; c0 += 32) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = p.cdC ? p.cdC[(size_t)bh * D * D + (size_t)vrow * D + c0 + i] : 0.f;
+            put_row32(sdCb + cs * kStateBox, vrow, (c0 & 63) >> 3, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= g0;
+            tmem_st32(tC + lane_base + c0, v);
+        }
+        tmem_st_wait();
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // descriptor templates
+    const uint64_t dK_ = smem_desc(0, 16, 1024);          // K-major operand
+    const uint64_t dM1 = smem_desc(0, kBoxBytes, 1024);   // MN-major, 64-element groups kBoxBytes apart ([64-row] tiles)
+    const uint64_t dM2 = smem_desc(0, kStateBox, 1024);   // MN-major over a [128-row] state tile
+    constexpr uint32_t id_kk32 = instr_desc(64, 32, 0, 0);
+    constexpr uint32_t id_kk64 = instr_desc(64, 64, 0, 0);
+    constexpr uint32_t id_km64 = instr_desc(64, 64, 0, 1);
+    constexpr uint32_t id_mm64 = instr_desc(64, 64, 1, 1);
+    constexpr uint32_t id_mm128 = instr_desc(128, 128, 1, 1);
+
+    bool ok = true;
+    int it = 0;
+    for (int ch = p.NC - 1; ch >= 0; --ch, ++it) {
+        const int t0 = ch * L, Lc = min(L, p.T - t0);
+        Gates* Gc = &G[ch & 1];
+        const int dcur = it & 1;  // dn buffer holding dn+
+        float* dn_in = sdn + dcur * D;
+        float* dn_out = sdn + (dcur ^ 1) * D;
+
+        // =============== phase 1: dN, dNb tiles and the dqn partial dots (math) =====================
+        float ipsi = 0.f, bt = 0.f, at = 0.f;
+        if (!is_ctrl) {
+            bt = Gc->b[row];
+            at = Gc->a[row];
+            float dyv[32], yv[32];
+            const int col = 64 * hf + 32 * cs;
+            float dot = 0.f;
+            if (row < Lc) {
+                const size_t o = (((size_t)b * p.T + t0 + row) * p.H + h) * D + col;
+                load32<GT>(reinterpret_cast<const GT*>(p.dy) + o, dyv);
+                load32<bf16>(p.ytil + o, yv);
+                ipsi = 1.f / p.psiv[(size_t)bh * p.T + t0 + row];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) { dot += dyv[i] * yv[i]; dyv[i] *= ipsi; }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) dyv[i] = 0.f;
+            }
+            put_row32(sdN + hf * kBoxBytes, row, 4 * cs, dyv);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) dyv[i] *= bt;
+            put_row32(sdNb + hf * kBoxBytes, row, 4 * cs, dyv);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 16);
+            if (hf == 0) part[cs * L + row] = dot;
+            if (tid < D) nk[tid] = p.savedn[((size_t)bh * (p.NC + 1) + ch) * D + tid];
+            fence_async_smem();
+        } else {
+            if (!mbar_wait(&bars[0], it & 1)) *abort_flag = 1;
+        }
+        __syncthreads();  // #1
+        if (*abort_flag) { ok = false; break; }
+
+        // =============== phase 2: group A MMAs (control) | dqn (math) ===============================
+        if (is_ctrl) {
+            if (lane == 0) {
+                tc_fence_after();
+                const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aCk = smem_u32(sCk),
+                               adN = smem_u32(sdN), adNb = smem_u32(sdNb), adC = smem_u32(sdCb);
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const uint32_t lo = (uint32_t)(16 * hh) << 16;
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint32_t ko = (ks >> 2) * kBoxBytes + (ks & 3) * 32;    // K-major step in a [64-row] tile
+                        const uint32_t kc = (ks >> 2) * kStateBox + (ks & 3) * 32;    // K-major step in a [128-row] tile
+                        // S = Q K^T (rows j of K: 32 per half)
+                        mma_ss(tS + lo, desc_at(dK_, aQ + ko), desc_at(dK_, aK + ko + hh * 32 * 128), id_kk32, ks > 0);
+                        // dds = dN V^T
+                        mma_ss(tDds + lo, desc_at(dK_, adN + ko), desc_at(dK_, aV + ko + hh * 32 * 128), id_kk32, ks > 0);
+                        // dVe = K dC+^T : B = dCb rows v (64 per half), K-major over c
+                        mma_ss(tVe + lo, desc_at(dK_, aK + ko), desc_at(dK_, adC + kc + hh * 64 * 128), id_kk64, ks > 0);
+                        // dKe = V dC+ : A = V K-major over v; B = dCb MN-major (N = c: box hh), K = v rows in steps of 16
+                        mma_ss(tKe + lo, desc_at(dK_, aV + ko), desc_at(dM2, adC + hh * kStateBox + ks * 2048), id_km64, ks > 0);
+                        // dQ = dNb C_k : A = dNb K-major over v; B = Ck MN-major (N = c: box hh), K = v rows
+                        mma_ss(tQ + lo, desc_at(dK_, adNb + ko), desc_at(dM2, aCk + hh * kStateBox + ks * 2048), id_km64, ks > 0);
+                    }
+                }
+                mma_commit(&bars[1]);
+            }
+            __syncwarp();
+            if (ch > 0) gates_warp(p, b, h, bh, ch - 1, &G[(ch - 1) & 1]);
+        } else {
+            if (tid < L) {
+                const size_t o = (size_t)bh * p.T + t0 + min(tid, Lc - 1);
+                const float qn = p.qnv[o];
+                const float dot = part[tid] + part[L + tid];
+                float r = 0.f;
+                if (tid < Lc && fabsf(qn) > Gc->emm[tid]) r = (qn > 0.f ? -1.f : 1.f) * dot / p.psiv[o];
+                sdqn[tid] = r;
+            }
+            // order sdqn before its readers without stalling the control warp: math-only named barrier
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (!mbar_wait(&bars[1], it & 1)) *abort_flag = 2;
+            tc_fence_after();
+            // ---- S / dds epilogue: this thread's 16 columns j of row t
+            float s[16], dd[16], dsv[16], dSv[16];
+            tmem_ld16(tS + lane_base + 16 * cs, s);
+            tmem_ld16(tDds + lane_base + 16 * cs, dd);
+            tmem_ld_wait();
+            const float rt = Gc->rowt[row], dq_t = sdqn[row];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int j = 32 * hf + 16 * cs + i;
+                const float dbar = (j <= row) ? __expf(rt + Gc->colt[j]) : 0.f;
+                dsv[i] = dbar * s[i];
+                dSv[i] = dbar * (dd[i] + dq_t);
+            }
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2) {
+                uint4 pk, pk2;
+                pk.x = pack_bf16(dsv[8 * q2 + 0], dsv[8 * q2 + 1]); pk.y = pack_bf16(dsv[8 * q2 + 2], dsv[8 * q2 + 3]);
+                pk.z = pack_bf16(dsv[8 * q2 + 4], dsv[8 * q2 + 5]); pk.w = pack_bf16(dsv[8 * q2 + 6], dsv[8 * q2 + 7]);
+                pk2.x = pack_bf16(dSv[8 * q2 + 0], dSv[8 * q2 + 1]); pk2.y = pack_bf16(dSv[8 * q2 + 2], dSv[8 * q2 + 3]);
+                pk2.z = pack_bf16(dSv[8 * q2 + 4], dSv[8 * q2 + 5]); pk2.w = pack_bf16(dSv[8 * q2 + 6], dSv[8 * q2 + 7]);
+                const uint32_t off = swz(row, 4 * hf + 2 * cs + q2);
+                *reinterpret_cast<uint4*>(sDS + off) = pk;
+                *reinterpret_cast<uint4*>(sdS + off) = pk2;
+            }
+            fence_async_smem();
+            tc_fence_before();
+        }
+        __syncthreads();  // #2
+        if (*abort_flag) { ok = false; break; }
+
+        // =============== phase 3: group B MMAs (control) | epilogues (math) ==========================
+        if (is_ctrl) {
+            if (lane == 0) {
+                tc_fence_after();
+                const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), adN = smem_u32(sdN), adNb = smem_u32(sdNb),
+                               aDS = smem_u32(sDS), adS = smem_u32(sdS);
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const uint32_t lo = (uint32_t)(16 * hh) << 16;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        // dVi = DS^T dN : A = DS MN-major (M = j), B = dN MN-major (N = v: box hh), K = t rows
+                        mma_ss(tVi + lo, desc_at(dM1, aDS + ks * 2048), desc_at(dM1, adN + hh * kBoxBytes + ks * 2048), id_mm64, ks > 0);
+                        // dQ += dS K : A = dS K-major over j, B = K MN-major (N = c: box hh), K = j rows
+                        mma_ss(tQ + lo, desc_at(dK_, adS + ks * 32), desc_at(dM1, aK + hh * kBoxBytes + ks * 2048), id_km64, 1);
+                        // dKi = dS^T Q : A = dS MN-major (M = j), B = Q MN-major (N = c: box hh), K = t rows
+                        mma_ss(tKi + lo, desc_at(dM1, adS + ks * 2048), desc_at(dM1, aQ + hh * kBoxBytes + ks * 2048), id_mm64, ks > 0);
+                    }
+                }
+                // dC += dNb^T Q : M = v, N = c, K = t
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    mma_ss(tC, desc_at(dM1, adNb + ks * 2048), desc_at(dM1, aQ + ks * 2048), id_mm128, 1);
+                mma_commit(&bars[2]);
+            }
+            __syncwarp();
+        } else {
+            if (!mbar_wait(&bars[2], it & 1)) *abort_flag = 3;
+            tc_fence_after();
+            const int col = 64 * hf + 32 * cs;
+            const bool live = row < Lc;
+            const size_t orow = ((size_t)b * p.T + t0 + row) * p.H + h;
+            float a1[32], a2[32];
+            // dV = dVi + a dVe
+            tmem_ld32(tVi + lane_base + 32 * cs, a1);
+            tmem_ld32(tVe + lane_base + 32 * cs, a2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) a1[i] += at * a2[i];
+            if (live) store32<GT>(reinterpret_cast<GT*>(p.dv) + orow * D + col, a1);
+            // dQ = acc + b dqn n
+            tmem_ld32(tQ + lane_base + 32 * cs, a1);
+            tmem_ld_wait();
+            const float bq = bt * sdqn[row];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) a1[i] += bq * nk[col + i];
+            float u = dot_row32(sQ + hf * kBoxBytes, row, 4 * cs, a1);
+            if (live) store32<GT>(reinterpret_cast<GT*>(p.dq) + orow * D + col, a1);
+            // dK = dKi + a (dKe + dn+)
+            tmem_ld32(tKi + lane_base + 32 * cs, a1);
+            tmem_ld32(tKe + lane_base + 32 * cs, a2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) a1[i] += at * (a2[i] + dn_in[col + i]);
+            float w = dot_row32(sK + hf * kBoxBytes, row, 4 * cs, a1);
+            if (live) store32<GT>(reinterpret_cast<GT*>(p.dk) + orow * D + col, a1);
+            u += __shfl_xor_sync(0xffffffffu, u, 16);
+            w += __shfl_xor_sync(0xffffffffu, w, 16);
+            if (hf == 0) {
+                part[(2 + cs) * L + row] = u;
+                part[(4 + cs) * L + row] = w;
+            }
+            // dn = g dn+ + sum_t b_t dqn_t q_t   (into the other buffer)
+            if (tid < D) {
+                const int cbx = tid >> 6, cc = tid & 63;
+                float acc = 0.f;
+#pragma unroll 8
+                for (int t = 0; t < L; ++t) {
+                    bf16 qv = *reinterpret_cast<const bf16*>(sQ + cbx * kBoxBytes + swz(t, cc >> 3) + (cc & 7) * 2);
+                    acc += Gc->b[t] * sdqn[t] * __bfloat162float(qv);
+                }
+                dn_out[tid] = Gc->g * dn_in[tid] + acc;
+            }
+        }
+        __syncthreads();  // #3
+        if (*abort_flag) { ok = false; break; }
+
+        // =============== phase 4: gate gradients + next tiles (control) | dC pass (math) ==============
+        if (is_ctrl) {
+            if (lane == 0 && ch > 0) issue_tiles(ch - 1);
+            float dF[2], wv[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                int t = lane + 32 * e;
+                float u = part[2 * L + t] + part[3 * L + t];
+                wv[e] = part[4 * L + t] + part[5 * L + t];
+                dF[e] = (t < Lc) ? (u - wv[e]) : 0.f;
+            }
+            // suffix sums over the 64 positions
+            float s0 = dF[0], s1 = dF[1];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                float y0 = __shfl_down_sync(0xffffffffu, s0, o), y1 = __shfl_down_sync(0xffffffffu, s1, o);
+                if (lane + o < 32) { s0 += y0; s1 += y1; }
+            }
+            const float tot1 = __shfl_sync(0xffffffffu, s1, 0);
+            s0 += tot1;
+            const float tot = __shfl_sync(0xffffffffu, s0, 0);
+            const float run = *srun;
+            float sf[2] = {s0, s1};
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                int t = lane + 32 * e;
+                if (t < Lc) {
+                    size_t gi = ((size_t)b * p.T + t0 + t) * p.H + h;
+                    p.dfg[gi] = (run + sf[e]) * (1.f - stable_sigmoid(Gc->fg[t]));
+                    p.dig[gi] = wv[e];
+                }
+            }
+            __syncwarp();
+            if (lane == 0) *srun = run + tot;
+        } else {
+            const int vrow = 32 * qd + lane;
+            const float gn = (ch > 0) ? G[(ch - 1) & 1].g : 1.f;
+            float* oc = (ch == 0 && p.odC) ? p.odC + (size_t)bh * D * D + (size_t)vrow * D : nullptr;
+            for (int c0 = 64 * cs; c0 < 64 * cs + 64; c0 += 32) {
+                float v[32];
+                tmem_ld32(tC + lane_base + c0, v);
+                tmem_ld_wait();
+                put_row32(sdCb + cs * kStateBox, vrow, (c0 & 63) >> 3, v);
+                if (oc) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; ++q4)
+                        *reinterpret_cast<float4*>(oc + c0 + 4 * q4) = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+                }
+                if (ch > 0) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] *= gn;
+                    tmem_st32(tC + lane_base + c0, v);
+                }
+            }
+            tmem_st_wait();
+            fence_async_smem();
+            tc_fence_before();
+        }
+        __syncthreads();  // #4
+    }
+
+    if (ok) {
+        if (p.odn && tid < D) p.odn[(size_t)bh * D + tid] = sdn[(it & 1) * D + tid];
+    } else if (tid == 0) {
+        atomicCAS(&g_tc_status, 0, 200 + *abort_flag);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (is_ctrl) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+}  // namespace bw
+
+bool tc_make_map3(CUtensorMap* m, const void* base, int B, int T, int W);
+bool tc_make_map2(CUtensorMap* m, const void* base, uint64_t rows, int W, int box_rows);
+
+int mlstm_bw_tc_launch(cudaStream_t st, const MlstmBwArgs& a, const void* saved, int gdtype) {
+    using namespace bw;
+    if (((uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.ytil | (uintptr_t)a.dytil | (uintptr_t)a.dq |
+         (uintptr_t)a.dk | (uintptr_t)a.dv | (uintptr_t)saved) & 15) {
+        set_error("mlstm_bw (tensor-core path): tensors must be 16-byte aligned");
+        return XLSTM_ERR_ARG;
+    }
+    Params p = {};
+    const int BH = a.B * a.H;
+    p.savedC = (const bf16*)saved;
+    p.savedn = (const float*)((const char*)saved + mlstm_tc_saved_C_bytes(BH, a.NC));
+    if (!tc_make_map3(&p.tmq, a.q, a.B, a.T, a.H * D) || !tc_make_map3(&p.tmk, a.k, a.B, a.T, a.H * D) ||
+        !tc_make_map3(&p.tmv, a.v, a.B, a.T, a.H * D) ||
+        !tc_make_map2(&p.tmc, p.savedC, (uint64_t)BH * (a.NC + 1) * D, D, D)) {
+        set_error("mlstm_bw: cuTensorMapEncodeTiled failed");
+        return XLSTM_ERR_CUDA;
+    }
+    p.ig = a.ig; p.fg = a.fg; p.cm = a.cm; p.ytil = (const bf16*)a.ytil; p.msv = a.msv; p.psiv = a.psiv; p.qnv = a.qnv;
+    p.dy = a.dytil; p.cdC = a.cdC; p.cdn = a.cdn; p.dq = a.dq; p.dk = a.dk; p.dv = a.dv; p.dig = a.dig; p.dfg = a.dfg;
+    p.odC = a.odC; p.odn = a.odn; p.B = a.B; p.H = a.H; p.T = a.T; p.NC = a.NC; p.gbf16 = gdtype == XLSTM_BF16;
+    size_t smem = Smem::total + 1024;
+    if (gdtype == XLSTM_BF16) {
+        XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        mlstm_bw_tc<bf16><<<BH, kThreads, smem, st>>>(p);
+    } else {
+        XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        mlstm_bw_tc<float><<<BH, kThreads, smem, st>>>(p);
+    }
+    XL_LAUNCH_OK("mlstm_bw_tc");
+    return XLSTM_OK;
+}
+
+}  // namespace xl
