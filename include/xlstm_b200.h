@@ -144,6 +144,18 @@ int xlstm_ce_fw_bw(void* stream, const float* logits, const uint32_t* targets,
                    const uint32_t* mask, float* dlogits, float* loss_accum, int rows, int C,
                    float inv, void* workspace, size_t workspace_bytes);
 
+/* The same op for hosts that cannot allocate device memory (a runtime whose buffer pool already
+ * owns all of it, or a step loop that must stay clear of the CUDA allocator): the per-row scratch
+ * is a fixed array inside the library instead of a caller workspace. It has no counterpart in the
+ * reference. At most XLSTM_CE_NOALLOC_MAX_ROWS rows per call, larger calls are refused with
+ * XLSTM_ERR_ARG. All calls on one device share the array: calls that may overlap on the GPU race,
+ * so keep them on one stream. The first call on a device resolves the array's address and should
+ * be made before any stream capture begins. */
+#define XLSTM_CE_NOALLOC_MAX_ROWS 65536
+int xlstm_ce_fw_bw_noalloc(void* stream, const float* logits, const uint32_t* targets,
+                           const uint32_t* mask, float* dlogits, float* loss_accum, int rows,
+                           int C, float inv);
+
 /* ---- AdamW over many tensors ----------------------------------------------------------------
  * Replaces ops::adamw and AdamwQueue::flush (src/gpu/ops.rs:1775-1933, src/gpu/cuda/
  * common.cu:323-361). `descs` is a HOST array. bc1 = 1-beta1^t, bc2 = 1-beta2^t are

@@ -53,6 +53,7 @@ SIGNATURES = {
     "xlstm_rmsnorm_bw": (_i, [_vp] * 7 + [_i, _i, _i, _vp, _sz]),
     "xlstm_ce_workspace_bytes": (_sz, [_i]),
     "xlstm_ce_fw_bw": (_i, [_vp] * 6 + [_i, _i, _f, _vp, _sz]),
+    "xlstm_ce_fw_bw_noalloc": (_i, [_vp] * 6 + [_i, _i, _f]),
     "xlstm_adamw_multi": (_i, [_vp, ctypes.POINTER(AdamwDesc), _i, _f, _f, _f, _f, _f, _f, _i]),
 }
 

@@ -194,3 +194,63 @@ extern "C" int xlstm_ce_fw_bw(void* stream, const float* logits, const uint32_t*
     XL_LAUNCH_OK("ce_loss_reduce");
     return XLSTM_OK;
 }
+
+// ---- the same op for callers that cannot allocate device memory --------------------------------
+//
+// xlstm_ce_fw_bw needs one float of scratch per row and asks the caller for it. Some hosts have no
+// way to supply that: the reference's own runtime hands every byte of device memory to its buffer
+// pool up front, and a step loop that must never touch the CUDA allocator (because cudaMalloc and
+// cudaFree can synchronise the whole device, or because the surrounding code runs where allocation
+// calls are not allowed) has the same problem. For them the scratch lives inside the library, in a
+// fixed array that every GPU loading the library keeps resident until the process exits.
+//
+// Limits and sharing rules, because the array is one per device and is never cleared:
+//   - at most XLSTM_CE_NOALLOC_MAX_ROWS rows per call (256 KiB of scratch); more is refused;
+//   - every element a call reads is written earlier in the same call, so stale contents from the
+//     previous call are harmless and nothing needs zeroing;
+//   - two calls whose kernels may overlap on the same device (different streams) race on the
+//     array; serialise them on one stream.
+// The first call on each device looks up the array's device address (cudaGetSymbolAddress, which
+// is not an allocation); make that first call before starting any stream capture.
+static constexpr int kCeNoAllocMaxRows = 65536;
+static __device__ __align__(256) float g_ce_noalloc_scratch[kCeNoAllocMaxRows];
+
+static float* ce_noalloc_scratch_ptr(int* rc) {
+    // In host code the array's name is only a handle; the kernels need its device address.
+    static std::atomic<float*> cached[64];
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        set_error("ce_fw_bw_noalloc: cudaGetDevice failed or device index out of range: %s", cudaGetErrorString(e));
+        *rc = XLSTM_ERR_CUDA;
+        return nullptr;
+    }
+    float* p = cached[dev].load(std::memory_order_acquire);
+    if (!p) {
+        void* addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, g_ce_noalloc_scratch);
+        if (e != cudaSuccess || !addr) {
+            set_error("ce_fw_bw_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            *rc = XLSTM_ERR_CUDA;
+            return nullptr;
+        }
+        p = (float*)addr;
+        cached[dev].store(p, std::memory_order_release);
+    }
+    *rc = XLSTM_OK;
+    return p;
+}
+
+extern "C" int xlstm_ce_fw_bw_noalloc(void* stream, const float* logits, const uint32_t* targets, const uint32_t* mask,
+                                      float* dlogits, float* loss_accum, int rows, int C, float inv) {
+    if (rows > kCeNoAllocMaxRows) {
+        set_error("ce_fw_bw_noalloc: %d rows exceed the built-in scratch of %d rows; split the call or use xlstm_ce_fw_bw "
+                  "with a caller-owned workspace", rows, kCeNoAllocMaxRows);
+        return XLSTM_ERR_ARG;
+    }
+    int rc = XLSTM_OK;
+    float* scratch = ce_noalloc_scratch_ptr(&rc);
+    if (!scratch) return rc;
+    return xlstm_ce_fw_bw(stream, logits, targets, mask, dlogits, loss_accum, rows, C, inv, scratch,
+                          (size_t)kCeNoAllocMaxRows * sizeof(float));
+}
