@@ -9,7 +9,8 @@ OUT = os.path.join(HERE, "libxlstm_b200.so")
 OBJ = os.path.join(HERE, "build")
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+EXTRA = os.environ.get("XL_EXTRA_NVCC_FLAGS", "").split()
+FLAGS = EXTRA + ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "--use_fast_math=false", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 
 

@@ -225,13 +225,15 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
     constexpr uint32_t idC = instr_desc(128, 128, 1, 1);
 
     bool ok = true;
+#ifdef XL_TC_PROFILE
     long long tprev = clock64();
-#define PROF(i)                                              \
-    if (p.prof && bh == 0 && tid == 0) {                     \
-        long long tn = clock64();                            \
-        p.prof[i] += tn - tprev;                             \
-        tprev = tn;                                          \
-    }
+    long long pacc[12];
+#pragma unroll
+    for (int i = 0; i < 12; ++i) pacc[i] = 0;
+#define PROF(i) { long long tn = clock64(); pacc[i] += tn - tprev; tprev = tn; }
+#else
+#define PROF(i)
+#endif
     for (int ch = 0; ch < p.NC; ++ch) {
         const int st = ch & 1;
         const int t0 = ch * L, Lc = min(L, p.T - t0);
@@ -435,6 +437,10 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
         PROF(11)
     }
 #undef PROF
+#ifdef XL_TC_PROFILE
+    if (p.prof && bh == 0 && tid == 0)
+        for (int i = 0; i < 12; ++i) p.prof[i] = pacc[i];
+#endif
 
     if (ok) {
         if (p.on) p.on[(size_t)bh * D + tid] = nvec[tid];
@@ -484,6 +490,7 @@ bool tc_make_map3(CUtensorMap* m, const void* base, int B, int T, int W) {
 
 static long long* g_prof = nullptr;
 extern "C" void xlstm_debug_set_prof(void* p) { g_prof = (long long*)p; }
+long long* tc_debug_prof() { return g_prof; }
 
 // [rows][W] bf16 row-major, box = {64 cols, box_rows}, 128-byte swizzle.
 bool tc_make_map2(CUtensorMap* m, const void* base, uint64_t rows, int W, int box_rows) {

@@ -29,8 +29,9 @@ namespace bw {
 
 static constexpr int D = 128;
 static constexpr int L = 64;
-static constexpr int kMathThreads = 256;
-static constexpr int kThreads = 288;  // 8 math warps + 1 control warp
+static constexpr int kMathWarps = 16;
+static constexpr int kMathThreads = kMathWarps * 32;
+static constexpr int kThreads = kMathThreads + 32;  // + 1 control warp
 static constexpr uint32_t kTileBytes = L * D * 2;
 static constexpr uint32_t kBoxBytes = L * 128;
 static constexpr uint32_t kStateBox = D * 128;
@@ -62,41 +63,43 @@ struct Params {
     float *odC, *odn;
     int B, H, T, NC;
     int gbf16;
+    long long* prof;  // optional per-phase cycle counts of CTA 0 (development aid; null in production)
 };
 
 struct Smem {
-    static constexpr uint32_t q = 0;
-    static constexpr uint32_t k = q + kTileBytes;
-    static constexpr uint32_t v = k + kTileBytes;
-    static constexpr uint32_t ck = v + kTileBytes;       // [128 x 128] entering state, bf16
-    static constexpr uint32_t dn_ = ck + 2 * kStateBox;  // dN  = dy/psi
-    static constexpr uint32_t dnb = dn_ + kTileBytes;    // dNb = b . dN
-    static constexpr uint32_t dcb = dnb + kTileBytes;    // bf16 dC+
-    static constexpr uint32_t ds_ = dcb + 2 * kStateBox; // DS  [64 x 64]
-    static constexpr uint32_t dS = ds_ + kBoxBytes;      // dS  [64 x 64]
-    static constexpr uint32_t gates = dS + kBoxBytes;    // 2 x Gates
+    static constexpr uint32_t q = 0;                       // 2 stages
+    static constexpr uint32_t k = q + 2 * kTileBytes;      // 2 stages
+    static constexpr uint32_t v = k + 2 * kTileBytes;
+    static constexpr uint32_t ck = v + kTileBytes;         // [128 x 128] entering state, bf16
+    static constexpr uint32_t dn_ = ck + 2 * kStateBox;    // dN  = dy/psi
+    static constexpr uint32_t dnb = dn_ + kTileBytes;      // dNb = b . dN
+    static constexpr uint32_t dcb = dnb + kTileBytes;      // bf16 dC+
+    static constexpr uint32_t ds_ = dcb + 2 * kStateBox;   // DS  [64 x 64]
+    static constexpr uint32_t dS = ds_ + kBoxBytes;        // dS  [64 x 64]
+    static constexpr uint32_t gates = dS + kBoxBytes;      // 2 x Gates
     static constexpr uint32_t nk = gates + 2 * sizeof(Gates);  // n entering the chunk [128]
-    static constexpr uint32_t dnv = nk + D * 4;          // dn, double buffered [2][128]
-    static constexpr uint32_t part = dnv + 2 * D * 4;    // partial sums [6][64]: dot(2), u(2), w(2)
-    static constexpr uint32_t dqn = part + 6 * L * 4;    // [64]
+    static constexpr uint32_t dnv = nk + D * 4;            // dn, double buffered [2][128]
+    static constexpr uint32_t dnp = dnv + 2 * D * 4;       // dn partial sums [4][128]
+    static constexpr uint32_t part = dnp + 4 * D * 4;      // partial sums [12][64]: dot(4), u(4), w(4)
+    static constexpr uint32_t dqn = part + 12 * L * 4;     // [64]
     static constexpr uint32_t misc = dqn + L * 4;
     static constexpr uint32_t total = misc + 256;
 };
 
 template <typename G>
-__device__ __forceinline__ void load32(const G* p, float* v);
+__device__ __forceinline__ void load16(const G* p, float* v);
 template <>
-__device__ __forceinline__ void load32<float>(const float* p, float* v) {
+__device__ __forceinline__ void load16<float>(const float* p, float* v) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
         float4 t = __ldcs(reinterpret_cast<const float4*>(p) + i);
         v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
     }
 }
 template <>
-__device__ __forceinline__ void load32<bf16>(const bf16* p, float* v) {
+__device__ __forceinline__ void load16<bf16>(const bf16* p, float* v) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2; ++i) {
         uint4 t = __ldcs(reinterpret_cast<const uint4*>(p) + i);
         float2 a = unpack_bf16(t.x), b = unpack_bf16(t.y), c = unpack_bf16(t.z), d = unpack_bf16(t.w);
         v[8 * i] = a.x; v[8 * i + 1] = a.y; v[8 * i + 2] = b.x; v[8 * i + 3] = b.y;
@@ -104,17 +107,17 @@ __device__ __forceinline__ void load32<bf16>(const bf16* p, float* v) {
     }
 }
 template <typename G>
-__device__ __forceinline__ void store32(G* p, const float* v);
+__device__ __forceinline__ void store16(G* p, const float* v);
 template <>
-__device__ __forceinline__ void store32<float>(float* p, const float* v) {
+__device__ __forceinline__ void store16<float>(float* p, const float* v) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 4; ++i)
         __stcs(reinterpret_cast<float4*>(p) + i, make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
 }
 template <>
-__device__ __forceinline__ void store32<bf16>(bf16* p, const float* v) {
+__device__ __forceinline__ void store16<bf16>(bf16* p, const float* v) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2; ++i) {
         uint4 t;
         t.x = pack_bf16(v[8 * i], v[8 * i + 1]); t.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
         t.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]); t.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
@@ -122,21 +125,22 @@ __device__ __forceinline__ void store32<bf16>(bf16* p, const float* v) {
     }
 }
 
-// 32 floats -> 4 swizzled 16-byte chunks of row `row`, starting at logical chunk `chunk0`.
-__device__ __forceinline__ void put_row32(unsigned char* tile, uint32_t row, uint32_t chunk0, const float* v) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        uint4 pk;
-        pk.x = pack_bf16(v[8 * q + 0], v[8 * q + 1]); pk.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
-        pk.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]); pk.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
-        *reinterpret_cast<uint4*>(tile + swz(row, chunk0 + q)) = pk;
-    }
+__device__ __forceinline__ uint4 pack8(const float* v) {
+    uint4 pk;
+    pk.x = pack_bf16(v[0], v[1]); pk.y = pack_bf16(v[2], v[3]); pk.z = pack_bf16(v[4], v[5]); pk.w = pack_bf16(v[6], v[7]);
+    return pk;
 }
-// dot of 32 floats with 32 bf16 of row `row` (chunks chunk0..chunk0+3) of a swizzled tile
-__device__ __forceinline__ float dot_row32(const unsigned char* tile, uint32_t row, uint32_t chunk0, const float* v) {
+// N floats (N = 8 * chunks) -> swizzled 16-byte chunks of row `row`, starting at logical chunk `chunk0`.
+template <int CHUNKS>
+__device__ __forceinline__ void put_row(unsigned char* tile, uint32_t row, uint32_t chunk0, const float* v) {
+#pragma unroll
+    for (int q = 0; q < CHUNKS; ++q) *reinterpret_cast<uint4*>(tile + swz(row, chunk0 + q)) = pack8(v + 8 * q);
+}
+// dot of 16 floats with 16 bf16 of row `row` (chunks chunk0, chunk0+1) of a swizzled tile
+__device__ __forceinline__ float dot_row16(const unsigned char* tile, uint32_t row, uint32_t chunk0, const float* v) {
     float acc = 0.f;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < 2; ++q) {
         uint4 x = *reinterpret_cast<const uint4*>(tile + swz(row, chunk0 + q));
         float2 f0 = unpack_bf16(x.x), f1 = unpack_bf16(x.y), f2 = unpack_bf16(x.z), f3 = unpack_bf16(x.w);
         acc += v[8 * q] * f0.x + v[8 * q + 1] * f0.y + v[8 * q + 2] * f1.x + v[8 * q + 3] * f1.y + v[8 * q + 4] * f2.x +
@@ -191,25 +195,25 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const bool is_ctrl = warp == 8;
+    const bool is_ctrl = warp == kMathWarps;
     const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
-    const int qd = warp & 3, cs = (warp >> 2) & 1;
+    const int qd = warp & 3, cq = (warp >> 2) & 3;
     const int row = 16 * qd + (lane & 15), hf = lane >> 4;
     const uint32_t lane_base = (uint32_t)(32 * qd) << 16;
+    const int col = 64 * hf + 16 * cq;  // this thread's 16 columns of a [64 x 128] position-indexed tile
 
     Gates* G = (Gates*)(sm + Smem::gates);
     float* nk = (float*)(sm + Smem::nk);
     float* sdn = (float*)(sm + Smem::dnv);
+    float* sdnp = (float*)(sm + Smem::dnp);
     float* part = (float*)(sm + Smem::part);
     float* sdqn = (float*)(sm + Smem::dqn);
-    uint64_t* bars = (uint64_t*)(sm + Smem::misc);  // [0] tiles, [1] group A, [2] group B
+    uint64_t* bars = (uint64_t*)(sm + Smem::misc);  // [0],[1] Q/K stages, [2] V, [3] Ck, [4] group A, [5] group B
     uint32_t* tmem_slot = (uint32_t*)(sm + Smem::misc + 64);
     int* abort_flag = (int*)(sm + Smem::misc + 72);
     float* srun = (float*)(sm + Smem::misc + 80);
     float* sred = (float*)(sm + Smem::misc + 96);  // 16 floats
 
-    unsigned char* sQ = sm + Smem::q;
-    unsigned char* sK = sm + Smem::k;
     unsigned char* sV = sm + Smem::v;
     unsigned char* sCk = sm + Smem::ck;
     unsigned char* sdN = sm + Smem::dn_;
@@ -219,7 +223,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     unsigned char* sdS = sm + Smem::dS;
 
     if (tid == 0) {
-        mbar_init(&bars[0], 1); mbar_init(&bars[1], 1); mbar_init(&bars[2], 1);
+        for (int i = 0; i < 6; ++i) mbar_init(&bars[i], 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -231,21 +235,41 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     const uint32_t tS = tmem + 0, tDds = tmem + 32, tVi = tmem + 64, tVe = tmem + 128, tQ = tmem + 192, tKi = tmem + 256,
                    tKe = tmem + 320, tC = tmem + 384;
 
-    auto issue_tiles = [&](int ch) {
-        mbar_expect_tx(&bars[0], 3 * kTileBytes + 2 * kStateBox);
+    auto issue_qk = [&](int ch, int stage) {
+        mbar_expect_tx(&bars[stage], 2 * kTileBytes);
         for (int cbx = 0; cbx < 2; ++cbx) {
-            tma_load_3d(sQ + cbx * kBoxBytes, &p.tmq, &bars[0], h * D + 64 * cbx, ch * L, b);
-            tma_load_3d(sK + cbx * kBoxBytes, &p.tmk, &bars[0], h * D + 64 * cbx, ch * L, b);
-            tma_load_3d(sV + cbx * kBoxBytes, &p.tmv, &bars[0], h * D + 64 * cbx, ch * L, b);
-            tma_load_2d(sCk + cbx * kStateBox, &p.tmc, &bars[0], 64 * cbx, (bh * (p.NC + 1) + ch) * D);
+            tma_load_3d(sm + Smem::q + stage * kTileBytes + cbx * kBoxBytes, &p.tmq, &bars[stage], h * D + 64 * cbx, ch * L, b);
+            tma_load_3d(sm + Smem::k + stage * kTileBytes + cbx * kBoxBytes, &p.tmk, &bars[stage], h * D + 64 * cbx, ch * L, b);
+        }
+    };
+    auto issue_v_ck = [&](int ch) {
+        mbar_expect_tx(&bars[2], kTileBytes);
+        mbar_expect_tx(&bars[3], 2 * kStateBox);
+        for (int cbx = 0; cbx < 2; ++cbx) {
+            tma_load_3d(sV + cbx * kBoxBytes, &p.tmv, &bars[2], h * D + 64 * cbx, ch * L, b);
+            tma_load_2d(sCk + cbx * kStateBox, &p.tmc, &bars[3], 64 * cbx, (bh * (p.NC + 1) + ch) * D);
+        }
+    };
+
+    // operands of the dN pass, prefetched one chunk ahead into registers
+    float dyv[16], yv[16];
+    float psi_r = 1.f;
+    auto prefetch_dy = [&](int ch) {
+        const int t0 = ch * L, Lc = min(L, p.T - t0);
+        if (row < Lc) {
+            const size_t o = (((size_t)b * p.T + t0 + row) * p.H + h) * D + col;
+            load16<GT>(reinterpret_cast<const GT*>(p.dy) + o, dyv);
+            load16<bf16>(p.ytil + o, yv);
+            psi_r = p.psiv[(size_t)bh * p.T + t0 + row];
         }
     };
 
     // ---- prologue -------------------------------------------------------------------------------
     if (is_ctrl) {
-        if (lane == 0) issue_tiles(p.NC - 1);
+        if (lane == 0) { issue_qk(p.NC - 1, 0); issue_v_ck(p.NC - 1); }
         gates_warp(p, b, h, bh, p.NC - 1, &G[(p.NC - 1) & 1]);
     } else {
+        prefetch_dy(p.NC - 1);
         // carry term of the forget-gate gradient: <dC_in, C_end> + dn_in . n_end
         float acc = 0.f;
         if (p.cdC) {
@@ -261,22 +285,20 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     __syncthreads();
     if (tid == 0) {
         float r = 0.f;
-        for (int w = 0; w < 8; ++w) r += sred[w];
+        for (int w = 0; w < kMathWarps; ++w) r += sred[w];
         *srun = r;
     }
     if (!is_ctrl) {
         // dC+ into TMEM (pre-scaled by g of the last chunk) and as bf16 into dCb
         const float g0 = G[(p.NC - 1) & 1].g;
-        const int vrow = 32 * qd + lane;
-        for (int c0 = 64 * cs; c0 < 64 * cs + 64; c0 += 32) {
-            float v[32];
+        const int vrow = 32 * qd + lane, c0 = 32 * cq;
+        float v[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = p.cdC ? p.cdC[(size_t)bh * D * D + (size_t)vrow * D + c0 + i] : 0.f;
-            put_row32(sdCb + cs * kStateBox, vrow, (c0 & 63) >> 3, v);
+        for (int i = 0; i < 32; ++i) v[i] = p.cdC ? p.cdC[(size_t)bh * D * D + (size_t)vrow * D + c0 + i] : 0.f;
+        put_row<4>(sdCb + (cq >> 1) * kStateBox, vrow, 4 * (cq & 1), v);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= g0;
-            tmem_st32(tC + lane_base + c0, v);
-        }
+        for (int i = 0; i < 32; ++i) v[i] *= g0;
+        tmem_st32(tC + lane_base + c0, v);
         tmem_st_wait();
     }
     fence_async_smem();
@@ -295,47 +317,58 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
 
     bool ok = true;
     int it = 0;
+#ifdef XL_TC_PROFILE
+    long long tprev = clock64();
+    long long pacc[13];
+#pragma unroll
+    for (int i = 0; i < 13; ++i) pacc[i] = 0;
+#define PROF(i) { long long tn = clock64(); pacc[i] += tn - tprev; tprev = tn; }
+#else
+#define PROF(i)
+#endif
     for (int ch = p.NC - 1; ch >= 0; --ch, ++it) {
         const int t0 = ch * L, Lc = min(L, p.T - t0);
+        const int stg = it & 1;
         Gates* Gc = &G[ch & 1];
-        const int dcur = it & 1;  // dn buffer holding dn+
-        float* dn_in = sdn + dcur * D;
-        float* dn_out = sdn + (dcur ^ 1) * D;
+        float* dn_in = sdn + stg * D;          // dn+
+        float* dn_out = sdn + (stg ^ 1) * D;
+        unsigned char* sQ = sm + Smem::q + stg * kTileBytes;
+        unsigned char* sK = sm + Smem::k + stg * kTileBytes;
 
+        PROF(0)
         // =============== phase 1: dN, dNb tiles and the dqn partial dots (math) =====================
-        float ipsi = 0.f, bt = 0.f, at = 0.f;
+        float bt = 0.f, at = 0.f;
         if (!is_ctrl) {
             bt = Gc->b[row];
             at = Gc->a[row];
-            float dyv[32], yv[32];
-            const int col = 64 * hf + 32 * cs;
             float dot = 0.f;
             if (row < Lc) {
-                const size_t o = (((size_t)b * p.T + t0 + row) * p.H + h) * D + col;
-                load32<GT>(reinterpret_cast<const GT*>(p.dy) + o, dyv);
-                load32<bf16>(p.ytil + o, yv);
-                ipsi = 1.f / p.psiv[(size_t)bh * p.T + t0 + row];
+                const float ipsi = 1.f / psi_r;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) { dot += dyv[i] * yv[i]; dyv[i] *= ipsi; }
+                for (int i = 0; i < 16; ++i) { dot += dyv[i] * yv[i]; dyv[i] *= ipsi; }
             } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) dyv[i] = 0.f;
+                for (int i = 0; i < 16; ++i) dyv[i] = 0.f;
             }
-            put_row32(sdN + hf * kBoxBytes, row, 4 * cs, dyv);
+            put_row<2>(sdN + hf * kBoxBytes, row, 2 * cq, dyv);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) dyv[i] *= bt;
-            put_row32(sdNb + hf * kBoxBytes, row, 4 * cs, dyv);
+            for (int i = 0; i < 16; ++i) dyv[i] *= bt;
+            put_row<2>(sdNb + hf * kBoxBytes, row, 2 * cq, dyv);
             dot += __shfl_xor_sync(0xffffffffu, dot, 16);
-            if (hf == 0) part[cs * L + row] = dot;
+            if (hf == 0) part[cq * L + row] = dot;
             if (tid < D) nk[tid] = p.savedn[((size_t)bh * (p.NC + 1) + ch) * D + tid];
             fence_async_smem();
         } else {
-            if (!mbar_wait(&bars[0], it & 1)) *abort_flag = 1;
+            if (lane == 0 && ch > 0) issue_qk(ch - 1, stg ^ 1);
+            bool w = mbar_wait(&bars[stg], (it >> 1) & 1) && mbar_wait(&bars[2], it & 1) && mbar_wait(&bars[3], it & 1);
+            if (!w) *abort_flag = 1;
         }
+        PROF(1)
         __syncthreads();  // #1
         if (*abort_flag) { ok = false; break; }
+        PROF(2)
 
-        // =============== phase 2: group A MMAs (control) | dqn (math) ===============================
+        // =============== phase 2: group A MMAs (control) | dqn, S/dds epilogue (math) ================
         if (is_ctrl) {
             if (lane == 0) {
                 tc_fence_after();
@@ -347,11 +380,19 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks) {
                         const uint32_t ko = (ks >> 2) * kBoxBytes + (ks & 3) * 32;    // K-major step in a [64-row] tile
-                        const uint32_t kc = (ks >> 2) * kStateBox + (ks & 3) * 32;    // K-major step in a [128-row] tile
                         // S = Q K^T (rows j of K: 32 per half)
                         mma_ss(tS + lo, desc_at(dK_, aQ + ko), desc_at(dK_, aK + ko + hh * 32 * 128), id_kk32, ks > 0);
                         // dds = dN V^T
                         mma_ss(tDds + lo, desc_at(dK_, adN + ko), desc_at(dK_, aV + ko + hh * 32 * 128), id_kk32, ks > 0);
+                    }
+                }
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const uint32_t lo = (uint32_t)(16 * hh) << 16;
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint32_t ko = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
+                        const uint32_t kc = (ks >> 2) * kStateBox + (ks & 3) * 32;    // K-major step in a [128-row] tile
                         // dVe = K dC+^T : B = dCb rows v (64 per half), K-major over c
                         mma_ss(tVe + lo, desc_at(dK_, aK + ko), desc_at(dK_, adC + kc + hh * 64 * 128), id_kk64, ks > 0);
                         // dKe = V dC+ : A = V K-major over v; B = dCb MN-major (N = c: box hh), K = v rows in steps of 16
@@ -360,52 +401,54 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
                         mma_ss(tQ + lo, desc_at(dK_, adNb + ko), desc_at(dM2, aCk + hh * kStateBox + ks * 2048), id_km64, ks > 0);
                     }
                 }
-                mma_commit(&bars[1]);
+                mma_commit(&bars[4]);
             }
             __syncwarp();
+            PROF(3)
             if (ch > 0) gates_warp(p, b, h, bh, ch - 1, &G[(ch - 1) & 1]);
+            PROF(4)
+            // V and C_k are consumed by group A only: refill them for the next chunk as soon as it is done
+            if (!mbar_wait(&bars[4], it & 1)) *abort_flag = 2;
+            if (lane == 0 && ch > 0) issue_v_ck(ch - 1);
         } else {
             if (tid < L) {
                 const size_t o = (size_t)bh * p.T + t0 + min(tid, Lc - 1);
                 const float qn = p.qnv[o];
-                const float dot = part[tid] + part[L + tid];
+                const float dot = part[tid] + part[L + tid] + part[2 * L + tid] + part[3 * L + tid];
                 float r = 0.f;
                 if (tid < Lc && fabsf(qn) > Gc->emm[tid]) r = (qn > 0.f ? -1.f : 1.f) * dot / p.psiv[o];
                 sdqn[tid] = r;
             }
+            if (ch > 0) prefetch_dy(ch - 1);  // lands during this chunk's remaining phases
             // order sdqn before its readers without stalling the control warp: math-only named barrier
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (!mbar_wait(&bars[1], it & 1)) *abort_flag = 2;
+            asm volatile("bar.sync 1, %0;" ::"n"(kMathThreads) : "memory");
+            PROF(3)
+            if (!mbar_wait(&bars[4], it & 1)) *abort_flag = 2;
             tc_fence_after();
-            // ---- S / dds epilogue: this thread's 16 columns j of row t
-            float s[16], dd[16], dsv[16], dSv[16];
-            tmem_ld16(tS + lane_base + 16 * cs, s);
-            tmem_ld16(tDds + lane_base + 16 * cs, dd);
+            PROF(4)
+            // ---- S / dds epilogue: this thread's 8 columns j of row t
+            float s[8], dd[8], dsv[8], dSv[8];
+            tmem_ld8(tS + lane_base + 8 * cq, s);
+            tmem_ld8(tDds + lane_base + 8 * cq, dd);
             tmem_ld_wait();
             const float rt = Gc->rowt[row], dq_t = sdqn[row];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const int j = 32 * hf + 16 * cs + i;
+            for (int i = 0; i < 8; ++i) {
+                const int j = 32 * hf + 8 * cq + i;
                 const float dbar = (j <= row) ? __expf(rt + Gc->colt[j]) : 0.f;
                 dsv[i] = dbar * s[i];
                 dSv[i] = dbar * (dd[i] + dq_t);
             }
-#pragma unroll
-            for (int q2 = 0; q2 < 2; ++q2) {
-                uint4 pk, pk2;
-                pk.x = pack_bf16(dsv[8 * q2 + 0], dsv[8 * q2 + 1]); pk.y = pack_bf16(dsv[8 * q2 + 2], dsv[8 * q2 + 3]);
-                pk.z = pack_bf16(dsv[8 * q2 + 4], dsv[8 * q2 + 5]); pk.w = pack_bf16(dsv[8 * q2 + 6], dsv[8 * q2 + 7]);
-                pk2.x = pack_bf16(dSv[8 * q2 + 0], dSv[8 * q2 + 1]); pk2.y = pack_bf16(dSv[8 * q2 + 2], dSv[8 * q2 + 3]);
-                pk2.z = pack_bf16(dSv[8 * q2 + 4], dSv[8 * q2 + 5]); pk2.w = pack_bf16(dSv[8 * q2 + 6], dSv[8 * q2 + 7]);
-                const uint32_t off = swz(row, 4 * hf + 2 * cs + q2);
-                *reinterpret_cast<uint4*>(sDS + off) = pk;
-                *reinterpret_cast<uint4*>(sdS + off) = pk2;
-            }
+            const uint32_t off = swz(row, 4 * hf + cq);
+            *reinterpret_cast<uint4*>(sDS + off) = pack8(dsv);
+            *reinterpret_cast<uint4*>(sdS + off) = pack8(dSv);
             fence_async_smem();
             tc_fence_before();
         }
+        PROF(5)
         __syncthreads();  // #2
         if (*abort_flag) { ok = false; break; }
+        PROF(6)
 
         // =============== phase 3: group B MMAs (control) | epilogues (math) ==========================
         if (is_ctrl) {
@@ -430,69 +473,72 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
                     mma_ss(tC, desc_at(dM1, adNb + ks * 2048), desc_at(dM1, aQ + ks * 2048), id_mm128, 1);
-                mma_commit(&bars[2]);
+                mma_commit(&bars[5]);
             }
             __syncwarp();
         } else {
-            if (!mbar_wait(&bars[2], it & 1)) *abort_flag = 3;
-            tc_fence_after();
-            const int col = 64 * hf + 32 * cs;
-            const bool live = row < Lc;
-            const size_t orow = ((size_t)b * p.T + t0 + row) * p.H + h;
-            float a1[32], a2[32];
-            // dV = dVi + a dVe
-            tmem_ld32(tVi + lane_base + 32 * cs, a1);
-            tmem_ld32(tVe + lane_base + 32 * cs, a2);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) a1[i] += at * a2[i];
-            if (live) store32<GT>(reinterpret_cast<GT*>(p.dv) + orow * D + col, a1);
-            // dQ = acc + b dqn n
-            tmem_ld32(tQ + lane_base + 32 * cs, a1);
-            tmem_ld_wait();
-            const float bq = bt * sdqn[row];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) a1[i] += bq * nk[col + i];
-            float u = dot_row32(sQ + hf * kBoxBytes, row, 4 * cs, a1);
-            if (live) store32<GT>(reinterpret_cast<GT*>(p.dq) + orow * D + col, a1);
-            // dK = dKi + a (dKe + dn+)
-            tmem_ld32(tKi + lane_base + 32 * cs, a1);
-            tmem_ld32(tKe + lane_base + 32 * cs, a2);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) a1[i] += at * (a2[i] + dn_in[col + i]);
-            float w = dot_row32(sK + hf * kBoxBytes, row, 4 * cs, a1);
-            if (live) store32<GT>(reinterpret_cast<GT*>(p.dk) + orow * D + col, a1);
-            u += __shfl_xor_sync(0xffffffffu, u, 16);
-            w += __shfl_xor_sync(0xffffffffu, w, 16);
-            if (hf == 0) {
-                part[(2 + cs) * L + row] = u;
-                part[(4 + cs) * L + row] = w;
-            }
-            // dn = g dn+ + sum_t b_t dqn_t q_t   (into the other buffer)
-            if (tid < D) {
-                const int cbx = tid >> 6, cc = tid & 63;
+            // dn partial sums while the MMAs run: dn_c += sum over this quarter of t of b_t dqn_t q_tc
+            {
+                const int c = tid & 127, tq = tid >> 7;
+                const int cbx = c >> 6, cc = c & 63;
                 float acc = 0.f;
 #pragma unroll 8
-                for (int t = 0; t < L; ++t) {
+                for (int t = 16 * tq; t < 16 * tq + 16; ++t) {
                     bf16 qv = *reinterpret_cast<const bf16*>(sQ + cbx * kBoxBytes + swz(t, cc >> 3) + (cc & 7) * 2);
                     acc += Gc->b[t] * sdqn[t] * __bfloat162float(qv);
                 }
-                dn_out[tid] = Gc->g * dn_in[tid] + acc;
+                sdnp[tq * D + c] = acc;
+            }
+            PROF(7)
+            if (!mbar_wait(&bars[5], it & 1)) *abort_flag = 3;
+            tc_fence_after();
+            PROF(8)
+            const bool live = row < Lc;
+            const size_t orow = ((size_t)b * p.T + t0 + row) * p.H + h;
+            float a1[16], a2[16];
+            // dV = dVi + a dVe
+            tmem_ld16(tVi + lane_base + 16 * cq, a1);
+            tmem_ld16(tVe + lane_base + 16 * cq, a2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) a1[i] += at * a2[i];
+            if (live) store16<GT>(reinterpret_cast<GT*>(p.dv) + orow * D + col, a1);
+            // dQ = acc + b dqn n
+            tmem_ld16(tQ + lane_base + 16 * cq, a1);
+            tmem_ld_wait();
+            const float bq = bt * sdqn[row];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) a1[i] += bq * nk[col + i];
+            float u = dot_row16(sQ + hf * kBoxBytes, row, 2 * cq, a1);
+            if (live) store16<GT>(reinterpret_cast<GT*>(p.dq) + orow * D + col, a1);
+            // dK = dKi + a (dKe + dn+)
+            tmem_ld16(tKi + lane_base + 16 * cq, a1);
+            tmem_ld16(tKe + lane_base + 16 * cq, a2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) a1[i] += at * (a2[i] + dn_in[col + i]);
+            float w = dot_row16(sK + hf * kBoxBytes, row, 2 * cq, a1);
+            if (live) store16<GT>(reinterpret_cast<GT*>(p.dk) + orow * D + col, a1);
+            u += __shfl_xor_sync(0xffffffffu, u, 16);
+            w += __shfl_xor_sync(0xffffffffu, w, 16);
+            if (hf == 0) {
+                part[(4 + cq) * L + row] = u;
+                part[(8 + cq) * L + row] = w;
             }
         }
+        PROF(9)
         __syncthreads();  // #3
         if (*abort_flag) { ok = false; break; }
+        PROF(10)
 
-        // =============== phase 4: gate gradients + next tiles (control) | dC pass (math) ==============
+        // =============== phase 4: gate gradients (control) | dC pass, dn (math) =======================
         if (is_ctrl) {
-            if (lane == 0 && ch > 0) issue_tiles(ch - 1);
             float dF[2], wv[2];
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 int t = lane + 32 * e;
-                float u = part[2 * L + t] + part[3 * L + t];
-                wv[e] = part[4 * L + t] + part[5 * L + t];
+                float u = part[4 * L + t] + part[5 * L + t] + part[6 * L + t] + part[7 * L + t];
+                wv[e] = part[8 * L + t] + part[9 * L + t] + part[10 * L + t] + part[11 * L + t];
                 dF[e] = (t < Lc) ? (u - wv[e]) : 0.f;
             }
             // suffix sums over the 64 positions
@@ -519,31 +565,38 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             __syncwarp();
             if (lane == 0) *srun = run + tot;
         } else {
-            const int vrow = 32 * qd + lane;
+            if (tid < D) dn_out[tid] = Gc->g * dn_in[tid] + (sdnp[tid] + sdnp[D + tid]) + (sdnp[2 * D + tid] + sdnp[3 * D + tid]);
+            const int vrow = 32 * qd + lane, c0 = 32 * cq;
             const float gn = (ch > 0) ? G[(ch - 1) & 1].g : 1.f;
-            float* oc = (ch == 0 && p.odC) ? p.odC + (size_t)bh * D * D + (size_t)vrow * D : nullptr;
-            for (int c0 = 64 * cs; c0 < 64 * cs + 64; c0 += 32) {
-                float v[32];
-                tmem_ld32(tC + lane_base + c0, v);
-                tmem_ld_wait();
-                put_row32(sdCb + cs * kStateBox, vrow, (c0 & 63) >> 3, v);
-                if (oc) {
+            float v[32];
+            tmem_ld32(tC + lane_base + c0, v);
+            tmem_ld_wait();
+            put_row<4>(sdCb + (cq >> 1) * kStateBox, vrow, 4 * (cq & 1), v);
+            if (ch == 0 && p.odC) {
+                float* oc = p.odC + (size_t)bh * D * D + (size_t)vrow * D + c0;
 #pragma unroll
-                    for (int q4 = 0; q4 < 8; ++q4)
-                        *reinterpret_cast<float4*>(oc + c0 + 4 * q4) = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
-                }
-                if (ch > 0) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] *= gn;
-                    tmem_st32(tC + lane_base + c0, v);
-                }
+                for (int q4 = 0; q4 < 8; ++q4)
+                    *reinterpret_cast<float4*>(oc + 4 * q4) = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
             }
-            tmem_st_wait();
+            if (ch > 0) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] *= gn;
+                tmem_st32(tC + lane_base + c0, v);
+                tmem_st_wait();
+            }
             fence_async_smem();
             tc_fence_before();
         }
+        PROF(11)
         __syncthreads();  // #4
+        PROF(12)
     }
+#undef PROF
+#ifdef XL_TC_PROFILE
+    // slots 0..15: math thread 0, 16..31: control lane 0 (CTA 0 only)
+    if (p.prof && bh == 0 && (tid == 0 || tid == kMathThreads))
+        for (int i = 0; i < 13; ++i) p.prof[(tid == 0 ? 0 : 16) + i] = pacc[i];
+#endif
 
     if (ok) {
         if (p.odn && tid < D) p.odn[(size_t)bh * D + tid] = sdn[(it & 1) * D + tid];
@@ -564,6 +617,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 }  // namespace bw
 
+long long* tc_debug_prof();
 bool tc_make_map3(CUtensorMap* m, const void* base, int B, int T, int W);
 bool tc_make_map2(CUtensorMap* m, const void* base, uint64_t rows, int W, int box_rows);
 
@@ -587,6 +641,7 @@ int mlstm_bw_tc_launch(cudaStream_t st, const MlstmBwArgs& a, const void* saved,
     p.ig = a.ig; p.fg = a.fg; p.cm = a.cm; p.ytil = (const bf16*)a.ytil; p.msv = a.msv; p.psiv = a.psiv; p.qnv = a.qnv;
     p.dy = a.dytil; p.cdC = a.cdC; p.cdn = a.cdn; p.dq = a.dq; p.dk = a.dk; p.dv = a.dv; p.dig = a.dig; p.dfg = a.dfg;
     p.odC = a.odC; p.odn = a.odn; p.B = a.B; p.H = a.H; p.T = a.T; p.NC = a.NC; p.gbf16 = gdtype == XLSTM_BF16;
+    p.prof = tc_debug_prof();
     size_t smem = Smem::total + 1024;
     if (gdtype == XLSTM_BF16) {
         XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
