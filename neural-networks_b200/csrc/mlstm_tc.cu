@@ -491,6 +491,11 @@ bool tc_make_map3(CUtensorMap* m, const void* base, int B, int T, int W) {
 static long long* g_prof = nullptr;
 extern "C" void xlstm_debug_set_prof(void* p) { g_prof = (long long*)p; }
 long long* tc_debug_prof() { return g_prof; }
+int* tc_status_ptr() {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_tc_status) != cudaSuccess) return nullptr;
+    return (int*)p;
+}
 
 // [rows][W] bf16 row-major, box = {64 cols, box_rows}, 128-byte swizzle.
 bool tc_make_map2(CUtensorMap* m, const void* base, uint64_t rows, int W, int box_rows) {

@@ -23,7 +23,7 @@ namespace xl {
 
 using namespace tc;
 
-extern __device__ int g_tc_status;
+int* tc_status_ptr();  // device address of the library's status word
 
 namespace bw {
 
@@ -63,6 +63,7 @@ struct Params {
     float *odC, *odn;
     int B, H, T, NC;
     int gbf16;
+    int* status;      // device status word (first bounded wait that ran out)
     long long* prof;  // optional per-phase cycle counts of CTA 0 (development aid; null in production)
 };
 
@@ -77,8 +78,8 @@ struct Smem {
     static constexpr uint32_t ds_ = dcb + 2 * kStateBox;   // DS  [64 x 64]
     static constexpr uint32_t dS = ds_ + kBoxBytes;        // dS  [64 x 64]
     static constexpr uint32_t gates = dS + kBoxBytes;      // 2 x Gates
-    static constexpr uint32_t nk = gates + 2 * sizeof(Gates);  // n entering the chunk [128]
-    static constexpr uint32_t dnv = nk + D * 4;            // dn, double buffered [2][128]
+    static constexpr uint32_t vec = gates + 2 * sizeof(Gates);  // 2 x [psi 64 | qn 64 | n entering the chunk 128]
+    static constexpr uint32_t dnv = vec + 2 * (2 * L + D) * 4;            // dn, double buffered [2][128]
     static constexpr uint32_t dnp = dnv + 2 * D * 4;       // dn partial sums [4][128]
     static constexpr uint32_t part = dnp + 4 * D * 4;      // partial sums [12][64]: dot(4), u(4), w(4)
     static constexpr uint32_t dqn = part + 12 * L * 4;     // [64]
@@ -149,25 +150,31 @@ __device__ __forceinline__ float dot_row16(const unsigned char* tile, uint32_t r
     return acc;
 }
 
-// Control warp: gate vectors of chunk `ch` (two positions per lane).
-__device__ __forceinline__ void gates_warp(const Params& p, int b, int h, int bh, int ch, Gates* G) {
+// Control warp: gate vectors of a chunk, two positions per lane. The global reads (gates_load) are
+// issued one chunk before the arithmetic (gates_compute) so their latency stays off the critical path.
+struct GateRaw {
+    float fr[2], iv[2], mt[2], m_prev;
+};
+__device__ __forceinline__ void gates_load(const Params& p, int b, int h, int bh, int ch, GateRaw& r) {
     const int lane = threadIdx.x & 31;
     const int t0 = ch * L, Lc = min(L, p.T - t0);
-    float lf[2], iv[2], fr[2], mt[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
         int t = lane + 32 * e;
-        lf[e] = 0.f; iv[e] = -INFINITY; fr[e] = 0.f;
+        r.fr[e] = INFINITY;   // log_sigmoid(+inf) = 0: positions past a ragged end leave fc unchanged
+        r.iv[e] = -INFINITY;
         if (t < Lc) {
             size_t gi = ((size_t)b * p.T + t0 + t) * p.H + h;
-            fr[e] = p.fg[gi];
-            lf[e] = log_sigmoid(fr[e]);
-            iv[e] = p.ig[gi];
+            r.fr[e] = p.fg[gi];
+            r.iv[e] = p.ig[gi];
         }
-        mt[e] = p.msv[(size_t)bh * p.T + t0 + min(t, Lc - 1)];
+        r.mt[e] = p.msv[(size_t)bh * p.T + t0 + min(t, Lc - 1)];
     }
-    const float m_prev = (ch == 0) ? (p.cm ? p.cm[bh] : 0.f) : p.msv[(size_t)bh * p.T + t0 - 1];
-    float fc0 = lf[0], fc1 = lf[1];
+    r.m_prev = (ch == 0) ? (p.cm ? p.cm[bh] : 0.f) : p.msv[(size_t)bh * p.T + t0 - 1];
+}
+__device__ __forceinline__ void gates_compute(const GateRaw& r, Gates* G) {
+    const int lane = threadIdx.x & 31;
+    float fc0 = log_sigmoid(r.fr[0]), fc1 = log_sigmoid(r.fr[1]);
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         float y0 = __shfl_up_sync(0xffffffffu, fc0, o), y1 = __shfl_up_sync(0xffffffffu, fc1, o);
@@ -175,19 +182,82 @@ __device__ __forceinline__ void gates_warp(const Params& p, int b, int h, int bh
     }
     fc1 += __shfl_sync(0xffffffffu, fc0, 31);
     const float fcL = __shfl_sync(0xffffffffu, fc1, 31);
-    const float mL = __shfl_sync(0xffffffffu, mt[1], 31);
+    const float mL = __shfl_sync(0xffffffffu, r.mt[1], 31);
     float fc[2] = {fc0, fc1};
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
         int t = lane + 32 * e;
-        G->rowt[t] = fc[e] - mt[e];
-        G->colt[t] = iv[e] - fc[e];
-        G->b[t] = expf(fc[e] + m_prev - mt[e]);
-        G->a[t] = expf(fcL - fc[e] + iv[e] - mL);
-        G->fg[t] = fr[e];
-        G->emm[t] = expf(-mt[e]);
+        G->rowt[t] = fc[e] - r.mt[e];
+        G->colt[t] = r.iv[e] - fc[e];
+        G->b[t] = expf(fc[e] + r.m_prev - r.mt[e]);
+        G->a[t] = expf(fcL - fc[e] + r.iv[e] - mL);
+        G->fg[t] = r.fr[e];
+        G->emm[t] = expf(-r.mt[e]);
     }
-    if (lane == 0) G->g = expf(fcL + m_prev - mL);
+    if (lane == 0) G->g = expf(fcL + r.m_prev - mL);
+}
+
+// Control warp: the per-chunk vectors psi, qn (64 each) and the entering normaliser n (128), read one
+// chunk ahead into registers and parked in a double-buffered shared array.
+struct VecRaw {
+    float v[8];
+};
+__device__ __forceinline__ void vec_load(const Params& p, int bh, int ch, VecRaw& r) {
+    const int lane = threadIdx.x & 31;
+    const int t0 = ch * L, Lc = min(L, p.T - t0);
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const size_t o = (size_t)bh * p.T + t0 + min(lane + 32 * e, Lc - 1);
+        r.v[e] = p.psiv[o];
+        r.v[2 + e] = p.qnv[o];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) r.v[4 + e] = p.savedn[((size_t)bh * (p.NC + 1) + ch) * D + lane + 32 * e];
+}
+__device__ __forceinline__ void vec_store(const VecRaw& r, float* dst /* [psi 64 | qn 64 | n 128] */) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        dst[lane + 32 * e] = r.v[e];
+        dst[L + lane + 32 * e] = r.v[2 + e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dst[2 * L + lane + 32 * e] = r.v[4 + e];
+}
+
+// Sum 16 per-lane values across the 32 lanes of a warp with a reduce-scatter butterfly (16
+// shuffles instead of 80). On return lane l holds, in the result, the warp-wide sum of element
+// index ((l >> 1) & 15) remapped by `butterfly_index`.
+__device__ __forceinline__ float butterfly16(float* v, int lane) {
+    // stage xor 16: keep 8
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const bool up = lane & 16;
+        float keep = up ? v[k + 8] : v[k], send = up ? v[k] : v[k + 8];
+        v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const bool up = lane & 8;
+        float keep = up ? v[k + 4] : v[k], send = up ? v[k] : v[k + 4];
+        v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const bool up = lane & 4;
+        float keep = up ? v[k + 2] : v[k], send = up ? v[k] : v[k + 2];
+        v[k] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+    {
+        const bool up = lane & 2;
+        float keep = up ? v[1] : v[0], send = up ? v[0] : v[1];
+        v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+    }
+    return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
+}
+// Which of the 16 elements lane `lane` ends up holding after butterfly16.
+__device__ __forceinline__ int butterfly_index(int lane) {
+    return ((lane & 16) ? 8 : 0) + ((lane & 8) ? 4 : 0) + ((lane & 4) ? 2 : 0) + ((lane & 2) ? 1 : 0);
 }
 
 template <typename GT>
@@ -198,17 +268,19 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     const bool is_ctrl = warp == kMathWarps;
     const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
     const int qd = warp & 3, cq = (warp >> 2) & 3;
-    const int row = 16 * qd + (lane & 15), hf = lane >> 4;
     const uint32_t lane_base = (uint32_t)(32 * qd) << 16;
-    const int col = 64 * hf + 16 * cq;  // this thread's 16 columns of a [64 x 128] position-indexed tile
+    const int x = 32 * qd + lane;          // this thread's lane of a 128-lane (feature-indexed) accumulator
+    const int srow = 16 * qd + (lane & 15);  // its row of the M = 64 tiles S and dds (lanes 0-15 of the quadrant)
+    // dN pass ownership: warp w owns positions 4w .. 4w+3, eight lanes per position
+    const int prow = 4 * warp + (lane >> 3), l8 = lane & 7;
 
     Gates* G = (Gates*)(sm + Smem::gates);
-    float* nk = (float*)(sm + Smem::nk);
+    float* svec = (float*)(sm + Smem::vec);
     float* sdn = (float*)(sm + Smem::dnv);
     float* sdnp = (float*)(sm + Smem::dnp);
     float* part = (float*)(sm + Smem::part);
     float* sdqn = (float*)(sm + Smem::dqn);
-    uint64_t* bars = (uint64_t*)(sm + Smem::misc);  // [0],[1] Q/K stages, [2] V, [3] Ck, [4] group A, [5] group B
+    uint64_t* bars = (uint64_t*)(sm + Smem::misc);  // [0],[1] Q/K stages, [2] V, [3] Ck, [4] group A, [5] group B, [6] S and dds only
     uint32_t* tmem_slot = (uint32_t*)(sm + Smem::misc + 64);
     int* abort_flag = (int*)(sm + Smem::misc + 72);
     float* srun = (float*)(sm + Smem::misc + 80);
@@ -223,7 +295,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     unsigned char* sdS = sm + Smem::dS;
 
     if (tid == 0) {
-        for (int i = 0; i < 6; ++i) mbar_init(&bars[i], 1);
+        for (int i = 0; i < 7; ++i) mbar_init(&bars[i], 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -232,8 +304,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tS = tmem + 0, tDds = tmem + 32, tVi = tmem + 64, tVe = tmem + 128, tQ = tmem + 192, tKi = tmem + 256,
-                   tKe = tmem + 320, tC = tmem + 384;
+    // S and dds are dead once DS/dS are in shared memory; dVi and dKi reuse their columns.
+    const uint32_t tS = tmem + 0, tDds = tmem + 64, tVi = tmem + 0, tKi = tmem + 64, tVe = tmem + 128, tKe = tmem + 192,
+                   tQ = tmem + 256, tC = tmem + 384;
 
     auto issue_qk = [&](int ch, int stage) {
         mbar_expect_tx(&bars[stage], 2 * kTileBytes);
@@ -251,23 +324,39 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
         }
     };
 
-    // operands of the dN pass, prefetched one chunk ahead into registers
-    float dyv[16], yv[16];
-    float psi_r = 1.f;
+    // Operands of the dN pass, prefetched one chunk ahead into registers. Piece i of a thread covers
+    // columns 4*(l8 + 8i) .. +3 of its position, so eight lanes read one contiguous run per instruction.
+    uint32_t dyraw[sizeof(GT) == 4 ? 16 : 8], yraw[8];
     auto prefetch_dy = [&](int ch) {
         const int t0 = ch * L, Lc = min(L, p.T - t0);
-        if (row < Lc) {
-            const size_t o = (((size_t)b * p.T + t0 + row) * p.H + h) * D + col;
-            load16<GT>(reinterpret_cast<const GT*>(p.dy) + o, dyv);
-            load16<bf16>(p.ytil + o, yv);
-            psi_r = p.psiv[(size_t)bh * p.T + t0 + row];
+        if (prow < Lc) {
+            const size_t o = (((size_t)b * p.T + t0 + prow) * p.H + h) * D;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int c = 4 * (l8 + 8 * i);
+                if (sizeof(GT) == 4) {
+                    uint4 t = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p.dy) + o + c));
+                    dyraw[4 * i] = t.x; dyraw[4 * i + 1] = t.y; dyraw[4 * i + 2] = t.z; dyraw[4 * i + 3] = t.w;
+                } else {
+                    uint2 t = __ldcs(reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(p.dy) + o + c));
+                    dyraw[2 * i] = t.x; dyraw[2 * i + 1] = t.y;
+                }
+                uint2 ty = __ldcs(reinterpret_cast<const uint2*>(p.ytil + o + c));
+                yraw[2 * i] = ty.x; yraw[2 * i + 1] = ty.y;
+            }
         }
     };
 
+    GateRaw graw;
+    VecRaw vraw;
     // ---- prologue -------------------------------------------------------------------------------
     if (is_ctrl) {
         if (lane == 0) { issue_qk(p.NC - 1, 0); issue_v_ck(p.NC - 1); }
-        gates_warp(p, b, h, bh, p.NC - 1, &G[(p.NC - 1) & 1]);
+        gates_load(p, b, h, bh, p.NC - 1, graw);
+        vec_load(p, bh, p.NC - 1, vraw);
+        gates_compute(graw, &G[(p.NC - 1) & 1]);
+        vec_store(vraw, svec + ((p.NC - 1) & 1) * (2 * L + D));
+        if (p.NC > 1) gates_load(p, b, h, bh, p.NC - 2, graw);
     } else {
         prefetch_dy(p.NC - 1);
         // carry term of the forget-gate gradient: <dC_in, C_end> + dn_in . n_end
@@ -291,11 +380,11 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     if (!is_ctrl) {
         // dC+ into TMEM (pre-scaled by g of the last chunk) and as bf16 into dCb
         const float g0 = G[(p.NC - 1) & 1].g;
-        const int vrow = 32 * qd + lane, c0 = 32 * cq;
+        const int c0 = 32 * cq;
         float v[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = p.cdC ? p.cdC[(size_t)bh * D * D + (size_t)vrow * D + c0 + i] : 0.f;
-        put_row<4>(sdCb + (cq >> 1) * kStateBox, vrow, 4 * (cq & 1), v);
+        for (int i = 0; i < 32; ++i) v[i] = p.cdC ? p.cdC[(size_t)bh * D * D + (size_t)x * D + c0 + i] : 0.f;
+        put_row<4>(sdCb + (cq >> 1) * kStateBox, x, 4 * (cq & 1), v);
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] *= g0;
         tmem_st32(tC + lane_base + c0, v);
@@ -309,10 +398,10 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     const uint64_t dK_ = smem_desc(0, 16, 1024);          // K-major operand
     const uint64_t dM1 = smem_desc(0, kBoxBytes, 1024);   // MN-major, 64-element groups kBoxBytes apart ([64-row] tiles)
     const uint64_t dM2 = smem_desc(0, kStateBox, 1024);   // MN-major over a [128-row] state tile
-    constexpr uint32_t id_kk32 = instr_desc(64, 32, 0, 0);
-    constexpr uint32_t id_kk64 = instr_desc(64, 64, 0, 0);
-    constexpr uint32_t id_km64 = instr_desc(64, 64, 0, 1);
-    constexpr uint32_t id_mm64 = instr_desc(64, 64, 1, 1);
+    constexpr uint32_t id64_kk = instr_desc(64, 64, 0, 0);     // S, dds
+    constexpr uint32_t id_kk = instr_desc(128, 64, 0, 0);      // feature-major outputs, 64 positions wide
+    constexpr uint32_t id_mk = instr_desc(128, 64, 1, 0);
+    constexpr uint32_t id_mm = instr_desc(128, 64, 1, 1);
     constexpr uint32_t id_mm128 = instr_desc(128, 128, 1, 1);
 
     bool ok = true;
@@ -334,29 +423,60 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
         float* dn_out = sdn + (stg ^ 1) * D;
         unsigned char* sQ = sm + Smem::q + stg * kTileBytes;
         unsigned char* sK = sm + Smem::k + stg * kTileBytes;
+        const float* spsi = svec + (ch & 1) * (2 * L + D);
+        const float* sqn = spsi + L;
+        const float* nk = spsi + 2 * L;
 
         PROF(0)
-        // =============== phase 1: dN, dNb tiles and the dqn partial dots (math) =====================
-        float bt = 0.f, at = 0.f;
+        // =============== phase 1: dN, dNb tiles and the dy.ytil row dots (math) =======================
         if (!is_ctrl) {
-            bt = Gc->b[row];
-            at = Gc->a[row];
+            const float bt = Gc->b[prow];
+            const float psi_r = spsi[prow];
             float dot = 0.f;
-            if (row < Lc) {
+            float dyv[16];
+            if (prow < Lc) {
                 const float ipsi = 1.f / psi_r;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) { dot += dyv[i] * yv[i]; dyv[i] *= ipsi; }
+                for (int i = 0; i < 4; ++i) {
+                    float d[4];
+                    if (sizeof(GT) == 4) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) d[e] = __uint_as_float(dyraw[4 * i + e]);
+                    } else {
+                        float2 a0 = unpack_bf16(dyraw[2 * i]), a1 = unpack_bf16(dyraw[2 * i + 1]);
+                        d[0] = a0.x; d[1] = a0.y; d[2] = a1.x; d[3] = a1.y;
+                    }
+                    float2 y0 = unpack_bf16(yraw[2 * i]), y1 = unpack_bf16(yraw[2 * i + 1]);
+                    dot += d[0] * y0.x + d[1] * y0.y + d[2] * y1.x + d[3] * y1.y;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) dyv[4 * i + e] = d[e] * ipsi;
+                }
             } else {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) dyv[i] = 0.f;
             }
-            put_row<2>(sdN + hf * kBoxBytes, row, 2 * cq, dyv);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) dyv[i] *= bt;
-            put_row<2>(sdNb + hf * kBoxBytes, row, 2 * cq, dyv);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 16);
-            if (hf == 0) part[cq * L + row] = dot;
-            if (tid < D) nk[tid] = p.savedn[((size_t)bh * (p.NC + 1) + ch) * D + tid];
+            for (int i = 0; i < 4; ++i) {
+                // columns 4*(l8 + 8i) .. +3: box i/2, 16-byte chunk (l8 + 8(i&1))/2, half (l8 & 1)
+                const uint32_t off = (uint32_t)(i >> 1) * kBoxBytes + swz(prow, (l8 + 8 * (i & 1)) >> 1) + (l8 & 1) * 8;
+                uint2 a, bb;
+                a.x = pack_bf16(dyv[4 * i], dyv[4 * i + 1]); a.y = pack_bf16(dyv[4 * i + 2], dyv[4 * i + 3]);
+                bb.x = pack_bf16(dyv[4 * i] * bt, dyv[4 * i + 1] * bt); bb.y = pack_bf16(dyv[4 * i + 2] * bt, dyv[4 * i + 3] * bt);
+                *reinterpret_cast<uint2*>(sdN + off) = a;
+                *reinterpret_cast<uint2*>(sdNb + off) = bb;
+            }
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+            if (l8 == 0) {
+                // dqn_t = sign(qn)(-dot/psi) where the q.n term, not the floor, set psi
+                float r = 0.f;
+                if (prow < Lc) {
+                    const float qn = sqn[prow];
+                    if (fabsf(qn) > Gc->emm[prow]) r = (qn > 0.f ? -1.f : 1.f) * dot / psi_r;
+                }
+                sdqn[prow] = r;
+            }
             fence_async_smem();
         } else {
             if (lane == 0 && ch > 0) issue_qk(ch - 1, stg ^ 1);
@@ -368,80 +488,66 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
         if (*abort_flag) { ok = false; break; }
         PROF(2)
 
-        // =============== phase 2: group A MMAs (control) | dqn, S/dds epilogue (math) ================
+        // =============== phase 2: group A MMAs (control) | S/dds epilogue (math) ======================
         if (is_ctrl) {
             if (lane == 0) {
                 tc_fence_after();
                 const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aCk = smem_u32(sCk),
                                adN = smem_u32(sdN), adNb = smem_u32(sdNb), adC = smem_u32(sdCb);
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const uint32_t lo = (uint32_t)(16 * hh) << 16;
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
-                        const uint32_t ko = (ks >> 2) * kBoxBytes + (ks & 3) * 32;    // K-major step in a [64-row] tile
-                        // S = Q K^T (rows j of K: 32 per half)
-                        mma_ss(tS + lo, desc_at(dK_, aQ + ko), desc_at(dK_, aK + ko + hh * 32 * 128), id_kk32, ks > 0);
-                        // dds = dN V^T
-                        mma_ss(tDds + lo, desc_at(dK_, adN + ko), desc_at(dK_, aV + ko + hh * 32 * 128), id_kk32, ks > 0);
-                    }
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t ko = (ks >> 2) * kBoxBytes + (ks & 3) * 32;  // K-major step in a [64-row] tile
+                    mma_ss(tS, desc_at(dK_, aQ + ko), desc_at(dK_, aK + ko), id64_kk, ks > 0);      // S = Q K^T
+                    mma_ss(tDds, desc_at(dK_, adN + ko), desc_at(dK_, aV + ko), id64_kk, ks > 0);   // dds = dN V^T
                 }
+                mma_commit(&bars[6]);
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const uint32_t lo = (uint32_t)(16 * hh) << 16;
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
-                        const uint32_t ko = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
-                        const uint32_t kc = (ks >> 2) * kStateBox + (ks & 3) * 32;    // K-major step in a [128-row] tile
-                        // dVe = K dC+^T : B = dCb rows v (64 per half), K-major over c
-                        mma_ss(tVe + lo, desc_at(dK_, aK + ko), desc_at(dK_, adC + kc + hh * 64 * 128), id_kk64, ks > 0);
-                        // dKe = V dC+ : A = V K-major over v; B = dCb MN-major (N = c: box hh), K = v rows in steps of 16
-                        mma_ss(tKe + lo, desc_at(dK_, aV + ko), desc_at(dM2, adC + hh * kStateBox + ks * 2048), id_km64, ks > 0);
-                        // dQ = dNb C_k : A = dNb K-major over v; B = Ck MN-major (N = c: box hh), K = v rows
-                        mma_ss(tQ + lo, desc_at(dK_, adNb + ko), desc_at(dM2, aCk + hh * kStateBox + ks * 2048), id_km64, ks > 0);
-                    }
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t ko = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
+                    const uint32_t kc = (ks >> 2) * kStateBox + (ks & 3) * 32;  // K-major step in a [128-row] tile
+                    // dVe^T[v,j] = sum_c dC+[v,c] K[j,c]
+                    mma_ss(tVe, desc_at(dK_, adC + kc), desc_at(dK_, aK + ko), id_kk, ks > 0);
+                    // dKe^T[c,j] = sum_v dC+[v,c] V[j,v] : A = dCb^T (MN-major over c, K = v rows), B = V K-major
+                    mma_ss(tKe, desc_at(dM2, adC + ks * 2048), desc_at(dK_, aV + ko), id_mk, ks > 0);
+                    // dQ^T[c,t] = sum_v C_k[v,c] dNb[t,v] : A = Ck^T (MN-major), B = dNb K-major
+                    mma_ss(tQ, desc_at(dM2, aCk + ks * 2048), desc_at(dK_, adNb + ko), id_mk, ks > 0);
                 }
                 mma_commit(&bars[4]);
             }
             __syncwarp();
             PROF(3)
-            if (ch > 0) gates_warp(p, b, h, bh, ch - 1, &G[(ch - 1) & 1]);
+            if (ch > 0) {
+                gates_compute(graw, &G[(ch - 1) & 1]);
+                vec_load(p, bh, ch - 1, vraw);
+                if (ch > 1) gates_load(p, b, h, bh, ch - 2, graw);
+            }
             PROF(4)
-            // V and C_k are consumed by group A only: refill them for the next chunk as soon as it is done
             if (!mbar_wait(&bars[4], it & 1)) *abort_flag = 2;
+            // V and C_k are read by group A only: refill them for the next chunk as soon as it is done
             if (lane == 0 && ch > 0) issue_v_ck(ch - 1);
         } else {
-            if (tid < L) {
-                const size_t o = (size_t)bh * p.T + t0 + min(tid, Lc - 1);
-                const float qn = p.qnv[o];
-                const float dot = part[tid] + part[L + tid] + part[2 * L + tid] + part[3 * L + tid];
-                float r = 0.f;
-                if (tid < Lc && fabsf(qn) > Gc->emm[tid]) r = (qn > 0.f ? -1.f : 1.f) * dot / p.psiv[o];
-                sdqn[tid] = r;
-            }
-            if (ch > 0) prefetch_dy(ch - 1);  // lands during this chunk's remaining phases
-            // order sdqn before its readers without stalling the control warp: math-only named barrier
-            asm volatile("bar.sync 1, %0;" ::"n"(kMathThreads) : "memory");
+            if (ch > 0) prefetch_dy(ch - 1);  // lands during the rest of this chunk
             PROF(3)
-            if (!mbar_wait(&bars[4], it & 1)) *abort_flag = 2;
+            if (!mbar_wait(&bars[6], it & 1)) *abort_flag = 2;
             tc_fence_after();
             PROF(4)
-            // ---- S / dds epilogue: this thread's 8 columns j of row t
-            float s[8], dd[8], dsv[8], dSv[8];
-            tmem_ld8(tS + lane_base + 8 * cq, s);
-            tmem_ld8(tDds + lane_base + 8 * cq, dd);
+            // ---- S / dds epilogue: rows live on lanes 0-15 of each quadrant; 16 columns j per thread
+            float s[16], dd[16];
+            tmem_ld16(tS + lane_base + 16 * cq, s);
+            tmem_ld16(tDds + lane_base + 16 * cq, dd);
             tmem_ld_wait();
-            const float rt = Gc->rowt[row], dq_t = sdqn[row];
+            if (lane < 16) {
+                const float rt = Gc->rowt[srow], dq_t = sdqn[srow];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int j = 32 * hf + 8 * cq + i;
-                const float dbar = (j <= row) ? __expf(rt + Gc->colt[j]) : 0.f;
-                dsv[i] = dbar * s[i];
-                dSv[i] = dbar * (dd[i] + dq_t);
+                for (int i = 0; i < 16; ++i) {
+                    const int j = 16 * cq + i;
+                    const float dbar = (j <= srow) ? __expf(rt + Gc->colt[j]) : 0.f;
+                    s[i] *= dbar;
+                    dd[i] = dbar * (dd[i] + dq_t);
+                }
+                put_row<2>(sDS, srow, 2 * cq, s);
+                put_row<2>(sdS, srow, 2 * cq, dd);
             }
-            const uint32_t off = swz(row, 4 * hf + cq);
-            *reinterpret_cast<uint4*>(sDS + off) = pack8(dsv);
-            *reinterpret_cast<uint4*>(sdS + off) = pack8(dSv);
             fence_async_smem();
             tc_fence_before();
         }
@@ -450,24 +556,20 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
         if (*abort_flag) { ok = false; break; }
         PROF(6)
 
-        // =============== phase 3: group B MMAs (control) | epilogues (math) ==========================
+        // =============== phase 3: group B MMAs (control) | feature-major epilogues (math) ==============
         if (is_ctrl) {
             if (lane == 0) {
                 tc_fence_after();
                 const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), adN = smem_u32(sdN), adNb = smem_u32(sdNb),
                                aDS = smem_u32(sDS), adS = smem_u32(sdS);
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const uint32_t lo = (uint32_t)(16 * hh) << 16;
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        // dVi = DS^T dN : A = DS MN-major (M = j), B = dN MN-major (N = v: box hh), K = t rows
-                        mma_ss(tVi + lo, desc_at(dM1, aDS + ks * 2048), desc_at(dM1, adN + hh * kBoxBytes + ks * 2048), id_mm64, ks > 0);
-                        // dQ += dS K : A = dS K-major over j, B = K MN-major (N = c: box hh), K = j rows
-                        mma_ss(tQ + lo, desc_at(dK_, adS + ks * 32), desc_at(dM1, aK + hh * kBoxBytes + ks * 2048), id_km64, 1);
-                        // dKi = dS^T Q : A = dS MN-major (M = j), B = Q MN-major (N = c: box hh), K = t rows
-                        mma_ss(tKi + lo, desc_at(dM1, adS + ks * 2048), desc_at(dM1, aQ + hh * kBoxBytes + ks * 2048), id_mm64, ks > 0);
-                    }
+                for (int ks = 0; ks < 4; ++ks) {
+                    // dVi^T[v,j] = sum_t dN[t,v] DS[t,j] : both MN-major, K = t rows
+                    mma_ss(tVi, desc_at(dM1, adN + ks * 2048), desc_at(dM1, aDS + ks * 2048), id_mm, ks > 0);
+                    // dQ^T[c,t] += sum_j K[j,c] dS[t,j] : A = K^T MN-major (K = j rows), B = dS K-major over j
+                    mma_ss(tQ, desc_at(dM1, aK + ks * 2048), desc_at(dK_, adS + ks * 32), id_mk, 1);
+                    // dKi^T[c,j] = sum_t Q[t,c] dS[t,j] : both MN-major, K = t rows
+                    mma_ss(tKi, desc_at(dM1, aQ + ks * 2048), desc_at(dM1, adS + ks * 2048), id_mm, ks > 0);
                 }
                 // dC += dNb^T Q : M = v, N = c, K = t
 #pragma unroll
@@ -477,53 +579,73 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             }
             __syncwarp();
         } else {
-            // dn partial sums while the MMAs run: dn_c += sum over this quarter of t of b_t dqn_t q_tc
+            // this thread's feature x, positions 16*cq .. +15
+            const uint32_t xoff = (uint32_t)(x >> 6) * kBoxBytes + (x & 7) * 2;
+            const uint32_t xch8 = (x & 63) >> 3;
+            auto tile_at = [&](const unsigned char* tile, int pos) {
+                return __bfloat162float(*reinterpret_cast<const bf16*>(tile + xoff + swz(pos, xch8)));
+            };
+            const float n_x = nk[x], dn_x = dn_in[x];
             {
-                const int c = tid & 127, tq = tid >> 7;
-                const int cbx = c >> 6, cc = c & 63;
                 float acc = 0.f;
-#pragma unroll 8
-                for (int t = 16 * tq; t < 16 * tq + 16; ++t) {
-                    bf16 qv = *reinterpret_cast<const bf16*>(sQ + cbx * kBoxBytes + swz(t, cc >> 3) + (cc & 7) * 2);
-                    acc += Gc->b[t] * sdqn[t] * __bfloat162float(qv);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int pos = 16 * cq + i;
+                    acc += Gc->b[pos] * sdqn[pos] * tile_at(sQ, pos);
                 }
-                sdnp[tq * D + c] = acc;
+                sdnp[cq * D + x] = acc;  // dn partial over this quarter of the positions
             }
             PROF(7)
             if (!mbar_wait(&bars[5], it & 1)) *abort_flag = 3;
             tc_fence_after();
             PROF(8)
-            const bool live = row < Lc;
-            const size_t orow = ((size_t)b * p.T + t0 + row) * p.H + h;
+            const size_t obase = (((size_t)b * p.T + t0 + 16 * cq) * p.H + h) * D + x;
+            const size_t ostride = (size_t)p.H * D;
+            const int nlive = min(16, Lc - 16 * cq);  // positions of this quarter inside the sequence
             float a1[16], a2[16];
             // dV = dVi + a dVe
             tmem_ld16(tVi + lane_base + 16 * cq, a1);
             tmem_ld16(tVe + lane_base + 16 * cq, a2);
             tmem_ld_wait();
+            {
+                GT* o = reinterpret_cast<GT*>(p.dv) + obase;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) a1[i] += at * a2[i];
-            if (live) store16<GT>(reinterpret_cast<GT*>(p.dv) + orow * D + col, a1);
-            // dQ = acc + b dqn n
+                for (int i = 0; i < 16; ++i)
+                    if (i < nlive) stf(o, (size_t)i * ostride, a1[i] + Gc->a[16 * cq + i] * a2[i]);
+            }
+            // dQ = acc + b dqn n ;  u = dQ . q
             tmem_ld16(tQ + lane_base + 16 * cq, a1);
             tmem_ld_wait();
-            const float bq = bt * sdqn[row];
+            {
+                GT* o = reinterpret_cast<GT*>(p.dq) + obase;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) a1[i] += bq * nk[col + i];
-            float u = dot_row16(sQ + hf * kBoxBytes, row, 2 * cq, a1);
-            if (live) store16<GT>(reinterpret_cast<GT*>(p.dq) + orow * D + col, a1);
-            // dK = dKi + a (dKe + dn+)
+                for (int i = 0; i < 16; ++i) {
+                    const int pos = 16 * cq + i;
+                    const float v = a1[i] + Gc->b[pos] * sdqn[pos] * n_x;
+                    if (i < nlive) stf(o, (size_t)i * ostride, v);
+                    a1[i] = v * tile_at(sQ, pos);
+                }
+            }
+            const float usum = butterfly16(a1, lane);
+            // dK = dKi + a (dKe + dn+) ;  w = dK . k
             tmem_ld16(tKi + lane_base + 16 * cq, a1);
             tmem_ld16(tKe + lane_base + 16 * cq, a2);
             tmem_ld_wait();
+            {
+                GT* o = reinterpret_cast<GT*>(p.dk) + obase;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) a1[i] += at * (a2[i] + dn_in[col + i]);
-            float w = dot_row16(sK + hf * kBoxBytes, row, 2 * cq, a1);
-            if (live) store16<GT>(reinterpret_cast<GT*>(p.dk) + orow * D + col, a1);
-            u += __shfl_xor_sync(0xffffffffu, u, 16);
-            w += __shfl_xor_sync(0xffffffffu, w, 16);
-            if (hf == 0) {
-                part[(4 + cq) * L + row] = u;
-                part[(8 + cq) * L + row] = w;
+                for (int i = 0; i < 16; ++i) {
+                    const int pos = 16 * cq + i;
+                    const float v = a1[i] + Gc->a[pos] * (a2[i] + dn_x);
+                    if (i < nlive) stf(o, (size_t)i * ostride, v);
+                    a1[i] = v * tile_at(sK, pos);
+                }
+            }
+            const float wsum = butterfly16(a1, lane);
+            if ((lane & 1) == 0) {
+                const int pos = 16 * cq + butterfly_index(lane);
+                part[(4 + qd) * L + pos] = usum;
+                part[(8 + qd) * L + pos] = wsum;
             }
         }
         PROF(9)
@@ -564,16 +686,17 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             }
             __syncwarp();
             if (lane == 0) *srun = run + tot;
+            if (ch > 0) vec_store(vraw, svec + ((ch - 1) & 1) * (2 * L + D));
         } else {
             if (tid < D) dn_out[tid] = Gc->g * dn_in[tid] + (sdnp[tid] + sdnp[D + tid]) + (sdnp[2 * D + tid] + sdnp[3 * D + tid]);
-            const int vrow = 32 * qd + lane, c0 = 32 * cq;
+            const int c0 = 32 * cq;
             const float gn = (ch > 0) ? G[(ch - 1) & 1].g : 1.f;
             float v[32];
             tmem_ld32(tC + lane_base + c0, v);
             tmem_ld_wait();
-            put_row<4>(sdCb + (cq >> 1) * kStateBox, vrow, 4 * (cq & 1), v);
+            put_row<4>(sdCb + (cq >> 1) * kStateBox, x, 4 * (cq & 1), v);
             if (ch == 0 && p.odC) {
-                float* oc = p.odC + (size_t)bh * D * D + (size_t)vrow * D + c0;
+                float* oc = p.odC + (size_t)bh * D * D + (size_t)x * D + c0;
 #pragma unroll
                 for (int q4 = 0; q4 < 8; ++q4)
                     *reinterpret_cast<float4*>(oc + 4 * q4) = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
@@ -601,7 +724,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     if (ok) {
         if (p.odn && tid < D) p.odn[(size_t)bh * D + tid] = sdn[(it & 1) * D + tid];
     } else if (tid == 0) {
-        atomicCAS(&g_tc_status, 0, 200 + *abort_flag);
+        atomicCAS(p.status, 0, 200 + *abort_flag);
     }
     tc_fence_before();
     __syncthreads();
@@ -642,6 +765,8 @@ int mlstm_bw_tc_launch(cudaStream_t st, const MlstmBwArgs& a, const void* saved,
     p.dy = a.dytil; p.cdC = a.cdC; p.cdn = a.cdn; p.dq = a.dq; p.dk = a.dk; p.dv = a.dv; p.dig = a.dig; p.dfg = a.dfg;
     p.odC = a.odC; p.odn = a.odn; p.B = a.B; p.H = a.H; p.T = a.T; p.NC = a.NC; p.gbf16 = gdtype == XLSTM_BF16;
     p.prof = tc_debug_prof();
+    p.status = tc_status_ptr();
+    if (!p.status) { set_error("mlstm_bw: cannot resolve the device status word"); return XLSTM_ERR_CUDA; }
     size_t smem = Smem::total + 1024;
     if (gdtype == XLSTM_BF16) {
         XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
