@@ -23,7 +23,7 @@ namespace cg = cooperative_groups;
 
 namespace xl {
 
-static constexpr int kThreads = 256;
+static constexpr int kThreads = 512;
 static constexpr int kPF = 2;  // pointwise items per thread whose global operands are prefetched
 
 struct SlstmArgs {
@@ -39,6 +39,8 @@ struct SlstmArgs {
     int dhd;                   // units per head
     int CS, UPC;               // cluster size, units per CTA
     int KS;                    // k-slices of the mat-vec
+    int CPT;                   // output columns per thread in the backward mat-vec (2 or 1)
+    long long* prof;           // development aid (profiling builds only)
 };
 
 struct SlstmSmem {
@@ -58,48 +60,68 @@ static SlstmSmem smem_layout(int K, int NOUT, int BG, int KS, int UPC, int nstat
     return l;
 }
 
-// out[b][j] partial sums over a k-slice: part[(ks*BG + b)*NOUTp + j] = sum_{k in slice} xin[k*BG+b] * Ws[k*NOUTp+j]
-template <int BG>
+// out[b][j] partial sums over a k-slice: part[(ks*BG + b)*NOUTp + j] = sum_{k in slice} xin[k*BG+b] * Ws[k*NOUTp+j].
+// CPT = 2: a thread owns a column pair and uses the packed fp32x2 FMA (one instruction per batch element and
+// row instead of two); CPT = 1: one column per thread, for narrow outputs where pairs would leave threads idle.
+template <int BG, int CPT>
 __device__ __forceinline__ void matvec(const float* __restrict__ Ws, const float* __restrict__ xin,
                                        float* __restrict__ part, int K, int NOUTp, int KS) {
-    const int npairs = NOUTp >> 1;
+    const int ncols = NOUTp / CPT;
     const int rows_per = (K + KS - 1) / KS;
-    for (int item = threadIdx.x; item < npairs * KS; item += kThreads) {
-        const int cp = item % npairs, ks = item / npairs;
+    for (int item = threadIdx.x; item < ncols * KS; item += kThreads) {
+        const int cp = item % ncols, ks = item / ncols;
         const int r0 = ks * rows_per, r1 = min(K, r0 + rows_per);
-        float a0[BG], a1[BG];
-#pragma unroll
-        for (int b = 0; b < BG; ++b) a0[b] = a1[b] = 0.f;
-        const float* wp = Ws + (size_t)r0 * NOUTp + 2 * cp;
+        const float* wp = Ws + (size_t)r0 * NOUTp + CPT * cp;
         const float* xp = xin + (size_t)r0 * BG;
+        if (CPT == 2) {
+            float2 acc[BG];
+#pragma unroll
+            for (int b = 0; b < BG; ++b) acc[b] = make_float2(0.f, 0.f);
 #pragma unroll 4
-        for (int r = r0; r < r1; ++r) {
-            const float2 w = *reinterpret_cast<const float2*>(wp);
-            if (BG % 4 == 0) {
+            for (int r = r0; r < r1; ++r) {
+                const float2 w = *reinterpret_cast<const float2*>(wp);
+                if (BG % 4 == 0) {
 #pragma unroll
-                for (int b4 = 0; b4 < BG / 4; ++b4) {
-                    const float4 x = *reinterpret_cast<const float4*>(xp + 4 * b4);
-                    a0[4 * b4 + 0] += x.x * w.x; a1[4 * b4 + 0] += x.x * w.y;
-                    a0[4 * b4 + 1] += x.y * w.x; a1[4 * b4 + 1] += x.y * w.y;
-                    a0[4 * b4 + 2] += x.z * w.x; a1[4 * b4 + 2] += x.z * w.y;
-                    a0[4 * b4 + 3] += x.w * w.x; a1[4 * b4 + 3] += x.w * w.y;
-                }
-            } else {
+                    for (int b4 = 0; b4 < BG / 4; ++b4) {
+                        const float4 x = *reinterpret_cast<const float4*>(xp + 4 * b4);
+                        acc[4 * b4 + 0] = __ffma2_rn(make_float2(x.x, x.x), w, acc[4 * b4 + 0]);
+                        acc[4 * b4 + 1] = __ffma2_rn(make_float2(x.y, x.y), w, acc[4 * b4 + 1]);
+                        acc[4 * b4 + 2] = __ffma2_rn(make_float2(x.z, x.z), w, acc[4 * b4 + 2]);
+                        acc[4 * b4 + 3] = __ffma2_rn(make_float2(x.w, x.w), w, acc[4 * b4 + 3]);
+                    }
+                } else {
 #pragma unroll
-                for (int b = 0; b < BG; ++b) {
-                    const float x = xp[b];
-                    a0[b] += x * w.x;
-                    a1[b] += x * w.y;
+                    for (int b = 0; b < BG; ++b) acc[b] = __ffma2_rn(make_float2(xp[b], xp[b]), w, acc[b]);
                 }
+                wp += NOUTp;
+                xp += BG;
             }
-            wp += NOUTp;
-            xp += BG;
-        }
 #pragma unroll
-        for (int b = 0; b < BG; ++b) {
-            float* o = part + ((size_t)ks * BG + b) * NOUTp + 2 * cp;
-            o[0] = a0[b];
-            o[1] = a1[b];
+            for (int b = 0; b < BG; ++b)
+                *reinterpret_cast<float2*>(part + ((size_t)ks * BG + b) * NOUTp + 2 * cp) = acc[b];
+        } else {
+            float acc[BG];
+#pragma unroll
+            for (int b = 0; b < BG; ++b) acc[b] = 0.f;
+#pragma unroll 4
+            for (int r = r0; r < r1; ++r) {
+                const float w = *wp;
+                if (BG % 4 == 0) {
+#pragma unroll
+                    for (int b4 = 0; b4 < BG / 4; ++b4) {
+                        const float4 x = *reinterpret_cast<const float4*>(xp + 4 * b4);
+                        acc[4 * b4 + 0] += x.x * w; acc[4 * b4 + 1] += x.y * w;
+                        acc[4 * b4 + 2] += x.z * w; acc[4 * b4 + 3] += x.w * w;
+                    }
+                } else {
+#pragma unroll
+                    for (int b = 0; b < BG; ++b) acc[b] += xp[b] * w;
+                }
+                wp += NOUTp;
+                xp += BG;
+            }
+#pragma unroll
+            for (int b = 0; b < BG; ++b) part[((size_t)ks * BG + b) * NOUTp + cp] = acc[b];
         }
     }
 }
@@ -168,8 +190,24 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
     }
     cluster.sync();  // every CTA's buffers exist before any remote write
 
+    // biases of the items this thread owns in the pointwise phase
+    float bias[kPF][4];
+#pragma unroll
+    for (int p = 0; p < kPF; ++p) {
+        const int it = tid + p * kThreads;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            bias[p][q] = (it < NI) ? a.bcat[q * H + hd * dhd + cr * UPC + it % UPC] : 0.f;
+    }
     int cur = 0;
+#ifdef XL_TC_PROFILE
+    long long tprev = clock64(), pacc[6] = {0, 0, 0, 0, 0, 0};
+#define SPROF(i) { long long tn = clock64(); pacc[i] += tn - tprev; tprev = tn; }
+#else
+#define SPROF(i)
+#endif
     for (int t = 0; t < T; ++t) {
+        SPROF(0)
         // issue this step's global reads early; they land while the mat-vec runs
         float gpre[kPF][4];
 #pragma unroll
@@ -184,9 +222,12 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
                 }
             }
         }
-        matvec<BG>(Ws, xin + (size_t)cur * K * BG, part, K, NOUTp, a.KS);
+        SPROF(1)
+        matvec<BG, 2>(Ws, xin + (size_t)cur * K * BG, part, K, NOUTp, a.KS);
+        SPROF(2)
         __syncthreads();
-        auto cell = [&](int it, const float* gin) {
+        SPROF(3)
+        auto cell = [&](int it, const float* gin, const float* bs) {
             const int b = it / UPC, ul = it % UPC;
             float hh = 0.f;
             if (b0 + b < a.B) {
@@ -198,22 +239,23 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
                     for (int q = 0; q < 4; ++q) gh[q] += pp[q * UPC];
                 }
                 float* gt = a.g + ((size_t)(b0 + b) * T + t) * 4 * H + j;
-                const float z_pre = gin[0] + gh[0] + a.bcat[j];
-                const float i_pre = gin[1] + gh[1] + a.bcat[H + j];
-                const float f_pre = gin[2] + gh[2] + a.bcat[2 * H + j];
-                const float o_pre = gin[3] + gh[3] + a.bcat[3 * H + j];
+                const float z_pre = gin[0] + gh[0] + bs[0];
+                const float i_pre = gin[1] + gh[1] + bs[1];
+                const float f_pre = gin[2] + gh[2] + bs[2];
+                const float o_pre = gin[3] + gh[3] + bs[3];
                 const size_t s = ((size_t)(b0 + b) * T + t) * H + j;
                 const float hp = xin[(size_t)cur * K * BG + (size_t)(cr * UPC + ul) * BG + b];
                 const float cp = st[it], np = st[NI + it], mp = st[2 * NI + it];
-                const float z = tanhf(z_pre);
-                const float o = stable_sigmoid(o_pre);
-                const float fm = log_sigmoid(f_pre) + mp;
+                // exp/log through the hardware approximations (relative error ~1e-6, inside the 1e-4 budget)
+                const float z = 1.f - __fdividef(2.f, 1.f + __expf(2.f * z_pre));
+                const float o = __fdividef(1.f, 1.f + __expf(-o_pre));
+                const float fm = fminf(f_pre, 0.f) - __logf(1.f + __expf(-fabsf(f_pre))) + mp;
                 const float m = (np == 0.f) ? i_pre : fmaxf(fm, i_pre);
-                const float ip = fminf(1.f, expf(i_pre - m));
-                const float fp = fminf(1.f, expf(fm - m));
+                const float ip = fminf(1.f, __expf(i_pre - m));
+                const float fp = fminf(1.f, __expf(fm - m));
                 const float c = fp * cp + ip * z;
                 const float n = fp * np + ip;
-                hh = o * c / n;
+                hh = __fdividef(o * c, n);
                 st[it] = c; st[NI + it] = n; st[2 * NI + it] = m;
                 __stcs(gt + (size_t)2 * H, f_pre);
                 __stcs(a.s.h_prev + s, hp);
@@ -232,7 +274,7 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
 #pragma unroll
         for (int p = 0; p < kPF; ++p) {
             const int it = tid + p * kThreads;
-            if (it < NI) cell(it, gpre[p]);
+            if (it < NI) cell(it, gpre[p], bias[p]);
         }
         for (int it = tid + kPF * kThreads; it < NI; it += kThreads) {
             const int b = it / UPC, ul = it % UPC;
@@ -242,13 +284,23 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
 #pragma unroll
                 for (int q = 0; q < 4; ++q) gin[q] = gt[(size_t)q * H];
             }
-            cell(it, gin);
+            float bs[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) bs[q] = a.bcat[q * H + hd * dhd + cr * UPC + ul];
+            cell(it, gin, bs);
         }
+        SPROF(4)
         __syncthreads();
         broadcast<BG>(cluster, stage, xin + (size_t)(cur ^ 1) * K * BG, CS, UPC, 1, UPC, 0, cr * UPC);
+        SPROF(5)
         cluster.sync();
         cur ^= 1;
     }
+#ifdef XL_TC_PROFILE
+    if (blockIdx.x == 0 && tid == 0 && a.prof)
+        for (int i = 0; i < 6; ++i) a.prof[i] = pacc[i];
+#endif
+#undef SPROF
     // final state
     for (int it = tid; it < NI; it += kThreads) {
         int b = it / UPC, ul = it % UPC;
@@ -382,7 +434,8 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmS
         prefetch(t - 1);
         cluster.sync();
         cur ^= 1;
-        matvec<BG>(Ws, xin + (size_t)cur * K * BG, part, K, NOUTp, a.KS);
+        if (a.CPT == 2) matvec<BG, 2>(Ws, xin + (size_t)cur * K * BG, part, K, NOUTp, a.KS);
+        else matvec<BG, 1>(Ws, xin + (size_t)cur * K * BG, part, K, NOUTp, a.KS);
         __syncthreads();
     }
     for (int it = tid; it < NI; it += kThreads) {
@@ -401,7 +454,7 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmS
 // Host side: geometry and launch
 // ---------------------------------------------------------------------------------------------
 struct Geo {
-    int BG, CS, UPC, KS;
+    int BG, CS, UPC, KS, CPT;
     SlstmSmem lay;
 };
 
@@ -411,14 +464,17 @@ static bool fits(int BG, int CS, int dhd, bool bwd, Geo* out) {
     if (dhd % CS) return false;
     int UPC = dhd / CS;
     int K = bwd ? 4 * dhd : dhd, NOUT = bwd ? UPC : 4 * UPC;
-    int NOUTp = (NOUT + 1) & ~1, npairs = NOUTp / 2;
-    int KS = kThreads / npairs;
+    int NOUTp = (NOUT + 1) & ~1;
+    int CPT = 2;
+    if (bwd && (NOUTp / 2) * 16 < kThreads) CPT = 1;  // narrow output: one column per thread keeps all threads busy
+    int ncols = NOUTp / CPT;
+    int KS = kThreads / ncols;
     if (KS < 1) KS = 1;
     if (KS > 16) KS = 16;
     if (KS > K) KS = K;
     SlstmSmem l = smem_layout(K, NOUT, BG, KS, UPC, bwd ? 2 : 3);
     if (l.total > kSmemCap) return false;
-    out->BG = BG; out->CS = CS; out->UPC = UPC; out->KS = KS; out->lay = l;
+    out->BG = BG; out->CS = CS; out->UPC = UPC; out->KS = KS; out->CPT = CPT; out->lay = l;
     return true;
 }
 
@@ -442,7 +498,14 @@ static bool pick_geometry(int B, int NH, int dhd, bool bwd, Geo* out) {
 template <int BG>
 static int launch(cudaStream_t st, bool bwd, const SlstmArgs& a, const Geo& g) {
     auto kern = bwd ? slstm_bw_cluster<BG> : slstm_fw_cluster<BG>;
-    XL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.lay.total));
+    // The attribute call and the cluster-occupancy query cost milliseconds on the host; do them once per
+    // (kernel, device, cluster size, shared-memory size).
+    static std::atomic<unsigned long long> checked[2][64];
+    int dev = 0;
+    XL_CUDA(cudaGetDevice(&dev));
+    const unsigned long long key = ((unsigned long long)g.lay.total << 8) | (unsigned)g.CS;
+    const bool known = dev >= 0 && dev < 64 && checked[bwd ? 1 : 0][dev].load() == key;
+    if (!known) XL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.lay.total));
     int nbg = (a.B + BG - 1) / BG;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(a.NH * nbg * g.CS));
@@ -456,24 +519,30 @@ static int launch(cudaStream_t st, bool bwd, const SlstmArgs& a, const Geo& g) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    int nclusters = 0;
-    XL_CUDA(cudaOccupancyMaxActiveClusters(&nclusters, kern, &cfg));
-    if (nclusters < 1) {
-        set_error("slstm: a cluster of %d CTAs with %zu B shared memory cannot be resident", g.CS, g.lay.total);
-        return XLSTM_DECLINED;
+    if (!known) {
+        int nclusters = 0;
+        XL_CUDA(cudaOccupancyMaxActiveClusters(&nclusters, kern, &cfg));
+        if (nclusters < 1) {
+            set_error("slstm: a cluster of %d CTAs with %zu B shared memory cannot be resident", g.CS, g.lay.total);
+            return XLSTM_DECLINED;
+        }
+        if (dev >= 0 && dev < 64) checked[bwd ? 1 : 0][dev].store(key);
     }
     XL_CUDA(cudaLaunchKernelEx(&cfg, kern, a, g.lay));
     count_launch();
     return XLSTM_OK;
 }
 
+long long* tc_debug_prof();
+
 static int run(cudaStream_t st, bool bwd, SlstmArgs a) {
     Geo g;
+    a.prof = tc_debug_prof();
     if (!pick_geometry(a.B, a.NH, a.dhd, bwd, &g)) {
         set_error("slstm: recurrent slice for %d units per head does not fit a cluster's shared memory", a.dhd);
         return XLSTM_DECLINED;
     }
-    a.CS = g.CS; a.UPC = g.UPC; a.KS = g.KS;
+    a.CS = g.CS; a.UPC = g.UPC; a.KS = g.KS; a.CPT = g.CPT;
     switch (g.BG) {
         case 8: return launch<8>(st, bwd, a, g);
         case 4: return launch<4>(st, bwd, a, g);
