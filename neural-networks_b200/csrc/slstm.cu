@@ -16,12 +16,21 @@
 // Math: src/nn2/slstm.rs:286-325, 399-423 with the GPU kernels' gate clamps
 // (src/gpu/cuda/slstm_fused.cu:132-142). Kernels replaced: src/gpu/cuda/slstm_coop.cu:103-515.
 #include <cooperative_groups.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace xl {
+
+// The two halves of the hardware cluster barrier. A step uses the barrier twice, alternating:
+// phase A (arrive right after the mat-vec, wait just before the broadcast) tells every CTA that all
+// readers of the exchange buffer are done, so one buffer suffices; phase B (arrive + wait after the
+// broadcast) publishes the new contents. Every thread of every CTA executes each call the same
+// number of times, so the barrier cannot be left waiting.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 static constexpr int kThreads = 512;
 static constexpr int kPF = 2;  // pointwise items per thread whose global operands are prefetched
@@ -53,7 +62,7 @@ static SlstmSmem smem_layout(int K, int NOUT, int BG, int KS, int UPC, int nstat
     auto a16 = [](size_t x) { return (x + 15) / 16 * 16; };
     l.ws = 0;
     l.xin = l.ws + a16((size_t)K * NOUTp * 4);
-    l.part = l.xin + a16((size_t)2 * K * BG * 4);
+    l.part = l.xin + a16((size_t)K * BG * 4);
     l.stage = l.part + a16((size_t)KS * BG * NOUTp * 4);
     l.state = l.stage + a16((size_t)BG * 4 * UPC * 4);
     l.total = l.state + a16((size_t)nstate * BG * UPC * 4);
@@ -162,7 +171,7 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
 
     extern __shared__ __align__(16) unsigned char smem[];
     float* Ws = (float*)(smem + lay.ws);
-    float* xin = (float*)(smem + lay.xin);      // [2][K][BG]
+    float* xin = (float*)(smem + lay.xin);      // [K][BG]: h of the whole head
     float* part = (float*)(smem + lay.part);    // [KS][BG][NOUTp]
     float* stage = (float*)(smem + lay.stage);  // [BG][UPC]
     float* st = (float*)(smem + lay.state);     // c,n,m: [3][BG*UPC]
@@ -199,7 +208,6 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
         for (int q = 0; q < 4; ++q)
             bias[p][q] = (it < NI) ? a.bcat[q * H + hd * dhd + cr * UPC + it % UPC] : 0.f;
     }
-    int cur = 0;
 #ifdef XL_TC_PROFILE
     long long tprev = clock64(), pacc[6] = {0, 0, 0, 0, 0, 0};
 #define SPROF(i) { long long tn = clock64(); pacc[i] += tn - tprev; tprev = tn; }
@@ -223,11 +231,19 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
             }
         }
         SPROF(1)
-        matvec<BG, 2>(Ws, xin + (size_t)cur * K * BG, part, K, NOUTp, a.KS);
+        // this CTA's own previous h (a saved record), read before peers may overwrite the buffer
+        float hprev[kPF];
+#pragma unroll
+        for (int p = 0; p < kPF; ++p) {
+            const int it = tid + p * kThreads;
+            hprev[p] = (it < NI) ? xin[(size_t)(cr * UPC + it % UPC) * BG + it / UPC] : 0.f;
+        }
+        matvec<BG, 2>(Ws, xin, part, K, NOUTp, a.KS);
+        if (NI <= kPF * kThreads) cluster_arrive();  // done reading the exchange buffer
         SPROF(2)
         __syncthreads();
         SPROF(3)
-        auto cell = [&](int it, const float* gin, const float* bs) {
+        auto cell = [&](int it, const float* gin, const float* bs, float hp) {
             const int b = it / UPC, ul = it % UPC;
             float hh = 0.f;
             if (b0 + b < a.B) {
@@ -244,7 +260,6 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
                 const float f_pre = gin[2] + gh[2] + bs[2];
                 const float o_pre = gin[3] + gh[3] + bs[3];
                 const size_t s = ((size_t)(b0 + b) * T + t) * H + j;
-                const float hp = xin[(size_t)cur * K * BG + (size_t)(cr * UPC + ul) * BG + b];
                 const float cp = st[it], np = st[NI + it], mp = st[2 * NI + it];
                 // exp/log through the hardware approximations (relative error ~1e-6, inside the 1e-4 budget)
                 const float z = 1.f - __fdividef(2.f, 1.f + __expf(2.f * z_pre));
@@ -274,7 +289,7 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
 #pragma unroll
         for (int p = 0; p < kPF; ++p) {
             const int it = tid + p * kThreads;
-            if (it < NI) cell(it, gpre[p], bias[p]);
+            if (it < NI) cell(it, gpre[p], bias[p], hprev[p]);
         }
         for (int it = tid + kPF * kThreads; it < NI; it += kThreads) {
             const int b = it / UPC, ul = it % UPC;
@@ -287,14 +302,16 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
             float bs[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) bs[q] = a.bcat[q * H + hd * dhd + cr * UPC + ul];
-            cell(it, gin, bs);
+            cell(it, gin, bs, xin[(size_t)(cr * UPC + ul) * BG + b]);
         }
         SPROF(4)
         __syncthreads();
-        broadcast<BG>(cluster, stage, xin + (size_t)(cur ^ 1) * K * BG, CS, UPC, 1, UPC, 0, cr * UPC);
+        if (NI > kPF * kThreads) cluster_arrive();  // wide CTAs read their previous h inside the cell
+        cluster_wait();                               // every CTA is done reading: the buffer may be overwritten
+        broadcast<BG>(cluster, stage, xin, CS, UPC, 1, UPC, 0, cr * UPC);
         SPROF(5)
-        cluster.sync();
-        cur ^= 1;
+        cluster_arrive();
+        cluster_wait();                               // the new h of the whole head is visible
     }
 #ifdef XL_TC_PROFILE
     if (blockIdx.x == 0 && tid == 0 && a.prof)
@@ -309,7 +326,7 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
         a.c[si] = st[it];
         a.n[si] = st[NI + it];
         a.m[si] = st[2 * NI + it];
-        a.h[si] = xin[(size_t)cur * K * BG + (size_t)(cr * UPC + ul) * BG + b];
+        a.h[si] = xin[(size_t)(cr * UPC + ul) * BG + b];
     }
 }
 
@@ -329,7 +346,7 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmS
 
     extern __shared__ __align__(16) unsigned char smem[];
     float* Ws = (float*)(smem + lay.ws);        // [K = gate*dhd+u][NOUTp = own rows]
-    float* xin = (float*)(smem + lay.xin);      // [2][K][BG]: gate deltas of the head
+    float* xin = (float*)(smem + lay.xin);      // [K][BG]: gate deltas of the head
     float* part = (float*)(smem + lay.part);    // [KS][BG][NOUTp]: dh partials for own units
     float* stage = (float*)(smem + lay.stage);  // [BG][4][UPC]
     float* st = (float*)(smem + lay.state);     // dc, dn: [2][BG*UPC]
@@ -355,8 +372,8 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmS
         st[NI + it] = live ? a.dn[si] : 0.f;
     }
     cluster.sync();
+    cluster_arrive();  // opens phase A for the first step: nobody is reading the exchange buffer yet
 
-    int cur = 0;
     // operands of the first processed step
     float pre[kPF][10];
     auto prefetch = [&](int t) {
@@ -430,14 +447,17 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmS
             cell(it, op);
         }
         __syncthreads();
-        broadcast<BG>(cluster, stage, xin + (size_t)(cur ^ 1) * K * BG, CS, UPC, 4, UPC, dhd, cr * UPC);
+        cluster_wait();  // every CTA finished the previous mat-vec: the exchange buffer may be overwritten
+        broadcast<BG>(cluster, stage, xin, CS, UPC, 4, UPC, dhd, cr * UPC);
         prefetch(t - 1);
-        cluster.sync();
-        cur ^= 1;
-        if (a.CPT == 2) matvec<BG, 2>(Ws, xin + (size_t)cur * K * BG, part, K, NOUTp, a.KS);
-        else matvec<BG, 1>(Ws, xin + (size_t)cur * K * BG, part, K, NOUTp, a.KS);
+        cluster_arrive();
+        cluster_wait();  // the gate deltas of the whole head are visible
+        if (a.CPT == 2) matvec<BG, 2>(Ws, xin, part, K, NOUTp, a.KS);
+        else matvec<BG, 1>(Ws, xin, part, K, NOUTp, a.KS);
+        cluster_arrive();  // done reading the exchange buffer
         __syncthreads();
     }
+    cluster_wait();  // balances the last arrive
     for (int it = tid; it < NI; it += kThreads) {
         int b = it / UPC, ul = it % UPC;
         if (b0 + b >= a.B) continue;
@@ -478,34 +498,56 @@ static bool fits(int BG, int CS, int dhd, bool bwd, Geo* out) {
     return true;
 }
 
-// Batch group: the largest of 8/4/2/1 that does not pad the batch by 2x or more. Cluster size:
-// the widest (<= 8, the portable limit) that keeps >= 8 units per CTA and the whole grid within
-// one wave of SMs; failing that, the narrowest whose slice fits shared memory.
-static bool pick_geometry(int B, int NH, int dhd, bool bwd, Geo* out) {
-    const int bgs[4] = {8, 4, 2, 1};
-    for (int bi = 0; bi < 4; ++bi) {
-        int BG = bgs[bi];
-        if (BG > 1 && BG / 2 >= B) continue;
-        int nbg = (B + BG - 1) / BG;
-        for (int CS = 8; CS >= 1; CS /= 2)
-            if ((dhd / CS >= 8 || CS == 1) && NH * nbg * CS <= sm_count() && fits(BG, CS, dhd, bwd, out)) return true;
-        for (int CS = 1; CS <= 8; CS *= 2)
-            if (fits(BG, CS, dhd, bwd, out)) return true;
-    }
+// Cluster size for a fixed batch group: the widest (<= 8, the portable limit) that keeps >= 8 units
+// per CTA and the whole grid within the SM count; failing that, the narrowest whose slice fits.
+static bool geometry_for(int BG, int B, int NH, int dhd, bool bwd, Geo* out) {
+    int nbg = (B + BG - 1) / BG;
+    for (int CS = 8; CS >= 1; CS /= 2)
+        if ((dhd / CS >= 8 || CS == 1) && NH * nbg * CS <= sm_count() && fits(BG, CS, dhd, bwd, out)) return true;
+    for (int CS = 1; CS <= 8; CS *= 2)
+        if (fits(BG, CS, dhd, bwd, out)) return true;
     return false;
+}
+
+// Clusters of this geometry that can be resident at once (GPC fragmentation makes this less than
+// SMs / CS). The attribute call and the occupancy query cost milliseconds on the host, so the
+// answer is cached per (kernel, device, cluster size, shared-memory size).
+template <int BG>
+static int coresident(bool bwd, const Geo& g, int* out) {
+    auto kern = bwd ? slstm_bw_cluster<BG> : slstm_fw_cluster<BG>;
+    static std::atomic<unsigned long long> key_of[2][64];
+    static std::atomic<int> val_of[2][64];
+    int dev = 0;
+    XL_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) dev = 0;
+    const unsigned long long key = ((unsigned long long)g.lay.total << 8) | (unsigned)g.CS;
+    if (key_of[bwd][dev].load() == key) { *out = val_of[bwd][dev].load(); return XLSTM_OK; }
+    XL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.lay.total));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)g.CS);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = g.lay.total;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)g.CS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    XL_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+    if (getenv("XLSTM_DEBUG"))
+        fprintf(stderr, "[xlstm] slstm %s: BG=%d CS=%d UPC=%d KS=%d CPT=%d smem=%zu clusters co-resident=%d\n", bwd ? "bw" : "fw",
+                BG, g.CS, g.UPC, g.KS, g.CPT, g.lay.total, n);
+    val_of[bwd][dev].store(n);
+    key_of[bwd][dev].store(key);
+    *out = n;
+    return XLSTM_OK;
 }
 
 template <int BG>
 static int launch(cudaStream_t st, bool bwd, const SlstmArgs& a, const Geo& g) {
     auto kern = bwd ? slstm_bw_cluster<BG> : slstm_fw_cluster<BG>;
-    // The attribute call and the cluster-occupancy query cost milliseconds on the host; do them once per
-    // (kernel, device, cluster size, shared-memory size).
-    static std::atomic<unsigned long long> checked[2][64];
-    int dev = 0;
-    XL_CUDA(cudaGetDevice(&dev));
-    const unsigned long long key = ((unsigned long long)g.lay.total << 8) | (unsigned)g.CS;
-    const bool known = dev >= 0 && dev < 64 && checked[bwd ? 1 : 0][dev].load() == key;
-    if (!known) XL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.lay.total));
     int nbg = (a.B + BG - 1) / BG;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(a.NH * nbg * g.CS));
@@ -519,31 +561,56 @@ static int launch(cudaStream_t st, bool bwd, const SlstmArgs& a, const Geo& g) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (!known) {
-        int nclusters = 0;
-        XL_CUDA(cudaOccupancyMaxActiveClusters(&nclusters, kern, &cfg));
-        if (nclusters < 1) {
-            set_error("slstm: a cluster of %d CTAs with %zu B shared memory cannot be resident", g.CS, g.lay.total);
-            return XLSTM_DECLINED;
-        }
-        if (dev >= 0 && dev < 64) checked[bwd ? 1 : 0][dev].store(key);
-    }
     XL_CUDA(cudaLaunchKernelEx(&cfg, kern, a, g.lay));
     count_launch();
     return XLSTM_OK;
 }
 
+static int coresident_any(int BG, bool bwd, const Geo& g, int* out) {
+    switch (BG) {
+        case 16: return coresident<16>(bwd, g, out);
+        case 12: return coresident<12>(bwd, g, out);
+        case 8: return coresident<8>(bwd, g, out);
+        case 4: return coresident<4>(bwd, g, out);
+        case 2: return coresident<2>(bwd, g, out);
+        default: return coresident<1>(bwd, g, out);
+    }
+}
+
 long long* tc_debug_prof();
 
+// Batch group: start from the largest of 8/4/2/1 that does not pad the batch by 2x or more, and grow
+// it (12, 16) while the clusters it needs exceed what can be resident at once: a second wave of
+// clusters doubles the time of a latency-bound loop, a wider batch group costs far less.
 static int run(cudaStream_t st, bool bwd, SlstmArgs a) {
-    Geo g;
     a.prof = tc_debug_prof();
-    if (!pick_geometry(a.B, a.NH, a.dhd, bwd, &g)) {
-        set_error("slstm: recurrent slice for %d units per head does not fit a cluster's shared memory", a.dhd);
+    const int cand[6] = {1, 2, 4, 8, 12, 16};
+    int first = 0;
+    for (int i = 3; i >= 0; --i)
+        if (cand[i] == 1 || cand[i] / 2 < a.B) { first = i; break; }
+    Geo chosen;
+    int chosen_bg = 0;
+    for (int i = first; i < 6; ++i) {
+        const int BG = cand[i];
+        if (i > first && BG / 2 >= a.B) break;
+        Geo g;
+        if (!geometry_for(BG, a.B, a.NH, a.dhd, bwd, &g)) continue;
+        int maxc = 0;
+        int rc = coresident_any(BG, bwd, g, &maxc);
+        if (rc) return rc;
+        if (maxc < 1) continue;
+        if (chosen_bg == 0) { chosen = g; chosen_bg = BG; }  // fallback: runs in waves
+        if (a.NH * ((a.B + BG - 1) / BG) <= maxc) { chosen = g; chosen_bg = BG; break; }
+    }
+    if (chosen_bg == 0) {
+        set_error("slstm: recurrent slice for %d units per head does not fit a resident cluster's shared memory", a.dhd);
         return XLSTM_DECLINED;
     }
+    const Geo& g = chosen;
     a.CS = g.CS; a.UPC = g.UPC; a.KS = g.KS; a.CPT = g.CPT;
-    switch (g.BG) {
+    switch (chosen_bg) {
+        case 16: return launch<16>(st, bwd, a, g);
+        case 12: return launch<12>(st, bwd, a, g);
         case 8: return launch<8>(st, bwd, a, g);
         case 4: return launch<4>(st, bwd, a, g);
         case 2: return launch<2>(st, bwd, a, g);

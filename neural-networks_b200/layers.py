@@ -1,0 +1,310 @@
+"""Host-side mirror of the reference's layer API above the op seam: `gpu::Linear`, `gpu::RmsNorm`,
+`gpu::MLstm`, `gpu::SLstm`, `gpu::Block<C>` and `gpu::Lm` (src/gpu/linear.rs, rms_norm.rs,
+mlstm.rs, slstm.rs, block.rs, lm.rs), with the same verbs: forward, backward (hand-written, no
+autograd), zero_grad, step (AdamW through one batched queue).
+
+The recurrent cores, RMSNorm, cross-entropy and AdamW run in libxlstm_b200.so through `ops`.
+Plain projections are library GEMMs (torch.matmul -> cuBLAS/cuBLASLt), as they are in the
+reference (src/gpu/ops.rs:186-441). Parameters of record are fp32; with `bf16=True` GEMM operands
+are narrowed to bf16 (the per-layer bf16 weight shadow is written by the AdamW kernel in the same
+pass that updates the weight, so it can never go stale) and q/k/v are stored as bf16.
+Element-wise glue between the ops (gate activations, residual adds, embedding gather/scatter,
+soft-cap) is expressed with torch tensor ops.
+"""
+import math
+
+import torch
+
+from . import ops
+
+
+class Param:
+    """One fp32 parameter with its gradient accumulator, AdamW moments and optional bf16 shadow."""
+
+    def __init__(self, value, decay, shadow=False, grad=None):
+        self.w = value.detach().to(torch.float32).contiguous().cuda()
+        self.g = grad if grad is not None else torch.zeros_like(self.w)
+        self.m = torch.zeros_like(self.w)
+        self.v = torch.zeros_like(self.w)
+        self.decay = decay
+        self.wb = self.w.to(torch.bfloat16) if shadow else None
+
+
+def _mm(a, b, bf16):
+    """a @ b with fp32 result; bf16 operands when asked (fp32 accumulate inside the library)."""
+    if bf16:
+        a16 = a if a.dtype == torch.bfloat16 else a.to(torch.bfloat16)
+        b16 = b if b.dtype == torch.bfloat16 else b.to(torch.bfloat16)
+        try:
+            return torch.mm(a16, b16, out_dtype=torch.float32)
+        except TypeError:
+            return torch.mm(a16, b16).float()
+    return torch.mm(a, b)
+
+
+class Linear:
+    """Y = X W + b (reference: gpu::Linear, src/gpu/linear.rs). W is [in, out]."""
+
+    def __init__(self, w, b, decay=True, bf16=False):
+        self.bf16 = bf16
+        self.w = Param(w, decay, shadow=bf16)
+        self.b = Param(b, False)
+
+    def forward(self, x):
+        self.x = x
+        y = _mm(x, self.w.wb if self.bf16 else self.w.w, self.bf16)
+        return y.add_(self.b.w)
+
+    def backward(self, dy, need_dx=True):
+        self.w.g.add_(_mm(self.x.t(), dy, self.bf16) if not self.bf16 else _mm(self.x.to(torch.bfloat16).t().contiguous(), dy, True))
+        self.b.g.add_(dy.sum(dim=0))
+        if not need_dx:
+            return None
+        wt = (self.w.wb if self.bf16 else self.w.w).t()
+        return _mm(dy, wt.contiguous() if self.bf16 else wt, self.bf16)
+
+    def params(self):
+        return [self.w, self.b]
+
+
+class RmsNorm:
+    """Grouped RMSNorm, eps 1e-6, gamma undecayed (reference: gpu::RmsNorm, src/gpu/rms_norm.rs)."""
+
+    def __init__(self, gamma, group=None):
+        self.gamma = Param(gamma, False)
+        self.group = group or gamma.numel()
+
+    def forward(self, x):
+        self.x = x
+        rows, f = x.shape
+        y = torch.empty_like(x)
+        self.inv = torch.empty((rows * (f // self.group),), dtype=torch.float32, device=x.device)
+        ops.rms_norm_forward_into(x, self.gamma.w, self.group, y, self.inv)
+        return y
+
+    def backward(self, dy):
+        dx = torch.empty_like(dy)
+        ops.rms_norm_backward_into(dy, self.x, self.inv, self.gamma.w, self.group, dx, self.gamma.g)
+        return dx
+
+    def params(self):
+        return [self.gamma]
+
+
+class MLstm:
+    """gpu::MLstm (src/gpu/mlstm.rs:167-876): six projections -> fused chunkwise core -> head-wise
+    RMSNorm -> output gate -> output projection. `p` holds wq,wk [in,H*dqk], wv,wo [in,H*dhv],
+    wi,wf [in,H], their biases, w_out [d,d], b_out, gamma [d]."""
+
+    def __init__(self, p, heads, dqk, dhv, bf16=False, chunk=64):
+        self.h, self.dqk, self.dhv, self.bf16, self.chunk = heads, dqk, dhv, bf16, chunk
+        mk = lambda n: Linear(p["w" + n], p["b" + n], True, bf16)
+        self.lq, self.lk, self.lv, self.lo, self.li, self.lf = (mk(n) for n in "qkvoif")
+        self.lout = Linear(p["w_out"], p["b_out"], True, bf16)
+        self.hn = RmsNorm(p["gamma"], group=dhv)
+        self.inv_sqrt = 1.0 / math.sqrt(dqk)
+        self.carry = None  # (C, n, m) when a call continues the previous one
+
+    def forward(self, x, B, T):
+        sdt = torch.bfloat16 if self.bf16 else torch.float32
+        self.st = ops.MlstmShape(B, self.h, T, self.dqk, self.dhv, self.chunk, sdt, torch.float32)
+        q = self.lq.forward(x).to(sdt)
+        k = self.lk.forward(x).mul_(self.inv_sqrt).to(sdt)
+        v = self.lv.forward(x).to(sdt)
+        self.o = torch.sigmoid_(self.lo.forward(x))
+        ig, fg = self.li.forward(x), self.lf.forward(x)
+        self.core_in = (q, k, v, ig, fg)
+        self.fused = ops.mlstm_fused_fw(q, k, v, ig, fg, self.st, carry_in=self.carry, want_state=False)
+        self.yhat = self.hn.forward(self.fused.ytil.float() if self.bf16 else self.fused.ytil)
+        self.hc = self.o * self.yhat
+        return self.lout.forward(self.hc)
+
+    def backward(self, dy):
+        d_hc = self.lout.backward(dy)
+        do_pre = d_hc * self.yhat * self.o * (1.0 - self.o)
+        d_ytil = self.hn.backward(d_hc * self.o)
+        q, k, v, ig, fg = self.core_in
+        dq, dk, dv, dig, dfg, _ = ops.mlstm_fused_bw(self.fused, q, k, v, ig, fg, d_ytil, self.st, carry_in=self.carry,
+                                                     want_dstate=False)
+        dx = self.lq.backward(dq)
+        dx.add_(self.lk.backward(dk.mul_(self.inv_sqrt)))
+        dx.add_(self.lv.backward(dv))
+        dx.add_(self.lo.backward(do_pre))
+        dx.add_(self.li.backward(dig))
+        dx.add_(self.lf.backward(dfg))
+        return dx
+
+    def params(self):
+        out = []
+        for l in (self.lq, self.lk, self.lv, self.lo, self.li, self.lf, self.lout):
+            out += l.params()
+        return out + self.hn.params()
+
+
+class SLstm:
+    """gpu::SLstm (src/gpu/slstm.rs:91-1335): hoisted x.Wx GEMM -> fused recurrent loop; the
+    post-cell norm is applied by the block. wh is dense [H,4H] (nh=1) or block-diagonal [nh,dh,4dh]."""
+
+    def __init__(self, p, hidden, nh=1, bf16=False):
+        self.H, self.nh, self.bf16 = hidden, nh, bf16
+        self.wx = Param(p["wx"], True, shadow=bf16)
+        self.wh = Param(p["wh"], True)
+        self.b = Param(p["bcat"], False)
+
+    def forward(self, x, B, T):
+        H = self.H
+        self.B, self.T, self.x = B, T, x
+        self.g = _mm(x, self.wx.wb if self.bf16 else self.wx.w, self.bf16).view(B, T, 4 * H)
+        self.slabs = ops.SlstmSlabs(B, T, H, x.device)
+        state = tuple(torch.empty((B, H), dtype=torch.float32, device=x.device) for _ in range(4))
+        out = torch.empty((B, T, H), dtype=torch.float32, device=x.device)
+        ops.slstm_fused_time(self.wh.w, self.g, self.b.w, state, out, self.slabs, nh=self.nh, carry=False)
+        return out.view(B * T, H)
+
+    def backward(self, dy):
+        B, T, H, nh = self.B, self.T, self.H, self.nh
+        ds = tuple(torch.empty((B, H), dtype=torch.float32, device=dy.device) for _ in range(3))
+        ops.slstm_fused_time_bwd(self.wh.w, dy.view(B, T, H).contiguous(), self.g, ds, self.slabs, nh=nh, carry=False)
+        dg = self.g.view(B * T, 4 * H)  # the loop left the four gate deltas here
+        xt = self.x.to(torch.bfloat16).t().contiguous() if self.bf16 else self.x.t()
+        self.wx.g.add_(_mm(xt, dg, self.bf16))
+        self.b.g.add_(dg.sum(dim=0))
+        hp = self.slabs.t["h_prev"].view(B * T, H)
+        if nh == 1:
+            self.wh.g.add_(torch.mm(hp.t(), dg))
+        else:
+            dh = H // nh
+            dg4 = dg.view(B * T, 4, nh, dh)
+            for hd in range(nh):
+                self.wh.g[hd].add_(torch.mm(hp[:, hd * dh:(hd + 1) * dh].t(), dg4[:, :, hd, :].reshape(B * T, 4 * dh)))
+        wt = (self.wx.wb if self.bf16 else self.wx.w).t()
+        return _mm(dg, wt.contiguous() if self.bf16 else wt, self.bf16)
+
+    def params(self):
+        return [self.wx, self.wh, self.b]
+
+
+class Block:
+    """gpu::Block<C> (src/gpu/block.rs:435-1185): z = x + [post](cell(norm1 x));
+    y = z + down(SiLU(gate(norm2 z)) * value(norm2 z))."""
+
+    def __init__(self, cell, p, post_norm=False, bf16=False):
+        self.cell = cell
+        self.n1, self.n2 = RmsNorm(p["g1"]), RmsNorm(p["g2"])
+        self.post = RmsNorm(p["gpost"]) if post_norm else None
+        self.lg = Linear(p["w_gate"], p["b_gate"], True, bf16)
+        self.lv = Linear(p["w_value"], p["b_value"], True, bf16)
+        self.ld = Linear(p["w_down"], p["b_down"], True, bf16)
+
+    def forward(self, x, B, T):
+        c = self.cell.forward(self.n1.forward(x), B, T)
+        if self.post is not None:
+            c = self.post.forward(c)
+        z = x + c
+        zn = self.n2.forward(z)
+        self.gate_pre, self.value = self.lg.forward(zn), self.lv.forward(zn)
+        self.gate_act = torch.nn.functional.silu(self.gate_pre)
+        return z + self.ld.forward(self.gate_act * self.value)
+
+    def backward(self, dy):
+        d_mixed = self.ld.backward(dy)
+        s = torch.sigmoid(self.gate_pre)
+        d_gate = d_mixed * self.value * (s * (1.0 + self.gate_pre * (1.0 - s)))
+        d_zn = self.lg.backward(d_gate)
+        d_zn.add_(self.lv.backward(d_mixed * self.gate_act))
+        d_z = self.n2.backward(d_zn).add_(dy)
+        d_c = self.post.backward(d_z) if self.post is not None else d_z
+        return self.n1.backward(self.cell.backward(d_c)).add_(d_z)
+
+    def params(self):
+        out = self.n1.params() + self.cell.params() + self.n2.params()
+        if self.post is not None:
+            out += self.post.params()
+        for l in (self.lg, self.lv, self.ld):
+            out += l.params()
+        return out
+
+
+class Lm:
+    """gpu::Lm (src/gpu/lm.rs:25-163): embedding -> blocks -> RMSNorm -> head (fp32) -> SoftCap -> CE.
+    `tied=True` uses the embedding table (transposed) as the head and sums its two gradients."""
+
+    def __init__(self, table, blocks, gamma, head_w=None, head_b=None, cap=30.0, tied=False):
+        self.table = Param(table, False)
+        self.blocks = blocks
+        self.norm = RmsNorm(gamma)
+        self.tied = tied
+        self.head = None if tied else Linear(head_w, head_b, decay=False, bf16=False)
+        self.cap = cap
+        self.loss = torch.zeros((1,), dtype=torch.float32, device="cuda")
+        self.on_block_backward = None  # hook(i) called when block i's gradients are complete
+
+    def forward(self, ids, B, T):
+        self.ids, self.B, self.T = ids.reshape(-1), B, T
+        x = self.table.w.index_select(0, self.ids)
+        for blk in self.blocks:
+            x = blk.forward(x, B, T)
+        self.normed = self.norm.forward(x)
+        pre = torch.mm(self.normed, self.table.w.t()) if self.tied else self.head.forward(self.normed)
+        self.logits = torch.tanh_(pre.div_(self.cap)).mul_(self.cap)
+        return self.logits
+
+    def backward(self, dlogits):
+        t = self.logits / self.cap
+        d_pre = dlogits * (1.0 - t * t)
+        if self.tied:
+            self.table.g.addmm_(d_pre.t(), self.normed)
+            d_n = torch.mm(d_pre, self.table.w)
+        else:
+            d_n = self.head.backward(d_pre)
+        d = self.norm.backward(d_n)
+        for i in range(len(self.blocks) - 1, -1, -1):
+            d = self.blocks[i].backward(d)
+            if self.on_block_backward is not None:
+                self.on_block_backward(i)
+        self.table.g.index_add_(0, self.ids, d)
+
+    def params(self):
+        out = [self.table]
+        for blk in self.blocks:
+            out += blk.params()
+        out += self.norm.params()
+        if self.head is not None:
+            out += self.head.params()
+        return out
+
+    def step(self, cfg):
+        q = ops.AdamwQueue()
+        for p in self.params():
+            q.push(p.w, p.g, p.m, p.v, p.decay, p.wb)
+        q.flush(cfg, zero_grad=True)
+
+    def forward_backward(self, ids, targets, B, T, inv=None):
+        """Forward, fused CE (loss accumulated on the device), backward. Returns the device loss scalar."""
+        logits = self.forward(ids, B, T)
+        self.loss.zero_()
+        dlogits = torch.empty_like(logits)
+        ops.softmax_cross_entropy(logits, targets, dlogits, self.loss, inv=inv)
+        self.backward(dlogits)
+        return self.loss
+
+    def train_step(self, ids, targets, B, T, cfg):
+        loss = self.forward_backward(ids, targets, B, T)
+        self.step(cfg)
+        return loss
+
+
+def build_lm(params, heads, dqk, dhv, nh_s=1, cap=30.0, tied=True, head_w=None, head_b=None, bf16=False, chunk=64):
+    """Builds an Lm from the host parameter dictionary `oracle.model.init_lm_params` produces."""
+    t = lambda a: torch.as_tensor(a, dtype=torch.float32)
+    d = params["table"].shape[1]
+    blocks = []
+    for bp in params["blocks"]:
+        c = {k_: (t(v_) if k_ != "kind" else v_) for k_, v_ in bp["cell"].items()}
+        bpt = {k_: t(v_) for k_, v_ in bp.items() if k_ != "cell"}
+        if c["kind"] == "mlstm":
+            blocks.append(Block(MLstm(c, heads, dqk, dhv, bf16=bf16, chunk=chunk), bpt, bf16=bf16))
+        else:
+            blocks.append(Block(SLstm(c, d, nh_s, bf16=bf16), bpt, post_norm=True, bf16=bf16))
+    return Lm(t(params["table"]), blocks, t(params["gamma"]), None if head_w is None else t(head_w),
+              None if head_b is None else t(head_b), cap=cap, tied=tied)

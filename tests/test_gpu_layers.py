@@ -1,0 +1,80 @@
+"""GPU parity of the layer stack (cells, block, flat LM) against the CPU oracle stack, in the
+manner of the reference's mlstm_matches_cpu / block tests / lm_matches_cpu (src/gpu/mlstm.rs:1004,
+src/gpu/block.rs:1328-1447, src/gpu/lm.rs:187-286): forward, backward and one AdamW step from the
+same host weights; compare loss, every gradient and every post-step weight.
+fp32 bar: 1e-4 rel-to-max for the loss and every gradient. The optimizer step is checked exactly
+(1e-6) by applying the oracle's AdamW to the GPU's own gradients: comparing post-step weights of
+two independent pipelines is ill-conditioned at t = 1, where every element moves by
+lr * g / (|g| + eps) and a 1e-9 difference on a near-zero gradient becomes a visible fraction of lr
+(the reference's own post-step bar is 2e-2 for that reason, src/gpu/lm.rs:187-286).
+With bf16 GEMM operands and bf16 q/k/v the whole-model gradients compound some twenty rounding
+points per block: loss within 5e-3 (the reference's bar), gradient tensors above the noise floor
+within 1.2e-1 rel-to-max and the full gradient direction within cos >= 0.995; the 2e-2 bar is held
+at the op level (tests/test_gpu_mlstm.py)."""
+import importlib
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import model as M
+
+pytestmark = pytest.mark.gpu
+
+
+def _compare(cfg, bf16, tol, loss_tol, slstm_at=(), nh_s=1, seed=0, noise_floor=0.0, cos_min=0.999999):
+    xl = importlib.import_module("neural-networks_b200")
+    layers = importlib.import_module("neural-networks_b200.layers")
+    vocab, d, nb, heads, dqk, dhv, up, B, T = cfg
+    rng = np.random.default_rng(seed)
+    p = M.init_lm_params(rng, vocab, d, nb, heads, dqk, dhv, up, std=0.02 if not slstm_at else 0.1, slstm_at=slstm_at, nh_s=nh_s)
+    ids = rng.integers(0, vocab, B * T)
+    tg = np.roll(ids.reshape(B, T), -1, axis=1).reshape(-1)
+    ref = M.build_lm(p, heads, dqk, dhv, nh_s=nh_s, tied=True)
+    loss_ref, grads_ref = ref.train_step(ids, tg, B, T, 1e-3, 0.1, 1)
+    lm = layers.build_lm(p, heads, dqk, dhv, nh_s=nh_s, tied=True, bf16=bf16)
+    tid = torch.tensor(ids, dtype=torch.int64, device="cuda")
+    ttg = torch.tensor(tg.astype(np.int32), device="cuda")
+    loss = lm.forward_backward(tid, ttg, B, T)
+    grads = [q.g.clone() for q in lm.params()]
+    w_before = [q.w.cpu().numpy().copy() for q in lm.params()]
+    cfg_ = xl.ops.AdamCfg(1e-3, 0.1, t=1)
+    lm.step(cfg_)
+    torch.cuda.synchronize()
+    assert xl._lib.lib.xlstm_device_status() == 0
+    assert abs(loss.item() - loss_ref) <= loss_tol * max(1.0, abs(loss_ref)), (loss.item(), loss_ref)
+    rp = ref.params()
+    assert len(rp) == len(grads)
+    from oracle import oracle as O
+    dot = nn_ = nr_ = 0.0
+    for i, (g, gr, q, r, w0) in enumerate(zip(grads, grads_ref, lm.params(), rp, w_before)):
+        gg = g.cpu().numpy().astype(np.float64)
+        dot += float((gg * gr).sum()); nn_ += float((gg * gg).sum()); nr_ += float((gr * gr).sum())
+        if np.abs(gr).max() >= noise_floor:
+            e = np.abs(gg - gr).max() / np.abs(gr).max()
+            assert e <= tol, "grad %d %s: rel-to-max %.3e" % (i, gr.shape, e)
+        # the optimizer step itself, checked exactly: AdamW(oracle) applied to the GPU's own gradient
+        want = O.adamw(w0, g.cpu().numpy(), np.zeros_like(w0), np.zeros_like(w0), 1e-3, 0.1 if q.decay else 0.0, 1,
+                       dtype=np.float32)[0]
+        ew = np.abs(q.w.cpu().numpy() - want).max() / max(np.abs(want).max(), 1e-12)
+        assert ew <= 1e-6, "post-step weight %d: rel-to-max %.3e" % (i, ew)
+        assert float(q.g.abs().max()) == 0.0
+        if q.wb is not None:
+            assert torch.equal(q.wb, q.w.to(torch.bfloat16))  # the bf16 shadow follows the weight
+    assert dot / np.sqrt(nn_ * nr_) >= cos_min
+
+
+def test_config1_byte_lm_fp32():
+    """BASELINE config 1: vocab 256, d=128, 2 mLSTM blocks of 4 heads x 32, up = 341, B8 x T256, fp32,
+    tied head, one AdamW step (lr 1e-3, wd 0.1)."""
+    _compare((256, 128, 2, 4, 32, 32, 341, 8, 256), False, 1e-4, 1e-4)
+
+
+def test_toy_lm_fp32_with_slstm_blocks():
+    _compare((13, 8, 2, 2, 4, 4, 12, 2, 12), False, 1e-4, 1e-4, slstm_at=(1,), nh_s=1)
+    _compare((13, 16, 2, 2, 8, 8, 24, 2, 12), False, 1e-4, 1e-4, slstm_at=(0,), nh_s=2, seed=1)
+
+
+def test_lm_bf16_operands_tensor_core_cells():
+    """Two mLSTM blocks with 2 heads x 128 (tensor-core path), bf16 GEMM operands and q/k/v storage."""
+    _compare((64, 256, 2, 2, 128, 128, 680, 2, 128), True, 1.2e-1, 5e-3, seed=2, noise_floor=1e-3, cos_min=0.995)
