@@ -398,6 +398,73 @@ def run_lm(args):
         dist.destroy_process_group()
 
 
+def run_ops(args):
+    """Secondary workload: each remaining hot-path kernel on its own, at the sizes of configs[2] and
+    configs[3]: HBM-bound kernels as achieved GB/s against the measured copy peak, the sLSTM loops as
+    microseconds per timestep. One JSON line."""
+    import torch
+    xl = importlib.import_module("neural-networks_b200")
+    ops = xl.ops
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    pk = peaks()
+    n_it, warm = max(args.steps, 5), max(args.warmup, 3)
+
+    def timeit(fn, n=n_it, w=warm):
+        for _ in range(w):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    res = {}
+
+    def hbm(name, nbytes, ms):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        res[name] = {"ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / pk["hbm"]}
+
+    l0 = xl._lib.lib.xlstm_launch_count()
+    rows, F = 32768, 2048
+    for group in (2048, 256):
+        x = torch.randn(rows, F, device="cuda"); gam = torch.ones(F, device="cuda"); y = torch.empty_like(x)
+        inv = torch.empty(rows * F // group, device="cuda"); dy = torch.randn_like(x); dx = torch.empty_like(x); dg = torch.zeros(F, device="cuda")
+        hbm("rmsnorm_fw_%dx%d_g%d" % (rows, F, group), 8 * rows * F, timeit(lambda: ops.rms_norm_forward_into(x, gam, group, y, inv)))
+        hbm("rmsnorm_bw_%dx%d_g%d" % (rows, F, group), 12 * rows * F, timeit(lambda: ops.rms_norm_backward_into(dy, x, inv, gam, group, dx, dg)))
+        del x, y, dy, dx
+    for r_, C in ((8192, 50304), (65536, 256)):
+        z = torch.randn(r_, C, device="cuda"); t = torch.randint(0, C, (r_,), device="cuda", dtype=torch.int32)
+        d = torch.empty_like(z); acc = torch.zeros(1, device="cuda")
+        hbm("ce_fw_bw_%dx%d" % (r_, C), 8 * r_ * C, timeit(lambda: ops.softmax_cross_entropy(z, t, d, acc)))
+        del z, d
+    n = 256 * 1024 * 1024
+    p_ = torch.randn(n, device="cuda"); g_ = torch.randn(n, device="cuda"); m_ = torch.zeros(n, device="cuda"); v_ = torch.zeros(n, device="cuda")
+    pb = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    cfg = ops.AdamCfg(1e-3, 0.1, t=1)
+    hbm("adamw_%d" % n, 28 * n, timeit(lambda: ops.adamw(p_, g_, m_, v_, cfg, True)))
+    hbm("adamw_shadow_zero_%d" % n, 34 * n, timeit(lambda: ops.adamw(p_, g_, m_, v_, cfg, True, p_bf16=pb, zero_grad=True)))
+    del p_, g_, m_, v_, pb
+    B, H, NH, T = 32, 1024, 4, 1024
+    wh = torch.randn(NH, H // NH, 4 * H // NH, device="cuda") / 16; g = torch.randn(B, T, 4 * H, device="cuda"); bc = torch.zeros(4 * H, device="cuda")
+    st = tuple(torch.zeros(B, H, device="cuda") for _ in range(4)); out = torch.empty(B, T, H, device="cuda"); slabs = ops.SlstmSlabs(B, T, H, "cuda")
+    dy = torch.randn(B, T, H, device="cuda"); ds = tuple(torch.zeros(B, H, device="cuda") for _ in range(3))
+    tf = timeit(lambda: ops.slstm_fused_time(wh, g, bc, st, out, slabs, nh=NH), n=10, w=20)
+    tb = timeit(lambda: ops.slstm_fused_time_bwd(wh, dy, g, ds, slabs, nh=NH), n=10, w=20)
+    res["slstm_fw_B32_H1024_NH4_T1024"] = {"ms": tf, "us_per_timestep": tf * 1e3 / T}
+    res["slstm_bw_B32_H1024_NH4_T1024"] = {"ms": tb, "us_per_timestep": tb * 1e3 / T}
+    launches = xl._lib.lib.xlstm_launch_count() - l0
+    worst = min(v["frac_of_hbm_peak"] for k, v in res.items() if "frac_of_hbm_peak" in v and not k.startswith("ce_fw_bw_65536"))
+    print(json.dumps({"metric": "op_microbench_min_hbm_fraction", "value": worst, "unit": "fraction of measured HBM peak", "n_gpus": 1,
+                      "steps": n_it, "warmup": warm, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "rmsnorm / cross-entropy / adamw / slstm kernels alone", "l2": "tensors larger than L2"},
+                      "peak": pk, "kernels": res, "gpu_launches": int(launches)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -407,13 +474,16 @@ def main():
     ap.add_argument("--grad-dtype", default="f32", choices=["f32", "bf16"])
     ap.add_argument("--recompute", action="store_true", help="backward recomputes chunk-boundary states")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--workload", default="mlstm", choices=["mlstm", "lm"], help="mlstm: configs[1] layer kernel (headline); lm: training step")
+    ap.add_argument("--workload", default="mlstm", choices=["mlstm", "lm", "ops"],
+                    help="mlstm: configs[1] layer kernel (headline); lm: training step; ops: the other hot-path kernels alone")
     ap.add_argument("--lm-blocks", type=int, default=0, help="override the LM depth (development)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "lm":
         run_lm(args)
+    elif args.workload == "ops":
+        run_ops(args)
     else:
         run_ours(args)
 

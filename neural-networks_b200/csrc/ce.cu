@@ -32,12 +32,25 @@ __global__ void __launch_bounds__(1024) ce_row_cta(const float* __restrict__ log
         const bool v4 = (C % 4 == 0) && (((uintptr_t)z & 15) == 0) && (((uintptr_t)d & 15) == 0);
         if (v4) {
             const float4* z4 = reinterpret_cast<const float4*>(z);
-            for (int j = threadIdx.x; j < C / 4; j += blockDim.x) {
-                float4 t = __ldcs(z4 + j);
-                if (CACHE) reinterpret_cast<float4*>(srow)[j] = t;
-                float m4 = fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w));
-                if (m4 > mx) { sum *= expf(mx - m4); mx = m4; }
-                sum += expf(t.x - mx) + expf(t.y - mx) + expf(t.z - mx) + expf(t.w - mx);
+            const int n4 = C / 4, stride = blockDim.x;
+            // four independent 16-byte loads in flight per thread before any of them is consumed
+            for (int j0 = threadIdx.x; j0 < n4; j0 += 4 * stride) {
+                float4 t[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int j = j0 + u * stride;
+                    t[u] = (j < n4) ? __ldcs(z4 + j) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int j = j0 + u * stride;
+                    if (j < n4) {
+                        if (CACHE) reinterpret_cast<float4*>(srow)[j] = t[u];
+                        float m4 = fmaxf(fmaxf(t[u].x, t[u].y), fmaxf(t[u].z, t[u].w));
+                        if (m4 > mx) { sum *= __expf(mx - m4); mx = m4; }
+                        sum += __expf(t[u].x - mx) + __expf(t[u].y - mx) + __expf(t[u].z - mx) + __expf(t[u].w - mx);
+                    }
+                }
             }
         } else {
             for (int j = threadIdx.x; j < C; j += blockDim.x) {
@@ -64,8 +77,8 @@ __global__ void __launch_bounds__(1024) ce_row_cta(const float* __restrict__ log
             for (int j = threadIdx.x; j < C / 4; j += blockDim.x) {
                 float4 t = CACHE ? reinterpret_cast<float4*>(srow)[j] : reinterpret_cast<const float4*>(z)[j];
                 float4 o;
-                o.x = expf(t.x - gmx) * is; o.y = expf(t.y - gmx) * is;
-                o.z = expf(t.z - gmx) * is; o.w = expf(t.w - gmx) * is;
+                o.x = __expf(t.x - gmx) * is; o.y = __expf(t.y - gmx) * is;
+                o.z = __expf(t.z - gmx) * is; o.w = __expf(t.w - gmx) * is;
                 uint32_t base = 4u * j;
                 if (tg == base) o.x -= 1.f;
                 else if (tg == base + 1u) o.y -= 1.f;

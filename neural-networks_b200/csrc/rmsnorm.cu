@@ -233,15 +233,15 @@ extern "C" int xlstm_rmsnorm_fw(void* stream, const float* x, const float* gamma
     int maxb = sm_count() * 8;
     if (vec_ok(x, y, x_hat, F, group) && ((uintptr_t)gamma & 15) == 0) {
         int g4 = group / 4;
-        int teams = g4 <= 128 ? kWarpsPerCta : 1;
+        int teams = g4 <= 512 ? kWarpsPerCta : 1;  // forward: a warp keeps up to 2048 floats of a row in registers
         long long nb = (ngroups + teams - 1) / teams;
         int grid = (int)(nb < maxb ? nb : maxb);
 #define RUN(V, TPG) rmsnorm_fw_vec<V, TPG><<<grid, kWarpsPerCta * 32, 0, st>>>(x, gamma, y, inv_rms, x_hat, ngroups, F, group, eps)
         if (g4 <= 32) RUN(1, 32);
         else if (g4 <= 64) RUN(2, 32);
         else if (g4 <= 128) RUN(4, 32);
-        else if (g4 <= 256) RUN(1, 256);
-        else if (g4 <= 512) RUN(2, 256);
+        else if (g4 <= 256) RUN(8, 32);
+        else if (g4 <= 512) RUN(16, 32);
         else RUN(4, 256);
 #undef RUN
         XL_LAUNCH_OK("rmsnorm_fw_vec");
