@@ -83,7 +83,9 @@ extern "C" size_t xlstm_mlstm_fw_workspace_bytes(const xlstm_mlstm_shape* s) {
 }
 extern "C" size_t xlstm_mlstm_bw_workspace_bytes(const xlstm_mlstm_shape* s, int have_saved) {
     if (!s || s->B <= 0 || s->H <= 0 || s->T <= 0 || s->dqk <= 0 || s->dhv <= 0 || s->L <= 0) return 0;
-    return have_saved ? 0 : saved_C_bytes(s) + saved_n_bytes(s);
+    if (have_saved) return 0;
+    if (use_tc(s)) return mlstm_tc_saved_C_bytes(s->B * s->H, num_chunks(s)) + mlstm_tc_saved_n_bytes(s->B * s->H, num_chunks(s));
+    return saved_C_bytes(s) + saved_n_bytes(s);
 }
 
 extern "C" int xlstm_mlstm_fw(void* stream, const xlstm_mlstm_shape* s, const void* q, const void* k, const void* v,
@@ -121,7 +123,23 @@ extern "C" int xlstm_mlstm_bw(void* stream, const xlstm_mlstm_shape* s, const vo
                  "mlstm_bw: carry C, n, m must be given together");
     XL_CHECK_ARG((carry_dC != nullptr) == (carry_dn != nullptr), "mlstm_bw: carry dC, dn must be given together");
     cudaStream_t st = (cudaStream_t)stream;
-    if (saved && use_tc(s)) {
+    if (use_tc(s)) {
+        if (!saved) {
+            // recompute the chunk-boundary states (bf16 record) into the workspace with the forward's state-only pass
+            size_t need = xlstm_mlstm_bw_workspace_bytes(s, 0);
+            if (!workspace || workspace_bytes < need) {
+                set_error("mlstm_bw: workspace of %zu B is smaller than the %zu B needed to recompute chunk states",
+                          workspace_bytes, need);
+                return XLSTM_ERR_WORKSPACE;
+            }
+            MlstmFwArgs f = {};
+            f.q = q; f.k = k; f.v = v; f.ig = ig; f.fg = fg; f.cC = carry_C; f.cn = carry_n; f.cm = carry_m;
+            f.B = s->B; f.H = s->H; f.T = s->T; f.dqk = s->dqk; f.dhv = s->dhv; f.L = eff_L(s); f.NC = num_chunks(s);
+            f.states_only = 1;
+            rc = mlstm_fw_tc_launch(st, f, workspace);
+            if (rc) return rc;
+            saved = workspace;
+        }
         MlstmBwArgs a = {};
         a.q = q; a.k = k; a.v = v; a.ig = ig; a.fg = fg; a.cm = carry_m; a.ytil = ytil; a.msv = msv; a.psiv = psiv;
         a.qnv = qnv; a.dytil = d_ytil; a.cdC = carry_dC; a.cdn = carry_dn;

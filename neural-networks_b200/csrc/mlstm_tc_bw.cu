@@ -768,11 +768,18 @@ int mlstm_bw_tc_launch(cudaStream_t st, const MlstmBwArgs& a, const void* saved,
     p.status = tc_status_ptr();
     if (!p.status) { set_error("mlstm_bw: cannot resolve the device status word"); return XLSTM_ERR_CUDA; }
     size_t smem = Smem::total + 1024;
+    static bool attr_set[2] = {false, false};
     if (gdtype == XLSTM_BF16) {
-        XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (!attr_set[1]) {
+            XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set[1] = true;
+        }
         mlstm_bw_tc<bf16><<<BH, kThreads, smem, st>>>(p);
     } else {
-        XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (!attr_set[0]) {
+            XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set[0] = true;
+        }
         mlstm_bw_tc<float><<<BH, kThreads, smem, st>>>(p);
     }
     XL_LAUNCH_OK("mlstm_bw_tc");

@@ -145,3 +145,12 @@ def test_tensor_core_path_bit_repeatable():
     b, _ = _run((2, 2, 200, 128, 128), 64, torch.bfloat16, torch.float32, seed=23)
     for n in FW + BW:
         assert np.array_equal(a[n], b[n]), n
+
+
+def test_tensor_core_backward_recomputes_chunk_states_when_no_record_is_kept():
+    """saved = NULL: the backward rebuilds the chunk-boundary states with the forward's state-only pass;
+    the gradients are bit-identical to the saved-record path."""
+    a, _ = _run((2, 2, 200, 128, 128), 64, torch.bfloat16, torch.float32, seed=24, save_states=True)
+    b, _ = _run((2, 2, 200, 128, 128), 64, torch.bfloat16, torch.float32, seed=24, save_states=False)
+    for n in BW:
+        assert np.array_equal(a[n], b[n]), n
