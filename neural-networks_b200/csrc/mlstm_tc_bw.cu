@@ -14,6 +14,7 @@
 // (src/gpu/cuda/mlstm_fused.cu:830-858 with the stabiliser held constant; the gate-gradient
 // identity replaces the reference's row/column sums and is checked against the CPU oracle.)
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "mlstm.cuh"
@@ -63,6 +64,7 @@ struct Params {
     float *odC, *odn;
     int B, H, T, NC;
     int gbf16;
+    int ablate;       // development aid: bit mask of work to skip (results are then wrong)
     int* status;      // device status word (first bounded wait that ran out)
     long long* prof;  // optional per-phase cycle counts of CTA 0 (development aid; null in production)
 };
@@ -78,7 +80,8 @@ struct Smem {
     static constexpr uint32_t ds_ = dcb + 2 * kStateBox;   // DS  [64 x 64]
     static constexpr uint32_t dS = ds_ + kBoxBytes;        // dS  [64 x 64]
     static constexpr uint32_t gates = dS + kBoxBytes;      // 2 x Gates
-    static constexpr uint32_t vec = gates + 2 * sizeof(Gates);  // 2 x [psi 64 | qn 64 | n entering the chunk 128]
+    static constexpr uint32_t graw = gates + 2 * sizeof(Gates);   // 2 x GateRawS
+    static constexpr uint32_t vec = graw + 2 * 784;  // 2 x [psi 64 | qn 64 | n entering the chunk 128]
     static constexpr uint32_t dnv = vec + 2 * (2 * L + D) * 4;            // dn, double buffered [2][128]
     static constexpr uint32_t dnp = dnv + 2 * D * 4;       // dn partial sums [4][128]
     static constexpr uint32_t part = dnp + 4 * D * 4;      // partial sums [12][64]: dot(4), u(4), w(4)
@@ -150,31 +153,51 @@ __device__ __forceinline__ float dot_row16(const unsigned char* tile, uint32_t r
     return acc;
 }
 
-// Control warp: gate vectors of a chunk, two positions per lane. The global reads (gates_load) are
-// issued one chunk before the arithmetic (gates_compute) so their latency stays off the critical path.
-struct GateRaw {
-    float fr[2], iv[2], mt[2], m_prev;
+// 4-byte asynchronous global -> shared copy (no register staging, no stall at issue).
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// Raw gate inputs of one chunk as the control warp stages them in shared memory.
+struct GateRawS {
+    float fr[L], iv[L], mt[L];
+    float m_prev;
+    float pad[3];
 };
-__device__ __forceinline__ void gates_load(const Params& p, int b, int h, int bh, int ch, GateRaw& r) {
+// Control warp: start the asynchronous copy of a chunk's raw gate inputs (two positions per lane).
+__device__ __forceinline__ void gates_fetch(const Params& p, int b, int h, int bh, int ch, GateRawS* r) {
     const int lane = threadIdx.x & 31;
     const int t0 = ch * L, Lc = min(L, p.T - t0);
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
         int t = lane + 32 * e;
-        r.fr[e] = INFINITY;   // log_sigmoid(+inf) = 0: positions past a ragged end leave fc unchanged
-        r.iv[e] = -INFINITY;
         if (t < Lc) {
             size_t gi = ((size_t)b * p.T + t0 + t) * p.H + h;
-            r.fr[e] = p.fg[gi];
-            r.iv[e] = p.ig[gi];
+            cp_async4(&r->fr[t], p.fg + gi);
+            cp_async4(&r->iv[t], p.ig + gi);
+        } else {
+            r->fr[t] = INFINITY;   // log_sigmoid(+inf) = 0: positions past a ragged end leave fc unchanged
+            r->iv[t] = -INFINITY;
         }
-        r.mt[e] = p.msv[(size_t)bh * p.T + t0 + min(t, Lc - 1)];
+        cp_async4(&r->mt[t], p.msv + (size_t)bh * p.T + t0 + min(t, Lc - 1));
     }
-    r.m_prev = (ch == 0) ? (p.cm ? p.cm[bh] : 0.f) : p.msv[(size_t)bh * p.T + t0 - 1];
+    if (lane == 0) {
+        if (ch == 0) {
+            if (p.cm) cp_async4(&r->m_prev, p.cm + bh); else r->m_prev = 0.f;
+        } else {
+            cp_async4(&r->m_prev, p.msv + (size_t)bh * p.T + t0 - 1);
+        }
+    }
 }
-__device__ __forceinline__ void gates_compute(const GateRaw& r, Gates* G) {
+// Control warp: gate vectors of a chunk from its staged raw inputs.
+__device__ __forceinline__ void gates_compute(const GateRawS* r, Gates* G) {
     const int lane = threadIdx.x & 31;
-    float fc0 = log_sigmoid(r.fr[0]), fc1 = log_sigmoid(r.fr[1]);
+    const float fr[2] = {r->fr[lane], r->fr[lane + 32]}, iv[2] = {r->iv[lane], r->iv[lane + 32]};
+    const float mt[2] = {r->mt[lane], r->mt[lane + 32]};
+    const float m_prev = r->m_prev;
+    float fc0 = log_sigmoid(fr[0]), fc1 = log_sigmoid(fr[1]);
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         float y0 = __shfl_up_sync(0xffffffffu, fc0, o), y1 = __shfl_up_sync(0xffffffffu, fc1, o);
@@ -182,47 +205,33 @@ __device__ __forceinline__ void gates_compute(const GateRaw& r, Gates* G) {
     }
     fc1 += __shfl_sync(0xffffffffu, fc0, 31);
     const float fcL = __shfl_sync(0xffffffffu, fc1, 31);
-    const float mL = __shfl_sync(0xffffffffu, r.mt[1], 31);
+    const float mL = __shfl_sync(0xffffffffu, mt[1], 31);
     float fc[2] = {fc0, fc1};
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
         int t = lane + 32 * e;
-        G->rowt[t] = fc[e] - r.mt[e];
-        G->colt[t] = r.iv[e] - fc[e];
-        G->b[t] = expf(fc[e] + r.m_prev - r.mt[e]);
-        G->a[t] = expf(fcL - fc[e] + r.iv[e] - mL);
-        G->fg[t] = r.fr[e];
-        G->emm[t] = expf(-r.mt[e]);
+        G->rowt[t] = fc[e] - mt[e];
+        G->colt[t] = iv[e] - fc[e];
+        G->b[t] = expf(fc[e] + m_prev - mt[e]);
+        G->a[t] = expf(fcL - fc[e] + iv[e] - mL);
+        G->fg[t] = fr[e];
+        G->emm[t] = expf(-mt[e]);
     }
-    if (lane == 0) G->g = expf(fcL + r.m_prev - mL);
+    if (lane == 0) G->g = expf(fcL + m_prev - mL);
 }
-
-// Control warp: the per-chunk vectors psi, qn (64 each) and the entering normaliser n (128), read one
-// chunk ahead into registers and parked in a double-buffered shared array.
-struct VecRaw {
-    float v[8];
-};
-__device__ __forceinline__ void vec_load(const Params& p, int bh, int ch, VecRaw& r) {
+// Control warp: start the asynchronous copy of a chunk's psi, qn (64 each) and entering normaliser n (128)
+// straight into their shared-memory slot [psi 64 | qn 64 | n 128].
+__device__ __forceinline__ void vec_fetch(const Params& p, int bh, int ch, float* dst) {
     const int lane = threadIdx.x & 31;
     const int t0 = ch * L, Lc = min(L, p.T - t0);
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
         const size_t o = (size_t)bh * p.T + t0 + min(lane + 32 * e, Lc - 1);
-        r.v[e] = p.psiv[o];
-        r.v[2 + e] = p.qnv[o];
+        cp_async4(dst + lane + 32 * e, p.psiv + o);
+        cp_async4(dst + L + lane + 32 * e, p.qnv + o);
     }
 #pragma unroll
-    for (int e = 0; e < 4; ++e) r.v[4 + e] = p.savedn[((size_t)bh * (p.NC + 1) + ch) * D + lane + 32 * e];
-}
-__device__ __forceinline__ void vec_store(const VecRaw& r, float* dst /* [psi 64 | qn 64 | n 128] */) {
-    const int lane = threadIdx.x & 31;
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-        dst[lane + 32 * e] = r.v[e];
-        dst[L + lane + 32 * e] = r.v[2 + e];
-    }
-#pragma unroll
-    for (int e = 0; e < 4; ++e) dst[2 * L + lane + 32 * e] = r.v[4 + e];
+    for (int e = 0; e < 4; ++e) cp_async4(dst + 2 * L + lane + 32 * e, p.savedn + ((size_t)bh * (p.NC + 1) + ch) * D + lane + 32 * e);
 }
 
 // Sum 16 per-lane values across the 32 lanes of a warp with a reduce-scatter butterfly (16
@@ -275,6 +284,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     const int prow = 4 * warp + (lane >> 3), l8 = lane & 7;
 
     Gates* G = (Gates*)(sm + Smem::gates);
+    GateRawS* GR = (GateRawS*)(sm + Smem::graw);
+    static_assert(sizeof(GateRawS) == 784, "GateRawS layout");
     float* svec = (float*)(sm + Smem::vec);
     float* sdn = (float*)(sm + Smem::dnv);
     float* sdnp = (float*)(sm + Smem::dnp);
@@ -326,37 +337,46 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
 
     // Operands of the dN pass, prefetched one chunk ahead into registers. Piece i of a thread covers
     // columns 4*(l8 + 8i) .. +3 of its position, so eight lanes read one contiguous run per instruction.
-    uint32_t dyraw[sizeof(GT) == 4 ? 16 : 8], yraw[8];
+    // The dN pass reads dy and ytil straight from global memory; one chunk ahead its lines are pulled into
+    // L2 (no registers held across phases). Piece i of a thread covers columns 4*(l8 + 8i) .. +3 of its
+    // position, so eight lanes read one contiguous run per instruction.
     auto prefetch_dy = [&](int ch) {
         const int t0 = ch * L, Lc = min(L, p.T - t0);
-        if (prow < Lc) {
+        if (prow < Lc && l8 < 4) {
             const size_t o = (((size_t)b * p.T + t0 + prow) * p.H + h) * D;
+            const char* pdy = reinterpret_cast<const char*>(p.dy) + o * sizeof(GT) + l8 * 128;
+            if (l8 * 128 < (int)(D * sizeof(GT))) asm volatile("prefetch.global.L2 [%0];" ::"l"(pdy));
+            if (l8 < 2) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.ytil + o) + l8 * 128));
+        }
+    };
+    auto load_dy = [&](int ch, uint32_t* dyraw, uint32_t* yraw) {
+        const int t0 = ch * L;
+        const size_t o = (((size_t)b * p.T + t0 + prow) * p.H + h) * D;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int c = 4 * (l8 + 8 * i);
-                if (sizeof(GT) == 4) {
-                    uint4 t = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p.dy) + o + c));
-                    dyraw[4 * i] = t.x; dyraw[4 * i + 1] = t.y; dyraw[4 * i + 2] = t.z; dyraw[4 * i + 3] = t.w;
-                } else {
-                    uint2 t = __ldcs(reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(p.dy) + o + c));
-                    dyraw[2 * i] = t.x; dyraw[2 * i + 1] = t.y;
-                }
-                uint2 ty = __ldcs(reinterpret_cast<const uint2*>(p.ytil + o + c));
-                yraw[2 * i] = ty.x; yraw[2 * i + 1] = ty.y;
+        for (int i = 0; i < 4; ++i) {
+            const int c = 4 * (l8 + 8 * i);
+            if (sizeof(GT) == 4) {
+                uint4 t = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(p.dy) + o + c));
+                dyraw[4 * i] = t.x; dyraw[4 * i + 1] = t.y; dyraw[4 * i + 2] = t.z; dyraw[4 * i + 3] = t.w;
+            } else {
+                uint2 t = __ldcs(reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(p.dy) + o + c));
+                dyraw[2 * i] = t.x; dyraw[2 * i + 1] = t.y;
             }
+            uint2 ty = __ldcs(reinterpret_cast<const uint2*>(p.ytil + o + c));
+            yraw[2 * i] = ty.x; yraw[2 * i + 1] = ty.y;
         }
     };
 
-    GateRaw graw;
-    VecRaw vraw;
     // ---- prologue -------------------------------------------------------------------------------
     if (is_ctrl) {
         if (lane == 0) { issue_qk(p.NC - 1, 0); issue_v_ck(p.NC - 1); }
-        gates_load(p, b, h, bh, p.NC - 1, graw);
-        vec_load(p, bh, p.NC - 1, vraw);
-        gates_compute(graw, &G[(p.NC - 1) & 1]);
-        vec_store(vraw, svec + ((p.NC - 1) & 1) * (2 * L + D));
-        if (p.NC > 1) gates_load(p, b, h, bh, p.NC - 2, graw);
+        gates_fetch(p, b, h, bh, p.NC - 1, &GR[(p.NC - 1) & 1]);
+        vec_fetch(p, bh, p.NC - 1, svec + ((p.NC - 1) & 1) * (2 * L + D));
+        cp_async_commit();
+        cp_async_wait_all();
+        __syncwarp();
+        gates_compute(&GR[(p.NC - 1) & 1], &G[(p.NC - 1) & 1]);
+        if (p.NC > 1) { gates_fetch(p, b, h, bh, p.NC - 2, &GR[(p.NC - 2) & 1]); cp_async_commit(); }
     } else {
         prefetch_dy(p.NC - 1);
         // carry term of the forget-gate gradient: <dC_in, C_end> + dn_in . n_end
@@ -429,11 +449,14 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
 
         PROF(0)
         // =============== phase 1: dN, dNb tiles and the dy.ytil row dots (math) =======================
-        if (!is_ctrl) {
+        if (!is_ctrl && (p.ablate & 8)) {
+        } else if (!is_ctrl) {
             const float bt = Gc->b[prow];
             const float psi_r = spsi[prow];
             float dot = 0.f;
             float dyv[16];
+            uint32_t dyraw[sizeof(GT) == 4 ? 16 : 8], yraw[8];
+            if (prow < Lc) load_dy(ch, dyraw, yraw);
             if (prow < Lc) {
                 const float ipsi = 1.f / psi_r;
 #pragma unroll
@@ -482,6 +505,21 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             if (lane == 0 && ch > 0) issue_qk(ch - 1, stg ^ 1);
             bool w = mbar_wait(&bars[stg], (it >> 1) & 1) && mbar_wait(&bars[2], it & 1) && mbar_wait(&bars[3], it & 1);
             if (!w) *abort_flag = 1;
+            // the two products that need only the tiles and dC+ start now, under the dN pass
+            if (w && lane == 0 && !(p.ablate & 4)) {
+                tc_fence_after();
+                const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), adC = smem_u32(sdCb);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t ko = (ks >> 2) * kBoxBytes + (ks & 3) * 32;  // K-major step in a [64-row] tile
+                    const uint32_t kc = (ks >> 2) * kStateBox + (ks & 3) * 32;  // K-major step in a [128-row] tile
+                    // dVe^T[v,j] = sum_c dC+[v,c] K[j,c]
+                    mma_ss(tVe, desc_at(dK_, adC + kc), desc_at(dK_, aK + ko), id_kk, ks > 0);
+                    // dKe^T[c,j] = sum_v dC+[v,c] V[j,v] : A = dCb^T (MN-major over c, K = v rows), B = V K-major
+                    mma_ss(tKe, desc_at(dM2, adC + ks * 2048), desc_at(dK_, aV + ko), id_mk, ks > 0);
+                }
+            }
+            __syncwarp();
         }
         PROF(1)
         __syncthreads();  // #1
@@ -490,13 +528,14 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
 
         // =============== phase 2: group A MMAs (control) | S/dds epilogue (math) ======================
         if (is_ctrl) {
-            if (lane == 0) {
+            if (lane == 0 && (p.ablate & 4)) { mma_commit(&bars[6]); mma_commit(&bars[4]); }
+            if (lane == 0 && !(p.ablate & 4)) {
                 tc_fence_after();
                 const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aCk = smem_u32(sCk),
-                               adN = smem_u32(sdN), adNb = smem_u32(sdNb), adC = smem_u32(sdCb);
+                               adN = smem_u32(sdN), adNb = smem_u32(sdNb);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t ko = (ks >> 2) * kBoxBytes + (ks & 3) * 32;  // K-major step in a [64-row] tile
+                    const uint32_t ko = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
                     mma_ss(tS, desc_at(dK_, aQ + ko), desc_at(dK_, aK + ko), id64_kk, ks > 0);      // S = Q K^T
                     mma_ss(tDds, desc_at(dK_, adN + ko), desc_at(dK_, aV + ko), id64_kk, ks > 0);   // dds = dN V^T
                 }
@@ -504,23 +543,17 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint32_t ko = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
-                    const uint32_t kc = (ks >> 2) * kStateBox + (ks & 3) * 32;  // K-major step in a [128-row] tile
-                    // dVe^T[v,j] = sum_c dC+[v,c] K[j,c]
-                    mma_ss(tVe, desc_at(dK_, adC + kc), desc_at(dK_, aK + ko), id_kk, ks > 0);
-                    // dKe^T[c,j] = sum_v dC+[v,c] V[j,v] : A = dCb^T (MN-major over c, K = v rows), B = V K-major
-                    mma_ss(tKe, desc_at(dM2, adC + ks * 2048), desc_at(dK_, aV + ko), id_mk, ks > 0);
                     // dQ^T[c,t] = sum_v C_k[v,c] dNb[t,v] : A = Ck^T (MN-major), B = dNb K-major
                     mma_ss(tQ, desc_at(dM2, aCk + ks * 2048), desc_at(dK_, adNb + ko), id_mk, ks > 0);
                 }
+                // dC += dNb^T Q : M = v, N = c, K = t (needs neither DS nor dS, so it does not wait for them)
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    mma_ss(tC, desc_at(dM1, adNb + ks * 2048), desc_at(dM1, aQ + ks * 2048), id_mm128, 1);
                 mma_commit(&bars[4]);
             }
             __syncwarp();
             PROF(3)
-            if (ch > 0) {
-                gates_compute(graw, &G[(ch - 1) & 1]);
-                vec_load(p, bh, ch - 1, vraw);
-                if (ch > 1) gates_load(p, b, h, bh, ch - 2, graw);
-            }
             PROF(4)
             if (!mbar_wait(&bars[4], it & 1)) *abort_flag = 2;
             // V and C_k are read by group A only: refill them for the next chunk as soon as it is done
@@ -536,7 +569,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             tmem_ld16(tS + lane_base + 16 * cq, s);
             tmem_ld16(tDds + lane_base + 16 * cq, dd);
             tmem_ld_wait();
-            if (lane < 16) {
+            if (lane < 16 && !(p.ablate & 16)) {
                 const float rt = Gc->rowt[srow], dq_t = sdqn[srow];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -558,10 +591,10 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
 
         // =============== phase 3: group B MMAs (control) | feature-major epilogues (math) ==============
         if (is_ctrl) {
-            if (lane == 0) {
+            if (lane == 0 && (p.ablate & 4)) mma_commit(&bars[5]);
+            if (lane == 0 && !(p.ablate & 4)) {
                 tc_fence_after();
-                const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), adN = smem_u32(sdN), adNb = smem_u32(sdNb),
-                               aDS = smem_u32(sDS), adS = smem_u32(sdS);
+                const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), adN = smem_u32(sdN), aDS = smem_u32(sDS), adS = smem_u32(sdS);
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
                     // dVi^T[v,j] = sum_t dN[t,v] DS[t,j] : both MN-major, K = t rows
@@ -571,18 +604,23 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
                     // dKi^T[c,j] = sum_t Q[t,c] dS[t,j] : both MN-major, K = t rows
                     mma_ss(tKi, desc_at(dM1, aQ + ks * 2048), desc_at(dM1, adS + ks * 2048), id_mm, ks > 0);
                 }
-                // dC += dNb^T Q : M = v, N = c, K = t
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    mma_ss(tC, desc_at(dM1, adNb + ks * 2048), desc_at(dM1, aQ + ks * 2048), id_mm128, 1);
                 mma_commit(&bars[5]);
             }
             __syncwarp();
+            if (ch > 0) {
+                cp_async_wait_all();  // raw gates of chunk ch-1, fetched during the previous chunk
+                __syncwarp();
+                gates_compute(&GR[(ch - 1) & 1], &G[(ch - 1) & 1]);
+                vec_fetch(p, bh, ch - 1, svec + ((ch - 1) & 1) * (2 * L + D));
+                if (ch > 1) gates_fetch(p, b, h, bh, ch - 2, &GR[ch & 1]);
+                cp_async_commit();
+            }
         } else {
             // this thread's feature x, positions 16*cq .. +15
             const uint32_t xoff = (uint32_t)(x >> 6) * kBoxBytes + (x & 7) * 2;
             const uint32_t xch8 = (x & 63) >> 3;
             auto tile_at = [&](const unsigned char* tile, int pos) {
+                if (p.ablate & 128) return 1.f;
                 return __bfloat162float(*reinterpret_cast<const bf16*>(tile + xoff + swz(pos, xch8)));
             };
             const float n_x = nk[x], dn_x = dn_in[x];
@@ -599,53 +637,61 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             if (!mbar_wait(&bars[5], it & 1)) *abort_flag = 3;
             tc_fence_after();
             PROF(8)
+            if (!(p.ablate & 2)) {
             const size_t obase = (((size_t)b * p.T + t0 + 16 * cq) * p.H + h) * D + x;
             const size_t ostride = (size_t)p.H * D;
             const int nlive = min(16, Lc - 16 * cq);  // positions of this quarter inside the sequence
             float a1[16], a2[16];
             // dV = dVi + a dVe
+            if (!(p.ablate & 256)) {
             tmem_ld16(tVi + lane_base + 16 * cq, a1);
             tmem_ld16(tVe + lane_base + 16 * cq, a2);
             tmem_ld_wait();
+            }
             {
                 GT* o = reinterpret_cast<GT*>(p.dv) + obase;
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
-                    if (i < nlive) stf(o, (size_t)i * ostride, a1[i] + Gc->a[16 * cq + i] * a2[i]);
+                    if (i < nlive && !(p.ablate & 1)) stf(o, (size_t)i * ostride, a1[i] + Gc->a[16 * cq + i] * a2[i]);
             }
             // dQ = acc + b dqn n ;  u = dQ . q
+            if (!(p.ablate & 256)) {
             tmem_ld16(tQ + lane_base + 16 * cq, a1);
             tmem_ld_wait();
+            }
             {
                 GT* o = reinterpret_cast<GT*>(p.dq) + obase;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int pos = 16 * cq + i;
                     const float v = a1[i] + Gc->b[pos] * sdqn[pos] * n_x;
-                    if (i < nlive) stf(o, (size_t)i * ostride, v);
+                    if (i < nlive && !(p.ablate & 1)) stf(o, (size_t)i * ostride, v);
                     a1[i] = v * tile_at(sQ, pos);
                 }
             }
-            const float usum = butterfly16(a1, lane);
+            const float usum = (p.ablate & 64) ? a1[0] : butterfly16(a1, lane);
             // dK = dKi + a (dKe + dn+) ;  w = dK . k
+            if (!(p.ablate & 256)) {
             tmem_ld16(tKi + lane_base + 16 * cq, a1);
             tmem_ld16(tKe + lane_base + 16 * cq, a2);
             tmem_ld_wait();
+            }
             {
                 GT* o = reinterpret_cast<GT*>(p.dk) + obase;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int pos = 16 * cq + i;
                     const float v = a1[i] + Gc->a[pos] * (a2[i] + dn_x);
-                    if (i < nlive) stf(o, (size_t)i * ostride, v);
+                    if (i < nlive && !(p.ablate & 1)) stf(o, (size_t)i * ostride, v);
                     a1[i] = v * tile_at(sK, pos);
                 }
             }
-            const float wsum = butterfly16(a1, lane);
+            const float wsum = (p.ablate & 64) ? a1[0] : butterfly16(a1, lane);
             if ((lane & 1) == 0) {
                 const int pos = 16 * cq + butterfly_index(lane);
                 part[(4 + qd) * L + pos] = usum;
                 part[(8 + qd) * L + pos] = wsum;
+            }
             }
         }
         PROF(9)
@@ -686,12 +732,13 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             }
             __syncwarp();
             if (lane == 0) *srun = run + tot;
-            if (ch > 0) vec_store(vraw, svec + ((ch - 1) & 1) * (2 * L + D));
+            cp_async_wait_all();  // psi, qn, n of the next chunk are in their slot before the block barrier
         } else {
             if (tid < D) dn_out[tid] = Gc->g * dn_in[tid] + (sdnp[tid] + sdnp[D + tid]) + (sdnp[2 * D + tid] + sdnp[3 * D + tid]);
             const int c0 = 32 * cq;
             const float gn = (ch > 0) ? G[(ch - 1) & 1].g : 1.f;
             float v[32];
+            if (!(p.ablate & 32)) {
             tmem_ld32(tC + lane_base + c0, v);
             tmem_ld_wait();
             put_row<4>(sdCb + (cq >> 1) * kStateBox, x, 4 * (cq & 1), v);
@@ -706,6 +753,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
                 for (int i = 0; i < 32; ++i) v[i] *= gn;
                 tmem_st32(tC + lane_base + c0, v);
                 tmem_st_wait();
+            }
             }
             fence_async_smem();
             tc_fence_before();
@@ -765,6 +813,10 @@ int mlstm_bw_tc_launch(cudaStream_t st, const MlstmBwArgs& a, const void* saved,
     p.dy = a.dytil; p.cdC = a.cdC; p.cdn = a.cdn; p.dq = a.dq; p.dk = a.dk; p.dv = a.dv; p.dig = a.dig; p.dfg = a.dfg;
     p.odC = a.odC; p.odn = a.odn; p.B = a.B; p.H = a.H; p.T = a.T; p.NC = a.NC; p.gbf16 = gdtype == XLSTM_BF16;
     p.prof = tc_debug_prof();
+    {
+        static const char* ab = getenv("XLSTM_ABLATE");
+        p.ablate = ab ? atoi(ab) : 0;
+    }
     p.status = tc_status_ptr();
     if (!p.status) { set_error("mlstm_bw: cannot resolve the device status word"); return XLSTM_ERR_CUDA; }
     size_t smem = Smem::total + 1024;
