@@ -291,6 +291,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     float* sdnp = (float*)(sm + Smem::dnp);
     float* part = (float*)(sm + Smem::part);
     float* sdqn = (float*)(sm + Smem::dqn);
+    float* sbq = part;  // [64] b_t dqn_t (row 0 of `part`)
     uint64_t* bars = (uint64_t*)(sm + Smem::misc);  // [0],[1] Q/K stages, [2] V, [3] Ck, [4] group A, [5] group B, [6] S and dds only
     uint32_t* tmem_slot = (uint32_t*)(sm + Smem::misc + 64);
     int* abort_flag = (int*)(sm + Smem::misc + 72);
@@ -493,12 +494,17 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             dot += __shfl_xor_sync(0xffffffffu, dot, 4);
             if (l8 == 0) {
                 // dqn_t = sign(qn)(-dot/psi) where the q.n term, not the floor, set psi
-                float r = 0.f;
+                float r = 0.f, u = 0.f;
                 if (prow < Lc) {
                     const float qn = sqn[prow];
                     if (fabsf(qn) > Gc->emm[prow]) r = (qn > 0.f ? -1.f : 1.f) * dot / psi_r;
+                    // dq_t . q_t: scaling q_t scales the numerator and q.n alike, so the row dot is
+                    // dy_t . ytil_t + dqn_t (q_t . n_t) without touching dq
+                    u = dot + r * qn;
                 }
                 sdqn[prow] = r;
+                sbq[prow] = bt * r;
+                part[4 * L + prow] = u;
             }
             fence_async_smem();
         } else {
@@ -624,13 +630,18 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
                 return __bfloat162float(*reinterpret_cast<const bf16*>(tile + xoff + swz(pos, xch8)));
             };
             const float n_x = nk[x], dn_x = dn_in[x];
-            {
-                float acc = 0.f;
+            auto load16 = [&](const float* src, float* dst) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int pos = 16 * cq + i;
-                    acc += Gc->b[pos] * sdqn[pos] * tile_at(sQ, pos);
+                for (int i = 0; i < 4; ++i) {
+                    const float4 t4 = *reinterpret_cast<const float4*>(src + 16 * cq + 4 * i);
+                    dst[4 * i] = t4.x; dst[4 * i + 1] = t4.y; dst[4 * i + 2] = t4.z; dst[4 * i + 3] = t4.w;
                 }
+            };
+            {
+                float acc = 0.f, bq[16];
+                load16(sbq, bq);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc += bq[i] * tile_at(sQ, 16 * cq + i);
                 sdnp[cq * D + x] = acc;  // dn partial over this quarter of the positions
             }
             PROF(7)
@@ -641,47 +652,45 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             const size_t obase = (((size_t)b * p.T + t0 + 16 * cq) * p.H + h) * D + x;
             const size_t ostride = (size_t)p.H * D;
             const int nlive = min(16, Lc - 16 * cq);  // positions of this quarter inside the sequence
-            float a1[16], a2[16];
+            float a1[16], a2[16], cf[16];
             // dV = dVi + a dVe
             if (!(p.ablate & 256)) {
             tmem_ld16(tVi + lane_base + 16 * cq, a1);
             tmem_ld16(tVe + lane_base + 16 * cq, a2);
             tmem_ld_wait();
             }
+            load16(Gc->a, cf);
             {
                 GT* o = reinterpret_cast<GT*>(p.dv) + obase;
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
-                    if (i < nlive && !(p.ablate & 1)) stf(o, (size_t)i * ostride, a1[i] + Gc->a[16 * cq + i] * a2[i]);
+                    if (i < nlive && !(p.ablate & 1)) stf(o, (size_t)i * ostride, a1[i] + cf[i] * a2[i]);
             }
-            // dQ = acc + b dqn n ;  u = dQ . q
+            // dQ = acc + b dqn n
             if (!(p.ablate & 256)) {
             tmem_ld16(tQ + lane_base + 16 * cq, a1);
             tmem_ld_wait();
             }
+            load16(sbq, cf);
             {
                 GT* o = reinterpret_cast<GT*>(p.dq) + obase;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int pos = 16 * cq + i;
-                    const float v = a1[i] + Gc->b[pos] * sdqn[pos] * n_x;
-                    if (i < nlive && !(p.ablate & 1)) stf(o, (size_t)i * ostride, v);
-                    a1[i] = v * tile_at(sQ, pos);
-                }
+                for (int i = 0; i < 16; ++i)
+                    if (i < nlive && !(p.ablate & 1)) stf(o, (size_t)i * ostride, a1[i] + cf[i] * n_x);
             }
-            const float usum = (p.ablate & 64) ? a1[0] : butterfly16(a1, lane);
             // dK = dKi + a (dKe + dn+) ;  w = dK . k
             if (!(p.ablate & 256)) {
             tmem_ld16(tKi + lane_base + 16 * cq, a1);
             tmem_ld16(tKe + lane_base + 16 * cq, a2);
             tmem_ld_wait();
             }
+            load16(Gc->a, cf);
             {
                 GT* o = reinterpret_cast<GT*>(p.dk) + obase;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int pos = 16 * cq + i;
-                    const float v = a1[i] + Gc->a[pos] * (a2[i] + dn_x);
+                    const float v = a1[i] + cf[i] * (a2[i] + dn_x);
                     if (i < nlive && !(p.ablate & 1)) stf(o, (size_t)i * ostride, v);
                     a1[i] = v * tile_at(sK, pos);
                 }
@@ -689,7 +698,6 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             const float wsum = (p.ablate & 64) ? a1[0] : butterfly16(a1, lane);
             if ((lane & 1) == 0) {
                 const int pos = 16 * cq + butterfly_index(lane);
-                part[(4 + qd) * L + pos] = usum;
                 part[(8 + qd) * L + pos] = wsum;
             }
             }
@@ -705,7 +713,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 int t = lane + 32 * e;
-                float u = part[4 * L + t] + part[5 * L + t] + part[6 * L + t] + part[7 * L + t];
+                float u = part[4 * L + t];
                 wv[e] = part[8 * L + t] + part[9 * L + t] + part[10 * L + t] + part[11 * L + t];
                 dF[e] = (t < Lc) ? (u - wv[e]) : 0.f;
             }
