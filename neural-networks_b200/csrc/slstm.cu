@@ -19,6 +19,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "slstm_cell.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -261,27 +262,19 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
                 const float o_pre = gin[3] + gh[3] + bs[3];
                 const size_t s = ((size_t)(b0 + b) * T + t) * H + j;
                 const float cp = st[it], np = st[NI + it], mp = st[2 * NI + it];
-                // exp/log through the hardware approximations (relative error ~1e-6, inside the 1e-4 budget)
-                const float z = 1.f - __fdividef(2.f, 1.f + __expf(2.f * z_pre));
-                const float o = __fdividef(1.f, 1.f + __expf(-o_pre));
-                const float fm = fminf(f_pre, 0.f) - __logf(1.f + __expf(-fabsf(f_pre))) + mp;
-                const float m = (np == 0.f) ? i_pre : fmaxf(fm, i_pre);
-                const float ip = fminf(1.f, __expf(i_pre - m));
-                const float fp = fminf(1.f, __expf(fm - m));
-                const float c = fp * cp + ip * z;
-                const float n = fp * np + ip;
-                hh = __fdividef(o * c, n);
-                st[it] = c; st[NI + it] = n; st[2 * NI + it] = m;
+                const SlstmFwCell r = slstm_cell_fw(z_pre, i_pre, f_pre, o_pre, cp, np, mp);
+                hh = r.h;
+                st[it] = r.c; st[NI + it] = r.n; st[2 * NI + it] = r.m;
                 __stcs(gt + (size_t)2 * H, f_pre);
                 __stcs(a.s.h_prev + s, hp);
                 __stcs(a.s.c_prev + s, cp);
                 __stcs(a.s.n_prev + s, np);
-                __stcs(a.s.zt + s, z);
-                __stcs(a.s.ot + s, o);
-                __stcs(a.s.ipr + s, ip);
-                __stcs(a.s.fpr + s, fp);
-                __stcs(a.s.c + s, c);
-                __stcs(a.s.n + s, n);
+                __stcs(a.s.zt + s, r.z);
+                __stcs(a.s.ot + s, r.o);
+                __stcs(a.s.ipr + s, r.ip);
+                __stcs(a.s.fpr + s, r.fp);
+                __stcs(a.s.c + s, r.c);
+                __stcs(a.s.n + s, r.n);
                 __stcs(a.out + s, hh);
             }
             stage[(size_t)b * UPC + ul] = hh;
@@ -409,18 +402,11 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmS
                 float* gt = a.g + ((size_t)(b0 + b) * T + t) * 4 * H + j;
                 float dhr = 0.f;
                 for (int ks = 0; ks < a.KS; ++ks) dhr += part[((size_t)ks * BG + b) * NOUTp + ul];
-                const float d_h = op[0] + dhr;
-                const float o = op[1], c = op[2], n = op[3], f = op[4], i = op[5], z = op[6];
-                dob = d_h * (c / n) * o * (1.f - o);
-                const float d_c = d_h * o / n + st[it];
-                const float d_n = d_h * o * (-c) / (n * n) + st[NI + it];
-                const float d_f_gate = d_c * op[7] + d_n * op[8];
-                const float d_i_gate = d_c * z + d_n;
-                dz = d_c * i * (1.f - z * z);
-                di = d_i_gate * i;
-                df = d_f_gate * f * (1.f - stable_sigmoid(op[9]));
-                st[it] = d_c * f;
-                st[NI + it] = d_n * f;
+                const SlstmBwCell r = slstm_cell_bw(op[0] + dhr, op[1], op[2], op[3], op[4], op[5], op[6], op[7], op[8],
+                                                    op[9], st[it], st[NI + it]);
+                dz = r.dz; di = r.di; df = r.df; dob = r.dob;
+                st[it] = r.dc;
+                st[NI + it] = r.dn;
                 __stcs(gt, dz);
                 __stcs(gt + (size_t)H, di);
                 __stcs(gt + (size_t)2 * H, df);
@@ -467,6 +453,248 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmS
         a.dh[si] = dhr;
         a.dc[si] = st[it];
         a.dn[si] = st[NI + it];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Grid-cooperative variant for heads too wide for a cluster's shared memory (dense H = 1024,
+// block-diagonal heads of 512 units): the G CTAs of a head span up to the whole GPU, launched
+// cooperatively so that all are resident. The exchange goes through global memory, and needs no
+// buffer of its own: forward peers read h_{t-1} from `out[:, t-1, :]`, backward peers read the gate
+// deltas from `g[:, t, :]`, both of which the call has to write anyway. One counter barrier per head
+// and step orders the writes before the reads; every wait is bounded and a timeout makes all CTAs
+// leave the loop. Batch entries are processed in sub-groups of BG per step so that the staged
+// vector fits beside the recurrent slice.
+// ---------------------------------------------------------------------------------------------
+struct GridSync {
+    unsigned int count[64];  // arrivals per head
+    unsigned int abort;
+    unsigned int pad[63];
+};
+static __device__ GridSync g_slstm_sync;
+static constexpr unsigned kSpinLimit = 1u << 21;  // about a second of polling
+
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Barrier among the CTAs of head `hd`: returns once `target` arrivals were counted, or false when the
+// wait ran out or another CTA gave up.
+__device__ __forceinline__ bool group_barrier(GridSync* gs, int hd, unsigned target, int* s_flag) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(&gs->count[hd], 1u);
+        bool ok = true;
+        unsigned spins = 0;
+        while (ld_acquire_u32(&gs->count[hd]) < target) {
+            ++spins;
+            if (spins > kSpinLimit || ((spins & 63u) == 0 && ld_acquire_u32(&gs->abort))) { ok = false; break; }
+        }
+        if (!ok) atomicExch(&gs->abort, 1u);
+        *s_flag = ok ? 1 : 0;
+    }
+    __syncthreads();
+    return *s_flag != 0;
+}
+
+struct GridSmem {
+    size_t ws, xin, part, state, total;
+};
+
+static GridSmem grid_layout(int K, int NOUTp, int BG, int KS, int UPC, int Bp, int nstate) {
+    GridSmem l;
+    auto a16 = [](size_t x) { return (x + 15) / 16 * 16; };
+    l.ws = 0;
+    l.xin = l.ws + a16((size_t)K * NOUTp * 4);
+    l.part = l.xin + a16((size_t)K * BG * 4);
+    l.state = l.part + a16((size_t)KS * BG * NOUTp * 4);
+    l.total = l.state + a16((size_t)nstate * Bp * UPC * 4);
+    return l;
+}
+
+template <int BG>
+__global__ void __launch_bounds__(kThreads) slstm_fw_grid(SlstmArgs a, GridSmem lay, GridSync* gs, int* status) {
+    const int G = a.CS, UPC = a.UPC, dhd = a.dhd, H = a.H, T = a.T, B = a.B;
+    const int hd = blockIdx.x / G, cr = blockIdx.x % G;
+    const int K = dhd, NOUT = 4 * UPC;
+    const int tid = threadIdx.x;
+    const int nsub = (B + BG - 1) / BG, NS = nsub * BG * UPC;
+
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* Ws = (float*)(smem + lay.ws);      // [K][4*UPC]
+    float* xin = (float*)(smem + lay.xin);    // [K][BG]: h_{t-1} of the head for one batch sub-group
+    float* part = (float*)(smem + lay.part);  // [KS][BG][4*UPC]
+    float* st = (float*)(smem + lay.state);   // c, n, m, h: [4][nsub*BG*UPC]
+    __shared__ int s_flag;
+
+    for (int i = tid; i < K * NOUT; i += kThreads) {
+        int r = i / NOUT, col = i % NOUT, gate = col / UPC, ul = col % UPC;
+        Ws[i] = a.wh[((size_t)hd * dhd + r) * 4 * dhd + gate * dhd + cr * UPC + ul];
+    }
+    for (int it = tid; it < NS; it += kThreads) {
+        int b = it / UPC, ul = it % UPC;
+        size_t si = (size_t)b * H + hd * dhd + cr * UPC + ul;
+        bool live = a.carry && b < B;
+        st[it] = live ? a.c[si] : 0.f;
+        st[NS + it] = live ? a.n[si] : 0.f;
+        st[2 * NS + it] = live ? a.m[si] : 0.f;
+        st[3 * NS + it] = live ? a.h[si] : 0.f;
+    }
+    __syncthreads();
+
+    bool ok = true;
+    for (int t = 0; t < T && ok; ++t) {
+        for (int sg = 0; sg < nsub; ++sg) {
+            const int b0 = sg * BG;
+            for (int e = tid; e < K * BG; e += kThreads) {
+                const int b = e / K, k = e % K;
+                float v = 0.f;
+                if (b0 + b < B) {
+                    if (t > 0) v = __ldcg(a.out + ((size_t)(b0 + b) * T + t - 1) * H + hd * dhd + k);
+                    else if (a.carry) v = a.h[(size_t)(b0 + b) * H + hd * dhd + k];
+                }
+                xin[(size_t)k * BG + b] = v;
+            }
+            __syncthreads();
+            matvec<BG, 2>(Ws, xin, part, K, NOUT, a.KS);
+            __syncthreads();
+            for (int it = tid; it < BG * UPC; it += kThreads) {
+                const int b = it / UPC, ul = it % UPC;
+                if (b0 + b >= B) continue;
+                const int j = hd * dhd + cr * UPC + ul;
+                const int si = (b0 + b) * UPC + ul;
+                float gh[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int ks = 0; ks < a.KS; ++ks) {
+                    const float* pp = part + ((size_t)ks * BG + b) * NOUT + ul;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) gh[q] += pp[q * UPC];
+                }
+                float* gt = a.g + ((size_t)(b0 + b) * T + t) * 4 * H + j;
+                float pre[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) pre[q] = __ldcs(gt + (size_t)q * H) + gh[q] + __ldg(a.bcat + q * H + j);
+                const float cp = st[si], np = st[NS + si], mp = st[2 * NS + si], hp = st[3 * NS + si];
+                const SlstmFwCell r = slstm_cell_fw(pre[0], pre[1], pre[2], pre[3], cp, np, mp);
+                st[si] = r.c; st[NS + si] = r.n; st[2 * NS + si] = r.m; st[3 * NS + si] = r.h;
+                const size_t s = ((size_t)(b0 + b) * T + t) * H + j;
+                __stcg(a.out + s, r.h);  // read by the head's other CTAs in the next step
+                __stcs(gt + (size_t)2 * H, pre[2]);
+                __stcs(a.s.h_prev + s, hp);
+                __stcs(a.s.c_prev + s, cp);
+                __stcs(a.s.n_prev + s, np);
+                __stcs(a.s.zt + s, r.z);
+                __stcs(a.s.ot + s, r.o);
+                __stcs(a.s.ipr + s, r.ip);
+                __stcs(a.s.fpr + s, r.fp);
+                __stcs(a.s.c + s, r.c);
+                __stcs(a.s.n + s, r.n);
+            }
+            __syncthreads();  // the next sub-group reuses xin and part
+        }
+        ok = group_barrier(gs, hd, (unsigned)(t + 1) * (unsigned)G, &s_flag);  // also orders the last read of the carried h before its update
+    }
+    if (!ok) {
+        if (tid == 0) atomicCAS(status, 0, 301);
+        return;
+    }
+    for (int it = tid; it < NS; it += kThreads) {
+        int b = it / UPC, ul = it % UPC;
+        if (b >= B) continue;
+        size_t si = (size_t)b * H + hd * dhd + cr * UPC + ul;
+        a.c[si] = st[it];
+        a.n[si] = st[NS + it];
+        a.m[si] = st[2 * NS + it];
+        a.h[si] = st[3 * NS + it];
+    }
+}
+
+template <int BG>
+__global__ void __launch_bounds__(kThreads) slstm_bw_grid(SlstmArgs a, GridSmem lay, GridSync* gs, int* status) {
+    const int G = a.CS, UPC = a.UPC, dhd = a.dhd, H = a.H, T = a.T, B = a.B;
+    const int hd = blockIdx.x / G, cr = blockIdx.x % G;
+    const int K = 4 * dhd, NOUT = UPC, NOUTp = (NOUT + 1) & ~1;
+    const int tid = threadIdx.x;
+    const int nsub = (B + BG - 1) / BG, NS = nsub * BG * UPC;
+
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* Ws = (float*)(smem + lay.ws);      // [K = gate*dhd + u][NOUTp = own rows]
+    float* xin = (float*)(smem + lay.xin);    // [K][BG]: gate deltas of the head for one batch sub-group
+    float* part = (float*)(smem + lay.part);  // [KS][BG][NOUTp]
+    float* st = (float*)(smem + lay.state);   // dc, dn, recurrent dh: [3][nsub*BG*UPC]
+    __shared__ int s_flag;
+
+    for (int i = tid; i < K * NOUTp; i += kThreads) {
+        int col = i / NOUTp, rl = i % NOUTp;
+        Ws[i] = rl < NOUT ? a.wh[((size_t)hd * dhd + cr * UPC + rl) * 4 * dhd + col] : 0.f;
+    }
+    for (int it = tid; it < NS; it += kThreads) {
+        int b = it / UPC, ul = it % UPC;
+        size_t si = (size_t)b * H + hd * dhd + cr * UPC + ul;
+        bool live = a.carry && b < B;
+        st[it] = live ? a.dc[si] : 0.f;
+        st[NS + it] = live ? a.dn[si] : 0.f;
+        st[2 * NS + it] = live ? a.dh[si] : 0.f;
+    }
+    __syncthreads();
+
+    bool ok = true;
+    for (int t = T - 1; t >= 0 && ok; --t) {
+        // gate deltas of this CTA's units, all batch entries
+        for (int it = tid; it < B * UPC; it += kThreads) {
+            const int b = it / UPC, ul = it % UPC;
+            const int j = hd * dhd + cr * UPC + ul;
+            const size_t s = ((size_t)b * T + t) * H + j;
+            float* gt = a.g + ((size_t)b * T + t) * 4 * H + j;
+            const SlstmBwCell r = slstm_cell_bw(__ldcs(a.dy + s) + st[2 * NS + it], __ldcs(a.s.ot + s), __ldcs(a.s.c + s),
+                                                __ldcs(a.s.n + s), __ldcs(a.s.fpr + s), __ldcs(a.s.ipr + s),
+                                                __ldcs(a.s.zt + s), __ldcs(a.s.c_prev + s), __ldcs(a.s.n_prev + s),
+                                                __ldcs(gt + (size_t)2 * H), st[it], st[NS + it]);
+            st[it] = r.dc;
+            st[NS + it] = r.dn;
+            __stcg(gt, r.dz);
+            __stcg(gt + (size_t)H, r.di);
+            __stcg(gt + (size_t)2 * H, r.df);
+            __stcg(gt + (size_t)3 * H, r.dob);
+        }
+        ok = group_barrier(gs, hd, (unsigned)(T - t) * (unsigned)G, &s_flag);
+        if (!ok) break;
+        // dh_{t-1} of the own units from the head's gate deltas
+        for (int sg = 0; sg < nsub; ++sg) {
+            const int b0 = sg * BG;
+            for (int e = tid; e < K * BG; e += kThreads) {
+                const int b = e / K, k = e % K;
+                const int gate = k / dhd, u = k % dhd;
+                float v = 0.f;
+                if (b0 + b < B) v = __ldcg(a.g + ((size_t)(b0 + b) * T + t) * 4 * H + (size_t)gate * H + hd * dhd + u);
+                xin[(size_t)k * BG + b] = v;
+            }
+            __syncthreads();
+            if (a.CPT == 2) matvec<BG, 2>(Ws, xin, part, K, NOUTp, a.KS);
+            else matvec<BG, 1>(Ws, xin, part, K, NOUTp, a.KS);
+            __syncthreads();
+            for (int it = tid; it < BG * UPC; it += kThreads) {
+                const int b = it / UPC, ul = it % UPC;
+                float dhr = 0.f;
+                for (int ks = 0; ks < a.KS; ++ks) dhr += part[((size_t)ks * BG + b) * NOUTp + ul];
+                st[2 * NS + (b0 + b) * UPC + ul] = dhr;
+            }
+            __syncthreads();
+        }
+    }
+    if (!ok) {
+        if (tid == 0) atomicCAS(status, 0, 302);
+        return;
+    }
+    for (int it = tid; it < NS; it += kThreads) {
+        int b = it / UPC, ul = it % UPC;
+        if (b >= B) continue;
+        size_t si = (size_t)b * H + hd * dhd + cr * UPC + ul;
+        a.dc[si] = st[it];
+        a.dn[si] = st[NS + it];
+        a.dh[si] = st[2 * NS + it];
     }
 }
 
@@ -578,6 +806,94 @@ static int coresident_any(int BG, bool bwd, const Geo& g, int* out) {
 }
 
 long long* tc_debug_prof();
+int* tc_status_ptr();
+
+struct GridGeo {
+    int BG, G, UPC, KS, CPT;
+    GridSmem lay;
+};
+
+// Widest split of a head over CTAs (all heads together within the SM count) whose slice fits, then the
+// largest batch sub-group that fits beside it.
+static bool grid_geometry(int B, int NH, int dhd, bool bwd, GridGeo* out) {
+    if (NH > 64) return false;
+    int gmax = sm_count() / NH;
+    if (gmax > dhd) gmax = dhd;
+    for (int G = gmax; G >= 1; --G) {
+        if (dhd % G) continue;
+        const int UPC = dhd / G;
+        const int K = bwd ? 4 * dhd : dhd, NOUT = bwd ? UPC : 4 * UPC, NOUTp = (NOUT + 1) & ~1;
+        int CPT = 2;
+        if (bwd && (NOUTp / 2) * 16 < kThreads) CPT = 1;
+        const int ncols = NOUTp / CPT;
+        int KS = kThreads / ncols;
+        if (KS < 1) KS = 1;
+        if (KS > 32) KS = 32;
+        if (KS > K) KS = K;
+        for (int BG = 8; BG >= 1; BG /= 2) {
+            if (BG > 1 && BG / 2 >= B) continue;
+            const int nsub = (B + BG - 1) / BG;
+            GridSmem l = grid_layout(K, NOUTp, BG, KS, UPC, nsub * BG, bwd ? 3 : 4);
+            if (l.total > kSmemCap) continue;
+            out->BG = BG; out->G = G; out->UPC = UPC; out->KS = KS; out->CPT = CPT; out->lay = l;
+            return true;
+        }
+    }
+    return false;
+}
+
+template <int BG>
+static int launch_grid(cudaStream_t st, bool bwd, SlstmArgs a, const GridGeo& g) {
+    auto kern = bwd ? slstm_bw_grid<BG> : slstm_fw_grid<BG>;
+    // per device: barrier words' address, and whether the whole grid can be resident at once
+    static std::atomic<unsigned long long> key_of[2][64];
+    static GridSync* sync_of[64];
+    int dev = 0;
+    XL_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) dev = 0;
+    const int grid = a.NH * g.G;
+    const unsigned long long key = ((unsigned long long)g.lay.total << 16) | (unsigned)grid;
+    if (key_of[bwd][dev].load() != key) {
+        XL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.lay.total));
+        int per_sm = 0;
+        XL_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, g.lay.total));
+        if (per_sm * sm_count() < grid) {
+            set_error("slstm: %d CTAs of %zu bytes cannot be resident together", grid, g.lay.total);
+            return XLSTM_DECLINED;
+        }
+        void* p = nullptr;
+        XL_CUDA(cudaGetSymbolAddress(&p, g_slstm_sync));
+        sync_of[dev] = (GridSync*)p;
+        if (getenv("XLSTM_DEBUG"))
+            fprintf(stderr, "[xlstm] slstm %s grid: G=%d UPC=%d BG=%d KS=%d CPT=%d smem=%zu CTAs=%d\n", bwd ? "bw" : "fw", g.G,
+                    g.UPC, g.BG, g.KS, g.CPT, g.lay.total, grid);
+        key_of[bwd][dev].store(key);
+    }
+    GridSync* gs = sync_of[dev];
+    XL_CUDA(cudaMemsetAsync(gs, 0, sizeof(GridSync), st));
+    a.CS = g.G; a.UPC = g.UPC; a.KS = g.KS; a.CPT = g.CPT;
+    GridSmem lay = g.lay;
+    int* status = tc_status_ptr();
+    if (!status) return XLSTM_ERR_CUDA;
+    void* args[4] = {&a, &lay, &gs, &status};
+    XL_CUDA(cudaLaunchCooperativeKernel((const void*)kern, dim3((unsigned)grid), dim3(kThreads), args, g.lay.total, st));
+    count_launch();
+    return XLSTM_OK;
+}
+
+static int run_grid(cudaStream_t st, bool bwd, const SlstmArgs& a) {
+    GridGeo g;
+    if (!grid_geometry(a.B, a.NH, a.dhd, bwd, &g)) {
+        set_error("slstm: recurrent slice for %d units per head over %d heads does not fit the GPU's shared memory", a.dhd, a.NH);
+        return XLSTM_DECLINED;
+    }
+    switch (g.BG) {
+        case 8: return launch_grid<8>(st, bwd, a, g);
+        case 4: return launch_grid<4>(st, bwd, a, g);
+        case 2: return launch_grid<2>(st, bwd, a, g);
+        default: return launch_grid<1>(st, bwd, a, g);
+    }
+}
 
 // Batch group: start from the largest of 8/4/2/1 that does not pad the batch by 2x or more, and grow
 // it (12, 16) while the clusters it needs exceed what can be resident at once: a second wave of
@@ -602,10 +918,7 @@ static int run(cudaStream_t st, bool bwd, SlstmArgs a) {
         if (chosen_bg == 0) { chosen = g; chosen_bg = BG; }  // fallback: runs in waves
         if (a.NH * ((a.B + BG - 1) / BG) <= maxc) { chosen = g; chosen_bg = BG; break; }
     }
-    if (chosen_bg == 0) {
-        set_error("slstm: recurrent slice for %d units per head does not fit a resident cluster's shared memory", a.dhd);
-        return XLSTM_DECLINED;
-    }
+    if (chosen_bg == 0) return run_grid(st, bwd, a);  // too wide for a cluster: split the head over the whole GPU
     const Geo& g = chosen;
     a.CS = g.CS; a.UPC = g.UPC; a.KS = g.KS; a.CPT = g.CPT;
     switch (chosen_bg) {

@@ -74,9 +74,17 @@ def test_carry_state_in_and_out():
     _check(*_case(4, 64, 2, 30, seed=2, carry=True))
 
 
+# Heads too wide for one cluster's shared memory run on the grid-cooperative kernels, which split a
+# head over up to all SMs and exchange through `out` / `g` in global memory.
+@pytest.mark.parametrize("B,H,NH,T,carry", [(4, 1024, 1, 9, False), (3, 2048, 4, 7, False), (8, 2048, 4, 5, True),
+                                            (11, 1024, 1, 4, True), (2, 1024, 2, 1, True)])
+def test_wide_heads_match_oracle(B, H, NH, T, carry):
+    _check(*_case(B, H, NH, T, seed=4, carry=carry))
+
+
 def test_dense_too_wide_is_declined():
     from gpu_util import ops, xl
-    B, H, T = 1, 1024, 4
+    B, H, T = 1, 4096, 4  # 256 MB of recurrent weights: more than the GPU's shared memory holds
     z = lambda *s: torch.zeros(s, device="cuda")
     before = xl._lib.lib.xlstm_launch_count()
     with pytest.raises(xl._lib.Declined):
