@@ -500,6 +500,29 @@ __device__ __forceinline__ bool group_barrier(GridSync* gs, int hd, unsigned tar
     return *s_flag != 0;
 }
 
+// xin[k][0..BG) <- vector k of each live batch entry of a sub-group, read from L2 (the writers are other
+// CTAs). A thread takes one k for all entries: consecutive lanes read consecutive addresses of each row
+// and write whole [BG] records. `seg` floats are contiguous in a row, segments `sstride` floats apart.
+template <int BG>
+__device__ __forceinline__ void stage_rows(float* xin, const float* base, size_t bstride, int nlive, int K, int seg,
+                                           size_t sstride) {
+    for (int k = threadIdx.x; k < K; k += kThreads) {
+        const size_t off = (size_t)(k / seg) * sstride + (size_t)(k % seg);
+        float v[BG];
+#pragma unroll
+        for (int b = 0; b < BG; ++b) v[b] = (b < nlive) ? __ldcg(base + (size_t)b * bstride + off) : 0.f;
+        float* dst = xin + (size_t)k * BG;
+        if (BG % 4 == 0) {
+#pragma unroll
+            for (int b4 = 0; b4 < BG / 4; ++b4)
+                *reinterpret_cast<float4*>(dst + 4 * b4) = make_float4(v[4 * b4], v[4 * b4 + 1], v[4 * b4 + 2], v[4 * b4 + 3]);
+        } else {
+#pragma unroll
+            for (int b = 0; b < BG; ++b) dst[b] = v[b];
+        }
+    }
+}
+
 struct GridSmem {
     size_t ws, xin, part, state, total;
 };
@@ -545,27 +568,37 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_grid(SlstmArgs a, GridSmem 
     }
     __syncthreads();
 
+    // thread `tid` owns item tid = b*UPC + ul (when there is one): its bias stays in registers and its gate
+    // pre-activations are fetched at the top of the step, under the staging and the mat-vec
+    float bias[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool own = tid < B * UPC;
+    const int own_j = hd * dhd + cr * UPC + tid % UPC;
+    if (own) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) bias[q] = a.bcat[q * H + own_j];
+    }
     bool ok = true;
     for (int t = 0; t < T && ok; ++t) {
+        float gpre[4] = {0.f, 0.f, 0.f, 0.f};
+        if (own) {
+            const float* gt = a.g + ((size_t)(tid / UPC) * T + t) * 4 * H + own_j;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) gpre[q] = __ldcs(gt + (size_t)q * H);
+        }
         for (int sg = 0; sg < nsub; ++sg) {
             const int b0 = sg * BG;
-            for (int e = tid; e < K * BG; e += kThreads) {
-                const int b = e / K, k = e % K;
-                float v = 0.f;
-                if (b0 + b < B) {
-                    if (t > 0) v = __ldcg(a.out + ((size_t)(b0 + b) * T + t - 1) * H + hd * dhd + k);
-                    else if (a.carry) v = a.h[(size_t)(b0 + b) * H + hd * dhd + k];
-                }
-                xin[(size_t)k * BG + b] = v;
-            }
+            const int nlive = min(BG, B - b0);
+            if (t > 0) stage_rows<BG>(xin, a.out + ((size_t)b0 * T + t - 1) * H + hd * dhd, (size_t)T * H, nlive, K, K, 0);
+            else stage_rows<BG>(xin, a.h + (size_t)b0 * H + hd * dhd, (size_t)H, a.carry ? nlive : 0, K, K, 0);
             __syncthreads();
             matvec<BG, 2>(Ws, xin, part, K, NOUT, a.KS);
             __syncthreads();
-            for (int it = tid; it < BG * UPC; it += kThreads) {
+            for (int gi = tid; gi < B * UPC; gi += kThreads) {  // global item b*UPC + ul; this sub-group's only
+                const int it = gi - b0 * UPC;
+                if (it < 0 || it >= BG * UPC) continue;
                 const int b = it / UPC, ul = it % UPC;
-                if (b0 + b >= B) continue;
                 const int j = hd * dhd + cr * UPC + ul;
-                const int si = (b0 + b) * UPC + ul;
+                const int si = gi;
                 float gh[4] = {0.f, 0.f, 0.f, 0.f};
                 for (int ks = 0; ks < a.KS; ++ks) {
                     const float* pp = part + ((size_t)ks * BG + b) * NOUT + ul;
@@ -574,8 +607,13 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_grid(SlstmArgs a, GridSmem 
                 }
                 float* gt = a.g + ((size_t)(b0 + b) * T + t) * 4 * H + j;
                 float pre[4];
+                if (gi == tid) {  // the item whose operands this thread fetched ahead
 #pragma unroll
-                for (int q = 0; q < 4; ++q) pre[q] = __ldcs(gt + (size_t)q * H) + gh[q] + __ldg(a.bcat + q * H + j);
+                    for (int q = 0; q < 4; ++q) pre[q] = gpre[q] + gh[q] + bias[q];
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) pre[q] = __ldcs(gt + (size_t)q * H) + gh[q] + __ldg(a.bcat + q * H + j);
+                }
                 const float cp = st[si], np = st[NS + si], mp = st[2 * NS + si], hp = st[3 * NS + si];
                 const SlstmFwCell r = slstm_cell_fw(pre[0], pre[1], pre[2], pre[3], cp, np, mp);
                 st[si] = r.c; st[NS + si] = r.n; st[2 * NS + si] = r.m; st[3 * NS + si] = r.h;
@@ -640,18 +678,35 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_grid(SlstmArgs a, GridSmem 
     }
     __syncthreads();
 
+    // operands of item `it` at step t; thread tid fetches those of item tid one step ahead
+    auto fetch = [&](int it, int t, float* op) {
+        const int b = it / UPC, ul = it % UPC;
+        const int j = hd * dhd + cr * UPC + ul;
+        const size_t s = ((size_t)b * T + t) * H + j;
+        op[0] = __ldcs(a.dy + s); op[1] = __ldcs(a.s.ot + s); op[2] = __ldcs(a.s.c + s); op[3] = __ldcs(a.s.n + s);
+        op[4] = __ldcs(a.s.fpr + s); op[5] = __ldcs(a.s.ipr + s); op[6] = __ldcs(a.s.zt + s);
+        op[7] = __ldcs(a.s.c_prev + s); op[8] = __ldcs(a.s.n_prev + s);
+        op[9] = __ldcs(a.g + ((size_t)b * T + t) * 4 * H + 2 * H + j);
+    };
+    float pre[10];
+    const bool own = tid < B * UPC;
+    if (own && T > 0) fetch(tid, T - 1, pre);
     bool ok = true;
     for (int t = T - 1; t >= 0 && ok; --t) {
         // gate deltas of this CTA's units, all batch entries
         for (int it = tid; it < B * UPC; it += kThreads) {
             const int b = it / UPC, ul = it % UPC;
             const int j = hd * dhd + cr * UPC + ul;
-            const size_t s = ((size_t)b * T + t) * H + j;
             float* gt = a.g + ((size_t)b * T + t) * 4 * H + j;
-            const SlstmBwCell r = slstm_cell_bw(__ldcs(a.dy + s) + st[2 * NS + it], __ldcs(a.s.ot + s), __ldcs(a.s.c + s),
-                                                __ldcs(a.s.n + s), __ldcs(a.s.fpr + s), __ldcs(a.s.ipr + s),
-                                                __ldcs(a.s.zt + s), __ldcs(a.s.c_prev + s), __ldcs(a.s.n_prev + s),
-                                                __ldcs(gt + (size_t)2 * H), st[it], st[NS + it]);
+            float op[10];
+            if (it == tid) {
+#pragma unroll
+                for (int q = 0; q < 10; ++q) op[q] = pre[q];
+            } else {
+                fetch(it, t, op);
+            }
+            const SlstmBwCell r = slstm_cell_bw(op[0] + st[2 * NS + it], op[1], op[2], op[3], op[4], op[5], op[6], op[7],
+                                                op[8], op[9], st[it], st[NS + it]);
             st[it] = r.dc;
             st[NS + it] = r.dn;
             __stcg(gt, r.dz);
@@ -659,18 +714,14 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_grid(SlstmArgs a, GridSmem 
             __stcg(gt + (size_t)2 * H, r.df);
             __stcg(gt + (size_t)3 * H, r.dob);
         }
+        if (own && t > 0) fetch(tid, t - 1, pre);  // lands under the barrier and the mat-vecs
         ok = group_barrier(gs, hd, (unsigned)(T - t) * (unsigned)G, &s_flag);
         if (!ok) break;
         // dh_{t-1} of the own units from the head's gate deltas
         for (int sg = 0; sg < nsub; ++sg) {
             const int b0 = sg * BG;
-            for (int e = tid; e < K * BG; e += kThreads) {
-                const int b = e / K, k = e % K;
-                const int gate = k / dhd, u = k % dhd;
-                float v = 0.f;
-                if (b0 + b < B) v = __ldcg(a.g + ((size_t)(b0 + b) * T + t) * 4 * H + (size_t)gate * H + hd * dhd + u);
-                xin[(size_t)k * BG + b] = v;
-            }
+            stage_rows<BG>(xin, a.g + ((size_t)b0 * T + t) * 4 * H + hd * dhd, (size_t)T * 4 * H, min(BG, B - b0), K, dhd,
+                           (size_t)H);
             __syncthreads();
             if (a.CPT == 2) matvec<BG, 2>(Ws, xin, part, K, NOUTp, a.KS);
             else matvec<BG, 1>(Ws, xin, part, K, NOUTp, a.KS);
