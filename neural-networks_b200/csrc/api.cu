@@ -72,19 +72,26 @@ extern "C" int xlstm_device_status(void) {
     return XLSTM_OK;
 }
 
+// Chunk-state record of the tensor-core path: one bf16 C and fp32 n per 128 x 128 sub-head and chunk boundary.
+static size_t tc_record_bytes(const xlstm_mlstm_shape* s) {
+    const int bhs = s->B * s->H * mlstm_tc_subheads(s->dqk, s->dhv);
+    return mlstm_tc_saved_C_bytes(bhs, num_chunks(s)) + mlstm_tc_saved_n_bytes(bhs, num_chunks(s));
+}
+
 extern "C" size_t xlstm_mlstm_saved_bytes(const xlstm_mlstm_shape* s) {
     if (!s || s->B <= 0 || s->H <= 0 || s->T <= 0 || s->dqk <= 0 || s->dhv <= 0 || s->L <= 0) return 0;
-    if (use_tc(s)) return mlstm_tc_saved_C_bytes(s->B * s->H, num_chunks(s)) + mlstm_tc_saved_n_bytes(s->B * s->H, num_chunks(s));
+    if (use_tc(s)) return tc_record_bytes(s);
     return saved_C_bytes(s) + saved_n_bytes(s);
 }
 extern "C" size_t xlstm_mlstm_fw_workspace_bytes(const xlstm_mlstm_shape* s) {
-    (void)s;
+    if (!s || s->B <= 0 || s->H <= 0 || s->T <= 0 || s->dqk <= 0 || s->dhv <= 0 || s->L <= 0) return 0;
+    if (use_tc(s)) return mlstm_tc_fw_workspace_bytes(s->B, s->H, s->T, s->dqk, s->dhv);
     return 0;
 }
 extern "C" size_t xlstm_mlstm_bw_workspace_bytes(const xlstm_mlstm_shape* s, int have_saved) {
     if (!s || s->B <= 0 || s->H <= 0 || s->T <= 0 || s->dqk <= 0 || s->dhv <= 0 || s->L <= 0) return 0;
+    if (use_tc(s)) return (have_saved ? 0 : tc_record_bytes(s)) + mlstm_tc_bw_workspace_bytes(s->B, s->H, s->T, s->dqk, s->dhv);
     if (have_saved) return 0;
-    if (use_tc(s)) return mlstm_tc_saved_C_bytes(s->B * s->H, num_chunks(s)) + mlstm_tc_saved_n_bytes(s->B * s->H, num_chunks(s));
     return saved_C_bytes(s) + saved_n_bytes(s);
 }
 
@@ -92,7 +99,6 @@ extern "C" int xlstm_mlstm_fw(void* stream, const xlstm_mlstm_shape* s, const vo
                               const float* ig, const float* fg, const float* carry_C, const float* carry_n,
                               const float* carry_m, void* ytil, float* msv, float* psiv, float* qnv, void* saved,
                               float* out_C, float* out_n, float* out_m, void* workspace, size_t workspace_bytes) {
-    (void)workspace; (void)workspace_bytes;
     int rc = check_shape("mlstm_fw", s);
     if (rc) return rc;
     XL_CHECK_ARG(q && k && v && ig && fg && ytil && msv && psiv && qnv, "mlstm_fw: null pointer");
@@ -105,7 +111,7 @@ extern "C" int xlstm_mlstm_fw(void* stream, const xlstm_mlstm_shape* s, const vo
     a.oC = out_C; a.on = out_n; a.om = out_m;
     a.B = s->B; a.H = s->H; a.T = s->T; a.dqk = s->dqk; a.dhv = s->dhv; a.L = eff_L(s); a.NC = num_chunks(s);
     a.states_only = 0;
-    if (use_tc(s)) return mlstm_fw_tc_launch((cudaStream_t)stream, a, saved);
+    if (use_tc(s)) return mlstm_fw_tc_launch((cudaStream_t)stream, a, saved, workspace, workspace_bytes);
     return mlstm_fw_simt_launch((cudaStream_t)stream, a, s->dtype);
 }
 
@@ -124,6 +130,8 @@ extern "C" int xlstm_mlstm_bw(void* stream, const xlstm_mlstm_shape* s, const vo
     XL_CHECK_ARG((carry_dC != nullptr) == (carry_dn != nullptr), "mlstm_bw: carry dC, dn must be given together");
     cudaStream_t st = (cudaStream_t)stream;
     if (use_tc(s)) {
+        char* ws = (char*)workspace;
+        size_t ws_left = workspace ? workspace_bytes : 0;
         if (!saved) {
             // recompute the chunk-boundary states (bf16 record) into the workspace with the forward's state-only pass
             size_t need = xlstm_mlstm_bw_workspace_bytes(s, 0);
@@ -136,16 +144,18 @@ extern "C" int xlstm_mlstm_bw(void* stream, const xlstm_mlstm_shape* s, const vo
             f.q = q; f.k = k; f.v = v; f.ig = ig; f.fg = fg; f.cC = carry_C; f.cn = carry_n; f.cm = carry_m;
             f.B = s->B; f.H = s->H; f.T = s->T; f.dqk = s->dqk; f.dhv = s->dhv; f.L = eff_L(s); f.NC = num_chunks(s);
             f.states_only = 1;
-            rc = mlstm_fw_tc_launch(st, f, workspace);
+            rc = mlstm_fw_tc_launch(st, f, workspace, nullptr, 0);
             if (rc) return rc;
             saved = workspace;
+            ws += tc_record_bytes(s);
+            ws_left -= tc_record_bytes(s);
         }
         MlstmBwArgs a = {};
         a.q = q; a.k = k; a.v = v; a.ig = ig; a.fg = fg; a.cm = carry_m; a.ytil = ytil; a.msv = msv; a.psiv = psiv;
         a.qnv = qnv; a.dytil = d_ytil; a.cdC = carry_dC; a.cdn = carry_dn;
         a.dq = dq; a.dk = dk; a.dv = dv; a.dig = dig; a.dfg = dfg; a.odC = out_dC; a.odn = out_dn;
         a.B = s->B; a.H = s->H; a.T = s->T; a.dqk = s->dqk; a.dhv = s->dhv; a.L = eff_L(s); a.NC = num_chunks(s);
-        return mlstm_bw_tc_launch(st, a, saved, s->gdtype);
+        return mlstm_bw_tc_launch(st, a, saved, s->gdtype, ws, ws_left);
     }
     const float *sC, *sn;
     if (saved) {

@@ -39,8 +39,13 @@ bool mlstm_simt_supported(int L, int dqk, int dhv, int dtype);
 bool mlstm_tc_supported(int L, int dqk, int dhv, int dtype);
 size_t mlstm_tc_saved_C_bytes(int BH, int NC);
 size_t mlstm_tc_saved_n_bytes(int BH, int NC);
-int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved);
-int mlstm_bw_tc_launch(cudaStream_t st, const MlstmBwArgs& a, const void* saved, int gdtype);
+// Heads wider than 128 (multiples of 128) run as 128 x 128 sub-heads; `saved` then holds one record per sub-head.
+int mlstm_tc_subheads(int dqk, int dhv);
+size_t mlstm_tc_fw_workspace_bytes(int B, int H, int T, int dqk, int dhv);
+size_t mlstm_tc_bw_workspace_bytes(int B, int H, int T, int dqk, int dhv);  // excluding a recomputed state record
+int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved, void* workspace, size_t workspace_bytes);
+int mlstm_bw_tc_launch(cudaStream_t st, const MlstmBwArgs& a, const void* saved, int gdtype, void* workspace,
+                       size_t workspace_bytes);
 int tc_status_read_and_clear(int* out);
 
 }  // namespace xl

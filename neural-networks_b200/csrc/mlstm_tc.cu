@@ -76,8 +76,9 @@ int* tc_status_ptr() {
 }
 
 bool mlstm_tc_supported(int L_, int dqk, int dhv, int dtype) {
-    return L_ == L && dqk == D && dhv == D && dtype == XLSTM_BF16;
+    return L_ == L && dqk >= D && dhv >= D && dqk % D == 0 && dhv % D == 0 && dqk <= 4 * D && dhv <= 4 * D && dtype == XLSTM_BF16;
 }
+int mlstm_tc_subheads(int dqk, int dhv) { return (dqk / D) * (dhv / D); }
 
 size_t mlstm_tc_saved_C_bytes(int BH, int NC) { return align_up((size_t)BH * (NC + 1) * D * D * sizeof(bf16), 256); }
 size_t mlstm_tc_saved_n_bytes(int BH, int NC) { return align_up((size_t)BH * (NC + 1) * D * sizeof(float), 256); }

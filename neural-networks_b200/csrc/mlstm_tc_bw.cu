@@ -64,11 +64,18 @@ struct Params {
     float *odC, *odn;
     int B, H, T, NC;
     int gbf16;
-    int ablate;       // development aid: bit mask of work to skip (results are then wrong)
+    // Heads wider than 128 run as nq x nv sub-heads of 128 x 128, one CTA each (see the forward kernel).
+    // Every gradient is linear in the sub-heads' contributions once dN = dy/psi and dqn are formed from
+    // the whole head, so the CTAs write fp32 partials and a second kernel sums them: dq, dk over vh
+    // (planes `qk_plane` apart), dv over qh (`v_plane`), the gate gradients over all (`g_plane`). The
+    // terms that belong to the normaliser branch (dqn) are taken by the vh = 0 sub-heads only.
+    int nq, nv;
+    const float* dotv;  // [B*H][T] dy_t . ytil_t over the whole head (nv > 1; else the CTA forms it itself)
+    size_t qk_plane, v_plane, g_plane;
     int* status;      // device status word (first bounded wait that ran out)
-    long long* prof;  // optional per-phase cycle counts of CTA 0 (development aid; null in production)
 };
 
+static constexpr int kVecFloats = 3 * L + D;
 struct Smem {
     static constexpr uint32_t q = 0;                       // 2 stages
     static constexpr uint32_t k = q + 2 * kTileBytes;      // 2 stages
@@ -81,8 +88,8 @@ struct Smem {
     static constexpr uint32_t dS = ds_ + kBoxBytes;        // dS  [64 x 64]
     static constexpr uint32_t gates = dS + kBoxBytes;      // 2 x Gates
     static constexpr uint32_t graw = gates + 2 * sizeof(Gates);   // 2 x GateRawS
-    static constexpr uint32_t vec = graw + 2 * 784;  // 2 x [psi 64 | qn 64 | n entering the chunk 128]
-    static constexpr uint32_t dnv = vec + 2 * (2 * L + D) * 4;            // dn, double buffered [2][128]
+    static constexpr uint32_t vec = graw + 2 * 784;  // 2 x [psi 64 | qn 64 | n entering the chunk 128 | dy.ytil 64]
+    static constexpr uint32_t dnv = vec + 2 * kVecFloats * 4;             // dn, double buffered [2][128]
     static constexpr uint32_t dnp = dnv + 2 * D * 4;       // dn partial sums [4][128]
     static constexpr uint32_t part = dnp + 4 * D * 4;      // partial sums [12][64]: dot(4), u(4), w(4)
     static constexpr uint32_t dqn = part + 12 * L * 4;     // [64]
@@ -221,7 +228,7 @@ __device__ __forceinline__ void gates_compute(const GateRawS* r, Gates* G) {
 }
 // Control warp: start the asynchronous copy of a chunk's psi, qn (64 each) and entering normaliser n (128)
 // straight into their shared-memory slot [psi 64 | qn 64 | n 128].
-__device__ __forceinline__ void vec_fetch(const Params& p, int bh, int ch, float* dst) {
+__device__ __forceinline__ void vec_fetch(const Params& p, int bh, int sbh, int ch, float* dst) {
     const int lane = threadIdx.x & 31;
     const int t0 = ch * L, Lc = min(L, p.T - t0);
 #pragma unroll
@@ -229,9 +236,10 @@ __device__ __forceinline__ void vec_fetch(const Params& p, int bh, int ch, float
         const size_t o = (size_t)bh * p.T + t0 + min(lane + 32 * e, Lc - 1);
         cp_async4(dst + lane + 32 * e, p.psiv + o);
         cp_async4(dst + L + lane + 32 * e, p.qnv + o);
+        if (p.dotv) cp_async4(dst + 2 * L + D + lane + 32 * e, p.dotv + o);
     }
 #pragma unroll
-    for (int e = 0; e < 4; ++e) cp_async4(dst + 2 * L + lane + 32 * e, p.savedn + ((size_t)bh * (p.NC + 1) + ch) * D + lane + 32 * e);
+    for (int e = 0; e < 4; ++e) cp_async4(dst + 2 * L + lane + 32 * e, p.savedn + ((size_t)sbh * (p.NC + 1) + ch) * D + lane + 32 * e);
 }
 
 // Sum 16 per-lane values across the 32 lanes of a warp with a reduce-scatter butterfly (16
@@ -269,13 +277,23 @@ __device__ __forceinline__ int butterfly_index(int lane) {
     return ((lane & 16) ? 8 : 0) + ((lane & 8) ? 4 : 0) + ((lane & 4) ? 2 : 0) + ((lane & 2) ? 1 : 0);
 }
 
-template <typename GT>
+// GT: type of the upstream gradient dy; OT: type the gradients are written in (fp32 for sub-head partials).
+// WIDE: heads split into sub-heads; the 128 x 128 instantiation folds all of that indexing away.
+template <typename GT, typename OT, bool WIDE>
 __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant__ Params p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool is_ctrl = warp == kMathWarps;
-    const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+    const int nq = WIDE ? p.nq : 1, nv = WIDE ? p.nv : 1;
+    const int nsub = nq * nv;
+    const int sbh = blockIdx.x, bh = sbh / nsub, sub = sbh % nsub, qh = sub / nv, vh = sub % nv;
+    const int b = bh / p.H, h = bh % p.H;
+    const int qcol = (h * nq + qh) * D, vcol = (h * nv + vh) * D;
+    const int dqk = nq * D, dhv = nv * D;
+    const size_t qk_plane = WIDE ? p.qk_plane : 0, v_plane = WIDE ? p.v_plane : 0, g_plane = WIDE ? p.g_plane : 0;
+    const float* dotv = WIDE ? p.dotv : nullptr;
+    const bool once = vh == 0;  // this sub-head carries the normaliser-branch terms of its q/k columns
     const int qd = warp & 3, cq = (warp >> 2) & 3;
     const uint32_t lane_base = (uint32_t)(32 * qd) << 16;
     const int x = 32 * qd + lane;          // this thread's lane of a 128-lane (feature-indexed) accumulator
@@ -323,16 +341,16 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     auto issue_qk = [&](int ch, int stage) {
         mbar_expect_tx(&bars[stage], 2 * kTileBytes);
         for (int cbx = 0; cbx < 2; ++cbx) {
-            tma_load_3d(sm + Smem::q + stage * kTileBytes + cbx * kBoxBytes, &p.tmq, &bars[stage], h * D + 64 * cbx, ch * L, b);
-            tma_load_3d(sm + Smem::k + stage * kTileBytes + cbx * kBoxBytes, &p.tmk, &bars[stage], h * D + 64 * cbx, ch * L, b);
+            tma_load_3d(sm + Smem::q + stage * kTileBytes + cbx * kBoxBytes, &p.tmq, &bars[stage], qcol + 64 * cbx, ch * L, b);
+            tma_load_3d(sm + Smem::k + stage * kTileBytes + cbx * kBoxBytes, &p.tmk, &bars[stage], qcol + 64 * cbx, ch * L, b);
         }
     };
     auto issue_v_ck = [&](int ch) {
         mbar_expect_tx(&bars[2], kTileBytes);
         mbar_expect_tx(&bars[3], 2 * kStateBox);
         for (int cbx = 0; cbx < 2; ++cbx) {
-            tma_load_3d(sV + cbx * kBoxBytes, &p.tmv, &bars[2], h * D + 64 * cbx, ch * L, b);
-            tma_load_2d(sCk + cbx * kStateBox, &p.tmc, &bars[3], 64 * cbx, (bh * (p.NC + 1) + ch) * D);
+            tma_load_3d(sV + cbx * kBoxBytes, &p.tmv, &bars[2], vcol + 64 * cbx, ch * L, b);
+            tma_load_2d(sCk + cbx * kStateBox, &p.tmc, &bars[3], 64 * cbx, (sbh * (p.NC + 1) + ch) * D);
         }
     };
 
@@ -344,7 +362,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     auto prefetch_dy = [&](int ch) {
         const int t0 = ch * L, Lc = min(L, p.T - t0);
         if (prow < Lc && l8 < 4) {
-            const size_t o = (((size_t)b * p.T + t0 + prow) * p.H + h) * D;
+            const size_t o = ((size_t)b * p.T + t0 + prow) * p.H * dhv + vcol;
             const char* pdy = reinterpret_cast<const char*>(p.dy) + o * sizeof(GT) + l8 * 128;
             if (l8 * 128 < (int)(D * sizeof(GT))) asm volatile("prefetch.global.L2 [%0];" ::"l"(pdy));
             if (l8 < 2) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.ytil + o) + l8 * 128));
@@ -352,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     };
     auto load_dy = [&](int ch, uint32_t* dyraw, uint32_t* yraw) {
         const int t0 = ch * L;
-        const size_t o = (((size_t)b * p.T + t0 + prow) * p.H + h) * D;
+        const size_t o = ((size_t)b * p.T + t0 + prow) * p.H * dhv + vcol;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int c = 4 * (l8 + 8 * i);
@@ -372,7 +390,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     if (is_ctrl) {
         if (lane == 0) { issue_qk(p.NC - 1, 0); issue_v_ck(p.NC - 1); }
         gates_fetch(p, b, h, bh, p.NC - 1, &GR[(p.NC - 1) & 1]);
-        vec_fetch(p, bh, p.NC - 1, svec + ((p.NC - 1) & 1) * (2 * L + D));
+        vec_fetch(p, bh, sbh, p.NC - 1, svec + ((p.NC - 1) & 1) * kVecFloats);
         cp_async_commit();
         cp_async_wait_all();
         __syncwarp();
@@ -383,14 +401,15 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
         // carry term of the forget-gate gradient: <dC_in, C_end> + dn_in . n_end
         float acc = 0.f;
         if (p.cdC) {
-            const bf16* Ce = p.savedC + ((size_t)bh * (p.NC + 1) + p.NC) * D * D;
-            const float* dCi = p.cdC + (size_t)bh * D * D;
-            for (int i = tid; i < D * D; i += kMathThreads) acc += dCi[i] * __bfloat162float(Ce[i]);
-            if (tid < D) acc += p.cdn[(size_t)bh * D + tid] * p.savedn[((size_t)bh * (p.NC + 1) + p.NC) * D + tid];
+            const bf16* Ce = p.savedC + ((size_t)sbh * (p.NC + 1) + p.NC) * D * D;
+            const float* dCi = p.cdC + ((size_t)bh * dhv + vh * D) * dqk + qh * D;  // block (vh, qh), rows dqk apart
+            for (int i = tid; i < D * D; i += kMathThreads) acc += dCi[(size_t)(i >> 7) * dqk + (i & 127)] * __bfloat162float(Ce[i]);
+            if (tid < D && once)
+                acc += p.cdn[(size_t)bh * dqk + qh * D + tid] * p.savedn[((size_t)sbh * (p.NC + 1) + p.NC) * D + tid];
         }
         acc = warp_sum(acc);
         if (lane == 0) sred[warp] = acc;
-        if (tid < D) sdn[tid] = p.cdn ? p.cdn[(size_t)bh * D + tid] : 0.f;
+        if (tid < D) sdn[tid] = (p.cdn && once) ? p.cdn[(size_t)bh * dqk + qh * D + tid] : 0.f;
     }
     __syncthreads();
     if (tid == 0) {
@@ -404,7 +423,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
         const int c0 = 32 * cq;
         float v[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = p.cdC ? p.cdC[(size_t)bh * D * D + (size_t)x * D + c0 + i] : 0.f;
+        for (int i = 0; i < 32; ++i) v[i] = p.cdC ? p.cdC[((size_t)bh * dhv + vh * D + x) * dqk + qh * D + c0 + i] : 0.f;
         put_row<4>(sdCb + (cq >> 1) * kStateBox, x, 4 * (cq & 1), v);
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] *= g0;
@@ -427,15 +446,6 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
 
     bool ok = true;
     int it = 0;
-#ifdef XL_TC_PROFILE
-    long long tprev = clock64();
-    long long pacc[13];
-#pragma unroll
-    for (int i = 0; i < 13; ++i) pacc[i] = 0;
-#define PROF(i) { long long tn = clock64(); pacc[i] += tn - tprev; tprev = tn; }
-#else
-#define PROF(i)
-#endif
     for (int ch = p.NC - 1; ch >= 0; --ch, ++it) {
         const int t0 = ch * L, Lc = min(L, p.T - t0);
         const int stg = it & 1;
@@ -444,14 +454,12 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
         float* dn_out = sdn + (stg ^ 1) * D;
         unsigned char* sQ = sm + Smem::q + stg * kTileBytes;
         unsigned char* sK = sm + Smem::k + stg * kTileBytes;
-        const float* spsi = svec + (ch & 1) * (2 * L + D);
+        const float* spsi = svec + (ch & 1) * kVecFloats;
         const float* sqn = spsi + L;
         const float* nk = spsi + 2 * L;
 
-        PROF(0)
         // =============== phase 1: dN, dNb tiles and the dy.ytil row dots (math) =======================
-        if (!is_ctrl && (p.ablate & 8)) {
-        } else if (!is_ctrl) {
+        if (!is_ctrl) {
             const float bt = Gc->b[prow];
             const float psi_r = spsi[prow];
             float dot = 0.f;
@@ -495,12 +503,13 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             if (l8 == 0) {
                 // dqn_t = sign(qn)(-dot/psi) where the q.n term, not the floor, set psi
                 float r = 0.f, u = 0.f;
-                if (prow < Lc) {
+                if (dotv) dot = spsi[2 * L + D + prow];  // the row dot over all of the head's v columns
+                if (prow < Lc && once) {
                     const float qn = sqn[prow];
                     if (fabsf(qn) > Gc->emm[prow]) r = (qn > 0.f ? -1.f : 1.f) * dot / psi_r;
                     // dq_t . q_t: scaling q_t scales the numerator and q.n alike, so the row dot is
                     // dy_t . ytil_t + dqn_t (q_t . n_t) without touching dq
-                    u = dot + r * qn;
+                    if (sub == 0) u = dot + r * qn;
                 }
                 sdqn[prow] = r;
                 sbq[prow] = bt * r;
@@ -512,7 +521,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             bool w = mbar_wait(&bars[stg], (it >> 1) & 1) && mbar_wait(&bars[2], it & 1) && mbar_wait(&bars[3], it & 1);
             if (!w) *abort_flag = 1;
             // the two products that need only the tiles and dC+ start now, under the dN pass
-            if (w && lane == 0 && !(p.ablate & 4)) {
+            if (w && lane == 0) {
                 tc_fence_after();
                 const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), adC = smem_u32(sdCb);
 #pragma unroll
@@ -527,15 +536,12 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             }
             __syncwarp();
         }
-        PROF(1)
         __syncthreads();  // #1
         if (*abort_flag) { ok = false; break; }
-        PROF(2)
 
         // =============== phase 2: group A MMAs (control) | S/dds epilogue (math) ======================
         if (is_ctrl) {
-            if (lane == 0 && (p.ablate & 4)) { mma_commit(&bars[6]); mma_commit(&bars[4]); }
-            if (lane == 0 && !(p.ablate & 4)) {
+            if (lane == 0) {
                 tc_fence_after();
                 const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aCk = smem_u32(sCk),
                                adN = smem_u32(sdN), adNb = smem_u32(sdNb);
@@ -559,23 +565,19 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
                 mma_commit(&bars[4]);
             }
             __syncwarp();
-            PROF(3)
-            PROF(4)
             if (!mbar_wait(&bars[4], it & 1)) *abort_flag = 2;
             // V and C_k are read by group A only: refill them for the next chunk as soon as it is done
             if (lane == 0 && ch > 0) issue_v_ck(ch - 1);
         } else {
             if (ch > 0) prefetch_dy(ch - 1);  // lands during the rest of this chunk
-            PROF(3)
             if (!mbar_wait(&bars[6], it & 1)) *abort_flag = 2;
             tc_fence_after();
-            PROF(4)
             // ---- S / dds epilogue: rows live on lanes 0-15 of each quadrant; 16 columns j per thread
             float s[16], dd[16];
             tmem_ld16(tS + lane_base + 16 * cq, s);
             tmem_ld16(tDds + lane_base + 16 * cq, dd);
             tmem_ld_wait();
-            if (lane < 16 && !(p.ablate & 16)) {
+            if (lane < 16) {
                 const float rt = Gc->rowt[srow], dq_t = sdqn[srow];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -590,15 +592,12 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             fence_async_smem();
             tc_fence_before();
         }
-        PROF(5)
         __syncthreads();  // #2
         if (*abort_flag) { ok = false; break; }
-        PROF(6)
 
         // =============== phase 3: group B MMAs (control) | feature-major epilogues (math) ==============
         if (is_ctrl) {
-            if (lane == 0 && (p.ablate & 4)) mma_commit(&bars[5]);
-            if (lane == 0 && !(p.ablate & 4)) {
+            if (lane == 0) {
                 tc_fence_after();
                 const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), adN = smem_u32(sdN), aDS = smem_u32(sDS), adS = smem_u32(sdS);
 #pragma unroll
@@ -617,7 +616,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
                 cp_async_wait_all();  // raw gates of chunk ch-1, fetched during the previous chunk
                 __syncwarp();
                 gates_compute(&GR[(ch - 1) & 1], &G[(ch - 1) & 1]);
-                vec_fetch(p, bh, ch - 1, svec + ((ch - 1) & 1) * (2 * L + D));
+                vec_fetch(p, bh, sbh, ch - 1, svec + ((ch - 1) & 1) * kVecFloats);
                 if (ch > 1) gates_fetch(p, b, h, bh, ch - 2, &GR[ch & 1]);
                 cp_async_commit();
             }
@@ -626,7 +625,6 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             const uint32_t xoff = (uint32_t)(x >> 6) * kBoxBytes + (x & 7) * 2;
             const uint32_t xch8 = (x & 63) >> 3;
             auto tile_at = [&](const unsigned char* tile, int pos) {
-                if (p.ablate & 128) return 1.f;
                 return __bfloat162float(*reinterpret_cast<const bf16*>(tile + xoff + swz(pos, xch8)));
             };
             const float n_x = nk[x], dn_x = dn_in[x];
@@ -644,68 +642,59 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
                 for (int i = 0; i < 16; ++i) acc += bq[i] * tile_at(sQ, 16 * cq + i);
                 sdnp[cq * D + x] = acc;  // dn partial over this quarter of the positions
             }
-            PROF(7)
             if (!mbar_wait(&bars[5], it & 1)) *abort_flag = 3;
             tc_fence_after();
-            PROF(8)
-            if (!(p.ablate & 2)) {
-            const size_t obase = (((size_t)b * p.T + t0 + 16 * cq) * p.H + h) * D + x;
-            const size_t ostride = (size_t)p.H * D;
+            const size_t rowbase = (size_t)b * p.T + t0 + 16 * cq;
+            const size_t qstride = (size_t)p.H * dqk, vstride = (size_t)p.H * dhv;
+            const size_t qbase = (size_t)vh * qk_plane + rowbase * qstride + qcol + x;
             const int nlive = min(16, Lc - 16 * cq);  // positions of this quarter inside the sequence
             float a1[16], a2[16], cf[16];
             // dV = dVi + a dVe
-            if (!(p.ablate & 256)) {
             tmem_ld16(tVi + lane_base + 16 * cq, a1);
             tmem_ld16(tVe + lane_base + 16 * cq, a2);
             tmem_ld_wait();
-            }
             load16(Gc->a, cf);
             {
-                GT* o = reinterpret_cast<GT*>(p.dv) + obase;
+                const size_t ostride = vstride;
+                OT* o = reinterpret_cast<OT*>(p.dv) + (size_t)qh * v_plane + rowbase * vstride + vcol + x;
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
-                    if (i < nlive && !(p.ablate & 1)) stf(o, (size_t)i * ostride, a1[i] + cf[i] * a2[i]);
+                    if (i < nlive) stf(o, (size_t)i * ostride, a1[i] + cf[i] * a2[i]);
             }
             // dQ = acc + b dqn n
-            if (!(p.ablate & 256)) {
             tmem_ld16(tQ + lane_base + 16 * cq, a1);
             tmem_ld_wait();
-            }
             load16(sbq, cf);
+            const size_t ostride = qstride;
             {
-                GT* o = reinterpret_cast<GT*>(p.dq) + obase;
+                OT* o = reinterpret_cast<OT*>(p.dq) + qbase;
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
-                    if (i < nlive && !(p.ablate & 1)) stf(o, (size_t)i * ostride, a1[i] + cf[i] * n_x);
+                    if (i < nlive) stf(o, (size_t)i * ostride, a1[i] + cf[i] * n_x);
             }
             // dK = dKi + a (dKe + dn+) ;  w = dK . k
-            if (!(p.ablate & 256)) {
             tmem_ld16(tKi + lane_base + 16 * cq, a1);
             tmem_ld16(tKe + lane_base + 16 * cq, a2);
             tmem_ld_wait();
-            }
             load16(Gc->a, cf);
             {
-                GT* o = reinterpret_cast<GT*>(p.dk) + obase;
+                OT* o = reinterpret_cast<OT*>(p.dk) + qbase;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int pos = 16 * cq + i;
                     const float v = a1[i] + cf[i] * (a2[i] + dn_x);
-                    if (i < nlive && !(p.ablate & 1)) stf(o, (size_t)i * ostride, v);
+                    if (i < nlive) stf(o, (size_t)i * ostride, v);
                     a1[i] = v * tile_at(sK, pos);
                 }
             }
-            const float wsum = (p.ablate & 64) ? a1[0] : butterfly16(a1, lane);
+            const float wsum = butterfly16(a1, lane);
             if ((lane & 1) == 0) {
                 const int pos = 16 * cq + butterfly_index(lane);
                 part[(8 + qd) * L + pos] = wsum;
             }
-            }
         }
-        PROF(9)
         __syncthreads();  // #3
         if (*abort_flag) { ok = false; break; }
-        PROF(10)
 
         // =============== phase 4: gate gradients (control) | dC pass, dn (math) =======================
         if (is_ctrl) {
@@ -733,7 +722,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             for (int e = 0; e < 2; ++e) {
                 int t = lane + 32 * e;
                 if (t < Lc) {
-                    size_t gi = ((size_t)b * p.T + t0 + t) * p.H + h;
+                    size_t gi = (size_t)sub * g_plane + ((size_t)b * p.T + t0 + t) * p.H + h;
                     p.dfg[gi] = (run + sf[e]) * (1.f - stable_sigmoid(Gc->fg[t]));
                     p.dig[gi] = wv[e];
                 }
@@ -746,12 +735,11 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             const int c0 = 32 * cq;
             const float gn = (ch > 0) ? G[(ch - 1) & 1].g : 1.f;
             float v[32];
-            if (!(p.ablate & 32)) {
             tmem_ld32(tC + lane_base + c0, v);
             tmem_ld_wait();
             put_row<4>(sdCb + (cq >> 1) * kStateBox, x, 4 * (cq & 1), v);
             if (ch == 0 && p.odC) {
-                float* oc = p.odC + (size_t)bh * D * D + (size_t)x * D + c0;
+                float* oc = p.odC + ((size_t)bh * dhv + vh * D + x) * dqk + qh * D + c0;
 #pragma unroll
                 for (int q4 = 0; q4 < 8; ++q4)
                     *reinterpret_cast<float4*>(oc + 4 * q4) = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
@@ -762,23 +750,14 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
                 tmem_st32(tC + lane_base + c0, v);
                 tmem_st_wait();
             }
-            }
             fence_async_smem();
             tc_fence_before();
         }
-        PROF(11)
         __syncthreads();  // #4
-        PROF(12)
     }
-#undef PROF
-#ifdef XL_TC_PROFILE
-    // slots 0..15: math thread 0, 16..31: control lane 0 (CTA 0 only)
-    if (p.prof && bh == 0 && (tid == 0 || tid == kMathThreads))
-        for (int i = 0; i < 13; ++i) p.prof[(tid == 0 ? 0 : 16) + i] = pacc[i];
-#endif
 
     if (ok) {
-        if (p.odn && tid < D) p.odn[(size_t)bh * D + tid] = sdn[(it & 1) * D + tid];
+        if (p.odn && tid < D && once) p.odn[(size_t)bh * dqk + qh * D + tid] = sdn[(it & 1) * D + tid];
     } else if (tid == 0) {
         atomicCAS(p.status, 0, 200 + *abort_flag);
     }
@@ -790,17 +769,107 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// dy_t . ytil_t over all of a head's v columns, for heads split into sub-heads: one warp per (position, head).
+template <typename GT>
+__global__ void __launch_bounds__(256) mlstm_bw_rowdot(const GT* __restrict__ dy, const bf16* __restrict__ ytil,
+                                                       float* __restrict__ dotv, int B, int H, int T, int dhv) {
+    const int lane = threadIdx.x & 31;
+    const size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);  // (b*T + t)*H + h
+    if (row >= (size_t)B * T * H) return;
+    float acc = 0.f;
+    for (int c = 4 * lane; c < dhv; c += 128) {
+        float d[4];
+        if (sizeof(GT) == 4) {
+            const float4 t4 = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(dy) + row * dhv + c));
+            d[0] = t4.x; d[1] = t4.y; d[2] = t4.z; d[3] = t4.w;
+        } else {
+            const uint2 t2 = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(dy) + row * dhv + c));
+            const float2 lo = unpack_bf16(t2.x), hi = unpack_bf16(t2.y);
+            d[0] = lo.x; d[1] = lo.y; d[2] = hi.x; d[3] = hi.y;
+        }
+        const uint2 y2 = __ldg(reinterpret_cast<const uint2*>(ytil + row * dhv + c));
+        const float2 y0 = unpack_bf16(y2.x), y1 = unpack_bf16(y2.y);
+        acc += d[0] * y0.x + d[1] * y0.y + d[2] * y1.x + d[3] * y1.y;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+        const int h = (int)(row % H);
+        const size_t bt = row / H;
+        dotv[((size_t)(bt / T) * H + h) * T + bt % T] = acc;
+    }
+}
+
+// out[i] = sum over `np` planes of part[p][i], four elements per thread (n is a multiple of 4).
+template <typename OT>
+__global__ void __launch_bounds__(256) sum_planes(const float* __restrict__ part, size_t plane, int np, OT* __restrict__ out,
+                                                  size_t n4) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n4) return;
+    float4 acc = __ldcs(reinterpret_cast<const float4*>(part) + i);
+    for (int q = 1; q < np; ++q) {
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(part + (size_t)q * plane) + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (sizeof(OT) == 4) {
+        reinterpret_cast<float4*>(out)[i] = acc;
+    } else {
+        uint2 pk;
+        pk.x = pack_bf16(acc.x, acc.y); pk.y = pack_bf16(acc.z, acc.w);
+        reinterpret_cast<uint2*>(out)[i] = pk;
+    }
+}
+// Scalar tail-safe variant for the gate gradients ([B, T, H] need not be a multiple of 4).
+__global__ void __launch_bounds__(256) sum_planes_scalar(const float* __restrict__ part, size_t plane, int np,
+                                                         float* __restrict__ out, size_t n) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    float acc = part[i];
+    for (int q = 1; q < np; ++q) acc += part[(size_t)q * plane + i];
+    out[i] = acc;
+}
 
 }  // namespace bw
 
-long long* tc_debug_prof();
 bool tc_make_map3(CUtensorMap* m, const void* base, int B, int T, int W);
 bool tc_make_map2(CUtensorMap* m, const void* base, uint64_t rows, int W, int box_rows);
 
-int mlstm_bw_tc_launch(cudaStream_t st, const MlstmBwArgs& a, const void* saved, int gdtype) {
+namespace {
+struct BwPlanes {
+    size_t qk, v, g, dot, total;  // byte offsets of the dq | dk | dv | dig | dfg | dot regions follow from these sizes
+};
+BwPlanes bw_planes(int B, int H, int T, int dqk, int dhv) {
+    BwPlanes w;
+    const int nq = dqk / bw::D, nv = dhv / bw::D;
+    w.qk = align_up((size_t)nv * B * T * H * dqk * sizeof(float), 256);
+    w.v = align_up((size_t)nq * B * T * H * dhv * sizeof(float), 256);
+    w.g = align_up((size_t)nq * nv * B * T * H * sizeof(float), 256);
+    w.dot = align_up((size_t)B * H * T * sizeof(float), 256);
+    w.total = 2 * w.qk + w.v + 2 * w.g + w.dot;
+    return w;
+}
+}  // namespace
+
+size_t mlstm_tc_bw_workspace_bytes(int B, int H, int T, int dqk, int dhv) {
+    if (mlstm_tc_subheads(dqk, dhv) <= 1) return 0;
+    return bw_planes(B, H, T, dqk, dhv).total;
+}
+
+template <typename GT, typename OT, bool WIDE>
+static int bw_launch_kernel(cudaStream_t st, const bw::Params& p, int ctas) {
+    using namespace bw;
+    static bool attr_set = false;  // one flag per instantiation
+    const size_t smem = Smem::total + 1024;
+    if (!attr_set) {
+        XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<GT, OT, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    mlstm_bw_tc<GT, OT, WIDE><<<ctas, kThreads, smem, st>>>(p);
+    XL_LAUNCH_OK("mlstm_bw_tc");
+    return XLSTM_OK;
+}
+
+int mlstm_bw_tc_launch(cudaStream_t st, const MlstmBwArgs& a, const void* saved, int gdtype, void* workspace,
+                       size_t workspace_bytes) {
     using namespace bw;
     if (((uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.ytil | (uintptr_t)a.dytil | (uintptr_t)a.dq |
          (uintptr_t)a.dk | (uintptr_t)a.dv | (uintptr_t)saved) & 15) {
@@ -809,40 +878,59 @@ int mlstm_bw_tc_launch(cudaStream_t st, const MlstmBwArgs& a, const void* saved,
     }
     Params p = {};
     const int BH = a.B * a.H;
+    p.nq = a.dqk / D; p.nv = a.dhv / D;
+    const int nsub = p.nq * p.nv;
+    const bool gbf = gdtype == XLSTM_BF16;
     p.savedC = (const bf16*)saved;
-    p.savedn = (const float*)((const char*)saved + mlstm_tc_saved_C_bytes(BH, a.NC));
-    if (!tc_make_map3(&p.tmq, a.q, a.B, a.T, a.H * D) || !tc_make_map3(&p.tmk, a.k, a.B, a.T, a.H * D) ||
-        !tc_make_map3(&p.tmv, a.v, a.B, a.T, a.H * D) ||
-        !tc_make_map2(&p.tmc, p.savedC, (uint64_t)BH * (a.NC + 1) * D, D, D)) {
+    p.savedn = (const float*)((const char*)saved + mlstm_tc_saved_C_bytes(BH * nsub, a.NC));
+    if (!tc_make_map3(&p.tmq, a.q, a.B, a.T, a.H * a.dqk) || !tc_make_map3(&p.tmk, a.k, a.B, a.T, a.H * a.dqk) ||
+        !tc_make_map3(&p.tmv, a.v, a.B, a.T, a.H * a.dhv) ||
+        !tc_make_map2(&p.tmc, p.savedC, (uint64_t)BH * nsub * (a.NC + 1) * D, D, D)) {
         set_error("mlstm_bw: cuTensorMapEncodeTiled failed");
         return XLSTM_ERR_CUDA;
     }
     p.ig = a.ig; p.fg = a.fg; p.cm = a.cm; p.ytil = (const bf16*)a.ytil; p.msv = a.msv; p.psiv = a.psiv; p.qnv = a.qnv;
     p.dy = a.dytil; p.cdC = a.cdC; p.cdn = a.cdn; p.dq = a.dq; p.dk = a.dk; p.dv = a.dv; p.dig = a.dig; p.dfg = a.dfg;
-    p.odC = a.odC; p.odn = a.odn; p.B = a.B; p.H = a.H; p.T = a.T; p.NC = a.NC; p.gbf16 = gdtype == XLSTM_BF16;
-    p.prof = tc_debug_prof();
-    {
-        static const char* ab = getenv("XLSTM_ABLATE");
-        p.ablate = ab ? atoi(ab) : 0;
-    }
+    p.odC = a.odC; p.odn = a.odn; p.B = a.B; p.H = a.H; p.T = a.T; p.NC = a.NC; p.gbf16 = gbf;
     p.status = tc_status_ptr();
     if (!p.status) { set_error("mlstm_bw: cannot resolve the device status word"); return XLSTM_ERR_CUDA; }
-    size_t smem = Smem::total + 1024;
-    static bool attr_set[2] = {false, false};
-    if (gdtype == XLSTM_BF16) {
-        if (!attr_set[1]) {
-            XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_set[1] = true;
-        }
-        mlstm_bw_tc<bf16><<<BH, kThreads, smem, st>>>(p);
-    } else {
-        if (!attr_set[0]) {
-            XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_set[0] = true;
-        }
-        mlstm_bw_tc<float><<<BH, kThreads, smem, st>>>(p);
+    if (nsub == 1) return gbf ? bw_launch_kernel<bf16, bf16, false>(st, p, BH) : bw_launch_kernel<float, float, false>(st, p, BH);
+
+    // wide heads: fp32 partial planes in the workspace, summed into the caller's buffers afterwards
+    const BwPlanes w = bw_planes(a.B, a.H, a.T, a.dqk, a.dhv);
+    if (!workspace || workspace_bytes < w.total || ((uintptr_t)workspace & 15)) {
+        set_error("mlstm_bw: heads wider than 128 need a 16-byte aligned workspace of %zu B beside the state record (got %zu)",
+                  w.total, workspace_bytes);
+        return XLSTM_ERR_WORKSPACE;
     }
-    XL_LAUNCH_OK("mlstm_bw_tc");
+    char* ws = (char*)workspace;
+    float* pdq = (float*)ws; float* pdk = (float*)(ws + w.qk); float* pdv = (float*)(ws + 2 * w.qk);
+    float* pdig = (float*)(ws + 2 * w.qk + w.v); float* pdfg = (float*)(ws + 2 * w.qk + w.v + w.g);
+    float* dotv = (float*)(ws + 2 * w.qk + w.v + 2 * w.g);
+    const size_t rows = (size_t)a.B * a.T * a.H;
+    p.dq = pdq; p.dk = pdk; p.dv = pdv; p.dig = pdig; p.dfg = pdfg;
+    p.qk_plane = rows * a.dqk; p.v_plane = rows * a.dhv; p.g_plane = rows;
+    if (p.nv > 1) {
+        if (gbf) mlstm_bw_rowdot<bf16><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const bf16*)a.dytil, p.ytil, dotv, a.B, a.H, a.T, a.dhv);
+        else mlstm_bw_rowdot<float><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const float*)a.dytil, p.ytil, dotv, a.B, a.H, a.T, a.dhv);
+        XL_LAUNCH_OK("mlstm_bw_rowdot");
+        p.dotv = dotv;
+    }
+    int rc = gbf ? bw_launch_kernel<bf16, float, true>(st, p, BH * nsub) : bw_launch_kernel<float, float, true>(st, p, BH * nsub);
+    if (rc) return rc;
+    auto sum_to = [&](const float* part, size_t plane, int np, void* out) {
+        const size_t n4 = plane / 4;
+        if (gbf) sum_planes<bf16><<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(part, plane, np, (bf16*)out, n4);
+        else sum_planes<float><<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(part, plane, np, (float*)out, n4);
+        count_launch();
+    };
+    sum_to(pdq, p.qk_plane, p.nv, a.dq);
+    sum_to(pdk, p.qk_plane, p.nv, a.dk);
+    sum_to(pdv, p.v_plane, p.nq, a.dv);
+    sum_planes_scalar<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(pdig, rows, nsub, a.dig, rows);
+    sum_planes_scalar<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(pdfg, rows, nsub, a.dfg, rows);
+    XL_LAUNCH_OK("mlstm_bw sum_planes");
+    count_launch();
     return XLSTM_OK;
 }
 

@@ -58,6 +58,13 @@ struct Params {
     float *oC, *on, *om;
     int B, H, T, NC;
     int states_only;  // 1: walk the state recurrence only (the backward's recompute pass)
+    // Heads wider than 128 run as nq x nv sub-heads of 128 x 128, one CTA each: sub-head (qh, vh) takes
+    // columns qh*128.. of q and k, vh*128.. of v, and owns block (vh, qh) of the matrix memory. The
+    // numerator of the output is additive over qh and q.n likewise, so with nq > 1 the CTAs write
+    // unnormalised partials (num, qnpart) and a small second kernel sums and normalises them.
+    int nq, nv;
+    float* num;     // [nq][B*T][H*nv*128] fp32 numerators (nq > 1 only)
+    float* qnpart;  // [nq][B*H][T] partial q.n (nq > 1 only)
     int* status;
 };
 
@@ -134,12 +141,20 @@ __device__ __forceinline__ float gates_compute(const GateRaw& r, float m_prev, G
     return mL;
 }
 
+// WIDE: heads split into sub-heads; the 128 x 128 instantiation folds all of that indexing away.
+template <bool WIDE>
 __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant__ Params p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool is_ctrl = warp == kMathWarps;
-    const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+    const int nq = WIDE ? p.nq : 1, nv = WIDE ? p.nv : 1;
+    const int nsub = nq * nv;
+    const int sbh = blockIdx.x, bh = sbh / nsub, sub = sbh % nsub, qh = sub / nv, vh = sub % nv;
+    const int b = bh / p.H, h = bh % p.H;
+    const int qcol = (h * nq + qh) * D, vcol = (h * nv + vh) * D;  // first column of this sub-head in q/k and in v/ytil
+    const int dqk = nq * D, dhv = nv * D;
+    const bool unnorm = nq > 1;
     const int qd = warp & 3, cq = (warp >> 2) & 3;
     const uint32_t lane_base = (uint32_t)(32 * qd) << 16;
     const int x = 32 * qd + lane;            // lane of a 128-lane accumulator
@@ -176,9 +191,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
         unsigned char* base = sm + Smem::q0 + (uint32_t)stage * 3 * kTileBytes;
         mbar_expect_tx(&bars[stage], (full ? 3 : 2) * kTileBytes);
         for (int cbx = 0; cbx < 2; ++cbx) {
-            if (full) tma_load_3d(base + 0 * kTileBytes + cbx * kBoxBytes, &p.tmq, &bars[stage], h * D + 64 * cbx, ch * L, b);
-            tma_load_3d(base + 1 * kTileBytes + cbx * kBoxBytes, &p.tmk, &bars[stage], h * D + 64 * cbx, ch * L, b);
-            tma_load_3d(base + 2 * kTileBytes + cbx * kBoxBytes, &p.tmv, &bars[stage], h * D + 64 * cbx, ch * L, b);
+            if (full) tma_load_3d(base + 0 * kTileBytes + cbx * kBoxBytes, &p.tmq, &bars[stage], qcol + 64 * cbx, ch * L, b);
+            tma_load_3d(base + 1 * kTileBytes + cbx * kBoxBytes, &p.tmk, &bars[stage], qcol + 64 * cbx, ch * L, b);
+            tma_load_3d(base + 2 * kTileBytes + cbx * kBoxBytes, &p.tmv, &bars[stage], vcol + 64 * cbx, ch * L, b);
         }
     };
 
@@ -191,8 +206,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
         m_prev = gates_compute(graw, m_prev, &G[0]);
         if (p.NC > 1) gates_load(p, b, h, 1, graw);
     } else if (tid < D) {
-        nvec[tid] = p.cn ? p.cn[(size_t)bh * D + tid] : 0.f;
-        if (p.savedn) p.savedn[((size_t)bh * (p.NC + 1) + 0) * D + tid] = nvec[tid];
+        nvec[tid] = p.cn ? p.cn[(size_t)bh * dqk + qh * D + tid] : 0.f;
+        if (p.savedn) p.savedn[((size_t)sbh * (p.NC + 1) + 0) * D + tid] = nvec[tid];
     }
     __syncthreads();
     if (!is_ctrl) {
@@ -200,8 +215,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
         const int c0 = 32 * cq;
         float v[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = p.cC ? p.cC[(size_t)bh * D * D + (size_t)x * D + c0 + i] : 0.f;
-        bf16* rec = p.savedC ? p.savedC + ((size_t)bh * (p.NC + 1) + 0) * D * D + (size_t)x * D + c0 : nullptr;
+        for (int i = 0; i < 32; ++i) v[i] = p.cC ? p.cC[((size_t)bh * dhv + vh * D + x) * dqk + qh * D + c0 + i] : 0.f;
+        bf16* rec = p.savedC ? p.savedC + ((size_t)sbh * (p.NC + 1) + 0) * D * D + (size_t)x * D + c0 : nullptr;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             uint4 pk = pack8(v + 8 * q);
@@ -343,10 +358,15 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
                 const float qn = rpart[tid] + rpart[L + tid] + rpart[2 * L + tid] + rpart[3 * L + tid] + Gc->b[tid] * sqn[tid];
                 const float mt = Gc->m[tid];
                 const float psi = fmaxf(fabsf(qn), expf(-mt));
-                sipsi[tid] = 1.f / psi;
-                if (tid < Lc) {
+                sipsi[tid] = unnorm ? 1.f : 1.f / psi;
+                if (tid < Lc && vh == 0) {
                     const size_t o = (size_t)bh * p.T + t0 + tid;
-                    p.msv[o] = mt; p.psiv[o] = psi; p.qnv[o] = qn;
+                    if (unnorm) {
+                        p.qnpart[(size_t)qh * p.B * p.H * p.T + o] = qn;
+                        if (qh == 0) p.msv[o] = mt;
+                    } else {
+                        p.msv[o] = mt; p.psiv[o] = psi; p.qnv[o] = qn;
+                    }
                 }
             }
             {   // n partial over this quarter of the positions: sum_j a_j K[j,x]
@@ -367,7 +387,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
                 float v[32];
                 tmem_ld32(tC + lane_base + c0, v);
                 tmem_ld_wait();
-                bf16* rec = p.savedC ? p.savedC + ((size_t)bh * (p.NC + 1) + ch + 1) * D * D + (size_t)x * D + c0 : nullptr;
+                bf16* rec = p.savedC ? p.savedC + ((size_t)sbh * (p.NC + 1) + ch + 1) * D * D + (size_t)x * D + c0 : nullptr;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     uint4 pk = pack8(v + 8 * q);
@@ -375,7 +395,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
                     if (rec) *reinterpret_cast<uint4*>(rec + 8 * q) = pk;
                 }
                 if (last && p.oC) {
-                    float* oc = p.oC + (size_t)bh * D * D + (size_t)x * D + c0;
+                    float* oc = p.oC + ((size_t)bh * dhv + vh * D + x) * dqk + qh * D + c0;
 #pragma unroll
                     for (int q = 0; q < 8; ++q)
                         *reinterpret_cast<float4*>(oc + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
@@ -391,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
             if (tid < D) {
                 const float nn = Gc->g * nvec[tid] + (npart[tid] + npart[D + tid]) + (npart[2 * D + tid] + npart[3 * D + tid]);
                 nvec[tid] = nn;
-                if (p.savedn) p.savedn[((size_t)bh * (p.NC + 1) + ch + 1) * D + tid] = nn;
+                if (p.savedn) p.savedn[((size_t)sbh * (p.NC + 1) + ch + 1) * D + tid] = nn;
             }
             if (full) {
                 if (!mbar_wait(&bars[4], ch & 1)) *abort_flag = 4;
@@ -400,13 +420,21 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
                 tmem_ld16(tHi + lane_base + 16 * cq, hi);
                 tmem_ld16(tHe + lane_base + 16 * cq, he);
                 tmem_ld_wait();
-                bf16* yo = p.ytil + (((size_t)b * p.T + t0 + 16 * cq) * p.H + h) * D + x;
-                const size_t ystride = (size_t)p.H * D;
+                const size_t ystride = (size_t)p.H * dhv;
+                const size_t yoff = ((size_t)b * p.T + t0 + 16 * cq) * ystride + vcol + x;
                 const int nlive = min(16, Lc - 16 * cq);
+                if (unnorm) {
+                    float* no = p.num + (size_t)qh * p.B * p.T * ystride + yoff;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int pos = 16 * cq + i;
-                    if (i < nlive) yo[(size_t)i * ystride] = __float2bfloat16_rn((hi[i] + Gc->b[pos] * he[i]) * sipsi[pos]);
+                    for (int i = 0; i < 16; ++i)
+                        if (i < nlive) no[(size_t)i * ystride] = hi[i] + Gc->b[16 * cq + i] * he[i];
+                } else {
+                    bf16* yo = p.ytil + yoff;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int pos = 16 * cq + i;
+                        if (i < nlive) yo[(size_t)i * ystride] = __float2bfloat16_rn((hi[i] + Gc->b[pos] * he[i]) * sipsi[pos]);
+                    }
                 }
             }
             fence_async_smem();
@@ -417,8 +445,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
     }
 
     if (ok) {
-        if (p.on && tid < D) p.on[(size_t)bh * D + tid] = nvec[tid];
-        if (p.om && tid == kMathThreads) p.om[bh] = m_prev;
+        if (p.on && tid < D && vh == 0) p.on[(size_t)bh * dqk + qh * D + tid] = nvec[tid];
+        if (p.om && tid == kMathThreads && sub == 0) p.om[bh] = m_prev;
     } else if (tid == 0) {
         atomicCAS(p.status, 0, 100 + *abort_flag);
     }
@@ -430,17 +458,65 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
     }
 }
 
+// Sum of the sub-heads' numerators and q.n partials, normaliser, output: one warp per (position, head).
+__global__ void __launch_bounds__(256) mlstm_fw_combine(const float* __restrict__ num, const float* __restrict__ qnpart,
+                                                        const float* __restrict__ msv, bf16* __restrict__ ytil,
+                                                        float* __restrict__ psiv, float* __restrict__ qnv, int B, int H,
+                                                        int T, int dhv, int nq) {
+    const int lane = threadIdx.x & 31;
+    const size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);  // (b*T + t)*H + h
+    if (row >= (size_t)B * T * H) return;
+    const int h = (int)(row % H);
+    const size_t bt = row / H;
+    const int t = (int)(bt % T), b = (int)(bt / T);
+    const size_t o = ((size_t)b * H + h) * T + t;
+    float qn = 0.f;
+    for (int q = 0; q < nq; ++q) qn += qnpart[(size_t)q * B * H * T + o];
+    const float psi = fmaxf(fabsf(qn), expf(-msv[o]));
+    if (lane == 0) { psiv[o] = psi; qnv[o] = qn; }
+    const float ipsi = 1.f / psi;
+    const size_t plane = (size_t)B * T * H * dhv;
+    for (int c = 4 * lane; c < dhv; c += 128) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q = 0; q < nq; ++q) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(num + (size_t)q * plane + row * dhv + c));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        uint2 pk;
+        pk.x = pack_bf16(acc.x * ipsi, acc.y * ipsi);
+        pk.y = pack_bf16(acc.z * ipsi, acc.w * ipsi);
+        *reinterpret_cast<uint2*>(ytil + row * dhv + c) = pk;
+    }
+}
+
 }  // namespace fw
 
-int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved) {
+size_t mlstm_tc_fw_workspace_bytes(int B, int H, int T, int dqk, int dhv) {
+    const int nq = dqk / fw::D;
+    if (nq <= 1) return 0;
+    return align_up((size_t)nq * B * T * H * dhv * sizeof(float), 256) + align_up((size_t)nq * B * H * T * sizeof(float), 256);
+}
+
+int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved, void* workspace, size_t workspace_bytes) {
     using namespace fw;
     if (((uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.ytil | (uintptr_t)saved) & 15) {
         set_error("mlstm_fw (tensor-core path): q, k, v, ytil and the state record must be 16-byte aligned");
         return XLSTM_ERR_ARG;
     }
     Params p = {};
-    if (!tc_make_map3(&p.tmq, a.q, a.B, a.T, a.H * D) || !tc_make_map3(&p.tmk, a.k, a.B, a.T, a.H * D) ||
-        !tc_make_map3(&p.tmv, a.v, a.B, a.T, a.H * D)) {
+    p.nq = a.dqk / D; p.nv = a.dhv / D;
+    const int nsub = p.nq * p.nv;
+    if (p.nq > 1 && !a.states_only) {
+        const size_t need = mlstm_tc_fw_workspace_bytes(a.B, a.H, a.T, a.dqk, a.dhv);
+        if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15)) {
+            set_error("mlstm_fw: heads wider than 128 in q/k need a 16-byte aligned workspace of %zu B (got %zu)", need, workspace_bytes);
+            return XLSTM_ERR_WORKSPACE;
+        }
+        p.num = (float*)workspace;
+        p.qnpart = (float*)((char*)workspace + align_up((size_t)p.nq * a.B * a.T * a.H * a.dhv * sizeof(float), 256));
+    }
+    if (!tc_make_map3(&p.tmq, a.q, a.B, a.T, a.H * a.dqk) || !tc_make_map3(&p.tmk, a.k, a.B, a.T, a.H * a.dqk) ||
+        !tc_make_map3(&p.tmv, a.v, a.B, a.T, a.H * a.dhv)) {
         set_error("mlstm_fw: cuTensorMapEncodeTiled failed");
         return XLSTM_ERR_CUDA;
     }
@@ -448,7 +524,7 @@ int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved) {
     p.ytil = (bf16*)a.ytil; p.msv = a.msv; p.psiv = a.psiv; p.qnv = a.qnv;
     if (saved) {
         p.savedC = (bf16*)saved;
-        p.savedn = (float*)((char*)saved + mlstm_tc_saved_C_bytes(a.B * a.H, a.NC));
+        p.savedn = (float*)((char*)saved + mlstm_tc_saved_C_bytes(a.B * a.H * nsub, a.NC));
     }
     p.oC = a.oC; p.on = a.on; p.om = a.om;
     p.B = a.B; p.H = a.H; p.T = a.T; p.NC = a.NC;
@@ -458,11 +534,19 @@ int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved) {
     static bool attr_set = false;
     const size_t smem = Smem::total + 1024;
     if (!attr_set) {
-        XL_CUDA(cudaFuncSetAttribute(mlstm_fw_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        XL_CUDA(cudaFuncSetAttribute(mlstm_fw_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        XL_CUDA(cudaFuncSetAttribute(mlstm_fw_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set = true;
     }
-    mlstm_fw_tc<<<a.B * a.H, kThreads, smem, st>>>(p);
+    if (nsub == 1) mlstm_fw_tc<false><<<a.B * a.H, kThreads, smem, st>>>(p);
+    else mlstm_fw_tc<true><<<a.B * a.H * nsub, kThreads, smem, st>>>(p);
     XL_LAUNCH_OK("mlstm_fw_tc");
+    if (p.nq > 1 && !a.states_only) {
+        const size_t rows = (size_t)a.B * a.T * a.H;
+        mlstm_fw_combine<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(p.num, p.qnpart, a.msv, (bf16*)a.ytil, a.psiv, a.qnv, a.B, a.H,
+                                                                     a.T, a.dhv, p.nq);
+        XL_LAUNCH_OK("mlstm_fw_combine");
+    }
     return XLSTM_OK;
 }
 

@@ -154,3 +154,25 @@ def test_tensor_core_backward_recomputes_chunk_states_when_no_record_is_kept():
     b, _ = _run((2, 2, 200, 128, 128), 64, torch.bfloat16, torch.float32, seed=24, save_states=False)
     for n in BW:
         assert np.array_equal(a[n], b[n]), n
+
+
+# ---- heads wider than 128: run as 128 x 128 sub-heads whose partial results are summed ---------
+@pytest.mark.parametrize("shape", [(1, 2, 200, 256, 256), (2, 1, 70, 128, 256), (1, 2, 130, 256, 128), (1, 1, 64, 384, 256)])
+@pytest.mark.parametrize("gdtype", [torch.float32, torch.bfloat16])
+def test_wide_heads_match_oracle(shape, gdtype):
+    from gpu_util import xl
+    got, ref = _run(shape, 64, torch.bfloat16, gdtype, seed=31)
+    assert xl._lib.lib.xlstm_device_status() == 0, xl._lib.lib.xlstm_last_error()
+    _assert_close(got, ref, 2e-2, FW + BW)
+
+
+def test_wide_heads_with_carry_and_recompute():
+    from gpu_util import xl
+    B, H, T, dqk, dhv = 2, 2, 150, 256, 256
+    r = np.random.default_rng(13)
+    f32 = lambda a: a.astype(np.float32).astype(np.float64)
+    carry = (f32(r.standard_normal((B * H, dhv, dqk))), f32(r.standard_normal((B * H, dqk))), f32(r.standard_normal((B * H,))))
+    dstate = (f32(r.standard_normal((B * H, dhv, dqk)) * 0.1), f32(r.standard_normal((B * H, dqk)) * 0.1))
+    got, ref = _run((B, H, T, dqk, dhv), 64, torch.bfloat16, torch.float32, carry=carry, dstate=dstate, save_states=False)
+    assert xl._lib.lib.xlstm_device_status() == 0, xl._lib.lib.xlstm_last_error()
+    _assert_close(got, ref, 2e-2, FW + BW)
