@@ -304,6 +304,8 @@ def run_ours(args):
 
 
 LM_CFG = dict(vocab=50304, d=1024, blocks=24, heads=8, dqk=128, dhv=128, slstm_every=8, slstm_heads=4, B=8, T=4096)
+# configs[3] at its own widths: d = 2048, mLSTM 8 heads x 256, sLSTM 4 heads x 512
+LM_CFG_FULL = dict(vocab=50304, d=2048, blocks=24, heads=8, dqk=256, dhv=256, slstm_every=8, slstm_heads=4, B=8, T=4096)
 
 
 def run_lm(args):
@@ -321,7 +323,7 @@ def run_lm(args):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    c = dict(LM_CFG)
+    c = dict(LM_CFG_FULL if args.lm_full else LM_CFG)
     if args.lm_blocks:
         c["blocks"] = args.lm_blocks
     up = (8 * c["d"] // 3 + 7) // 8 * 8
@@ -329,7 +331,9 @@ def run_lm(args):
     slstm_at = tuple(i for i in range(c["blocks"]) if i % c["slstm_every"] == 0)
     p = M.init_lm_params(rng, c["vocab"], c["d"], c["blocks"], c["heads"], c["dqk"], c["dhv"], up, std=0.02, slstm_at=slstm_at,
                          nh_s=c["slstm_heads"])
-    lm = layers.build_lm(p, c["heads"], c["dqk"], c["dhv"], nh_s=c["slstm_heads"], tied=True, bf16=True)
+    # the full widths need both memory levers to fit 24 blocks in HBM; the reduced model runs without them
+    lm = layers.build_lm(p, c["heads"], c["dqk"], c["dhv"], nh_s=c["slstm_heads"], tied=True, bf16=True,
+                         remat=bool(args.lm_full), head_rows=4096 if args.lm_full else 0)
     nparams = sum(q.w.numel() for q in lm.params())
     buckets = dp.attach(lm)
     B, T = c["B"], c["T"]
@@ -382,11 +386,13 @@ def run_lm(args):
         line = {"metric": "train_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": "xlstm_lm_train_step (reduced stand-in for configs[3]: d=1024, mLSTM 8x128, sLSTM 4x256)",
+                "config": {"workload": ("xlstm_lm_train_step (configs[3] widths: d=%d, mLSTM %dx%d, sLSTM %dx%d)" if args.lm_full else
+                                        "xlstm_lm_train_step (reduced stand-in for configs[3]: d=%d, mLSTM %dx%d, sLSTM %dx%d)")
+                                       % (c["d"], c["heads"], c["dqk"], c["slstm_heads"], c["d"] // c["slstm_heads"]),
                            "blocks": c["blocks"], "vocab": c["vocab"], "params": nparams, "per_gpu_batch": [B, T],
                            "parallelism": "dp%d (gradient all-reduce per block, overlapped with backward)" % world,
                            "l2": "activations far larger than L2"},
-                "loss": lv,
+                "loss": lv, "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
                 "roofline": {"kernel": "whole step (6*P*tokens dense FLOPs)", "bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12,
                              "peak": sustained, "unit": "TFLOP/s", "frac": flops / (ms * 1e-3) / 1e12 / sustained, "traffic": None,
                              "peak_source": pk["src"] + " (sustained)"},
@@ -477,6 +483,7 @@ def main():
     ap.add_argument("--workload", default="mlstm", choices=["mlstm", "lm", "ops"],
                     help="mlstm: configs[1] layer kernel (headline); lm: training step; ops: the other hot-path kernels alone")
     ap.add_argument("--lm-blocks", type=int, default=0, help="override the LM depth (development)")
+    ap.add_argument("--lm-full", action="store_true", help="LM workload at the full widths of configs[3] (d=2048, heads of 256 / 512)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

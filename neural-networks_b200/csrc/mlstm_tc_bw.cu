@@ -502,18 +502,14 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             dot += __shfl_xor_sync(0xffffffffu, dot, 4);
             if (l8 == 0) {
                 // dqn_t = sign(qn)(-dot/psi) where the q.n term, not the floor, set psi
-                float r = 0.f, u = 0.f;
+                float r = 0.f;
                 if (dotv) dot = spsi[2 * L + D + prow];  // the row dot over all of the head's v columns
                 if (prow < Lc && once) {
                     const float qn = sqn[prow];
                     if (fabsf(qn) > Gc->emm[prow]) r = (qn > 0.f ? -1.f : 1.f) * dot / psi_r;
-                    // dq_t . q_t: scaling q_t scales the numerator and q.n alike, so the row dot is
-                    // dy_t . ytil_t + dqn_t (q_t . n_t) without touching dq
-                    if (sub == 0) u = dot + r * qn;
                 }
                 sdqn[prow] = r;
                 sbq[prow] = bt * r;
-                part[4 * L + prow] = u;
             }
             fence_async_smem();
         } else {
@@ -636,10 +632,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
                 }
             };
             {
-                float acc = 0.f, bq[16];
-                load16(sbq, bq);
+                float acc = 0.f;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) acc += bq[i] * tile_at(sQ, 16 * cq + i);
+                for (int i = 0; i < 16; ++i) acc += sbq[16 * cq + i] * tile_at(sQ, 16 * cq + i);
                 sdnp[cq * D + x] = acc;  // dn partial over this quarter of the positions
             }
             if (!mbar_wait(&bars[5], it & 1)) *abort_flag = 3;
@@ -648,43 +643,65 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             const size_t qstride = (size_t)p.H * dqk, vstride = (size_t)p.H * dhv;
             const size_t qbase = (size_t)vh * qk_plane + rowbase * qstride + qcol + x;
             const int nlive = min(16, Lc - 16 * cq);  // positions of this quarter inside the sequence
-            float a1[16], a2[16], cf[16];
+            float a1[16], a2[16];
+            // per-position scale factors are read four at a time right where they are used (short live ranges)
+            auto quad = [&](const float* src, int i4) { return *reinterpret_cast<const float4*>(src + 16 * cq + 4 * i4); };
             // dV = dVi + a dVe
             tmem_ld16(tVi + lane_base + 16 * cq, a1);
             tmem_ld16(tVe + lane_base + 16 * cq, a2);
             tmem_ld_wait();
-            load16(Gc->a, cf);
             {
-                const size_t ostride = vstride;
                 OT* o = reinterpret_cast<OT*>(p.dv) + (size_t)qh * v_plane + rowbase * vstride + vcol + x;
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    if (i < nlive) stf(o, (size_t)i * ostride, a1[i] + cf[i] * a2[i]);
+                for (int i4 = 0; i4 < 4; ++i4) {
+                    const float4 c4 = quad(Gc->a, i4);
+                    const float cfv[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = 4 * i4 + e;
+                        if (i < nlive) stf(o, (size_t)i * vstride, a1[i] + cfv[e] * a2[i]);
+                    }
+                }
             }
-            // dQ = acc + b dqn n
+            // dQ = acc + b dqn n ;  u = dQ . q. (u also equals dy.ytil + dqn (q.n), but taking it from the same
+            // rounded dS that forms dK keeps the errors of u and w correlated, so they cancel in the suffix
+            // sums of u - w as the exact terms do.)
             tmem_ld16(tQ + lane_base + 16 * cq, a1);
             tmem_ld_wait();
-            load16(sbq, cf);
-            const size_t ostride = qstride;
             {
                 OT* o = reinterpret_cast<OT*>(p.dq) + qbase;
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    if (i < nlive) stf(o, (size_t)i * ostride, a1[i] + cf[i] * n_x);
+                for (int i4 = 0; i4 < 4; ++i4) {
+                    const float4 c4 = quad(sbq, i4);
+                    const float cfv[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = 4 * i4 + e;
+                        const float v = a1[i] + cfv[e] * n_x;
+                        if (i < nlive) stf(o, (size_t)i * qstride, v);
+                        a1[i] = v * tile_at(sQ, 16 * cq + i);
+                    }
+                }
             }
+            const float usum = butterfly16(a1, lane);
+            if ((lane & 1) == 0) part[(4 + qd) * L + 16 * cq + butterfly_index(lane)] = usum;
             // dK = dKi + a (dKe + dn+) ;  w = dK . k
             tmem_ld16(tKi + lane_base + 16 * cq, a1);
             tmem_ld16(tKe + lane_base + 16 * cq, a2);
             tmem_ld_wait();
-            load16(Gc->a, cf);
             {
                 OT* o = reinterpret_cast<OT*>(p.dk) + qbase;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int pos = 16 * cq + i;
-                    const float v = a1[i] + cf[i] * (a2[i] + dn_x);
-                    if (i < nlive) stf(o, (size_t)i * ostride, v);
-                    a1[i] = v * tile_at(sK, pos);
+                for (int i4 = 0; i4 < 4; ++i4) {
+                    const float4 c4 = quad(Gc->a, i4);
+                    const float cfv[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = 4 * i4 + e;
+                        const float v = a1[i] + cfv[e] * (a2[i] + dn_x);
+                        if (i < nlive) stf(o, (size_t)i * qstride, v);
+                        a1[i] = v * tile_at(sK, 16 * cq + i);
+                    }
                 }
             }
             const float wsum = butterfly16(a1, lane);
@@ -702,7 +719,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 int t = lane + 32 * e;
-                float u = part[4 * L + t];
+                float u = part[4 * L + t] + part[5 * L + t] + part[6 * L + t] + part[7 * L + t];
                 wv[e] = part[8 * L + t] + part[9 * L + t] + part[10 * L + t] + part[11 * L + t];
                 dF[e] = (t < Lc) ? (u - wv[e]) : 0.f;
             }

@@ -66,6 +66,9 @@ class Linear:
     def params(self):
         return [self.w, self.b]
 
+    def release(self):
+        self.x = None
+
 
 class RmsNorm:
     """Grouped RMSNorm, eps 1e-6, gamma undecayed (reference: gpu::RmsNorm, src/gpu/rms_norm.rs)."""
@@ -89,6 +92,9 @@ class RmsNorm:
 
     def params(self):
         return [self.gamma]
+
+    def release(self):
+        self.x = self.inv = None
 
 
 class MLstm:
@@ -140,6 +146,11 @@ class MLstm:
             out += l.params()
         return out + self.hn.params()
 
+    def release(self):
+        self.o = self.core_in = self.fused = self.yhat = self.hc = None
+        for l in (self.lq, self.lk, self.lv, self.lo, self.li, self.lf, self.lout, self.hn):
+            l.release()
+
 
 class SLstm:
     """gpu::SLstm (src/gpu/slstm.rs:91-1335): hoisted x.Wx GEMM -> fused recurrent loop; the
@@ -183,6 +194,9 @@ class SLstm:
     def params(self):
         return [self.wx, self.wh, self.b]
 
+    def release(self):
+        self.x = self.g = self.slabs = None
+
 
 class Block:
     """gpu::Block<C> (src/gpu/block.rs:435-1185): z = x + [post](cell(norm1 x));
@@ -224,12 +238,25 @@ class Block:
             out += l.params()
         return out
 
+    def release(self):
+        """Drops everything the forward saved for the backward."""
+        self.gate_pre = self.value = self.gate_act = None
+        for l in (self.cell, self.n1, self.n2, self.lg, self.lv, self.ld):
+            l.release()
+        if self.post is not None:
+            self.post.release()
+
 
 class Lm:
     """gpu::Lm (src/gpu/lm.rs:25-163): embedding -> blocks -> RMSNorm -> head (fp32) -> SoftCap -> CE.
-    `tied=True` uses the embedding table (transposed) as the head and sums its two gradients."""
+    `tied=True` uses the embedding table (transposed) as the head and sums its two gradients.
 
-    def __init__(self, table, blocks, gamma, head_w=None, head_b=None, cap=30.0, tied=False):
+    Two memory levers for wide models, both exact: `remat=True` keeps only each block's input and
+    re-runs the block's forward right before its backward; `head_rows=n` (tied head, through
+    `forward_backward`) walks the head GEMM, soft-cap and cross-entropy over n rows at a time, so the
+    [rows, vocab] logits never exist as a whole."""
+
+    def __init__(self, table, blocks, gamma, head_w=None, head_b=None, cap=30.0, tied=False, remat=False, head_rows=0):
         self.table = Param(table, False)
         self.blocks = blocks
         self.norm = RmsNorm(gamma)
@@ -238,16 +265,42 @@ class Lm:
         self.cap = cap
         self.loss = torch.zeros((1,), dtype=torch.float32, device="cuda")
         self.on_block_backward = None  # hook(i) called when block i's gradients are complete
+        self.remat, self.head_rows = remat, head_rows
+        assert not head_rows or tied, "the row-chunked head is implemented for the tied head"
 
-    def forward(self, ids, B, T):
+    def forward_hidden(self, ids, B, T):
+        """Embedding, blocks and the final norm; returns the normed hidden state [rows, d]."""
         self.ids, self.B, self.T = ids.reshape(-1), B, T
         x = self.table.w.index_select(0, self.ids)
+        self.block_in = []
         for blk in self.blocks:
+            if self.remat:
+                self.block_in.append(x)
             x = blk.forward(x, B, T)
+            if self.remat:
+                blk.release()
         self.normed = self.norm.forward(x)
-        pre = torch.mm(self.normed, self.table.w.t()) if self.tied else self.head.forward(self.normed)
+        return self.normed
+
+    def forward(self, ids, B, T):
+        normed = self.forward_hidden(ids, B, T)
+        pre = torch.mm(normed, self.table.w.t()) if self.tied else self.head.forward(normed)
         self.logits = torch.tanh_(pre.div_(self.cap)).mul_(self.cap)
         return self.logits
+
+    def backward_hidden(self, d_n):
+        d = self.norm.backward(d_n)
+        for i in range(len(self.blocks) - 1, -1, -1):
+            blk = self.blocks[i]
+            if self.remat:
+                blk.forward(self.block_in[i], self.B, self.T)
+                self.block_in[i] = None
+            d = blk.backward(d)
+            if self.remat:
+                blk.release()
+            if self.on_block_backward is not None:
+                self.on_block_backward(i)
+        self.table.g.index_add_(0, self.ids, d)
 
     def backward(self, dlogits):
         t = self.logits / self.cap
@@ -257,12 +310,7 @@ class Lm:
             d_n = torch.mm(d_pre, self.table.w)
         else:
             d_n = self.head.backward(d_pre)
-        d = self.norm.backward(d_n)
-        for i in range(len(self.blocks) - 1, -1, -1):
-            d = self.blocks[i].backward(d)
-            if self.on_block_backward is not None:
-                self.on_block_backward(i)
-        self.table.g.index_add_(0, self.ids, d)
+        self.backward_hidden(d_n)
 
     def params(self):
         out = [self.table]
@@ -281,11 +329,27 @@ class Lm:
 
     def forward_backward(self, ids, targets, B, T, inv=None):
         """Forward, fused CE (loss accumulated on the device), backward. Returns the device loss scalar."""
-        logits = self.forward(ids, B, T)
         self.loss.zero_()
-        dlogits = torch.empty_like(logits)
-        ops.softmax_cross_entropy(logits, targets, dlogits, self.loss, inv=inv)
-        self.backward(dlogits)
+        if not self.head_rows:
+            logits = self.forward(ids, B, T)
+            dlogits = torch.empty_like(logits)
+            ops.softmax_cross_entropy(logits, targets, dlogits, self.loss, inv=inv)
+            self.backward(dlogits)
+            return self.loss
+        normed = self.forward_hidden(ids, B, T)
+        rows = normed.shape[0]
+        inv = inv if inv is not None else 1.0 / rows
+        d_n = torch.empty_like(normed)
+        wt = self.table.w.t()
+        for lo in range(0, rows, self.head_rows):
+            hi = min(rows, lo + self.head_rows)
+            logits = torch.tanh_(torch.mm(normed[lo:hi], wt).div_(self.cap)).mul_(self.cap)
+            d_pre = torch.empty_like(logits)
+            ops.softmax_cross_entropy(logits, targets[lo:hi], d_pre, self.loss, inv=inv)
+            d_pre.mul_(logits.div_(self.cap).square_().neg_().add_(1.0))  # through the soft-cap: 1 - tanh^2
+            self.table.g.addmm_(d_pre.t(), normed[lo:hi])
+            torch.mm(d_pre, self.table.w, out=d_n[lo:hi])
+        self.backward_hidden(d_n)
         return self.loss
 
     def train_step(self, ids, targets, B, T, cfg):
@@ -294,7 +358,8 @@ class Lm:
         return loss
 
 
-def build_lm(params, heads, dqk, dhv, nh_s=1, cap=30.0, tied=True, head_w=None, head_b=None, bf16=False, chunk=64):
+def build_lm(params, heads, dqk, dhv, nh_s=1, cap=30.0, tied=True, head_w=None, head_b=None, bf16=False, chunk=64,
+             remat=False, head_rows=0):
     """Builds an Lm from the host parameter dictionary `oracle.model.init_lm_params` produces."""
     t = lambda a: torch.as_tensor(a, dtype=torch.float32)
     d = params["table"].shape[1]
@@ -307,4 +372,4 @@ def build_lm(params, heads, dqk, dhv, nh_s=1, cap=30.0, tied=True, head_w=None, 
         else:
             blocks.append(Block(SLstm(c, d, nh_s, bf16=bf16), bpt, post_norm=True, bf16=bf16))
     return Lm(t(params["table"]), blocks, t(params["gamma"]), None if head_w is None else t(head_w),
-              None if head_b is None else t(head_b), cap=cap, tied=tied)
+              None if head_b is None else t(head_b), cap=cap, tied=tied, remat=remat, head_rows=head_rows)

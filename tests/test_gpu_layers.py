@@ -78,3 +78,27 @@ def test_toy_lm_fp32_with_slstm_blocks():
 def test_lm_bf16_operands_tensor_core_cells():
     """Two mLSTM blocks with 2 heads x 128 (tensor-core path), bf16 GEMM operands and q/k/v storage."""
     _compare((64, 256, 2, 2, 128, 128, 680, 2, 128), True, 1.2e-1, 5e-3, seed=2, noise_floor=1e-3, cos_min=0.995)
+
+
+def test_remat_and_row_chunked_head_are_exact():
+    """Re-running each block's forward before its backward, and walking the tied head + soft-cap + CE over
+    row chunks, change memory only: loss and gradients equal the plain path's (bit-equal for everything
+    but the table gradient, whose head part is summed chunk by chunk)."""
+    layers = importlib.import_module("neural-networks_b200.layers")
+    vocab, d, nb, heads, dqk, dhv, up, B, T = 97, 64, 3, 2, 32, 32, 176, 3, 50
+    rng = np.random.default_rng(7)
+    p = M.init_lm_params(rng, vocab, d, nb, heads, dqk, dhv, up, std=0.1, slstm_at=(1,), nh_s=2)
+    ids = torch.tensor(rng.integers(0, vocab, B * T), dtype=torch.int64, device="cuda")
+    tg = torch.tensor(rng.integers(0, vocab, B * T).astype(np.int32), device="cuda")
+    out = []
+    for kw in (dict(), dict(remat=True, head_rows=64)):
+        lm = layers.build_lm(p, heads, dqk, dhv, nh_s=2, tied=True, **kw)
+        loss = lm.forward_backward(ids, tg, B, T).item()
+        out.append((loss, [q.g.clone() for q in lm.params()]))
+    (l0, g0), (l1, g1) = out
+    assert abs(l0 - l1) <= 1e-6 * abs(l0)
+    for i, (a, b) in enumerate(zip(g0, g1)):
+        if i == 0:
+            assert float((a - b).abs().max()) <= 1e-5 * float(a.abs().max())
+        else:
+            assert torch.equal(a, b), i
