@@ -331,9 +331,10 @@ def run_lm(args):
     slstm_at = tuple(i for i in range(c["blocks"]) if i % c["slstm_every"] == 0)
     p = M.init_lm_params(rng, c["vocab"], c["d"], c["blocks"], c["heads"], c["dqk"], c["dhv"], up, std=0.02, slstm_at=slstm_at,
                          nh_s=c["slstm_heads"])
-    # the full widths need both memory levers to fit 24 blocks in HBM; the reduced model runs without them
+    # the full widths need block rematerialisation to fit 24 blocks in HBM; the head runs row-chunked with
+    # fp32-accurate split-bf16 products in both models
     lm = layers.build_lm(p, c["heads"], c["dqk"], c["dhv"], nh_s=c["slstm_heads"], tied=True, bf16=True,
-                         remat=bool(args.lm_full), head_rows=4096 if args.lm_full else 0)
+                         remat=bool(args.lm_full), head_rows=4096, head_split=True)
     nparams = sum(q.w.numel() for q in lm.params())
     buckets = dp.attach(lm)
     B, T = c["B"], c["T"]

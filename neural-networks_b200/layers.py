@@ -30,16 +30,41 @@ class Param:
         self.wb = self.w.to(torch.bfloat16) if shadow else None
 
 
+def _b16(a):
+    return a if a.dtype == torch.bfloat16 else a.to(torch.bfloat16)
+
+
 def _mm(a, b, bf16):
     """a @ b with fp32 result; bf16 operands when asked (fp32 accumulate inside the library)."""
     if bf16:
-        a16 = a if a.dtype == torch.bfloat16 else a.to(torch.bfloat16)
-        b16 = b if b.dtype == torch.bfloat16 else b.to(torch.bfloat16)
         try:
-            return torch.mm(a16, b16, out_dtype=torch.float32)
+            return torch.mm(_b16(a), _b16(b), out_dtype=torch.float32)
         except TypeError:
-            return torch.mm(a16, b16).float()
+            return torch.mm(_b16(a), _b16(b)).float()
     return torch.mm(a, b)
+
+
+def _split3(a):
+    """fp32 -> three bf16 terms whose sum carries the full 24-bit significand."""
+    hi = a.to(torch.bfloat16)
+    r = a - hi.float()
+    mid = r.to(torch.bfloat16)
+    lo = r.sub_(mid.float()).to(torch.bfloat16)
+    return hi, mid, lo
+
+
+def _mm_split(a3, b3):
+    """fp32-accurate product of two fp32 matrices given as bf16 triples: the six partial products whose
+    weight is above 2^-24 run on the bf16 tensor cores with fp32 accumulation, smallest terms first."""
+    (ah, am, al), (bh, bm, bl) = a3, b3
+    mm = lambda x, y: torch.mm(x, y, out_dtype=torch.float32)
+    out = mm(al, bh)
+    out.add_(mm(ah, bl))
+    out.add_(mm(am, bm))
+    out.add_(mm(am, bh))
+    out.add_(mm(ah, bm))
+    out.add_(mm(ah, bh))
+    return out
 
 
 class Linear:
@@ -51,17 +76,19 @@ class Linear:
         self.b = Param(b, False)
 
     def forward(self, x):
-        self.x = x
-        y = _mm(x, self.w.wb if self.bf16 else self.w.w, self.bf16)
+        """x: fp32, or already narrowed to bf16 by a caller that feeds several projections from it."""
+        self.x = _b16(x) if self.bf16 else x
+        y = _mm(self.x, self.w.wb if self.bf16 else self.w.w, self.bf16)
         return y.add_(self.b.w)
 
     def backward(self, dy, need_dx=True):
-        self.w.g.add_(_mm(self.x.t(), dy, self.bf16) if not self.bf16 else _mm(self.x.to(torch.bfloat16).t().contiguous(), dy, True))
         self.b.g.add_(dy.sum(dim=0))
+        if self.bf16:
+            dy = _b16(dy)  # narrowed once for both products
+        self.w.g.add_(_mm(self.x.t(), dy, self.bf16))
         if not need_dx:
             return None
-        wt = (self.w.wb if self.bf16 else self.w.w).t()
-        return _mm(dy, wt.contiguous() if self.bf16 else wt, self.bf16)
+        return _mm(dy, (self.w.wb if self.bf16 else self.w.w).t(), self.bf16)
 
     def params(self):
         return [self.w, self.b]
@@ -114,6 +141,8 @@ class MLstm:
     def forward(self, x, B, T):
         sdt = torch.bfloat16 if self.bf16 else torch.float32
         self.st = ops.MlstmShape(B, self.h, T, self.dqk, self.dhv, self.chunk, sdt, torch.float32)
+        if self.bf16:
+            x = _b16(x)  # one narrowing feeds all six projections
         q = self.lq.forward(x).to(sdt)
         k = self.lk.forward(x).mul_(self.inv_sqrt).to(sdt)
         v = self.lv.forward(x).to(sdt)
@@ -164,8 +193,8 @@ class SLstm:
 
     def forward(self, x, B, T):
         H = self.H
-        self.B, self.T, self.x = B, T, x
-        self.g = _mm(x, self.wx.wb if self.bf16 else self.wx.w, self.bf16).view(B, T, 4 * H)
+        self.B, self.T, self.x = B, T, (_b16(x) if self.bf16 else x)
+        self.g = _mm(self.x, self.wx.wb if self.bf16 else self.wx.w, self.bf16).view(B, T, 4 * H)
         self.slabs = ops.SlstmSlabs(B, T, H, x.device)
         state = tuple(torch.empty((B, H), dtype=torch.float32, device=x.device) for _ in range(4))
         out = torch.empty((B, T, H), dtype=torch.float32, device=x.device)
@@ -177,8 +206,8 @@ class SLstm:
         ds = tuple(torch.empty((B, H), dtype=torch.float32, device=dy.device) for _ in range(3))
         ops.slstm_fused_time_bwd(self.wh.w, dy.view(B, T, H).contiguous(), self.g, ds, self.slabs, nh=nh, carry=False)
         dg = self.g.view(B * T, 4 * H)  # the loop left the four gate deltas here
-        xt = self.x.to(torch.bfloat16).t().contiguous() if self.bf16 else self.x.t()
-        self.wx.g.add_(_mm(xt, dg, self.bf16))
+        dgn = _b16(dg) if self.bf16 else dg
+        self.wx.g.add_(_mm(self.x.t(), dgn, self.bf16))
         self.b.g.add_(dg.sum(dim=0))
         hp = self.slabs.t["h_prev"].view(B * T, H)
         if nh == 1:
@@ -188,8 +217,7 @@ class SLstm:
             dg4 = dg.view(B * T, 4, nh, dh)
             for hd in range(nh):
                 self.wh.g[hd].add_(torch.mm(hp[:, hd * dh:(hd + 1) * dh].t(), dg4[:, :, hd, :].reshape(B * T, 4 * dh)))
-        wt = (self.wx.wb if self.bf16 else self.wx.w).t()
-        return _mm(dg, wt.contiguous() if self.bf16 else wt, self.bf16)
+        return _mm(dgn, (self.wx.wb if self.bf16 else self.wx.w).t(), self.bf16)
 
     def params(self):
         return [self.wx, self.wh, self.b]
@@ -216,6 +244,8 @@ class Block:
             c = self.post.forward(c)
         z = x + c
         zn = self.n2.forward(z)
+        if self.lg.bf16:
+            zn = _b16(zn)
         self.gate_pre, self.value = self.lg.forward(zn), self.lv.forward(zn)
         self.gate_act = torch.nn.functional.silu(self.gate_pre)
         return z + self.ld.forward(self.gate_act * self.value)
@@ -256,7 +286,8 @@ class Lm:
     `forward_backward`) walks the head GEMM, soft-cap and cross-entropy over n rows at a time, so the
     [rows, vocab] logits never exist as a whole."""
 
-    def __init__(self, table, blocks, gamma, head_w=None, head_b=None, cap=30.0, tied=False, remat=False, head_rows=0):
+    def __init__(self, table, blocks, gamma, head_w=None, head_b=None, cap=30.0, tied=False, remat=False, head_rows=0,
+                 head_split=False):
         self.table = Param(table, False)
         self.blocks = blocks
         self.norm = RmsNorm(gamma)
@@ -266,6 +297,9 @@ class Lm:
         self.loss = torch.zeros((1,), dtype=torch.float32, device="cuda")
         self.on_block_backward = None  # hook(i) called when block i's gradients are complete
         self.remat, self.head_rows = remat, head_rows
+        # head_split: the fp32 head products (row-chunked path) run as six bf16 tensor-core GEMMs on
+        # 3-way split operands, which keeps fp32 accuracy (see _mm_split) at several times the SIMT rate
+        self.head_split = head_split
         assert not head_rows or tied, "the row-chunked head is implemented for the tied head"
 
     def forward_hidden(self, ids, B, T):
@@ -341,14 +375,27 @@ class Lm:
         inv = inv if inv is not None else 1.0 / rows
         d_n = torch.empty_like(normed)
         wt = self.table.w.t()
+        if self.head_split:
+            w3 = _split3(self.table.w)
+            w3t = tuple(p.t() for p in w3)
         for lo in range(0, rows, self.head_rows):
             hi = min(rows, lo + self.head_rows)
-            logits = torch.tanh_(torch.mm(normed[lo:hi], wt).div_(self.cap)).mul_(self.cap)
+            if self.head_split:
+                n3 = _split3(normed[lo:hi])
+                pre = _mm_split(n3, w3t)
+            else:
+                pre = torch.mm(normed[lo:hi], wt)
+            logits = torch.tanh_(pre.div_(self.cap)).mul_(self.cap)
             d_pre = torch.empty_like(logits)
             ops.softmax_cross_entropy(logits, targets[lo:hi], d_pre, self.loss, inv=inv)
             d_pre.mul_(logits.div_(self.cap).square_().neg_().add_(1.0))  # through the soft-cap: 1 - tanh^2
-            self.table.g.addmm_(d_pre.t(), normed[lo:hi])
-            torch.mm(d_pre, self.table.w, out=d_n[lo:hi])
+            if self.head_split:
+                d3 = _split3(d_pre)
+                self.table.g.add_(_mm_split(tuple(p.t() for p in d3), n3))
+                d_n[lo:hi] = _mm_split(d3, w3)
+            else:
+                self.table.g.addmm_(d_pre.t(), normed[lo:hi])
+                torch.mm(d_pre, self.table.w, out=d_n[lo:hi])
         self.backward_hidden(d_n)
         return self.loss
 
@@ -359,7 +406,7 @@ class Lm:
 
 
 def build_lm(params, heads, dqk, dhv, nh_s=1, cap=30.0, tied=True, head_w=None, head_b=None, bf16=False, chunk=64,
-             remat=False, head_rows=0):
+             remat=False, head_rows=0, head_split=False):
     """Builds an Lm from the host parameter dictionary `oracle.model.init_lm_params` produces."""
     t = lambda a: torch.as_tensor(a, dtype=torch.float32)
     d = params["table"].shape[1]
@@ -372,4 +419,5 @@ def build_lm(params, heads, dqk, dhv, nh_s=1, cap=30.0, tied=True, head_w=None, 
         else:
             blocks.append(Block(SLstm(c, d, nh_s, bf16=bf16), bpt, post_norm=True, bf16=bf16))
     return Lm(t(params["table"]), blocks, t(params["gamma"]), None if head_w is None else t(head_w),
-              None if head_b is None else t(head_b), cap=cap, tied=tied, remat=remat, head_rows=head_rows)
+              None if head_b is None else t(head_b), cap=cap, tied=tied, remat=remat, head_rows=head_rows,
+              head_split=head_split)

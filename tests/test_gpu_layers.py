@@ -102,3 +102,19 @@ def test_remat_and_row_chunked_head_are_exact():
             assert float((a - b).abs().max()) <= 1e-5 * float(a.abs().max())
         else:
             assert torch.equal(a, b), i
+
+
+def test_split_bf16_product_is_fp32_accurate():
+    """The head's split product (six bf16 tensor-core GEMMs on 3-way split operands) against an fp64 product:
+    no worse than the plain fp32 GEMM it replaces."""
+    layers = importlib.import_module("neural-networks_b200.layers")
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randn((512, 768), device="cuda", generator=g)
+    b = torch.randn((768, 640), device="cuda", generator=g) * 0.02
+    ref = a.double() @ b.double()
+    got = layers._mm_split(layers._split3(a), layers._split3(b))
+    plain = a @ b
+    scale = float(ref.abs().max())
+    e_split = float((got.double() - ref).abs().max()) / scale
+    e_plain = float((plain.double() - ref).abs().max()) / scale
+    assert e_split <= max(2.0 * e_plain, 2e-6), (e_split, e_plain)
