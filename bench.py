@@ -331,10 +331,12 @@ def run_lm(args):
     slstm_at = tuple(i for i in range(c["blocks"]) if i % c["slstm_every"] == 0)
     p = M.init_lm_params(rng, c["vocab"], c["d"], c["blocks"], c["heads"], c["dqk"], c["dhv"], up, std=0.02, slstm_at=slstm_at,
                          nh_s=c["slstm_heads"])
-    # the full widths need block rematerialisation to fit 24 blocks in HBM; the head runs row-chunked with
-    # fp32-accurate split-bf16 products in both models
+    # full widths: the first `--lm-remat` mLSTM blocks keep only their input and re-run their forward in the
+    # backward, so that 24 blocks fit in HBM; sLSTM blocks (the long sequential loops) are never re-run
+    remat = [i for i in range(c["blocks"]) if i not in slstm_at][:args.lm_remat] if args.lm_full else ()
+    # (the reduced model needs none); the head runs row-chunked with fp32-accurate split-bf16 products in both
     lm = layers.build_lm(p, c["heads"], c["dqk"], c["dhv"], nh_s=c["slstm_heads"], tied=True, bf16=True,
-                         remat=bool(args.lm_full), head_rows=4096, head_split=True)
+                         remat=remat, head_rows=4096, head_split=True)
     nparams = sum(q.w.numel() for q in lm.params())
     buckets = dp.attach(lm)
     B, T = c["B"], c["T"]
@@ -484,6 +486,7 @@ def main():
     ap.add_argument("--workload", default="mlstm", choices=["mlstm", "lm", "ops"],
                     help="mlstm: configs[1] layer kernel (headline); lm: training step; ops: the other hot-path kernels alone")
     ap.add_argument("--lm-blocks", type=int, default=0, help="override the LM depth (development)")
+    ap.add_argument("--lm-remat", type=int, default=4, help="blocks rematerialised in the full-width LM workload")
     ap.add_argument("--lm-full", action="store_true", help="LM workload at the full widths of configs[3] (d=2048, heads of 256 / 512)")
     args = ap.parse_args()
     if args.impl == "reference":

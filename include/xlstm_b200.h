@@ -144,6 +144,14 @@ int xlstm_ce_fw_bw(void* stream, const float* logits, const uint32_t* targets,
                    const uint32_t* mask, float* dlogits, float* loss_accum, int rows, int C,
                    float inv, void* workspace, size_t workspace_bytes);
 
+/* The same loss with the flat LM's soft-cap folded in (reference: softcap_forward/backward,
+ * src/gpu/cuda/common.cu:4-12, applied by gpu::Lm between the head and the loss, src/gpu/lm.rs:84-163):
+ * pre_logits are the head's outputs x, the loss is taken on cap*tanh(x/cap), and d_pre (may alias
+ * pre_logits) is the gradient with respect to x. Saves the capped logits' round trips through HBM. */
+int xlstm_softcap_ce_fw_bw(void* stream, const float* pre_logits, const uint32_t* targets,
+                           const uint32_t* mask, float* d_pre, float* loss_accum, int rows, int C,
+                           float inv, float cap, void* workspace, size_t workspace_bytes);
+
 /* The same op for hosts that cannot allocate device memory (a runtime whose buffer pool already
  * owns all of it, or a step loop that must stay clear of the CUDA allocator): the per-row scratch
  * is a fixed array inside the library instead of a caller workspace. It has no counterpart in the
@@ -155,6 +163,28 @@ int xlstm_ce_fw_bw(void* stream, const float* logits, const uint32_t* targets,
 int xlstm_ce_fw_bw_noalloc(void* stream, const float* logits, const uint32_t* targets,
                            const uint32_t* mask, float* dlogits, float* loss_accum, int rows,
                            int C, float inv);
+
+/* ---- element-wise glue, one pass each (replace swiglu_forward/backward, src/gpu/cuda/block.cu:6-29, and
+ * ogate_fwd/ogate_bwd, src/gpu/cuda/mlstm_ops.cu:147-153, 400-407, with the bf16 narrowing of outputs
+ * that feed a GEMM folded in, src/gpu/cuda/bf16_cast.cu:22-60). Flat arrays of n elements; out_dtype is
+ * XLSTM_F32 or XLSTM_BF16 and applies to the outputs typed void*. */
+/* out = SiLU(gate_pre) * value */
+int xlstm_swiglu_fw(void* stream, const float* gate_pre, const float* value, void* out, int out_dtype, size_t n);
+/* d_gate = d_mixed * value * SiLU'(gate_pre); d_value = d_mixed * SiLU(gate_pre) */
+int xlstm_swiglu_bw(void* stream, const float* d_mixed, const float* gate_pre, const float* value,
+                    void* d_gate, void* d_value, int out_dtype, size_t n);
+/* o <- sigmoid(o) in place; hc = o * yhat */
+int xlstm_ogate_fw(void* stream, float* o, const float* yhat, void* hc, int out_dtype, size_t n);
+/* do_pre = d_hc * yhat * o * (1 - o) with o the activated gate; d_yhat = d_hc * o (fp32) */
+int xlstm_ogate_bw(void* stream, const float* d_hc, const float* o, const float* yhat, void* do_pre,
+                   int out_dtype, float* d_yhat, size_t n);
+/* Embedding backward without float atomics (replaces embedding_scatter_add / embedding_scatter_merge,
+ * src/gpu/cuda/common.cu:127-168): table_g[id] += sum of the rows d[pos] with ids[pos] == id, in ascending
+ * position order. The caller passes the ids sorted stably (`sorted_ids`) and the positions in that order
+ * (`order`), both int32 [n]; d is [n, dm] fp32, table_g [vocab, dm] fp32. */
+int xlstm_embedding_scatter_add(void* stream, const float* d, const int* sorted_ids, const int* order,
+                                float* table_g, int n, int dm);
+
 
 /* ---- AdamW over many tensors ----------------------------------------------------------------
  * Replaces ops::adamw and AdamwQueue::flush (src/gpu/ops.rs:1775-1933, src/gpu/cuda/

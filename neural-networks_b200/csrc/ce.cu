@@ -12,11 +12,27 @@
 
 namespace xl {
 
+// Soft-cap cap*tanh(x/cap) of the flat LM's head (src/nn2/ops.rs:25-42), fused into the loss kernels when
+// CAP: the input is then the pre-cap logit, and the gradient is taken through the cap,
+// d/dx = (p - onehot) * inv * (1 - tanh^2).
+template <bool CAP>
+__device__ __forceinline__ float capped(float x, float cap, float icap) {
+    if (!CAP) return x;
+    return cap * (1.f - __fdividef(2.f, 1.f + __expf(2.f * x * icap)));
+}
+template <bool CAP>
+__device__ __forceinline__ float through_cap(float g, float t, float icap) {
+    if (!CAP) return g;
+    const float u = t * icap;
+    return g * (1.f - u * u);
+}
+
 // ---- wide rows: one CTA per row, row cached in shared memory ---------------------------------
-template <bool CACHE>
+template <bool CACHE, bool CAP>
 __global__ void __launch_bounds__(1024) ce_row_cta(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
                                                    const uint32_t* __restrict__ mask, float* __restrict__ dlogits,
-                                                   float* __restrict__ row_loss, int rows, int C, float inv) {
+                                                   float* __restrict__ row_loss, int rows, int C, float inv, float cap) {
+    const float icap = CAP ? 1.f / cap : 0.f;
     extern __shared__ __align__(16) float srow[];  // [C] when CACHE
     __shared__ float red[32];
     for (int r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -45,6 +61,10 @@ __global__ void __launch_bounds__(1024) ce_row_cta(const float* __restrict__ log
                 for (int u = 0; u < 4; ++u) {
                     const int j = j0 + u * stride;
                     if (j < n4) {
+                        if (CAP) {
+                            t[u].x = capped<CAP>(t[u].x, cap, icap); t[u].y = capped<CAP>(t[u].y, cap, icap);
+                            t[u].z = capped<CAP>(t[u].z, cap, icap); t[u].w = capped<CAP>(t[u].w, cap, icap);
+                        }
                         if (CACHE) reinterpret_cast<float4*>(srow)[j] = t[u];
                         float m4 = fmaxf(fmaxf(t[u].x, t[u].y), fmaxf(t[u].z, t[u].w));
                         if (m4 > mx) { sum *= __expf(mx - m4); mx = m4; }
@@ -54,7 +74,7 @@ __global__ void __launch_bounds__(1024) ce_row_cta(const float* __restrict__ log
             }
         } else {
             for (int j = threadIdx.x; j < C; j += blockDim.x) {
-                float t = z[j];
+                float t = capped<CAP>(z[j], cap, icap);
                 if (CACHE) srow[j] = t;
                 if (t > mx) { sum *= expf(mx - t); mx = t; }
                 sum += expf(t - mx);
@@ -66,7 +86,7 @@ __global__ void __launch_bounds__(1024) ce_row_cta(const float* __restrict__ log
         const float is = 1.f / gsum;
         const uint32_t tg = targets[r];
         if (threadIdx.x == 0) {
-            float zt = CACHE ? srow[tg] : z[tg];
+            float zt = CACHE ? srow[tg] : capped<CAP>(z[tg], cap, icap);
             float pt = expf(zt - gmx) * is;
             row_loss[r] = -logf(fmaxf(pt, 1e-30f));
         }
@@ -76,6 +96,10 @@ __global__ void __launch_bounds__(1024) ce_row_cta(const float* __restrict__ log
             float4* d4 = reinterpret_cast<float4*>(d);
             for (int j = threadIdx.x; j < C / 4; j += blockDim.x) {
                 float4 t = CACHE ? reinterpret_cast<float4*>(srow)[j] : reinterpret_cast<const float4*>(z)[j];
+                if (CAP && !CACHE) {
+                    t.x = capped<CAP>(t.x, cap, icap); t.y = capped<CAP>(t.y, cap, icap);
+                    t.z = capped<CAP>(t.z, cap, icap); t.w = capped<CAP>(t.w, cap, icap);
+                }
                 float4 o;
                 o.x = __expf(t.x - gmx) * is; o.y = __expf(t.y - gmx) * is;
                 o.z = __expf(t.z - gmx) * is; o.w = __expf(t.w - gmx) * is;
@@ -84,15 +108,16 @@ __global__ void __launch_bounds__(1024) ce_row_cta(const float* __restrict__ log
                 else if (tg == base + 1u) o.y -= 1.f;
                 else if (tg == base + 2u) o.z -= 1.f;
                 else if (tg == base + 3u) o.w -= 1.f;
-                o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
+                o.x = through_cap<CAP>(o.x * inv, t.x, icap); o.y = through_cap<CAP>(o.y * inv, t.y, icap);
+                o.z = through_cap<CAP>(o.z * inv, t.z, icap); o.w = through_cap<CAP>(o.w * inv, t.w, icap);
                 __stcs(d4 + j, o);
             }
         } else {
             for (int j = threadIdx.x; j < C; j += blockDim.x) {
-                float t = CACHE ? srow[j] : z[j];
+                float t = CACHE ? srow[j] : capped<CAP>(z[j], cap, icap);
                 float o = expf(t - gmx) * is;
                 if ((uint32_t)j == tg) o -= 1.f;
-                d[j] = o * inv;
+                d[j] = through_cap<CAP>(o * inv, t, icap);
             }
         }
         __syncthreads();  // srow is reused by the next row
@@ -100,10 +125,11 @@ __global__ void __launch_bounds__(1024) ce_row_cta(const float* __restrict__ log
 }
 
 // ---- narrow rows (C <= 1024): one warp per row, row in registers -----------------------------
-template <int VPL>
+template <int VPL, bool CAP>
 __global__ void __launch_bounds__(256) ce_row_warp(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
                                                    const uint32_t* __restrict__ mask, float* __restrict__ dlogits,
-                                                   float* __restrict__ row_loss, int rows, int C, float inv) {
+                                                   float* __restrict__ row_loss, int rows, int C, float inv, float cap) {
+    const float icap = CAP ? 1.f / cap : 0.f;
     const int lane = threadIdx.x & 31;
     const int wglobal = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int wstride = gridDim.x * (blockDim.x >> 5);
@@ -116,11 +142,13 @@ __global__ void __launch_bounds__(256) ce_row_warp(const float* __restrict__ log
             continue;
         }
         float v[VPL];
+        float tc[CAP ? VPL : 1];  // capped logits, needed again for the gradient through the cap
         float mx = -INFINITY;
 #pragma unroll
         for (int i = 0; i < VPL; ++i) {
             int j = i * 32 + lane;
-            v[i] = j < C ? z[j] : -INFINITY;
+            v[i] = j < C ? capped<CAP>(z[j], cap, icap) : -INFINITY;
+            if (CAP) tc[i] = j < C ? v[i] : 0.f;
             mx = fmaxf(mx, v[i]);
         }
         mx = warp_max(mx);
@@ -139,7 +167,7 @@ __global__ void __launch_bounds__(256) ce_row_warp(const float* __restrict__ log
             int j = i * 32 + lane;
             float p = v[i] * is;
             if ((uint32_t)j == tg) { pt = p; p -= 1.f; }
-            if (j < C) d[j] = p * inv;
+            if (j < C) d[j] = through_cap<CAP>(p * inv, CAP ? tc[i] : 0.f, icap);
         }
         pt = warp_sum(pt);
         if (lane == 0) row_loss[r] = -logf(fmaxf(pt, 1e-30f));
@@ -161,9 +189,9 @@ using namespace xl;
 
 extern "C" size_t xlstm_ce_workspace_bytes(int rows) { return rows > 0 ? (size_t)rows * sizeof(float) : 0; }
 
-extern "C" int xlstm_ce_fw_bw(void* stream, const float* logits, const uint32_t* targets, const uint32_t* mask,
-                              float* dlogits, float* loss_accum, int rows, int C, float inv, void* workspace,
-                              size_t workspace_bytes) {
+template <bool CAP>
+static int ce_run(void* stream, const float* logits, const uint32_t* targets, const uint32_t* mask, float* dlogits,
+                  float* loss_accum, int rows, int C, float inv, float cap, void* workspace, size_t workspace_bytes) {
     XL_CHECK_ARG(logits && targets && dlogits && loss_accum, "ce_fw_bw: null pointer");
     XL_CHECK_ARG(rows >= 0 && C > 0, "ce_fw_bw: bad shape rows=%d C=%d", rows, C);
     if (rows == 0) return XLSTM_OK;
@@ -178,7 +206,7 @@ extern "C" int xlstm_ce_fw_bw(void* stream, const float* logits, const uint32_t*
         int wpb = 8;
         int nb = (rows + wpb - 1) / wpb, maxb = sm_count() * 8;
         int grid = nb < maxb ? nb : maxb;
-#define RUN(V) ce_row_warp<V><<<grid, 256, 0, st>>>(logits, targets, mask, dlogits, row_loss, rows, C, inv)
+#define RUN(V) ce_row_warp<V, CAP><<<grid, 256, 0, st>>>(logits, targets, mask, dlogits, row_loss, rows, C, inv, cap)
         if (C <= 32) RUN(1);
         else if (C <= 64) RUN(2);
         else if (C <= 128) RUN(4);
@@ -191,21 +219,34 @@ extern "C" int xlstm_ce_fw_bw(void* stream, const float* logits, const uint32_t*
         size_t smem = (size_t)C * sizeof(float);
         int threads = C >= 8192 ? 1024 : 256;
         if (smem <= 200 * 1024) {
-            XL_CUDA(cudaFuncSetAttribute(ce_row_cta<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            XL_CUDA(cudaFuncSetAttribute(ce_row_cta<true, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             int per_sm = (int)((220 * 1024) / (smem + 1024));
             if (per_sm < 1) per_sm = 1;
             if (per_sm > 2048 / threads) per_sm = 2048 / threads;
             int maxb = sm_count() * per_sm;
-            ce_row_cta<true><<<rows < maxb ? rows : maxb, threads, smem, st>>>(logits, targets, mask, dlogits, row_loss, rows, C, inv);
+            ce_row_cta<true, CAP><<<rows < maxb ? rows : maxb, threads, smem, st>>>(logits, targets, mask, dlogits, row_loss, rows, C, inv, cap);
         } else {
             int maxb = sm_count() * 2;
-            ce_row_cta<false><<<rows < maxb ? rows : maxb, 1024, 0, st>>>(logits, targets, mask, dlogits, row_loss, rows, C, inv);
+            ce_row_cta<false, CAP><<<rows < maxb ? rows : maxb, 1024, 0, st>>>(logits, targets, mask, dlogits, row_loss, rows, C, inv, cap);
         }
         XL_LAUNCH_OK("ce_row_cta");
     }
     ce_loss_reduce<<<1, 1024, 0, st>>>(row_loss, loss_accum, rows, inv);
     XL_LAUNCH_OK("ce_loss_reduce");
     return XLSTM_OK;
+}
+
+extern "C" int xlstm_ce_fw_bw(void* stream, const float* logits, const uint32_t* targets, const uint32_t* mask,
+                              float* dlogits, float* loss_accum, int rows, int C, float inv, void* workspace,
+                              size_t workspace_bytes) {
+    return ce_run<false>(stream, logits, targets, mask, dlogits, loss_accum, rows, C, inv, 0.f, workspace, workspace_bytes);
+}
+
+extern "C" int xlstm_softcap_ce_fw_bw(void* stream, const float* pre_logits, const uint32_t* targets, const uint32_t* mask,
+                                      float* d_pre, float* loss_accum, int rows, int C, float inv, float cap, void* workspace,
+                                      size_t workspace_bytes) {
+    XL_CHECK_ARG(cap > 0.f, "softcap_ce_fw_bw: cap must be positive (got %g)", (double)cap);
+    return ce_run<true>(stream, pre_logits, targets, mask, d_pre, loss_accum, rows, C, inv, cap, workspace, workspace_bytes);
 }
 
 // ---- the same op for callers that cannot allocate device memory --------------------------------

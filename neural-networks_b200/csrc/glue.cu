@@ -1,0 +1,210 @@
+// Element-wise glue between the GEMMs and the recurrent cores, one HBM pass each, with the narrowing
+// to bf16 folded into the producer (the reference's most frequent launches are stand-alone casts,
+// src/gpu/cuda/bf16_cast.cu:22-60):
+//   SwiGLU forward/backward        src/gpu/cuda/block.cu:6-29 (swiglu_forward / swiglu_backward)
+//   output gate forward/backward   src/gpu/cuda/mlstm_ops.cu:147-153, 400-407 (ogate_fwd / ogate_bwd)
+// All tensors are flat arrays of n elements; 128-bit accesses when n and the pointers allow, scalar
+// otherwise. Outputs that feed a GEMM may be asked for in bf16 (RNE), everything else is fp32.
+#include "common.cuh"
+
+#include <cuda_bf16.h>
+
+namespace xl {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void st4(float* p, size_t i4, float4 v) { __stcs(reinterpret_cast<float4*>(p) + i4, v); }
+__device__ __forceinline__ void st4(bf16* p, size_t i4, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    __stcs(reinterpret_cast<uint2*>(p) + i4, pk);
+}
+__device__ __forceinline__ void st1(float* p, size_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void st1(bf16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+__device__ __forceinline__ float4 ld4(const float* p, size_t i4) { return __ldcs(reinterpret_cast<const float4*>(p) + i4); }
+
+__device__ __forceinline__ float silu_f(float x, float* sig) {
+    const float s = stable_sigmoid(x);
+    *sig = s;
+    return x * s;
+}
+
+// out = SiLU(gate) * value
+template <typename OT>
+__global__ void __launch_bounds__(256) swiglu_fw_k(const float* __restrict__ gate, const float* __restrict__ value,
+                                                   OT* __restrict__ out, size_t n, int vec) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    float s;
+    if (vec) {
+        if (i >= n / 4) return;
+        const float4 g = ld4(gate, i), v = ld4(value, i);
+        st4(out, i, make_float4(silu_f(g.x, &s) * v.x, silu_f(g.y, &s) * v.y, silu_f(g.z, &s) * v.z, silu_f(g.w, &s) * v.w));
+    } else {
+        if (i >= n) return;
+        st1(out, i, silu_f(gate[i], &s) * value[i]);
+    }
+}
+
+// d_gate = d * value * SiLU'(gate), d_value = d * SiLU(gate);  SiLU'(x) = s (1 + x (1 - s))
+template <typename OT>
+__global__ void __launch_bounds__(256) swiglu_bw_k(const float* __restrict__ d, const float* __restrict__ gate,
+                                                   const float* __restrict__ value, OT* __restrict__ d_gate,
+                                                   OT* __restrict__ d_value, size_t n, int vec) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    auto one = [](float dd, float g, float v, float* dg, float* dv) {
+        float s;
+        const float act = silu_f(g, &s);
+        *dg = dd * v * (s * (1.f + g * (1.f - s)));
+        *dv = dd * act;
+    };
+    if (vec) {
+        if (i >= n / 4) return;
+        const float4 dd = ld4(d, i), g = ld4(gate, i), v = ld4(value, i);
+        float4 dg, dv;
+        one(dd.x, g.x, v.x, &dg.x, &dv.x); one(dd.y, g.y, v.y, &dg.y, &dv.y);
+        one(dd.z, g.z, v.z, &dg.z, &dv.z); one(dd.w, g.w, v.w, &dg.w, &dv.w);
+        st4(d_gate, i, dg);
+        st4(d_value, i, dv);
+    } else {
+        if (i >= n) return;
+        float dg, dv;
+        one(d[i], gate[i], value[i], &dg, &dv);
+        st1(d_gate, i, dg);
+        st1(d_value, i, dv);
+    }
+}
+
+// o <- sigmoid(o) in place (kept for the backward), hc = o * yhat
+template <typename OT>
+__global__ void __launch_bounds__(256) ogate_fw_k(float* __restrict__ o, const float* __restrict__ yhat, OT* __restrict__ hc,
+                                                  size_t n, int vec) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (vec) {
+        if (i >= n / 4) return;
+        float4 a = ld4(o, i);
+        const float4 y = ld4(yhat, i);
+        a.x = stable_sigmoid(a.x); a.y = stable_sigmoid(a.y); a.z = stable_sigmoid(a.z); a.w = stable_sigmoid(a.w);
+        reinterpret_cast<float4*>(o)[i] = a;
+        st4(hc, i, make_float4(a.x * y.x, a.y * y.y, a.z * y.z, a.w * y.w));
+    } else {
+        if (i >= n) return;
+        const float a = stable_sigmoid(o[i]);
+        o[i] = a;
+        st1(hc, i, a * yhat[i]);
+    }
+}
+
+// do_pre = d_hc * yhat * o (1 - o), d_yhat = d_hc * o   (o is the activated gate)
+template <typename OT>
+__global__ void __launch_bounds__(256) ogate_bw_k(const float* __restrict__ d_hc, const float* __restrict__ o,
+                                                  const float* __restrict__ yhat, OT* __restrict__ do_pre,
+                                                  float* __restrict__ d_yhat, size_t n, int vec) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (vec) {
+        if (i >= n / 4) return;
+        const float4 d = ld4(d_hc, i), a = ld4(o, i), y = ld4(yhat, i);
+        st4(do_pre, i, make_float4(d.x * y.x * a.x * (1.f - a.x), d.y * y.y * a.y * (1.f - a.y), d.z * y.z * a.z * (1.f - a.z),
+                                   d.w * y.w * a.w * (1.f - a.w)));
+        st4(d_yhat, i, make_float4(d.x * a.x, d.y * a.y, d.z * a.z, d.w * a.w));
+    } else {
+        if (i >= n) return;
+        const float d = d_hc[i], a = o[i];
+        st1(do_pre, i, d * yhat[i] * a * (1.f - a));
+        d_yhat[i] = d * a;
+    }
+}
+
+// table_g[id] += sum of the rows of d that carry token id, summed in ascending position order so the result
+// does not depend on scheduling (no float atomics). `sorted_ids` are the token ids sorted stably and `order`
+// the positions in that order; CTA p works only when p starts a run of equal ids, and then owns that row.
+__global__ void __launch_bounds__(256) embedding_scatter_add_k(const float* __restrict__ d, const int* __restrict__ sorted_ids,
+                                                               const int* __restrict__ order, float* __restrict__ table_g,
+                                                               int n, int dm) {
+    const int p = blockIdx.x;
+    const int id = sorted_ids[p];
+    if (p > 0 && sorted_ids[p - 1] == id) return;
+    int end = p + 1;
+    while (end < n && sorted_ids[end] == id) ++end;
+    float* dst = table_g + (size_t)id * dm;
+    for (int c = threadIdx.x; c < dm; c += 256) {
+        float acc = dst[c];
+        for (int q = p; q < end; ++q) acc += d[(size_t)order[q] * dm + c];
+        dst[c] = acc;
+    }
+}
+
+static inline int can_vec(size_t n, std::initializer_list<const void*> ptrs) {
+    if (n % 4) return 0;
+    for (const void* p : ptrs)
+        if ((uintptr_t)p & 15) return 0;
+    return 1;
+}
+static inline unsigned blocks_for(size_t n, int vec) { return (unsigned)(((vec ? n / 4 : n) + 255) / 256); }
+
+}  // namespace xl
+
+using namespace xl;
+
+#define GLUE_CHECK(who)                                                                               \
+    XL_CHECK_ARG(out_dtype == XLSTM_F32 || out_dtype == XLSTM_BF16, who ": out_dtype must be XLSTM_F32 or XLSTM_BF16"); \
+    if (n == 0) return XLSTM_OK;
+
+extern "C" int xlstm_swiglu_fw(void* stream, const float* gate_pre, const float* value, void* out, int out_dtype, size_t n) {
+    XL_CHECK_ARG(gate_pre && value && out, "swiglu_fw: null pointer");
+    GLUE_CHECK("swiglu_fw")
+    cudaStream_t st = (cudaStream_t)stream;
+    const int vec = can_vec(n, {gate_pre, value, out});
+    if (out_dtype == XLSTM_BF16) swiglu_fw_k<bf16><<<blocks_for(n, vec), 256, 0, st>>>(gate_pre, value, (bf16*)out, n, vec);
+    else swiglu_fw_k<float><<<blocks_for(n, vec), 256, 0, st>>>(gate_pre, value, (float*)out, n, vec);
+    XL_LAUNCH_OK("swiglu_fw");
+    return XLSTM_OK;
+}
+
+extern "C" int xlstm_swiglu_bw(void* stream, const float* d_mixed, const float* gate_pre, const float* value, void* d_gate,
+                               void* d_value, int out_dtype, size_t n) {
+    XL_CHECK_ARG(d_mixed && gate_pre && value && d_gate && d_value, "swiglu_bw: null pointer");
+    GLUE_CHECK("swiglu_bw")
+    cudaStream_t st = (cudaStream_t)stream;
+    const int vec = can_vec(n, {d_mixed, gate_pre, value, d_gate, d_value});
+    if (out_dtype == XLSTM_BF16)
+        swiglu_bw_k<bf16><<<blocks_for(n, vec), 256, 0, st>>>(d_mixed, gate_pre, value, (bf16*)d_gate, (bf16*)d_value, n, vec);
+    else
+        swiglu_bw_k<float><<<blocks_for(n, vec), 256, 0, st>>>(d_mixed, gate_pre, value, (float*)d_gate, (float*)d_value, n, vec);
+    XL_LAUNCH_OK("swiglu_bw");
+    return XLSTM_OK;
+}
+
+extern "C" int xlstm_ogate_fw(void* stream, float* o, const float* yhat, void* hc, int out_dtype, size_t n) {
+    XL_CHECK_ARG(o && yhat && hc, "ogate_fw: null pointer");
+    GLUE_CHECK("ogate_fw")
+    cudaStream_t st = (cudaStream_t)stream;
+    const int vec = can_vec(n, {o, yhat, hc});
+    if (out_dtype == XLSTM_BF16) ogate_fw_k<bf16><<<blocks_for(n, vec), 256, 0, st>>>(o, yhat, (bf16*)hc, n, vec);
+    else ogate_fw_k<float><<<blocks_for(n, vec), 256, 0, st>>>(o, yhat, (float*)hc, n, vec);
+    XL_LAUNCH_OK("ogate_fw");
+    return XLSTM_OK;
+}
+
+extern "C" int xlstm_ogate_bw(void* stream, const float* d_hc, const float* o, const float* yhat, void* do_pre, int out_dtype,
+                              float* d_yhat, size_t n) {
+    XL_CHECK_ARG(d_hc && o && yhat && do_pre && d_yhat, "ogate_bw: null pointer");
+    GLUE_CHECK("ogate_bw")
+    cudaStream_t st = (cudaStream_t)stream;
+    const int vec = can_vec(n, {d_hc, o, yhat, do_pre, d_yhat});
+    if (out_dtype == XLSTM_BF16) ogate_bw_k<bf16><<<blocks_for(n, vec), 256, 0, st>>>(d_hc, o, yhat, (bf16*)do_pre, d_yhat, n, vec);
+    else ogate_bw_k<float><<<blocks_for(n, vec), 256, 0, st>>>(d_hc, o, yhat, (float*)do_pre, d_yhat, n, vec);
+    XL_LAUNCH_OK("ogate_bw");
+    return XLSTM_OK;
+}
+
+extern "C" int xlstm_embedding_scatter_add(void* stream, const float* d, const int* sorted_ids, const int* order, float* table_g,
+                                           int n, int dm) {
+    XL_CHECK_ARG(d && sorted_ids && order && table_g, "embedding_scatter_add: null pointer");
+    XL_CHECK_ARG(n >= 0 && dm > 0, "embedding_scatter_add: bad shape n=%d dm=%d", n, dm);
+    if (n == 0) return XLSTM_OK;
+    embedding_scatter_add_k<<<(unsigned)n, 256, 0, (cudaStream_t)stream>>>(d, sorted_ids, order, table_g, n, dm);
+    XL_LAUNCH_OK("embedding_scatter_add");
+    return XLSTM_OK;
+}

@@ -78,11 +78,12 @@ class Linear:
     def forward(self, x):
         """x: fp32, or already narrowed to bf16 by a caller that feeds several projections from it."""
         self.x = _b16(x) if self.bf16 else x
-        y = _mm(self.x, self.w.wb if self.bf16 else self.w.w, self.bf16)
-        return y.add_(self.b.w)
+        if self.bf16:
+            return torch.addmm(self.b.w, self.x, self.w.wb, out_dtype=torch.float32)  # bias in the GEMM epilogue
+        return torch.addmm(self.b.w, self.x, self.w.w)
 
     def backward(self, dy, need_dx=True):
-        self.b.g.add_(dy.sum(dim=0))
+        self.b.g.add_(dy.sum(dim=0, dtype=torch.float32))
         if self.bf16:
             dy = _b16(dy)  # narrowed once for both products
         self.w.g.add_(_mm(self.x.t(), dy, self.bf16))
@@ -146,18 +147,18 @@ class MLstm:
         q = self.lq.forward(x).to(sdt)
         k = self.lk.forward(x).mul_(self.inv_sqrt).to(sdt)
         v = self.lv.forward(x).to(sdt)
-        self.o = torch.sigmoid_(self.lo.forward(x))
+        self.o = self.lo.forward(x)  # activated in place by the output-gate kernel below
         ig, fg = self.li.forward(x), self.lf.forward(x)
         self.core_in = (q, k, v, ig, fg)
         self.fused = ops.mlstm_fused_fw(q, k, v, ig, fg, self.st, carry_in=self.carry, want_state=False)
         self.yhat = self.hn.forward(self.fused.ytil.float() if self.bf16 else self.fused.ytil)
-        self.hc = self.o * self.yhat
-        return self.lout.forward(self.hc)
+        hc = ops.ogate_forward(self.o, self.yhat, torch.bfloat16 if self.bf16 else torch.float32)
+        return self.lout.forward(hc)
 
     def backward(self, dy):
         d_hc = self.lout.backward(dy)
-        do_pre = d_hc * self.yhat * self.o * (1.0 - self.o)
-        d_ytil = self.hn.backward(d_hc * self.o)
+        do_pre, d_yhat = ops.ogate_backward(d_hc, self.o, self.yhat, torch.bfloat16 if self.bf16 else torch.float32)
+        d_ytil = self.hn.backward(d_yhat)
         q, k, v, ig, fg = self.core_in
         dq, dk, dv, dig, dfg, _ = ops.mlstm_fused_bw(self.fused, q, k, v, ig, fg, d_ytil, self.st, carry_in=self.carry,
                                                      want_dstate=False)
@@ -176,7 +177,7 @@ class MLstm:
         return out + self.hn.params()
 
     def release(self):
-        self.o = self.core_in = self.fused = self.yhat = self.hc = None
+        self.o = self.core_in = self.fused = self.yhat = None
         for l in (self.lq, self.lk, self.lv, self.lo, self.li, self.lf, self.lout, self.hn):
             l.release()
 
@@ -247,15 +248,14 @@ class Block:
         if self.lg.bf16:
             zn = _b16(zn)
         self.gate_pre, self.value = self.lg.forward(zn), self.lv.forward(zn)
-        self.gate_act = torch.nn.functional.silu(self.gate_pre)
-        return z + self.ld.forward(self.gate_act * self.value)
+        nd = torch.bfloat16 if self.ld.bf16 else torch.float32
+        return self.ld.forward(ops.swiglu_forward(self.gate_pre, self.value, nd)).add_(z)
 
     def backward(self, dy):
         d_mixed = self.ld.backward(dy)
-        s = torch.sigmoid(self.gate_pre)
-        d_gate = d_mixed * self.value * (s * (1.0 + self.gate_pre * (1.0 - s)))
+        d_gate, d_value = ops.swiglu_backward(d_mixed, self.gate_pre, self.value, torch.bfloat16 if self.lg.bf16 else torch.float32)
         d_zn = self.lg.backward(d_gate)
-        d_zn.add_(self.lv.backward(d_mixed * self.gate_act))
+        d_zn.add_(self.lv.backward(d_value))
         d_z = self.n2.backward(d_zn).add_(dy)
         d_c = self.post.backward(d_z) if self.post is not None else d_z
         return self.n1.backward(self.cell.backward(d_c)).add_(d_z)
@@ -270,7 +270,7 @@ class Block:
 
     def release(self):
         """Drops everything the forward saved for the backward."""
-        self.gate_pre = self.value = self.gate_act = None
+        self.gate_pre = self.value = None
         for l in (self.cell, self.n1, self.n2, self.lg, self.lv, self.ld):
             l.release()
         if self.post is not None:
@@ -281,8 +281,9 @@ class Lm:
     """gpu::Lm (src/gpu/lm.rs:25-163): embedding -> blocks -> RMSNorm -> head (fp32) -> SoftCap -> CE.
     `tied=True` uses the embedding table (transposed) as the head and sums its two gradients.
 
-    Two memory levers for wide models, both exact: `remat=True` keeps only each block's input and
-    re-runs the block's forward right before its backward; `head_rows=n` (tied head, through
+    Two memory levers for wide models, both exact: `remat` (True for every block, or the collection of
+    block indices to treat so) keeps only a block's input and re-runs its forward right before its
+    backward; `head_rows=n` (tied head, through
     `forward_backward`) walks the head GEMM, soft-cap and cross-entropy over n rows at a time, so the
     [rows, vocab] logits never exist as a whole."""
 
@@ -296,7 +297,8 @@ class Lm:
         self.cap = cap
         self.loss = torch.zeros((1,), dtype=torch.float32, device="cuda")
         self.on_block_backward = None  # hook(i) called when block i's gradients are complete
-        self.remat, self.head_rows = remat, head_rows
+        self.remat = set(range(len(blocks))) if remat is True else set(remat or ())
+        self.head_rows = head_rows
         # head_split: the fp32 head products (row-chunked path) run as six bf16 tensor-core GEMMs on
         # 3-way split operands, which keeps fp32 accuracy (see _mm_split) at several times the SIMT rate
         self.head_split = head_split
@@ -306,12 +308,12 @@ class Lm:
         """Embedding, blocks and the final norm; returns the normed hidden state [rows, d]."""
         self.ids, self.B, self.T = ids.reshape(-1), B, T
         x = self.table.w.index_select(0, self.ids)
-        self.block_in = []
-        for blk in self.blocks:
-            if self.remat:
-                self.block_in.append(x)
+        self.block_in = [None] * len(self.blocks)
+        for i, blk in enumerate(self.blocks):
+            if i in self.remat:
+                self.block_in[i] = x
             x = blk.forward(x, B, T)
-            if self.remat:
+            if i in self.remat:
                 blk.release()
         self.normed = self.norm.forward(x)
         return self.normed
@@ -326,15 +328,14 @@ class Lm:
         d = self.norm.backward(d_n)
         for i in range(len(self.blocks) - 1, -1, -1):
             blk = self.blocks[i]
-            if self.remat:
+            if i in self.remat:
                 blk.forward(self.block_in[i], self.B, self.T)
                 self.block_in[i] = None
             d = blk.backward(d)
-            if self.remat:
-                blk.release()
+            blk.release()
             if self.on_block_backward is not None:
                 self.on_block_backward(i)
-        self.table.g.index_add_(0, self.ids, d)
+        ops.embedding_scatter_add(self.table.g, self.ids, d)
 
     def backward(self, dlogits):
         t = self.logits / self.cap
@@ -385,10 +386,8 @@ class Lm:
                 pre = _mm_split(n3, w3t)
             else:
                 pre = torch.mm(normed[lo:hi], wt)
-            logits = torch.tanh_(pre.div_(self.cap)).mul_(self.cap)
-            d_pre = torch.empty_like(logits)
-            ops.softmax_cross_entropy(logits, targets[lo:hi], d_pre, self.loss, inv=inv)
-            d_pre.mul_(logits.div_(self.cap).square_().neg_().add_(1.0))  # through the soft-cap: 1 - tanh^2
+            d_pre = pre  # the fused soft-cap + loss kernel writes the gradient over its input
+            ops.softcap_cross_entropy(pre, targets[lo:hi], d_pre, self.loss, self.cap, inv=inv)
             if self.head_split:
                 d3 = _split3(d_pre)
                 self.table.g.add_(_mm_split(tuple(p.t() for p in d3), n3))

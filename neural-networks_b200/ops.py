@@ -158,6 +158,63 @@ def softmax_cross_entropy(logits, targets, dlogits, loss_accum, mask=None, inv=N
                              inv, _ptr(ws), wsb), "softmax_cross_entropy")
 
 
+def softcap_cross_entropy(pre_logits, targets, d_pre, loss_accum, cap, mask=None, inv=None):
+    """Soft-cap (softcap_forward/backward, src/gpu/cuda/common.cu:4-12) fused into the loss: the loss of
+    cap*tanh(pre/cap) and its gradient with respect to `pre_logits` (d_pre may alias pre_logits)."""
+    rows, c = pre_logits.shape
+    if inv is None:
+        inv = 1.0 / rows
+    wsb = lib.xlstm_ce_workspace_bytes(rows)
+    ws = torch.empty((max(wsb, 1),), dtype=torch.uint8, device=pre_logits.device)
+    check(lib.xlstm_softcap_ce_fw_bw(_stream(), _ptr(pre_logits), _ptr(targets), _ptr(mask), _ptr(d_pre), _ptr(loss_accum),
+                                     rows, c, inv, float(cap), _ptr(ws), wsb), "softcap_cross_entropy")
+
+
+def _dt(t):
+    return _DT[t]
+
+
+def swiglu_forward(gate_pre, value, out_dtype=torch.float32):
+    """swiglu_forward (src/gpu/cuda/block.cu:6-29): SiLU(gate_pre) * value, optionally narrowed to bf16."""
+    out = torch.empty(gate_pre.shape, dtype=out_dtype, device=gate_pre.device)
+    check(lib.xlstm_swiglu_fw(_stream(), _ptr(gate_pre), _ptr(value), _ptr(out), _dt(out_dtype), gate_pre.numel()), "swiglu_forward")
+    return out
+
+
+def swiglu_backward(d_mixed, gate_pre, value, out_dtype=torch.float32):
+    """swiglu_backward: (d_gate_pre, d_value), optionally narrowed to bf16 for the GEMMs that consume them."""
+    dg = torch.empty(gate_pre.shape, dtype=out_dtype, device=gate_pre.device)
+    dv = torch.empty(gate_pre.shape, dtype=out_dtype, device=gate_pre.device)
+    check(lib.xlstm_swiglu_bw(_stream(), _ptr(d_mixed), _ptr(gate_pre), _ptr(value), _ptr(dg), _ptr(dv), _dt(out_dtype),
+                              gate_pre.numel()), "swiglu_backward")
+    return dg, dv
+
+
+def ogate_forward(o, yhat, out_dtype=torch.float32):
+    """ogate_fwd (src/gpu/cuda/mlstm_ops.cu:147-153): o <- sigmoid(o) in place; returns o * yhat."""
+    hc = torch.empty(o.shape, dtype=out_dtype, device=o.device)
+    check(lib.xlstm_ogate_fw(_stream(), _ptr(o), _ptr(yhat), _ptr(hc), _dt(out_dtype), o.numel()), "ogate_forward")
+    return hc
+
+
+def ogate_backward(d_hc, o, yhat, out_dtype=torch.float32):
+    """ogate_bwd (src/gpu/cuda/mlstm_ops.cu:400-407): (do_pre [out_dtype], d_yhat [fp32])."""
+    do_pre = torch.empty(o.shape, dtype=out_dtype, device=o.device)
+    d_yhat = torch.empty(o.shape, dtype=torch.float32, device=o.device)
+    check(lib.xlstm_ogate_bw(_stream(), _ptr(d_hc), _ptr(o), _ptr(yhat), _ptr(do_pre), _dt(out_dtype), _ptr(d_yhat), o.numel()),
+          "ogate_backward")
+    return do_pre, d_yhat
+
+
+def embedding_scatter_add(table_g, ids, d):
+    """embedding_scatter_add (src/gpu/cuda/common.cu:127-168): table_g[ids[p]] += d[p], summed in position
+    order for each token (deterministic; the sort is a library call, the accumulation is the kernel)."""
+    sorted_ids, order = torch.sort(ids.reshape(-1), stable=True)
+    sid, pos = sorted_ids.to(torch.int32), order.to(torch.int32)
+    check(lib.xlstm_embedding_scatter_add(_stream(), _ptr(d), _ptr(sid), _ptr(pos), _ptr(table_g), ids.numel(), d.shape[1]),
+          "embedding_scatter_add")
+
+
 class AdamCfg:
     """reference: AdamCfg, src/nn2/optim.rs:12-33."""
 

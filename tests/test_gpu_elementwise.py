@@ -57,6 +57,72 @@ def test_softmax_ce(rows, C, masked):
     assert rel_to_max(host(logits), d) <= 1e-4
 
 
+@pytest.mark.parametrize("rows,C", [(6, 9), (37, 1000), (64, 5000), (16, 50304), (3, 70001)])
+def test_softcap_fused_into_ce(rows, C):
+    """Loss of cap*tanh(x/cap) and its gradient with respect to x, against the oracle's CE composed with the
+    soft-cap in float64 (src/nn2/ops.rs:25-42 then src/nn2/loss.rs:10-53)."""
+    from gpu_util import ops, dev, host, rel_to_max
+    r = np.random.default_rng(2)
+    cap = 30.0
+    x = (r.standard_normal((rows, C)) * 25).astype(np.float32).astype(np.float64)  # well into the cap's bend
+    t = r.integers(0, C, rows)
+    z = cap * np.tanh(x / cap)
+    loss, dz = O.softmax_ce(z, t, inv=1.0 / rows)
+    dx = dz * (1.0 - (z / cap) ** 2)
+    pre = dev(x)
+    acc = torch.zeros((1,), device="cuda")
+    ops.softcap_cross_entropy(pre, torch.tensor(t.astype(np.int32), device="cuda"), pre, acc, cap)  # in place
+    torch.cuda.synchronize()
+    assert abs(acc.item() - loss) <= 1e-4 * max(1.0, abs(loss))
+    assert rel_to_max(host(pre), dx) <= 1e-4
+
+
+@pytest.mark.parametrize("n", [8, 4 * 1000 + 3, 1 << 20])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_and_output_gate_glue(n, out_dtype):
+    """SwiGLU and output-gate forward/backward against float64 formulas (src/nn2/block.rs:128-216,
+    src/nn2/mlstm.rs:347-577); bf16 outputs within one rounding (2^-8 relative)."""
+    from gpu_util import ops, dev, host
+    r = np.random.default_rng(3)
+    f32 = lambda a: a.astype(np.float32).astype(np.float64)
+    g, v, d, y = (f32(r.standard_normal(n) * 2) for _ in range(4))
+    sig = 1.0 / (1.0 + np.exp(-g))
+    tol = 1e-6 if out_dtype == torch.float32 else 2.0 ** -8
+    close = lambda got, ref: np.abs(got - ref).max() <= tol * max(1.0, np.abs(ref).max())
+    assert close(host(ops.swiglu_forward(dev(g), dev(v), out_dtype).float()), g * sig * v)
+    dg, dv = ops.swiglu_backward(dev(d), dev(g), dev(v), out_dtype)
+    assert close(host(dg.float()), d * v * sig * (1.0 + g * (1.0 - sig)))
+    assert close(host(dv.float()), d * g * sig)
+    o = dev(g)
+    hc = ops.ogate_forward(o, dev(y), out_dtype)
+    assert np.abs(host(o) - sig).max() <= 1e-6
+    assert close(host(hc.float()), sig * y)
+    do_pre, d_yhat = ops.ogate_backward(dev(d), o, dev(y), out_dtype)
+    assert close(host(do_pre.float()), d * y * sig * (1.0 - sig))
+    assert np.abs(host(d_yhat) - d * sig).max() <= 1e-6 * max(1.0, np.abs(d * sig).max())
+
+
+def test_embedding_scatter_add_is_exact_and_repeatable():
+    """Token-row sums in position order: equal to a sequential float32 accumulation, bit for bit, on ids with
+    heavy repeats (src/gpu/cuda/common.cu:127-168 is deterministic too, by slicing)."""
+    from gpu_util import ops
+    r = np.random.default_rng(4)
+    n, dm, vocab = 3000, 96, 50
+    ids = r.integers(0, vocab, n)
+    d = r.standard_normal((n, dm)).astype(np.float32)
+    g0 = r.standard_normal((vocab, dm)).astype(np.float32)
+    want = g0.copy()
+    for p in range(n):
+        want[ids[p]] += d[p]
+    outs = []
+    for _ in range(2):
+        g = torch.tensor(g0, device="cuda")
+        ops.embedding_scatter_add(g, torch.tensor(ids, device="cuda"), torch.tensor(d, device="cuda"))
+        outs.append(g.cpu().numpy())
+    assert np.array_equal(outs[0], outs[1])
+    assert np.array_equal(outs[0], want)
+
+
 @pytest.mark.parametrize("wd", [0.0, 0.01])
 def test_adamw_single_and_batched(wd):
     from gpu_util import ops, dev, host, rel_to_max
