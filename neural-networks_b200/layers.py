@@ -82,14 +82,22 @@ class Linear:
             return torch.addmm(self.b.w, self.x, self.w.wb, out_dtype=torch.float32)  # bias in the GEMM epilogue
         return torch.addmm(self.b.w, self.x, self.w.w)
 
-    def backward(self, dy, need_dx=True):
+    def backward(self, dy, need_dx=True, accum=None):
+        """Accumulates dW, db; returns dx, added into `accum` (inside the GEMM, beta = 1) when one is given."""
         self.b.g.add_(dy.sum(dim=0, dtype=torch.float32))
         if self.bf16:
             dy = _b16(dy)  # narrowed once for both products
-        self.w.g.add_(_mm(self.x.t(), dy, self.bf16))
+            torch.addmm(self.w.g, self.x.t(), dy, out_dtype=torch.float32, out=self.w.g)
+        else:
+            self.w.g.addmm_(self.x.t(), dy)
         if not need_dx:
             return None
-        return _mm(dy, (self.w.wb if self.bf16 else self.w.w).t(), self.bf16)
+        wt = (self.w.wb if self.bf16 else self.w.w).t()
+        if accum is None:
+            return _mm(dy, wt, self.bf16)
+        if self.bf16:
+            return torch.addmm(accum, dy, wt, out_dtype=torch.float32, out=accum)
+        return accum.addmm_(dy, wt)
 
     def params(self):
         return [self.w, self.b]
@@ -163,11 +171,11 @@ class MLstm:
         dq, dk, dv, dig, dfg, _ = ops.mlstm_fused_bw(self.fused, q, k, v, ig, fg, d_ytil, self.st, carry_in=self.carry,
                                                      want_dstate=False)
         dx = self.lq.backward(dq)
-        dx.add_(self.lk.backward(dk.mul_(self.inv_sqrt)))
-        dx.add_(self.lv.backward(dv))
-        dx.add_(self.lo.backward(do_pre))
-        dx.add_(self.li.backward(dig))
-        dx.add_(self.lf.backward(dfg))
+        self.lk.backward(dk.mul_(self.inv_sqrt), accum=dx)
+        self.lv.backward(dv, accum=dx)
+        self.lo.backward(do_pre, accum=dx)
+        self.li.backward(dig, accum=dx)
+        self.lf.backward(dfg, accum=dx)
         return dx
 
     def params(self):
@@ -255,7 +263,7 @@ class Block:
         d_mixed = self.ld.backward(dy)
         d_gate, d_value = ops.swiglu_backward(d_mixed, self.gate_pre, self.value, torch.bfloat16 if self.lg.bf16 else torch.float32)
         d_zn = self.lg.backward(d_gate)
-        d_zn.add_(self.lv.backward(d_value))
+        self.lv.backward(d_value, accum=d_zn)
         d_z = self.n2.backward(d_zn).add_(dy)
         d_c = self.post.backward(d_z) if self.post is not None else d_z
         return self.n1.backward(self.cell.backward(d_c)).add_(d_z)
