@@ -51,6 +51,7 @@ struct SlstmArgs {
     int KS;                    // k-slices of the mat-vec
     int CPT;                   // output columns per thread in the backward mat-vec (2 or 1)
     long long* prof;           // development aid (profiling builds only)
+    unsigned epoch;            // launch number, part of the tags of the grid kernels' flagged exchange
 };
 
 struct SlstmSmem {
@@ -523,6 +524,52 @@ __device__ __forceinline__ void stage_rows(float* xin, const float* base, size_t
     }
 }
 
+// Flagged exchange ("value + tag in one 8-byte word"): instead of writing a vector, arriving at a counter and
+// having every reader wait for the count, a producer stores each value together with a tag that names the
+// launch and the step, and a consumer re-reads a word until its tag is the one it wants. An 8-byte aligned
+// store is single-copy atomic, so a matching tag proves the value beside it, with no fence and no barrier:
+// a step costs one L2 round trip. Two buffers alternate by step parity; a producer can only reach step t+2
+// after every CTA of the head consumed step t, so the buffer it overwrites is no longer being read.
+static constexpr size_t kLLWords = (size_t)1 << 18;  // 2 MiB: two buffers of B x H values up to B*H = 131072
+static __device__ __align__(16) uint2 g_slstm_ll[kLLWords];
+
+__device__ __forceinline__ unsigned ll_tag(unsigned epoch, int t) { return (epoch << 20) | (unsigned)(t + 1); }
+__device__ __forceinline__ void ll_store(uint2* p, float v, unsigned tag) {
+    asm volatile("st.relaxed.gpu.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ll_load(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.relaxed.gpu.global.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+
+// stage_rows over the flagged exchange: every word is polled until it carries `tag`. Returns false when a
+// word did not arrive within the polling budget (the caller then raises the abort flag and unwinds).
+template <int BG>
+__device__ __forceinline__ bool stage_rows_ll(float* xin, const uint2* base, size_t bstride, int nlive, int K, int seg,
+                                              size_t sstride, unsigned tag, const unsigned* abort_word) {
+    bool ok = true;
+    for (int k = threadIdx.x; k < K; k += kThreads) {
+        const size_t off = (size_t)(k / seg) * sstride + (size_t)(k % seg);
+        uint2 w[BG];
+#pragma unroll
+        for (int b = 0; b < BG; ++b) w[b] = (b < nlive) ? ll_load(base + (size_t)b * bstride + off) : make_uint2(0u, tag);
+        unsigned spins = 0;
+        for (;;) {
+            bool all = true;
+#pragma unroll
+            for (int b = 0; b < BG; ++b)
+                if (w[b].y != tag) { all = false; w[b] = ll_load(base + (size_t)b * bstride + off); }
+            if (all) break;
+            if (++spins > kSpinLimit || ((spins & 255u) == 0 && ld_acquire_u32(abort_word))) { ok = false; break; }
+        }
+        float* dst = xin + (size_t)k * BG;
+#pragma unroll
+        for (int b = 0; b < BG; ++b) dst[b] = __uint_as_float(w[b].x);
+    }
+    return ok;
+}
+
 struct GridSmem {
     size_t ws, xin, part, state, total;
 };
@@ -538,8 +585,8 @@ static GridSmem grid_layout(int K, int NOUTp, int BG, int KS, int UPC, int Bp, i
     return l;
 }
 
-template <int BG>
-__global__ void __launch_bounds__(kThreads) slstm_fw_grid(SlstmArgs a, GridSmem lay, GridSync* gs, int* status) {
+template <int BG, bool LL>
+__global__ void __launch_bounds__(kThreads) slstm_fw_grid(SlstmArgs a, GridSmem lay, GridSync* gs, int* status, uint2* ll) {
     const int G = a.CS, UPC = a.UPC, dhd = a.dhd, H = a.H, T = a.T, B = a.B;
     const int hd = blockIdx.x / G, cr = blockIdx.x % G;
     const int K = dhd, NOUT = 4 * UPC;
@@ -578,6 +625,8 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_grid(SlstmArgs a, GridSmem 
         for (int q = 0; q < 4; ++q) bias[q] = a.bcat[q * H + own_j];
     }
     bool ok = true;
+    if (tid == 0) s_flag = 1;
+    __syncthreads();
     for (int t = 0; t < T && ok; ++t) {
         float gpre[4] = {0.f, 0.f, 0.f, 0.f};
         if (own) {
@@ -588,9 +637,16 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_grid(SlstmArgs a, GridSmem 
         for (int sg = 0; sg < nsub; ++sg) {
             const int b0 = sg * BG;
             const int nlive = min(BG, B - b0);
-            if (t > 0) stage_rows<BG>(xin, a.out + ((size_t)b0 * T + t - 1) * H + hd * dhd, (size_t)T * H, nlive, K, K, 0);
-            else stage_rows<BG>(xin, a.h + (size_t)b0 * H + hd * dhd, (size_t)H, a.carry ? nlive : 0, K, K, 0);
+            if (t > 0 && LL) {
+                const uint2* src = ll + ((size_t)((t - 1) & 1) * B + b0) * H + hd * dhd;
+                if (!stage_rows_ll<BG>(xin, src, (size_t)H, nlive, K, K, 0, ll_tag(a.epoch, t - 1), &gs->abort)) s_flag = 0;
+            } else if (t > 0) {
+                stage_rows<BG>(xin, a.out + ((size_t)b0 * T + t - 1) * H + hd * dhd, (size_t)T * H, nlive, K, K, 0);
+            } else {
+                stage_rows<BG>(xin, a.h + (size_t)b0 * H + hd * dhd, (size_t)H, a.carry ? nlive : 0, K, K, 0);
+            }
             __syncthreads();
+            if (LL && !s_flag) { ok = false; break; }
             matvec<BG, 2>(Ws, xin, part, K, NOUT, a.KS);
             __syncthreads();
             for (int gi = tid; gi < B * UPC; gi += kThreads) {  // global item b*UPC + ul; this sub-group's only
@@ -618,7 +674,8 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_grid(SlstmArgs a, GridSmem 
                 const SlstmFwCell r = slstm_cell_fw(pre[0], pre[1], pre[2], pre[3], cp, np, mp);
                 st[si] = r.c; st[NS + si] = r.n; st[2 * NS + si] = r.m; st[3 * NS + si] = r.h;
                 const size_t s = ((size_t)(b0 + b) * T + t) * H + j;
-                __stcg(a.out + s, r.h);  // read by the head's other CTAs in the next step
+                if (LL) ll_store(ll + ((size_t)(t & 1) * B + b0 + b) * H + j, r.h, ll_tag(a.epoch, t));
+                __stcg(a.out + s, r.h);  // the record; without the flagged exchange also what the other CTAs read next step
                 __stcs(gt + (size_t)2 * H, pre[2]);
                 __stcs(a.s.h_prev + s, hp);
                 __stcs(a.s.c_prev + s, cp);
@@ -632,10 +689,12 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_grid(SlstmArgs a, GridSmem 
             }
             __syncthreads();  // the next sub-group reuses xin and part
         }
-        ok = group_barrier(gs, hd, (unsigned)(t + 1) * (unsigned)G, &s_flag);  // also orders the last read of the carried h before its update
+        // without the flagged exchange: one counter barrier per step (it also orders the last read of the carried
+        // h before its update; the flagged form is only launched for T >= 2, where the second step does that)
+        if (!LL && ok) ok = group_barrier(gs, hd, (unsigned)(t + 1) * (unsigned)G, &s_flag);
     }
     if (!ok) {
-        if (tid == 0) atomicCAS(status, 0, 301);
+        if (tid == 0) { atomicExch(&gs->abort, 1u); atomicCAS(status, 0, 301); }
         return;
     }
     for (int it = tid; it < NS; it += kThreads) {
@@ -736,7 +795,7 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_grid(SlstmArgs a, GridSmem 
         }
     }
     if (!ok) {
-        if (tid == 0) atomicCAS(status, 0, 302);
+        if (tid == 0) { atomicExch(&gs->abort, 1u); atomicCAS(status, 0, 302); }
         return;
     }
     for (int it = tid; it < NS; it += kThreads) {
@@ -893,12 +952,14 @@ static bool grid_geometry(int B, int NH, int dhd, bool bwd, GridGeo* out) {
     return false;
 }
 
-template <int BG>
+template <int BG, bool LL>
 static int launch_grid(cudaStream_t st, bool bwd, SlstmArgs a, const GridGeo& g) {
-    auto kern = bwd ? slstm_bw_grid<BG> : slstm_fw_grid<BG>;
+    const void* kern = bwd ? (const void*)slstm_bw_grid<BG> : (const void*)slstm_fw_grid<BG, LL>;
     // per device: barrier words' address, and whether the whole grid can be resident at once
     static std::atomic<unsigned long long> key_of[2][64];
     static GridSync* sync_of[64];
+    static uint2* ll_of[64];
+    static unsigned epoch_of[64];
     int dev = 0;
     XL_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) dev = 0;
@@ -915,6 +976,8 @@ static int launch_grid(cudaStream_t st, bool bwd, SlstmArgs a, const GridGeo& g)
         void* p = nullptr;
         XL_CUDA(cudaGetSymbolAddress(&p, g_slstm_sync));
         sync_of[dev] = (GridSync*)p;
+        XL_CUDA(cudaGetSymbolAddress(&p, g_slstm_ll));
+        ll_of[dev] = (uint2*)p;
         if (getenv("XLSTM_DEBUG"))
             fprintf(stderr, "[xlstm] slstm %s grid: G=%d UPC=%d BG=%d KS=%d CPT=%d smem=%zu CTAs=%d\n", bwd ? "bw" : "fw", g.G,
                     g.UPC, g.BG, g.KS, g.CPT, g.lay.total, grid);
@@ -926,8 +989,10 @@ static int launch_grid(cudaStream_t st, bool bwd, SlstmArgs a, const GridGeo& g)
     GridSmem lay = g.lay;
     int* status = tc_status_ptr();
     if (!status) return XLSTM_ERR_CUDA;
-    void* args[4] = {&a, &lay, &gs, &status};
-    XL_CUDA(cudaLaunchCooperativeKernel((const void*)kern, dim3((unsigned)grid), dim3(kThreads), args, g.lay.total, st));
+    uint2* ll = ll_of[dev];
+    a.epoch = (++epoch_of[dev]) & 0xfffu;
+    void* args[5] = {&a, &lay, &gs, &status, &ll};  // the backward kernel takes the first four
+    XL_CUDA(cudaLaunchCooperativeKernel(kern, dim3((unsigned)grid), dim3(kThreads), args, g.lay.total, st));
     count_launch();
     return XLSTM_OK;
 }
@@ -938,11 +1003,16 @@ static int run_grid(cudaStream_t st, bool bwd, const SlstmArgs& a) {
         set_error("slstm: recurrent slice for %d units per head over %d heads does not fit the GPU's shared memory", a.dhd, a.NH);
         return XLSTM_DECLINED;
     }
+    // Flagged exchange: forward only, and only where it measured faster than the counter barrier, which is when
+    // the whole batch is one sub-group (512-unit heads at B = 8: 4.3 vs 5.1 us per step; with several
+    // sub-groups per step the polling costs more than the one barrier it saves). Its two buffers must fit the
+    // built-in array, the tags need T < 2^20, and the second step is what orders the carried h (see the kernel).
+    const bool ll = !bwd && a.B <= g.BG && (size_t)2 * a.B * a.H <= kLLWords && a.T >= 2 && a.T < (1 << 20);
     switch (g.BG) {
-        case 8: return launch_grid<8>(st, bwd, a, g);
-        case 4: return launch_grid<4>(st, bwd, a, g);
-        case 2: return launch_grid<2>(st, bwd, a, g);
-        default: return launch_grid<1>(st, bwd, a, g);
+        case 8: return ll ? launch_grid<8, true>(st, bwd, a, g) : launch_grid<8, false>(st, bwd, a, g);
+        case 4: return ll ? launch_grid<4, true>(st, bwd, a, g) : launch_grid<4, false>(st, bwd, a, g);
+        case 2: return ll ? launch_grid<2, true>(st, bwd, a, g) : launch_grid<2, false>(st, bwd, a, g);
+        default: return ll ? launch_grid<1, true>(st, bwd, a, g) : launch_grid<1, false>(st, bwd, a, g);
     }
 }
 
