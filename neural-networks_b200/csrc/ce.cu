@@ -80,6 +80,13 @@ __global__ void __launch_bounds__(1024) ce_row_cta(const float* __restrict__ log
                 sum += expf(t - mx);
             }
         }
+        if (CACHE && r + (int)gridDim.x < rows) {
+            // pull this CTA's next row into L2 while this row is reduced and its gradient written, so that DRAM
+            // keeps reading through those phases and the next pass 1 starts from L2
+            const char* nz = reinterpret_cast<const char*>(logits + (size_t)(r + gridDim.x) * C);
+            for (size_t o = (size_t)threadIdx.x * 128; o < (size_t)C * sizeof(float); o += (size_t)blockDim.x * 128)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(nz + o));
+        }
         float gmx = block_max(mx, red);
         sum = (mx == -INFINITY) ? 0.f : sum * expf(mx - gmx);
         float gsum = block_sum(sum, red);
