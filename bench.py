@@ -186,9 +186,20 @@ def run_ours(args):
     torch.cuda.synchronize()
     q, k, v, ig, fg, dy = dev_in
 
-    def step():
+    marks = []  # (before forward, between, after backward) events of every timed step
+
+    def step(timed=False):
+        if timed:
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            marks.append(ev)
+            ev[0].record()
         fused = ops.mlstm_fused_fw(q, k, v, ig, fg, st, save_states=not args.recompute, want_state=False)
-        return fused, ops.mlstm_fused_bw(fused, q, k, v, ig, fg, dy, st, want_dstate=False)
+        if timed:
+            ev[1].record()
+        g = ops.mlstm_fused_bw(fused, q, k, v, ig, fg, dy, st, want_dstate=False)
+        if timed:
+            ev[2].record()
+        return fused, g
 
     def barrier():
         if world > 1:
@@ -208,7 +219,7 @@ def run_ours(args):
     barrier()
     e0.record()
     for _ in range(args.steps):
-        step()
+        step(timed=True)
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
@@ -220,19 +231,10 @@ def run_ours(args):
         ms = float(t.item())
     ms_per_step = ms / args.steps
 
-    # ---- per-kernel timing for the roofline (forward and backward separately) -----------
-    fw_ms, bw_ms = [], []
-    for _ in range(max(3, min(args.steps, 10))):
-        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        torch.cuda._sleep(2_000_000)  # ~1 ms of device time, so the host has both launches queued before the first starts
-        a.record()
-        fused = ops.mlstm_fused_fw(q, k, v, ig, fg, st, save_states=not args.recompute, want_state=False)
-        b.record()
-        ops.mlstm_fused_bw(fused, q, k, v, ig, fg, dy, st, want_dstate=False)
-        c.record()
-        torch.cuda.synchronize()
-        fw_ms.append(a.elapsed_time(b)); bw_ms.append(b.elapsed_time(c))
-    fw_t, bw_t = float(np.mean(fw_ms)), float(np.mean(bw_ms))
+    # ---- per-kernel durations for the roofline: CUDA events around each op inside the timed region above.
+    # The device runs behind the host there, so the gap between two marks is the op's kernels and nothing else.
+    fw_t = float(np.median([m[0].elapsed_time(m[1]) for m in marks]))
+    bw_t = float(np.median([m[1].elapsed_time(m[2]) for m in marks]))
 
     # ---- end to end from pinned host buffers ----------------------------------------------
     outs_host = None
@@ -274,6 +276,11 @@ def run_ours(args):
         tokens = cfg["B"] * cfg["T"]
         value = (ff + fb) * world / (ms_per_step * 1e-3) / 1e12
         achieved = bb / (bw_t * 1e-3) / 1e9
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of this workload at its default
+        # settings (profiles/mlstm_tc_cfg2.md); includes the 138 MB chunk-state record, which the algorithmic bytes
+        # leave out. Other settings were not captured.
+        default_cfg = args.grad_dtype == "f32" and not args.recompute and cfg["B"] == 16
+        traffic = {"bw": 545564928 + 366242560, "fw": 204251648 + 165690368} if default_cfg else {"bw": None, "fw": None}
         cpu = cpu_sample() if world == 1 and not args.no_cpu else None
         line = {
             "metric": "mlstm_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -286,10 +293,10 @@ def run_ours(args):
             "tokens_per_s": tokens * world / (ms_per_step * 1e-3),
             "frac_of_bf16_peak": value / world / pk["tensor"],
             "roofline": {"kernel": "mlstm backward", "bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
-                         "frac": achieved / pk["hbm"], "traffic": None, "peak_source": pk["src"],
+                         "frac": achieved / pk["hbm"], "traffic": traffic["bw"], "peak_source": pk["src"],
                          "algorithmic_bytes": bb, "launch_ms": bw_t,
                          "forward": {"achieved": bf / (fw_t * 1e-3) / 1e9, "frac": bf / (fw_t * 1e-3) / 1e9 / pk["hbm"],
-                                     "algorithmic_bytes": bf, "launch_ms": fw_t}},
+                                     "algorithmic_bytes": bf, "launch_ms": fw_t, "traffic": traffic["fw"]}},
             "e2e": {"value": (ff + fb) * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
             "gpu_launches": int(launches),
@@ -316,7 +323,6 @@ def run_lm(args):
     kernels cover today (configs[3] itself asks for d = 2048 with heads of 256 / 512)."""
     import torch
     import torch.distributed as dist
-    from oracle import model as M  # host-side seeded weight generator only (numpy); nothing is computed by the oracle
     xl = importlib.import_module("neural-networks_b200")
     layers = importlib.import_module("neural-networks_b200.layers")
     dp = importlib.import_module("neural-networks_b200.dp")
@@ -330,7 +336,7 @@ def run_lm(args):
     up = (8 * c["d"] // 3 + 7) // 8 * 8
     rng = np.random.default_rng(0)  # identical replicas on every rank
     slstm_at = tuple(i for i in range(c["blocks"]) if i % c["slstm_every"] == 0)
-    p = M.init_lm_params(rng, c["vocab"], c["d"], c["blocks"], c["heads"], c["dqk"], c["dhv"], up, std=0.02, slstm_at=slstm_at,
+    p = layers.init_lm_params(rng, c["vocab"], c["d"], c["blocks"], c["heads"], c["dqk"], c["dhv"], up, std=0.02, slstm_at=slstm_at,
                          nh_s=c["slstm_heads"])
     # full widths: the first `--lm-remat` mLSTM blocks keep only their input and re-run their forward in the
     # backward, so that 24 blocks fit in HBM; sLSTM blocks (the long sequential loops) are never re-run

@@ -412,6 +412,32 @@ class Lm:
         return loss
 
 
+def init_lm_params(rng, vocab, d, n_blocks, heads, dqk, dhv, up, std=0.02, slstm_at=(), nh_s=1):
+    """Seeded N(0, std) host weights (numpy Generator `rng`) in the dictionary layout `build_lm` takes: norm
+    gains 1, every other tensor N(0, std) rounded to fp32. Blocks listed in `slstm_at` are sLSTM blocks with
+    `nh_s` block-diagonal heads (dense recurrence when nh_s == 1)."""
+    import numpy as np
+
+    def n(*shape):
+        return (rng.standard_normal(shape, dtype=np.float32) * np.float32(std))
+
+    blocks = []
+    for i in range(n_blocks):
+        blk = dict(g1=np.ones(d, np.float32), g2=np.ones(d, np.float32), w_gate=n(d, up), b_gate=n(up), w_value=n(d, up),
+                   b_value=n(up), w_down=n(up, d), b_down=n(d))
+        if i in slstm_at:
+            dh = d // nh_s
+            cell = dict(kind="slstm", wx=n(d, 4 * d), wh=n(nh_s, dh, 4 * dh) if nh_s > 1 else n(d, 4 * d), bcat=n(4 * d))
+            blk["gpost"] = np.ones(d, np.float32)
+        else:
+            cell = dict(kind="mlstm", wq=n(d, heads * dqk), wk=n(d, heads * dqk), wv=n(d, heads * dhv), wo=n(d, heads * dhv),
+                        wi=n(d, heads), wf=n(d, heads), bq=n(heads * dqk), bk=n(heads * dqk), bv=n(heads * dhv),
+                        bo=n(heads * dhv), bi=n(heads), bf=n(heads), w_out=n(d, d), b_out=n(d), gamma=np.ones(d, np.float32))
+        blk["cell"] = cell
+        blocks.append(blk)
+    return dict(table=n(vocab, d), blocks=blocks, gamma=np.ones(d, np.float32))
+
+
 def build_lm(params, heads, dqk, dhv, nh_s=1, cap=30.0, tied=True, head_w=None, head_b=None, bf16=False, chunk=64,
              remat=False, head_rows=0, head_split=False):
     """Builds an Lm from the host parameter dictionary `oracle.model.init_lm_params` produces."""
