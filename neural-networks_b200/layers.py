@@ -146,6 +146,8 @@ class MLstm:
         self.hn = RmsNorm(p["gamma"], group=dhv)
         self.inv_sqrt = 1.0 / math.sqrt(dqk)
         self.carry = None  # (C, n, m) when a call continues the previous one
+        self.stateful = False  # inference: keep the state a call ends with as the next call's carry
+        self.shard_group = None  # head-sharded inference: process group whose ranks split the heads
 
     def forward(self, x, B, T):
         sdt = torch.bfloat16 if self.bf16 else torch.float32
@@ -158,10 +160,20 @@ class MLstm:
         self.o = self.lo.forward(x)  # activated in place by the output-gate kernel below
         ig, fg = self.li.forward(x), self.lf.forward(x)
         self.core_in = (q, k, v, ig, fg)
-        self.fused = ops.mlstm_fused_fw(q, k, v, ig, fg, self.st, carry_in=self.carry, want_state=False)
+        self.fused = ops.mlstm_fused_fw(q, k, v, ig, fg, self.st, carry_in=self.carry, want_state=self.stateful,
+                                        save_states=not self.stateful)
+        if self.stateful:
+            self.carry = self.fused.state
         self.yhat = self.hn.forward(self.fused.ytil.float() if self.bf16 else self.fused.ytil)
         hc = ops.ogate_forward(self.o, self.yhat, torch.bfloat16 if self.bf16 else torch.float32)
-        return self.lout.forward(hc)
+        if self.shard_group is None:
+            return self.lout.forward(hc)
+        # heads are split over the group's ranks: W_out's rows are too, and the partial products are summed
+        # (the one exchange head sharding needs; the bias is added once, after the sum)
+        import torch.distributed as dist
+        y = _mm(hc, self.lout.w.wb if self.bf16 else self.lout.w.w, self.bf16)
+        dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.shard_group)
+        return y.add_(self.lout.b.w)
 
     def backward(self, dy):
         d_hc = self.lout.backward(dy)
@@ -199,15 +211,20 @@ class SLstm:
         self.wx = Param(p["wx"], True, shadow=bf16)
         self.wh = Param(p["wh"], True)
         self.b = Param(p["bcat"], False)
+        self.stateful = False  # inference: (c, n, m, h) persists from call to call
+        self.state = None
 
     def forward(self, x, B, T):
         H = self.H
         self.B, self.T, self.x = B, T, (_b16(x) if self.bf16 else x)
         self.g = _mm(self.x, self.wx.wb if self.bf16 else self.wx.w, self.bf16).view(B, T, 4 * H)
         self.slabs = ops.SlstmSlabs(B, T, H, x.device)
-        state = tuple(torch.empty((B, H), dtype=torch.float32, device=x.device) for _ in range(4))
+        carry = self.stateful and self.state is not None
+        state = self.state if carry else tuple(torch.empty((B, H), dtype=torch.float32, device=x.device) for _ in range(4))
         out = torch.empty((B, T, H), dtype=torch.float32, device=x.device)
-        ops.slstm_fused_time(self.wh.w, self.g, self.b.w, state, out, self.slabs, nh=self.nh, carry=False)
+        ops.slstm_fused_time(self.wh.w, self.g, self.b.w, state, out, self.slabs, nh=self.nh, carry=carry)
+        if self.stateful:
+            self.state = state  # updated in place to the state after the last position
         return out.view(B * T, H)
 
     def backward(self, dy):
