@@ -168,11 +168,15 @@ int xlstm_ce_fw_bw_noalloc(void* stream, const float* logits, const uint32_t* ta
  * ogate_fwd/ogate_bwd, src/gpu/cuda/mlstm_ops.cu:147-153, 400-407, with the bf16 narrowing of outputs
  * that feed a GEMM folded in, src/gpu/cuda/bf16_cast.cu:22-60). Flat arrays of n elements; out_dtype is
  * XLSTM_F32 or XLSTM_BF16 and applies to the outputs typed void*. */
-/* out = SiLU(gate_pre) * value */
-int xlstm_swiglu_fw(void* stream, const float* gate_pre, const float* value, void* out, int out_dtype, size_t n);
-/* d_gate = d_mixed * value * SiLU'(gate_pre); d_value = d_mixed * SiLU(gate_pre) */
+/* out = SiLU(gate_pre + bias_gate) * (value + bias_value). The biases ([cols] each, or both NULL) are the
+ * gate/value projections' biases, folded in here so that those GEMMs need no bias pass (the reference seeds
+ * the GEMM output with broadcast_row, src/gpu/cuda/common.cu:20-48); element i is in column i % cols. */
+int xlstm_swiglu_fw(void* stream, const float* gate_pre, const float* value, const float* bias_gate,
+                    const float* bias_value, int cols, void* out, int out_dtype, size_t n);
+/* with g = gate_pre + bias_gate, v = value + bias_value: d_gate = d_mixed * v * SiLU'(g); d_value = d_mixed * SiLU(g) */
 int xlstm_swiglu_bw(void* stream, const float* d_mixed, const float* gate_pre, const float* value,
-                    void* d_gate, void* d_value, int out_dtype, size_t n);
+                    const float* bias_gate, const float* bias_value, int cols, void* d_gate, void* d_value,
+                    int out_dtype, size_t n);
 /* o <- sigmoid(o) in place; hc = o * yhat */
 int xlstm_ogate_fw(void* stream, float* o, const float* yhat, void* hc, int out_dtype, size_t n);
 /* do_pre = d_hc * yhat * o * (1 - o) with o the activated gate; d_yhat = d_hc * o (fp32) */

@@ -31,26 +31,37 @@ __device__ __forceinline__ float silu_f(float x, float* sig) {
     return x * s;
 }
 
-// out = SiLU(gate) * value
+// Optional per-column biases of the two projections, folded in here so that the GEMMs' outputs need no
+// bias pass of their own: element i belongs to column i % cols.
+__device__ __forceinline__ float4 bias4(const float* b, size_t i4, int cols) {
+    if (!b) return make_float4(0.f, 0.f, 0.f, 0.f);
+    return __ldg(reinterpret_cast<const float4*>(b + (4 * i4) % (size_t)cols));
+}
+__device__ __forceinline__ float bias1(const float* b, size_t i, int cols) { return b ? __ldg(b + i % (size_t)cols) : 0.f; }
+__device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+
+// out = SiLU(gate + bg) * (value + bv)
 template <typename OT>
 __global__ void __launch_bounds__(256) swiglu_fw_k(const float* __restrict__ gate, const float* __restrict__ value,
+                                                   const float* __restrict__ bg, const float* __restrict__ bv, int cols,
                                                    OT* __restrict__ out, size_t n, int vec) {
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     float s;
     if (vec) {
         if (i >= n / 4) return;
-        const float4 g = ld4(gate, i), v = ld4(value, i);
+        const float4 g = add4(ld4(gate, i), bias4(bg, i, cols)), v = add4(ld4(value, i), bias4(bv, i, cols));
         st4(out, i, make_float4(silu_f(g.x, &s) * v.x, silu_f(g.y, &s) * v.y, silu_f(g.z, &s) * v.z, silu_f(g.w, &s) * v.w));
     } else {
         if (i >= n) return;
-        st1(out, i, silu_f(gate[i], &s) * value[i]);
+        st1(out, i, silu_f(gate[i] + bias1(bg, i, cols), &s) * (value[i] + bias1(bv, i, cols)));
     }
 }
 
 // d_gate = d * value * SiLU'(gate), d_value = d * SiLU(gate);  SiLU'(x) = s (1 + x (1 - s))
 template <typename OT>
 __global__ void __launch_bounds__(256) swiglu_bw_k(const float* __restrict__ d, const float* __restrict__ gate,
-                                                   const float* __restrict__ value, OT* __restrict__ d_gate,
+                                                   const float* __restrict__ value, const float* __restrict__ bg,
+                                                   const float* __restrict__ bv, int cols, OT* __restrict__ d_gate,
                                                    OT* __restrict__ d_value, size_t n, int vec) {
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     auto one = [](float dd, float g, float v, float* dg, float* dv) {
@@ -61,7 +72,7 @@ __global__ void __launch_bounds__(256) swiglu_bw_k(const float* __restrict__ d, 
     };
     if (vec) {
         if (i >= n / 4) return;
-        const float4 dd = ld4(d, i), g = ld4(gate, i), v = ld4(value, i);
+        const float4 dd = ld4(d, i), g = add4(ld4(gate, i), bias4(bg, i, cols)), v = add4(ld4(value, i), bias4(bv, i, cols));
         float4 dg, dv;
         one(dd.x, g.x, v.x, &dg.x, &dv.x); one(dd.y, g.y, v.y, &dg.y, &dv.y);
         one(dd.z, g.z, v.z, &dg.z, &dv.z); one(dd.w, g.w, v.w, &dg.w, &dv.w);
@@ -70,7 +81,7 @@ __global__ void __launch_bounds__(256) swiglu_bw_k(const float* __restrict__ d, 
     } else {
         if (i >= n) return;
         float dg, dv;
-        one(d[i], gate[i], value[i], &dg, &dv);
+        one(d[i], gate[i] + bias1(bg, i, cols), value[i] + bias1(bv, i, cols), &dg, &dv);
         st1(d_gate, i, dg);
         st1(d_value, i, dv);
     }
@@ -151,27 +162,43 @@ using namespace xl;
     XL_CHECK_ARG(out_dtype == XLSTM_F32 || out_dtype == XLSTM_BF16, who ": out_dtype must be XLSTM_F32 or XLSTM_BF16"); \
     if (n == 0) return XLSTM_OK;
 
-extern "C" int xlstm_swiglu_fw(void* stream, const float* gate_pre, const float* value, void* out, int out_dtype, size_t n) {
+// the biases are read as float4 in the vector path: usable when cols is a multiple of 4 and they are 16-byte aligned
+static inline int bias_vec_ok(const float* bg, const float* bv, int cols) {
+    if (!bg && !bv) return 1;
+    return cols % 4 == 0 && !((uintptr_t)bg & 15) && !((uintptr_t)bv & 15);
+}
+
+extern "C" int xlstm_swiglu_fw(void* stream, const float* gate_pre, const float* value, const float* bias_gate,
+                               const float* bias_value, int cols, void* out, int out_dtype, size_t n) {
     XL_CHECK_ARG(gate_pre && value && out, "swiglu_fw: null pointer");
+    XL_CHECK_ARG((!bias_gate && !bias_value) || (cols > 0 && n % (size_t)cols == 0), "swiglu_fw: biases need cols > 0 dividing n");
     GLUE_CHECK("swiglu_fw")
     cudaStream_t st = (cudaStream_t)stream;
-    const int vec = can_vec(n, {gate_pre, value, out});
-    if (out_dtype == XLSTM_BF16) swiglu_fw_k<bf16><<<blocks_for(n, vec), 256, 0, st>>>(gate_pre, value, (bf16*)out, n, vec);
-    else swiglu_fw_k<float><<<blocks_for(n, vec), 256, 0, st>>>(gate_pre, value, (float*)out, n, vec);
+    const int vec = can_vec(n, {gate_pre, value, out}) && bias_vec_ok(bias_gate, bias_value, cols);
+    if (cols <= 0) cols = 1;
+    if (out_dtype == XLSTM_BF16)
+        swiglu_fw_k<bf16><<<blocks_for(n, vec), 256, 0, st>>>(gate_pre, value, bias_gate, bias_value, cols, (bf16*)out, n, vec);
+    else
+        swiglu_fw_k<float><<<blocks_for(n, vec), 256, 0, st>>>(gate_pre, value, bias_gate, bias_value, cols, (float*)out, n, vec);
     XL_LAUNCH_OK("swiglu_fw");
     return XLSTM_OK;
 }
 
-extern "C" int xlstm_swiglu_bw(void* stream, const float* d_mixed, const float* gate_pre, const float* value, void* d_gate,
-                               void* d_value, int out_dtype, size_t n) {
+extern "C" int xlstm_swiglu_bw(void* stream, const float* d_mixed, const float* gate_pre, const float* value,
+                               const float* bias_gate, const float* bias_value, int cols, void* d_gate, void* d_value,
+                               int out_dtype, size_t n) {
     XL_CHECK_ARG(d_mixed && gate_pre && value && d_gate && d_value, "swiglu_bw: null pointer");
+    XL_CHECK_ARG((!bias_gate && !bias_value) || (cols > 0 && n % (size_t)cols == 0), "swiglu_bw: biases need cols > 0 dividing n");
     GLUE_CHECK("swiglu_bw")
     cudaStream_t st = (cudaStream_t)stream;
-    const int vec = can_vec(n, {d_mixed, gate_pre, value, d_gate, d_value});
+    const int vec = can_vec(n, {d_mixed, gate_pre, value, d_gate, d_value}) && bias_vec_ok(bias_gate, bias_value, cols);
+    if (cols <= 0) cols = 1;
     if (out_dtype == XLSTM_BF16)
-        swiglu_bw_k<bf16><<<blocks_for(n, vec), 256, 0, st>>>(d_mixed, gate_pre, value, (bf16*)d_gate, (bf16*)d_value, n, vec);
+        swiglu_bw_k<bf16><<<blocks_for(n, vec), 256, 0, st>>>(d_mixed, gate_pre, value, bias_gate, bias_value, cols, (bf16*)d_gate,
+                                                              (bf16*)d_value, n, vec);
     else
-        swiglu_bw_k<float><<<blocks_for(n, vec), 256, 0, st>>>(d_mixed, gate_pre, value, (float*)d_gate, (float*)d_value, n, vec);
+        swiglu_bw_k<float><<<blocks_for(n, vec), 256, 0, st>>>(d_mixed, gate_pre, value, bias_gate, bias_value, cols, (float*)d_gate,
+                                                               (float*)d_value, n, vec);
     XL_LAUNCH_OK("swiglu_bw");
     return XLSTM_OK;
 }

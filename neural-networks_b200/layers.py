@@ -75,12 +75,24 @@ class Linear:
         self.w = Param(w, decay, shadow=bf16)
         self.b = Param(b, False)
 
-    def forward(self, x):
-        """x: fp32, or already narrowed to bf16 by a caller that feeds several projections from it."""
+    def forward(self, x, bias=True, residual=None, narrow=False, scale=1.0):
+        """x: fp32, or already narrowed to bf16 by a caller that feeds several projections from it.
+        bias=False: the product alone (the consumer kernel adds the bias). residual: returns residual + x W + b,
+        with one pass that seeds the output with residual + b and the product accumulated inside the GEMM (the
+        reference's broadcast_row_resid seed, src/gpu/cuda/common.cu:20-48). narrow (bf16 layers): the result
+        straight from the GEMM epilogue as bf16, scale * (x W + b), rounded once."""
         self.x = _b16(x) if self.bf16 else x
-        if self.bf16:
-            return torch.addmm(self.b.w, self.x, self.w.wb, out_dtype=torch.float32)  # bias in the GEMM epilogue
-        return torch.addmm(self.b.w, self.x, self.w.w)
+        w = self.w.wb if self.bf16 else self.w.w
+        if narrow and self.bf16:
+            return torch.addmm(self.b.w.to(torch.bfloat16), self.x, w, beta=scale, alpha=scale)
+        assert scale == 1.0, "scale is folded only into the narrowed epilogue"
+        if residual is not None:
+            out = torch.add(residual, self.b.w)
+            if self.bf16:
+                return torch.addmm(out, self.x, w, out_dtype=torch.float32, out=out)
+            return out.addmm_(self.x, w)
+        y = _mm(self.x, w, self.bf16)
+        return y.add_(self.b.w) if bias else y
 
     def backward(self, dy, need_dx=True, accum=None):
         """Accumulates dW, db; returns dx, added into `accum` (inside the GEMM, beta = 1) when one is given."""
@@ -149,14 +161,21 @@ class MLstm:
         self.stateful = False  # inference: keep the state a call ends with as the next call's carry
         self.shard_group = None  # head-sharded inference: process group whose ranks split the heads
 
-    def forward(self, x, B, T):
+    def forward(self, x, B, T, residual=None):
+        """residual: when given, the call returns residual + cell(x) (the block's first residual add, done inside
+        the output projection's GEMM)."""
         sdt = torch.bfloat16 if self.bf16 else torch.float32
         self.st = ops.MlstmShape(B, self.h, T, self.dqk, self.dhv, self.chunk, sdt, torch.float32)
         if self.bf16:
             x = _b16(x)  # one narrowing feeds all six projections
-        q = self.lq.forward(x).to(sdt)
-        k = self.lk.forward(x).mul_(self.inv_sqrt).to(sdt)
-        v = self.lv.forward(x).to(sdt)
+        if self.bf16:  # bf16 q, k, v straight from the GEMM epilogue (bias and the 1/sqrt(dqk) of k folded in)
+            q = self.lq.forward(x, narrow=True)
+            k = self.lk.forward(x, narrow=True, scale=self.inv_sqrt)
+            v = self.lv.forward(x, narrow=True)
+        else:
+            q = self.lq.forward(x)
+            k = self.lk.forward(x).mul_(self.inv_sqrt)
+            v = self.lv.forward(x)
         self.o = self.lo.forward(x)  # activated in place by the output-gate kernel below
         ig, fg = self.li.forward(x), self.lf.forward(x)
         self.core_in = (q, k, v, ig, fg)
@@ -167,13 +186,14 @@ class MLstm:
         self.yhat = self.hn.forward(self.fused.ytil.float() if self.bf16 else self.fused.ytil)
         hc = ops.ogate_forward(self.o, self.yhat, torch.bfloat16 if self.bf16 else torch.float32)
         if self.shard_group is None:
-            return self.lout.forward(hc)
+            return self.lout.forward(hc, residual=residual)
         # heads are split over the group's ranks: W_out's rows are too, and the partial products are summed
         # (the one exchange head sharding needs; the bias is added once, after the sum)
         import torch.distributed as dist
         y = _mm(hc, self.lout.w.wb if self.bf16 else self.lout.w.w, self.bf16)
         dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.shard_group)
-        return y.add_(self.lout.b.w)
+        y.add_(self.lout.b.w)
+        return y if residual is None else y.add_(residual)
 
     def backward(self, dy):
         d_hc = self.lout.backward(dy)
@@ -265,20 +285,23 @@ class Block:
         self.ld = Linear(p["w_down"], p["b_down"], True, bf16)
 
     def forward(self, x, B, T):
-        c = self.cell.forward(self.n1.forward(x), B, T)
-        if self.post is not None:
-            c = self.post.forward(c)
-        z = x + c
+        if self.post is None:
+            z = self.cell.forward(self.n1.forward(x), B, T, residual=x)
+        else:
+            z = x + self.post.forward(self.cell.forward(self.n1.forward(x), B, T))
         zn = self.n2.forward(z)
         if self.lg.bf16:
             zn = _b16(zn)
-        self.gate_pre, self.value = self.lg.forward(zn), self.lv.forward(zn)
+        # the two projections without their biases: the SwiGLU kernels add them (forward and backward)
+        self.gate_pre, self.value = self.lg.forward(zn, bias=False), self.lv.forward(zn, bias=False)
         nd = torch.bfloat16 if self.ld.bf16 else torch.float32
-        return self.ld.forward(ops.swiglu_forward(self.gate_pre, self.value, nd)).add_(z)
+        mixed = ops.swiglu_forward(self.gate_pre, self.value, nd, self.lg.b.w, self.lv.b.w)
+        return self.ld.forward(mixed, residual=z)
 
     def backward(self, dy):
         d_mixed = self.ld.backward(dy)
-        d_gate, d_value = ops.swiglu_backward(d_mixed, self.gate_pre, self.value, torch.bfloat16 if self.lg.bf16 else torch.float32)
+        d_gate, d_value = ops.swiglu_backward(d_mixed, self.gate_pre, self.value, torch.bfloat16 if self.lg.bf16 else torch.float32,
+                                              self.lg.b.w, self.lv.b.w)
         d_zn = self.lg.backward(d_gate)
         self.lv.backward(d_value, accum=d_zn)
         d_z = self.n2.backward(d_zn).add_(dy)

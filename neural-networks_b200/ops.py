@@ -174,19 +174,21 @@ def _dt(t):
     return _DT[t]
 
 
-def swiglu_forward(gate_pre, value, out_dtype=torch.float32):
-    """swiglu_forward (src/gpu/cuda/block.cu:6-29): SiLU(gate_pre) * value, optionally narrowed to bf16."""
+def swiglu_forward(gate_pre, value, out_dtype=torch.float32, bias_gate=None, bias_value=None):
+    """swiglu_forward (src/gpu/cuda/block.cu:6-29): SiLU(gate_pre + bias_gate) * (value + bias_value), optionally
+    narrowed to bf16. The biases are the two projections' (both or neither), folded in here."""
     out = torch.empty(gate_pre.shape, dtype=out_dtype, device=gate_pre.device)
-    check(lib.xlstm_swiglu_fw(_stream(), _ptr(gate_pre), _ptr(value), _ptr(out), _dt(out_dtype), gate_pre.numel()), "swiglu_forward")
+    check(lib.xlstm_swiglu_fw(_stream(), _ptr(gate_pre), _ptr(value), _ptr(bias_gate), _ptr(bias_value), gate_pre.shape[-1],
+                              _ptr(out), _dt(out_dtype), gate_pre.numel()), "swiglu_forward")
     return out
 
 
-def swiglu_backward(d_mixed, gate_pre, value, out_dtype=torch.float32):
+def swiglu_backward(d_mixed, gate_pre, value, out_dtype=torch.float32, bias_gate=None, bias_value=None):
     """swiglu_backward: (d_gate_pre, d_value), optionally narrowed to bf16 for the GEMMs that consume them."""
     dg = torch.empty(gate_pre.shape, dtype=out_dtype, device=gate_pre.device)
     dv = torch.empty(gate_pre.shape, dtype=out_dtype, device=gate_pre.device)
-    check(lib.xlstm_swiglu_bw(_stream(), _ptr(d_mixed), _ptr(gate_pre), _ptr(value), _ptr(dg), _ptr(dv), _dt(out_dtype),
-                              gate_pre.numel()), "swiglu_backward")
+    check(lib.xlstm_swiglu_bw(_stream(), _ptr(d_mixed), _ptr(gate_pre), _ptr(value), _ptr(bias_gate), _ptr(bias_value),
+                              gate_pre.shape[-1], _ptr(dg), _ptr(dv), _dt(out_dtype), gate_pre.numel()), "swiglu_backward")
     return dg, dv
 
 

