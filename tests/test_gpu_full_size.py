@@ -1,0 +1,180 @@
+"""Parity at BASELINE.json's full sizes. The oracle cannot run a whole config in seconds, so each case uses a
+property that does not depend on size and pins it to the oracle on a sample:
+  - sequences are independent, so one batch entry (and a few heads) of the full-size GPU result is compared
+    with the oracle run on that entry alone;
+  - carry == whole (src/gpu/mlstm.rs:1337-1533, src/gpu/slstm.rs:1843-1938): two half-length calls chained
+    through the carried state / BPTT state reproduce the whole-sequence call;
+  - every gradient is linear in the upstream gradient;
+  - softmax-CE gradient rows sum to zero; sampled rows / elements of the streaming kernels equal the oracle.
+Generated on the device (seeded torch generator), so the host only ever holds the sampled slices."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _gen(shape, seed, scale=1.0, shift=0.0, dtype=torch.float32):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, device="cuda", generator=g) * scale + shift).to(dtype)
+
+
+def _np(t):
+    return t.detach().float().cpu().numpy().astype(np.float64)
+
+
+def _rel(got, ref):
+    return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+@pytest.mark.parametrize("B,H,T,d,heads_checked", [(16, 8, 2048, 128, (0, 5)), (8, 8, 4096, 256, (3,))])
+def test_mlstm_full_size_sample_against_oracle_carry_and_linearity(B, H, T, d, heads_checked):
+    """configs[1] (B16 H8 S2048 d128) and the mLSTM layer of configs[3] (B8 H8 S4096 d256), bf16 storage."""
+    from gpu_util import ops, xl
+    st = ops.MlstmShape(B, H, T, d, d, 64, torch.bfloat16, torch.float32)
+    q = _gen((B * T, H * d), 1, dtype=torch.bfloat16)
+    k = _gen((B * T, H * d), 2, scale=d ** -0.5, dtype=torch.bfloat16)
+    v = _gen((B * T, H * d), 3, dtype=torch.bfloat16)
+    ig, fg = _gen((B * T, H), 4), _gen((B * T, H), 5, shift=3.0)
+    dy = _gen((B * T, H * d), 6)
+    fused = ops.mlstm_fused_fw(q, k, v, ig, fg, st)
+    grads = ops.mlstm_fused_bw(fused, q, k, v, ig, fg, dy, st)
+    torch.cuda.synchronize()
+    assert xl._lib.lib.xlstm_device_status() == 0
+
+    # (1) one batch entry, a few heads, against the oracle on that entry alone
+    b = B // 2 + 1
+    rows = slice(b * T, (b + 1) * T)
+    for h in heads_checked:
+        cols = slice(h * d, (h + 1) * d)
+        args = [_np(a[rows, cols]) for a in (q, k, v)] + [_np(ig[rows, h:h + 1]), _np(fg[rows, h:h + 1])]
+        ofw = O.mlstm_core_fw(*args, 1, 1, T, d, d)
+        obw = O.mlstm_core_bw(*args, _np(dy[rows, cols]), 1, 1, T, d, d)
+        assert _rel(_np(fused.ytil[rows, cols]), ofw["ytil"]) <= 2e-2
+        for name, g in zip(("dq", "dk", "dv"), grads[:3]):
+            assert _rel(_np(g[rows, cols]), obw[name]) <= 2e-2, name
+        for name, g in zip(("dig", "dfg"), grads[3:5]):
+            assert _rel(_np(g[rows, h:h + 1]), obw[name]) <= 2e-2, name
+
+    # (2) carry == whole: two half-length calls chained through (C, n, m) forward and (dC, dn) backward
+    Th = T // 2
+    sth = ops.MlstmShape(B, H, Th, d, d, 64, torch.bfloat16, torch.float32)
+    half = lambda a, i: a.view(B, T, -1)[:, i * Th:(i + 1) * Th, :].reshape(B * Th, -1).contiguous()
+    f0 = ops.mlstm_fused_fw(*(half(a, 0) for a in (q, k, v, ig, fg)), sth)
+    f1 = ops.mlstm_fused_fw(*(half(a, 1) for a in (q, k, v, ig, fg)), sth, carry_in=f0.state)
+    y2 = torch.cat([f0.ytil.view(B, Th, -1), f1.ytil.view(B, Th, -1)], dim=1).reshape(B * T, -1)
+    assert float((y2.float() - fused.ytil.float()).abs().max()) <= 3e-2 * float(fused.ytil.float().abs().max())
+    g1 = ops.mlstm_fused_bw(f1, *(half(a, 1) for a in (q, k, v, ig, fg)), half(dy, 1), sth, carry_in=f0.state)
+    g0 = ops.mlstm_fused_bw(f0, *(half(a, 0) for a in (q, k, v, ig, fg)), half(dy, 0), sth, dstate_in=g1[5])
+    for i, name in enumerate(("dq", "dk", "dv", "dig", "dfg")):
+        joined = torch.cat([g0[i].view(B, Th, -1), g1[i].view(B, Th, -1)], dim=1).reshape(B * T, -1)
+        whole = grads[i].view(B * T, -1)
+        assert float((joined - whole).abs().max()) <= 3e-2 * float(whole.abs().max()), name
+
+    # (3) the backward is linear in dy
+    dy2 = _gen((B * T, H * d), 7)
+    ga = ops.mlstm_fused_bw(fused, q, k, v, ig, fg, dy2, st)
+    gc = ops.mlstm_fused_bw(fused, q, k, v, ig, fg, 0.5 * dy - 2.0 * dy2, st)
+    for i, name in enumerate(("dq", "dk", "dv", "dig", "dfg")):
+        want = 0.5 * grads[i] - 2.0 * ga[i]
+        assert float((gc[i] - want).abs().max()) <= 2e-2 * float(want.abs().max()), name
+
+
+@pytest.mark.parametrize("B,H,NH,T", [(32, 1024, 4, 1024), (8, 2048, 4, 1024)])
+def test_slstm_full_size_sample_against_oracle_and_carry(B, H, NH, T):
+    """configs[2] (B32, 4 x 256, S1024) on the cluster kernels and the sLSTM layer of configs[3] (B8, 4 x 512; the
+    sequence cut to 1024 positions to bound the oracle's time) on the grid kernels; fp32."""
+    from gpu_util import ops, xl
+    dh = H // NH
+    wh = _gen((NH, dh, 4 * dh), 11, scale=dh ** -0.5)
+    g0 = _gen((B, T, 4 * H), 12)
+    bc = torch.zeros(4 * H, device="cuda"); bc[2 * H:3 * H] = 4.5
+    dy = _gen((B, T, H), 13)
+
+    def run(gin, dyin, Tn, state=None, dstate=None):
+        g = gin.clone()
+        stt = state if state is not None else tuple(torch.empty((B, H), device="cuda") for _ in range(4))
+        out = torch.empty((B, Tn, H), device="cuda")
+        slabs = ops.SlstmSlabs(B, Tn, H, "cuda")
+        ops.slstm_fused_time(wh, g, bc, stt, out, slabs, nh=NH, carry=state is not None)
+        return g, stt, out, slabs
+
+    g, stt, out, slabs = run(g0, dy, T)
+    ds = tuple(torch.empty((B, H), device="cuda") for _ in range(3))
+    ops.slstm_fused_time_bwd(wh, dy, g, ds, slabs, nh=NH, carry=False)
+    torch.cuda.synchronize()
+    assert xl._lib.lib.xlstm_device_status() == 0
+
+    # (1) one batch entry against the oracle on that entry alone
+    b = B - 3
+    fw = O.slstm_fw(_np(wh), _np(g0[b:b + 1]), _np(bc), 1, H, NH, T)
+    bw = O.slstm_bw(_np(wh), _np(dy[b:b + 1]), fw, 1, H, NH, T)
+    assert _rel(_np(out[b:b + 1]), fw["out"]) <= 1e-4
+    assert _rel(_np(g[b:b + 1]), bw["dg"]) <= 1e-4
+
+    # (2) carry == whole, forward and backward
+    Th = T // 2
+    ga, sa, oa, sla = run(g0[:, :Th].contiguous(), None, Th)
+    state_mid = tuple(t.clone() for t in sa)
+    gb, sb, ob, slb = run(g0[:, Th:].contiguous(), None, Th, state=sa)
+    assert float((torch.cat([oa, ob], dim=1) - out).abs().max()) <= 1e-4 * float(out.abs().max())
+    dsb = tuple(torch.empty((B, H), device="cuda") for _ in range(3))
+    ops.slstm_fused_time_bwd(wh, dy[:, Th:].contiguous(), gb, dsb, slb, nh=NH, carry=False)
+    ops.slstm_fused_time_bwd(wh, dy[:, :Th].contiguous(), ga, dsb, sla, nh=NH, carry=True)
+    joined = torch.cat([ga, gb], dim=1)
+    assert float((joined - g).abs().max()) <= 1e-4 * float(g.abs().max())
+    del state_mid
+
+
+def test_streaming_kernels_at_configs3_sizes():
+    """RMSNorm on [32768, 2048], soft-cap + cross-entropy on [8192, 50304] (one row chunk of the head), AdamW on
+    268 M parameters: sampled rows / elements against the oracle, and whole-tensor identities."""
+    from gpu_util import ops
+    r = np.random.default_rng(0)
+    rows, F = 32768, 2048
+    x, gam = _gen((rows, F), 21), _gen((F,), 22, scale=0.1, shift=1.0)
+    y = torch.empty_like(x); inv = torch.empty((rows,), device="cuda")
+    ops.rms_norm_forward_into(x, gam, F, y, inv)
+    pick = r.integers(0, rows, 16)
+    want = O.rmsnorm_fw(_np(x[pick]), _np(gam), F)[0]
+    assert _rel(_np(y[pick]), want) <= 1e-5
+    ms = ((y / gam) ** 2).mean(dim=1)
+    assert float((ms - 1.0).abs().max()) <= 1e-3  # every row normalised
+    del x, y
+
+    rows, C, cap = 8192, 50304, 30.0
+    pre = _gen((rows, C), 23, scale=10.0)
+    tg = torch.randint(0, C, (rows,), device="cuda", dtype=torch.int32)
+    keep = pre[pick % rows].clone()
+    ref_loss = 0.0  # float64 log-sum-exp over all rows, a slab of rows at a time (torch, independent of the kernel)
+    for lo in range(0, rows, 1024):
+        zc = cap * torch.tanh(pre[lo:lo + 1024].double() / cap)
+        ref_loss += float((torch.logsumexp(zc, dim=1) - zc[torch.arange(zc.shape[0]), tg[lo:lo + 1024].long()]).sum())
+    ref_loss /= rows
+    acc = torch.zeros(1, device="cuda")
+    ops.softcap_cross_entropy(pre, tg, pre, acc, cap)  # gradient written in place
+    z = cap * np.tanh(_np(keep) / cap)
+    loss_s, dz = O.softmax_ce(z, _np(tg[pick % rows]).astype(np.int64), inv=1.0 / rows)
+    assert _rel(_np(pre[pick % rows]), dz * (1.0 - (z / cap) ** 2)) <= 1e-4
+    zs = cap * torch.tanh(keep.double() / cap)
+    # oracle and torch agree on the sampled rows' loss; the gradient rows, taken back through the cap, sum to zero
+    lse = torch.logsumexp(zs, dim=1) - zs[torch.arange(len(pick)), tg[pick % rows].long()]
+    assert abs(float(lse.sum()) / rows - loss_s) <= 1e-6 * max(1.0, abs(loss_s))
+    assert abs(acc.item() - ref_loss) <= 1e-5 * ref_loss
+    rs = (_np(pre[pick % rows]) / (1.0 - (z / cap) ** 2)).sum(axis=1)
+    assert np.abs(rs).max() <= 1e-6
+    del pre
+
+    n = 268_435_456
+    p, gr = _gen((n,), 24), _gen((n,), 25, scale=0.01)
+    m, vv = torch.zeros_like(p), torch.zeros_like(p)
+    idx = torch.tensor(r.integers(0, n, 4096), device="cuda")
+    p0, g0 = _np(p[idx]), _np(gr[idx])
+    q = ops.AdamwQueue()
+    q.push(p, gr, m, vv, True, None)
+    q.flush(ops.AdamCfg(1e-3, 0.1, t=1), zero_grad=True)
+    wp, wm, wv = O.adamw(p0, g0, np.zeros_like(p0), np.zeros_like(p0), 1e-3, 0.1, 1, dtype=np.float32)
+    assert _rel(_np(p[idx]), wp) <= 1e-6 and _rel(_np(m[idx]), wm) <= 1e-6 and _rel(_np(vv[idx]), wv) <= 1e-6
+    assert float(gr.abs().max()) == 0.0
