@@ -25,6 +25,7 @@ using namespace tc;
 int* tc_status_ptr();
 long long* tc_debug_prof();
 bool tc_make_map3(CUtensorMap* m, const void* base, int B, int T, int W);
+bool tc_make_map2(CUtensorMap* m, const void* base, uint64_t rows, int W, int box_rows);
 
 namespace fw {
 
@@ -49,6 +50,7 @@ struct Gates {
 
 struct Params {
     CUtensorMap tmq, tmk, tmv;
+    CUtensorMap tmc;  // the bf16 C record as rows of 128: [sub-heads * (NC+1) * 128][128], box {64, 128} (when a record is kept)
     const float *ig, *fg;
     const float *cC, *cn, *cm;
     bf16* ytil;
@@ -316,6 +318,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
                 m_prev = gates_compute(graw, m_prev, &G[st ^ 1]);
                 if (ch + 2 < p.NC) gates_load(p, b, h, ch + 2, graw);
             }
+            if (p.savedC && lane == 0) tma_store_wait_read();  // the previous record store has read sCb: phase 3 may overwrite it
         } else if (full) {
             if (!mbar_wait(&bars[2], ch & 1)) *abort_flag = 2;
             tc_fence_after();
@@ -387,13 +390,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
                 float v[32];
                 tmem_ld32(tC + lane_base + c0, v);
                 tmem_ld_wait();
-                bf16* rec = p.savedC ? p.savedC + ((size_t)sbh * (p.NC + 1) + ch + 1) * D * D + (size_t)x * D + c0 : nullptr;
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint4 pk = pack8(v + 8 * q);
-                    *reinterpret_cast<uint4*>(sCb + (cq >> 1) * kStateBox + swz(x, 4 * (cq & 1) + q)) = pk;
-                    if (rec) *reinterpret_cast<uint4*>(rec + 8 * q) = pk;
-                }
+                for (int q = 0; q < 4; ++q)  // the record of this state is stored from this copy by TMA, after the barrier
+                    *reinterpret_cast<uint4*>(sCb + (cq >> 1) * kStateBox + swz(x, 4 * (cq & 1) + q)) = pack8(v + 8 * q);
                 if (last && p.oC) {
                     float* oc = p.oC + ((size_t)bh * dhv + vh * D + x) * dqk + qh * D + c0;
 #pragma unroll
@@ -442,7 +441,15 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
         }
         __syncthreads();  // #3
         if (*abort_flag) { ok = false; break; }
+        if (p.savedC && tid == kMathThreads) {
+            // record slot ch+1 <- the bf16 state copy, straight from shared memory (two 64-column boxes)
+            const int row0 = (sbh * (p.NC + 1) + ch + 1) * D;
+            tma_store_2d(&p.tmc, sCb, 0, row0);
+            tma_store_2d(&p.tmc, sCb + kStateBox, 64, row0);
+            tma_store_commit();
+        }
     }
+    if (p.savedC && tid == kMathThreads) tma_store_wait_all();
 
     if (ok) {
         if (p.on && tid < D && vh == 0) p.on[(size_t)bh * dqk + qh * D + tid] = nvec[tid];
@@ -523,6 +530,10 @@ int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved, void*
     p.ig = a.ig; p.fg = a.fg; p.cC = a.cC; p.cn = a.cn; p.cm = a.cm;
     p.ytil = (bf16*)a.ytil; p.msv = a.msv; p.psiv = a.psiv; p.qnv = a.qnv;
     if (saved) {
+        if (!tc_make_map2(&p.tmc, saved, (uint64_t)a.B * a.H * nsub * (a.NC + 1) * D, D, D)) {
+            set_error("mlstm_fw: cuTensorMapEncodeTiled failed for the state record");
+            return XLSTM_ERR_CUDA;
+        }
         p.savedC = (bf16*)saved;
         p.savedn = (float*)((char*)saved + mlstm_tc_saved_C_bytes(a.B * a.H * nsub, a.NC));
     }
