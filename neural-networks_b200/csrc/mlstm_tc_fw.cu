@@ -50,6 +50,7 @@ struct Gates {
 
 struct Params {
     CUtensorMap tmq, tmk, tmv;
+    CUtensorMap tmy;  // ytil [B][T][H*dhv] bf16, box {64, 64, 1}: the output tile is stored from shared memory
     CUtensorMap tmc;  // the bf16 C record as rows of 128: [sub-heads * (NC+1) * 128][128], box {64, 128} (when a record is kept)
     const float *ig, *fg;
     const float *cC, *cn, *cm;
@@ -82,7 +83,8 @@ struct Smem {
     static constexpr uint32_t qn = rpart + 4 * L * 4;         // q.n [64]
     static constexpr uint32_t ipsi = qn + L * 4;              // 1/psi [64]
     static constexpr uint32_t misc = ipsi + L * 4;
-    static constexpr uint32_t total = misc + 256;
+    static constexpr uint32_t yt = (misc + 256 + 1023) & ~1023u;  // output tile [64 x 128] bf16 (two swizzled boxes)
+    static constexpr uint32_t total = yt + kTileBytes;
 };
 
 __device__ __forceinline__ uint4 pack8(const float* v) {
@@ -176,6 +178,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
     unsigned char* sVa = sm + Smem::va;
     unsigned char* sCb = sm + Smem::cb;
     unsigned char* sP = sm + Smem::p;
+    unsigned char* sY = sm + Smem::yt;
 
     if (tid == 0) {
         for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
@@ -318,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
                 m_prev = gates_compute(graw, m_prev, &G[st ^ 1]);
                 if (ch + 2 < p.NC) gates_load(p, b, h, ch + 2, graw);
             }
-            if (p.savedC && lane == 0) tma_store_wait_read();  // the previous record store has read sCb: phase 3 may overwrite it
+            if (lane == 0) tma_store_wait_read();  // the previous chunk's stores have read sCb and the output tile: phase 3 may overwrite them
         } else if (full) {
             if (!mbar_wait(&bars[2], ch & 1)) *abort_flag = 2;
             tc_fence_after();
@@ -428,11 +431,14 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
                     for (int i = 0; i < 16; ++i)
                         if (i < nlive) no[(size_t)i * ystride] = hi[i] + Gc->b[16 * cq + i] * he[i];
                 } else {
-                    bf16* yo = p.ytil + yoff;
+                    // into the shared output tile (feature x of positions 16*cq..+15); TMA stores it after the barrier
+                    // and clips the rows past a ragged end
+                    unsigned char* ydst = sY + (uint32_t)(x >> 6) * kBoxBytes + (x & 7) * 2;
+                    const uint32_t xch8 = (x & 63) >> 3;
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const int pos = 16 * cq + i;
-                        if (i < nlive) yo[(size_t)i * ystride] = __float2bfloat16_rn((hi[i] + Gc->b[pos] * he[i]) * sipsi[pos]);
+                        *reinterpret_cast<bf16*>(ydst + swz(pos, xch8)) = __float2bfloat16_rn((hi[i] + Gc->b[pos] * he[i]) * sipsi[pos]);
                     }
                 }
             }
@@ -441,15 +447,21 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
         }
         __syncthreads();  // #3
         if (*abort_flag) { ok = false; break; }
-        if (p.savedC && tid == kMathThreads) {
-            // record slot ch+1 <- the bf16 state copy, straight from shared memory (two 64-column boxes)
-            const int row0 = (sbh * (p.NC + 1) + ch + 1) * D;
-            tma_store_2d(&p.tmc, sCb, 0, row0);
-            tma_store_2d(&p.tmc, sCb + kStateBox, 64, row0);
+        if (tid == kMathThreads && (p.savedC || (full && !unnorm))) {
+            if (p.savedC) {
+                // record slot ch+1 <- the bf16 state copy, straight from shared memory (two 64-column boxes)
+                const int row0 = (sbh * (p.NC + 1) + ch + 1) * D;
+                tma_store_2d(&p.tmc, sCb, 0, row0);
+                tma_store_2d(&p.tmc, sCb + kStateBox, 64, row0);
+            }
+            if (full && !unnorm) {
+                tma_store_3d(&p.tmy, sY, vcol, t0, b);
+                tma_store_3d(&p.tmy, sY + kBoxBytes, vcol + 64, t0, b);
+            }
             tma_store_commit();
         }
     }
-    if (p.savedC && tid == kMathThreads) tma_store_wait_all();
+    if (tid == kMathThreads) tma_store_wait_all();
 
     if (ok) {
         if (p.on && tid < D && vh == 0) p.on[(size_t)bh * dqk + qh * D + tid] = nvec[tid];
@@ -529,6 +541,10 @@ int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved, void*
     }
     p.ig = a.ig; p.fg = a.fg; p.cC = a.cC; p.cn = a.cn; p.cm = a.cm;
     p.ytil = (bf16*)a.ytil; p.msv = a.msv; p.psiv = a.psiv; p.qnv = a.qnv;
+    if (!a.states_only && p.nq == 1 && !tc_make_map3(&p.tmy, a.ytil, a.B, a.T, a.H * a.dhv)) {
+        set_error("mlstm_fw: cuTensorMapEncodeTiled failed for the output");
+        return XLSTM_ERR_CUDA;
+    }
     if (saved) {
         if (!tc_make_map2(&p.tmc, saved, (uint64_t)a.B * a.H * nsub * (a.NC + 1) * D, D, D)) {
             set_error("mlstm_fw: cuTensorMapEncodeTiled failed for the state record");
