@@ -280,7 +280,7 @@ def run_ours(args):
         # settings (profiles/mlstm_tc_cfg2.md); includes the 138 MB chunk-state record, which the algorithmic bytes
         # leave out. Other settings were not captured.
         default_cfg = args.grad_dtype == "f32" and not args.recompute and cfg["B"] == 16
-        traffic = {"bw": 545564928 + 366242560, "fw": 204251648 + 165690368} if default_cfg else {"bw": None, "fw": None}
+        traffic = {"bw": 545305088 + 368029952, "fw": 203553280 + 163480320} if default_cfg else {"bw": None, "fw": None}
         cpu = cpu_sample() if world == 1 and not args.no_cpu else None
         line = {
             "metric": "mlstm_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
