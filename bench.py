@@ -237,26 +237,48 @@ def run_ours(args):
     bw_t = float(np.median([m[1].elapsed_time(m[2]) for m in marks]))
 
     # ---- end to end from pinned host buffers ----------------------------------------------
+    # Every step copies its inputs from pinned host memory, runs forward + backward through `ops`, and copies every
+    # result back to pinned host memory; all of it is inside the timed region. The three stages run on three
+    # streams with double-buffered device inputs, so step i+1's upload and step i-1's download overlap step i
+    # (PCIe is full duplex): steady state is the slower of the two copy directions, not their sum.
+    s_in, s_out, s_cmp = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+    dbuf = [[torch.empty(t.shape, dtype=t.dtype, device="cuda") for t in host_in] for _ in range(2)]
     outs_host = None
+    free_ev = [None, None]  # compute finished reading device-input set j
 
-    def e2e_step():
+    def e2e_run(nsteps):
         nonlocal outs_host
-        d = [t.cuda(non_blocking=True) for t in host_in]
-        fused = ops.mlstm_fused_fw(d[0], d[1], d[2], d[3], d[4], st, save_states=not args.recompute, want_state=False)
-        g = ops.mlstm_fused_bw(fused, d[0], d[1], d[2], d[3], d[4], d[5], st, want_dstate=False)
-        res = [fused.ytil, g[0], g[1], g[2], g[3], g[4]]
-        if outs_host is None:
-            outs_host = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
-        for h, r in zip(outs_host, res):
-            h.copy_(r, non_blocking=True)
-        return res
+        last_out = None
+        for i in range(nsteps):
+            j = i & 1
+            with torch.cuda.stream(s_in):
+                if free_ev[j] is not None:
+                    s_in.wait_event(free_ev[j])
+                for dst, src in zip(dbuf[j], host_in):
+                    dst.copy_(src, non_blocking=True)
+                ev_in = torch.cuda.Event(); ev_in.record(s_in)
+            s_cmp.wait_event(ev_in)
+            d = dbuf[j]
+            fused = ops.mlstm_fused_fw(d[0], d[1], d[2], d[3], d[4], st, save_states=not args.recompute, want_state=False)
+            g = ops.mlstm_fused_bw(fused, d[0], d[1], d[2], d[3], d[4], d[5], st, want_dstate=False)
+            res = [fused.ytil, g[0], g[1], g[2], g[3], g[4]]
+            ev_c = torch.cuda.Event(); ev_c.record(s_cmp)
+            free_ev[j] = ev_c
+            if outs_host is None:
+                outs_host = [[torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res] for _ in range(2)]
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_c)
+                for h, r in zip(outs_host[j], res):
+                    r.record_stream(s_out)
+                    h.copy_(r, non_blocking=True)
+                last_out = torch.cuda.Event(); last_out.record(s_out)
+        s_cmp.wait_event(last_out)  # the timed region ends when the last result is on the host
 
-    e2e_steps = max(1, min(args.steps, 5))
-    e2e_step()
+    e2e_steps = max(2, min(args.steps, 6))
+    e2e_run(2)
     barrier()
     e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    e2e_run(e2e_steps)
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
@@ -266,7 +288,7 @@ def run_ours(args):
         e2e_ms = float(t.item())
     e2e_ms /= e2e_steps
     h2d = sum(t.numel() * t.element_size() for t in host_in)
-    d2h = sum(t.numel() * t.element_size() for t in outs_host)
+    d2h = sum(t.numel() * t.element_size() for t in outs_host[0])
 
     if rank == 0:
         ff, fb = flops_fwd_bwd(**cfg)
