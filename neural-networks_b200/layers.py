@@ -53,17 +53,15 @@ def _split3(a):
     return hi, mid, lo
 
 
-def _mm_split(a3, b3):
+def _mm_split(a3, b3, accum=None):
     """fp32-accurate product of two fp32 matrices given as bf16 triples: the six partial products whose
-    weight is above 2^-24 run on the bf16 tensor cores with fp32 accumulation, smallest terms first."""
+    weight is above 2^-24 run on the bf16 tensor cores with fp32 accumulation, smallest terms first, each
+    accumulated into the result inside its GEMM (beta = 1). `accum`: add the product into this tensor."""
     (ah, am, al), (bh, bm, bl) = a3, b3
-    mm = lambda x, y: torch.mm(x, y, out_dtype=torch.float32)
-    out = mm(al, bh)
-    out.add_(mm(ah, bl))
-    out.add_(mm(am, bm))
-    out.add_(mm(am, bh))
-    out.add_(mm(ah, bm))
-    out.add_(mm(ah, bh))
+    out = torch.mm(al, bh, out_dtype=torch.float32) if accum is None else \
+        torch.addmm(accum, al, bh, out_dtype=torch.float32, out=accum)
+    for x, y in ((ah, bl), (am, bm), (am, bh), (ah, bm), (ah, bh)):
+        torch.addmm(out, x, y, out_dtype=torch.float32, out=out)
     return out
 
 
@@ -438,7 +436,7 @@ class Lm:
             ops.softcap_cross_entropy(pre, targets[lo:hi], d_pre, self.loss, self.cap, inv=inv)
             if self.head_split:
                 d3 = _split3(d_pre)
-                self.table.g.add_(_mm_split(tuple(p.t() for p in d3), n3))
+                _mm_split(tuple(p.t() for p in d3), n3, accum=self.table.g)
                 d_n[lo:hi] = _mm_split(d3, w3)
             else:
                 self.table.g.addmm_(d_pre.t(), normed[lo:hi])
