@@ -255,12 +255,17 @@ class SLstm:
         self.b.g.add_(dg.sum(dim=0))
         hp = self.slabs.t["h_prev"].view(B * T, H)
         if nh == 1:
-            self.wh.g.add_(torch.mm(hp.t(), dg))
+            self.wh.g.add_(_mm(hp.t(), dgn, self.bf16))
         else:
+            # one batched product over the heads: [nh, dh, rows] x [nh, rows, 4*dh]; the gate deltas are regrouped
+            # head-major once (bf16 operands in bf16 mode, as the reference's h_prev^T dg, src/gpu/ops.rs:300-361)
             dh = H // nh
-            dg4 = dg.view(B * T, 4, nh, dh)
-            for hd in range(nh):
-                self.wh.g[hd].add_(torch.mm(hp[:, hd * dh:(hd + 1) * dh].t(), dg4[:, :, hd, :].reshape(B * T, 4 * dh)))
+            dgh = dgn.view(B * T, 4, nh, dh).permute(2, 0, 1, 3).reshape(nh, B * T, 4 * dh)
+            hph = (_b16(hp) if self.bf16 else hp).view(B * T, nh, dh).permute(1, 2, 0)
+            if self.bf16:
+                self.wh.g.add_(torch.bmm(hph, dgh, out_dtype=torch.float32))
+            else:
+                self.wh.g.baddbmm_(hph, dgh)
         return _mm(dgn, (self.wx.wb if self.bf16 else self.wx.w).t(), self.bf16)
 
     def params(self):
