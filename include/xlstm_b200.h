@@ -182,6 +182,11 @@ int xlstm_ogate_fw(void* stream, float* o, const float* yhat, void* hc, int out_
 /* do_pre = d_hc * yhat * o * (1 - o) with o the activated gate; d_yhat = d_hc * o (fp32) */
 int xlstm_ogate_bw(void* stream, const float* d_hc, const float* o, const float* yhat, void* do_pre,
                    int out_dtype, float* d_yhat, size_t n);
+/* x = hi + mid + lo as three bf16 arrays (hi = bf16(x), mid = bf16(x - hi), lo = bf16(x - hi - mid)): the
+ * operands of an fp32-accurate product run as six bf16 tensor-core GEMMs (the fp32 head of gpu::Lm,
+ * src/gpu/lm.rs:84-163, which the reference runs as a cublasSgemm). No reference counterpart. */
+int xlstm_split3_bf16(void* stream, const float* x, void* hi, void* mid, void* lo, size_t n);
+
 /* Embedding backward without float atomics (replaces embedding_scatter_add / embedding_scatter_merge,
  * src/gpu/cuda/common.cu:127-168): table_g[id] += sum of the rows d[pos] with ids[pos] == id, in ascending
  * position order. The caller passes the ids sorted stably (`sorted_ids`) and the positions in that order

@@ -60,6 +60,7 @@ SIGNATURES = {
     "xlstm_ogate_fw": (_i, [_vp] * 4 + [_i, _sz]),
     "xlstm_ogate_bw": (_i, [_vp] * 5 + [_i, _vp, _sz]),
     "xlstm_embedding_scatter_add": (_i, [_vp] * 5 + [_i, _i]),
+    "xlstm_split3_bf16": (_i, [_vp] * 5 + [_sz]),
     "xlstm_adamw_multi": (_i, [_vp, ctypes.POINTER(AdamwDesc), _i, _f, _f, _f, _f, _f, _f, _i]),
 }
 

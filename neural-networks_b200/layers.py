@@ -45,12 +45,8 @@ def _mm(a, b, bf16):
 
 
 def _split3(a):
-    """fp32 -> three bf16 terms whose sum carries the full 24-bit significand."""
-    hi = a.to(torch.bfloat16)
-    r = a - hi.float()
-    mid = r.to(torch.bfloat16)
-    lo = r.sub_(mid.float()).to(torch.bfloat16)
-    return hi, mid, lo
+    """fp32 -> three bf16 terms whose sum carries the full 24-bit significand (one kernel pass)."""
+    return ops.split3_bf16(a)
 
 
 def _mm_split(a3, b3, accum=None):

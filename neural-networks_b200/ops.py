@@ -208,6 +208,14 @@ def ogate_backward(d_hc, o, yhat, out_dtype=torch.float32):
     return do_pre, d_yhat
 
 
+def split3_bf16(x):
+    """fp32 tensor -> (hi, mid, lo) bf16 tensors with hi + mid + lo == x to 24 bits, in one pass."""
+    x = x.contiguous()
+    hi, mid, lo = (torch.empty(x.shape, dtype=torch.bfloat16, device=x.device) for _ in range(3))
+    check(lib.xlstm_split3_bf16(_stream(), _ptr(x), _ptr(hi), _ptr(mid), _ptr(lo), x.numel()), "split3_bf16")
+    return hi, mid, lo
+
+
 def embedding_scatter_add(table_g, ids, d):
     """embedding_scatter_add (src/gpu/cuda/common.cu:127-168): table_g[ids[p]] += d[p], summed in position
     order for each token (deterministic; the sort is a library call, the accumulation is the kernel)."""
