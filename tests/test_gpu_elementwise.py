@@ -111,6 +111,20 @@ def test_swiglu_and_output_gate_glue(n, out_dtype):
     assert np.abs(host(d_yhat) - d * sig).max() <= 1e-6 * max(1.0, np.abs(d * sig).max())
 
 
+@pytest.mark.parametrize("n", [8, 1003, 1 << 18])
+def test_split3_bf16_carries_the_full_significand(n):
+    """hi = bf16(x), mid = bf16(x - hi), lo = bf16(x - hi - mid): each term is a bf16 number and their sum is x to
+    within 2^-24 relative (three 8-bit significands)."""
+    from gpu_util import ops
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn((n,), device="cuda", generator=g) * torch.exp(3.0 * torch.randn((n,), device="cuda", generator=g))
+    hi, mid, lo = ops.split3_bf16(x)
+    assert torch.equal(hi, x.to(torch.bfloat16))
+    assert torch.equal(mid, (x - hi.float()).to(torch.bfloat16))
+    back = hi.double() + mid.double() + lo.double()
+    assert float(((back - x.double()).abs() / x.double().abs().clamp_min(1e-30)).max()) <= 2.0 ** -23
+
+
 def test_embedding_scatter_add_is_exact_and_repeatable():
     """Token-row sums in position order: equal to a sequential float32 accumulation, bit for bit, on ids with
     heavy repeats (src/gpu/cuda/common.cu:127-168 is deterministic too, by slicing)."""
