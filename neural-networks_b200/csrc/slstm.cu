@@ -271,7 +271,8 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
             const int it = tid + p * kThreads;
             hprev[p] = (it < NI) ? xin[(size_t)(cr * UPC + it % UPC) * BG + it / UPC] : 0.f;
         }
-        matvec<BG, 2>(Ws, xin, part, K, NOUTp, a.KS);
+        if (a.CPT == 4) matvec<BG, 4>(Ws, xin, part, K, NOUTp, a.KS);
+        else matvec<BG, 2>(Ws, xin, part, K, NOUTp, a.KS);
         if (NI <= kPF * kThreads) cluster_arrive();  // done reading the exchange buffer
         SPROF(2)
         __syncthreads();
@@ -358,36 +359,58 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
 // ---------------------------------------------------------------------------------------------
 // Backward
 // ---------------------------------------------------------------------------------------------
+// dh_{t-1}[u] = sum_k delta_t[k] Wh[u][k] over the head's 4*dhd gate deltas. A CTA keeps the COLUMNS of Wh that
+// belong to its own units' deltas (all dhd rows x its 4*UPC columns), so its mat-vec needs only the deltas it has
+// just computed and yields a partial dh for every unit of the head; it then hands each peer the slice of partials
+// that peer's units need (distributed shared memory), and a CTA's recurrent dh is the sum of the CS slices it
+// received, in rank order. Against broadcasting the deltas to every peer this moves a quarter of the data and
+// gives the mat-vec a wide output. The receive buffers alternate by step parity, so one cluster barrier per step
+// both publishes the step's partials and fences the reuse of the buffer read two steps earlier.
+struct SlstmBwSmem {
+    size_t ws, xin, part, recv, state, total;
+};
+
+static SlstmBwSmem bw_layout(int K, int NOUTp, int BG, int KS, int UPC, int CS) {
+    SlstmBwSmem l;
+    auto a16 = [](size_t x) { return (x + 15) / 16 * 16; };
+    l.ws = 0;
+    l.xin = l.ws + a16((size_t)K * NOUTp * 4);
+    l.part = l.xin + a16((size_t)K * BG * 4);
+    l.recv = l.part + a16((size_t)KS * BG * NOUTp * 4);
+    l.state = l.recv + a16((size_t)2 * CS * BG * UPC * 4);
+    l.total = l.state + a16((size_t)2 * BG * UPC * 4);
+    return l;
+}
+
 template <int BG>
-__global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmSmem lay) {
+__global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmBwSmem lay) {
     cg::cluster_group cluster = cg::this_cluster();
     const int CS = a.CS, UPC = a.UPC, dhd = a.dhd, H = a.H, T = a.T;
     const int cr = (int)cluster.block_rank();
     const int cid = blockIdx.x / CS;
     const int nbg = (a.B + BG - 1) / BG;
     const int hd = cid / nbg, b0 = (cid % nbg) * BG;
-    const int K = 4 * dhd, NOUT = UPC, NOUTp = (NOUT + 1) & ~1;
+    const int K = 4 * UPC, NOUT = dhd, NOUTp = (NOUT + 1) & ~1;
     const int tid = threadIdx.x;
 
     extern __shared__ __align__(16) unsigned char smem[];
-    float* Ws = (float*)(smem + lay.ws);        // [K = gate*dhd+u][NOUTp = own rows]
-    float* xin = (float*)(smem + lay.xin);      // [K][BG]: gate deltas of the head
-    float* part = (float*)(smem + lay.part);    // [KS][BG][NOUTp]: dh partials for own units
-    float* stage = (float*)(smem + lay.stage);  // [BG][4][UPC]
-    float* st = (float*)(smem + lay.state);     // dc, dn: [2][BG*UPC]
+    float* Ws = (float*)(smem + lay.ws);      // [K = gate*UPC + ul][NOUTp]: Wh[u][gate*dhd + own unit ul] for every unit u
+    float* xin = (float*)(smem + lay.xin);    // [K][BG]: this CTA's own gate deltas
+    float* part = (float*)(smem + lay.part);  // [KS][BG][NOUTp]: k-slices of the partial dh for the whole head
+    float* recv = (float*)(smem + lay.recv);  // [2 parities][CS senders][BG][UPC]: partial dh of the own units
+    float* st = (float*)(smem + lay.state);   // dc, dn: [2][BG*UPC]
     const int NI = BG * UPC;
 
-    // transposed slice: Ws[gate*dhd + u][rl] = wh[hd][cr*UPC + rl][gate*dhd + u]
     for (int i = tid; i < K * NOUTp; i += kThreads) {
-        int col = i / NOUTp, rl = i % NOUTp;
-        Ws[i] = rl < NOUT ? a.wh[((size_t)hd * dhd + cr * UPC + rl) * 4 * dhd + col] : 0.f;
+        const int k = i / NOUTp, u = i % NOUTp, gate = k / UPC, ul = k % UPC;
+        Ws[i] = u < NOUT ? a.wh[((size_t)hd * dhd + u) * 4 * dhd + gate * dhd + cr * UPC + ul] : 0.f;
     }
-    // dh carry goes into k-slice 0 of the partial buffer, the other slices start at zero
-    for (int i = tid; i < a.KS * BG * NOUTp; i += kThreads) {
-        int ks = i / (BG * NOUTp), b = (i / NOUTp) % BG, rl = i % NOUTp;
+    // the dh carry takes sender 0's place in the buffer the first processed step reads (parity T & 1)
+    for (int i = tid; i < 2 * CS * NI; i += kThreads) {
+        const int par = i / (CS * NI), sdr = (i / NI) % CS, it = i % NI, b = it / UPC, ul = it % UPC;
         float v = 0.f;
-        if (ks == 0 && rl < NOUT && a.carry && b0 + b < a.B) v = a.dh[(size_t)(b0 + b) * H + hd * dhd + cr * UPC + rl];
-        part[i] = v;
+        if (par == (T & 1) && sdr == 0 && a.carry && b0 + b < a.B) v = a.dh[(size_t)(b0 + b) * H + hd * dhd + cr * UPC + ul];
+        recv[i] = v;
     }
     for (int it = tid; it < NI; it += kThreads) {
         int b = it / UPC, ul = it % UPC;
@@ -396,8 +419,7 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmS
         st[it] = live ? a.dc[si] : 0.f;
         st[NI + it] = live ? a.dn[si] : 0.f;
     }
-    cluster.sync();
-    cluster_arrive();  // opens phase A for the first step: nobody is reading the exchange buffer yet
+    cluster.sync();  // every CTA's buffers exist before any remote write
 
     // operands of the first processed step
     float pre[kPF][10];
@@ -426,6 +448,7 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmS
     };
     prefetch(T - 1);
     for (int t = T - 1; t >= 0; --t) {
+        const float* rp = recv + (size_t)((t + 1) & 1) * CS * NI;  // what the peers sent during step t+1 (or the carry)
         auto cell = [&](int it, const float* op) {
             const int b = it / UPC, ul = it % UPC;
             float dz = 0.f, di = 0.f, df = 0.f, dob = 0.f;
@@ -433,7 +456,7 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmS
                 const int j = hd * dhd + cr * UPC + ul;
                 float* gt = a.g + ((size_t)(b0 + b) * T + t) * 4 * H + j;
                 float dhr = 0.f;
-                for (int ks = 0; ks < a.KS; ++ks) dhr += part[((size_t)ks * BG + b) * NOUTp + ul];
+                for (int sdr = 0; sdr < CS; ++sdr) dhr += rp[(size_t)sdr * NI + it];
                 const SlstmBwCell r = slstm_cell_bw(op[0] + dhr, op[1], op[2], op[3], op[4], op[5], op[6], op[7], op[8],
                                                     op[9], st[it], st[NI + it]);
                 dz = r.dz; di = r.di; df = r.df; dob = r.dob;
@@ -444,8 +467,10 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmS
                 __stcs(gt + (size_t)2 * H, df);
                 __stcs(gt + (size_t)3 * H, dob);
             }
-            float* sg = stage + (size_t)b * 4 * UPC + ul;
-            sg[0] = dz; sg[UPC] = di; sg[2 * UPC] = df; sg[3 * UPC] = dob;
+            xin[(size_t)(0 * UPC + ul) * BG + b] = dz;
+            xin[(size_t)(1 * UPC + ul) * BG + b] = di;
+            xin[(size_t)(2 * UPC + ul) * BG + b] = df;
+            xin[(size_t)(3 * UPC + ul) * BG + b] = dob;
         };
 #pragma unroll
         for (int p = 0; p < kPF; ++p) {
@@ -465,23 +490,29 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_cluster(SlstmArgs a, SlstmS
             cell(it, op);
         }
         __syncthreads();
-        cluster_wait();  // every CTA finished the previous mat-vec: the exchange buffer may be overwritten
-        broadcast<BG>(cluster, stage, xin, CS, UPC, 4, UPC, dhd, cr * UPC);
         prefetch(t - 1);
-        cluster_arrive();
-        cluster_wait();  // the gate deltas of the whole head are visible
-        if (a.CPT == 2) matvec<BG, 2>(Ws, xin, part, K, NOUTp, a.KS);
-        else matvec<BG, 1>(Ws, xin, part, K, NOUTp, a.KS);
-        cluster_arrive();  // done reading the exchange buffer
+        if (a.CPT == 4) matvec<BG, 4>(Ws, xin, part, K, NOUTp, a.KS);
+        else matvec<BG, 2>(Ws, xin, part, K, NOUTp, a.KS);
         __syncthreads();
+        // sum the k-slices and hand every peer the partials of its units
+        float* wbase = recv + (size_t)((t & 1) * CS + cr) * NI;
+        for (int e = tid; e < BG * NOUT; e += kThreads) {
+            const int b = e / NOUT, u = e % NOUT;
+            float v = 0.f;
+            for (int ks = 0; ks < a.KS; ++ks) v += part[((size_t)ks * BG + b) * NOUTp + u];
+            float* remote = cluster.map_shared_rank(wbase, u / UPC);
+            remote[b * UPC + u % UPC] = v;
+        }
+        cluster_arrive();
+        cluster_wait();  // this step's partials are visible everywhere; the other parity's buffer is free again
     }
-    cluster_wait();  // balances the last arrive
+    const float* rp = recv;  // written during step 0 (parity 0), or the untouched carry when T == 0
     for (int it = tid; it < NI; it += kThreads) {
         int b = it / UPC, ul = it % UPC;
         if (b0 + b >= a.B) continue;
         size_t si = (size_t)(b0 + b) * H + hd * dhd + cr * UPC + ul;
         float dhr = 0.f;
-        for (int ks = 0; ks < a.KS; ++ks) dhr += part[((size_t)ks * BG + b) * NOUTp + ul];
+        for (int sdr = 0; sdr < CS; ++sdr) dhr += rp[(size_t)sdr * NI + it];
         a.dh[si] = dhr;
         a.dc[si] = st[it];
         a.dn[si] = st[NI + it];
@@ -678,7 +709,8 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_grid(SlstmArgs a, GridSmem 
             }
             __syncthreads();
             if (LL && !s_flag) { ok = false; break; }
-            matvec<BG, 2>(Ws, xin, part, K, NOUT, a.KS);
+            if (a.CPT == 4) matvec<BG, 4>(Ws, xin, part, K, NOUT, a.KS);
+            else matvec<BG, 2>(Ws, xin, part, K, NOUT, a.KS);
             __syncthreads();
             for (int gi = tid; gi < B * UPC; gi += kThreads) {  // global item b*UPC + ul; this sub-group's only
                 const int it = gi - b0 * UPC;
@@ -879,7 +911,9 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_grid_ps(SlstmArgs a, GridSm
 // ---------------------------------------------------------------------------------------------
 struct Geo {
     int BG, CS, UPC, KS, CPT;
-    SlstmSmem lay;
+    SlstmSmem lay;      // forward
+    SlstmBwSmem blay;   // backward
+    size_t total;       // dynamic shared memory of the kernel this geometry is for
 };
 
 static const size_t kSmemCap = 220 * 1024;
@@ -887,19 +921,31 @@ static const size_t kSmemCap = 220 * 1024;
 static bool fits(int BG, int CS, int dhd, bool bwd, Geo* out) {
     if (dhd % CS) return false;
     int UPC = dhd / CS;
-    int K = bwd ? 4 * dhd : dhd, NOUT = bwd ? UPC : 4 * UPC;
+    // forward: K = dhd inputs (the head's h), 4*UPC outputs; backward: K = 4*UPC own deltas, dhd outputs
+    int K = bwd ? 4 * UPC : dhd, NOUT = bwd ? dhd : 4 * UPC;
     int NOUTp = (NOUT + 1) & ~1;
+    // wide outputs: four columns per thread (fewest shared-memory wavefronts per FMA) on as many k-slices as the
+    // partial buffer affords, even though that leaves threads idle in the mat-vec (6.09 vs 6.44 us per backward
+    // step at 4 x 256-unit heads); narrow outputs: column pairs
     int CPT = 2;
-    if (bwd && (NOUTp / 2) * 16 < kThreads) CPT = 1;  // narrow output: one column per thread keeps all threads busy
+    if (bwd && NOUTp % 4 == 0 && NOUTp >= 128) CPT = 4;
+    if (!bwd && NOUTp % 4 == 0 && NOUTp >= 128) CPT = 4;  // 4.77 vs 5.09 us per forward step at 4 x 256-unit heads
     int ncols = NOUTp / CPT;
     int KS = kThreads / ncols;
     if (KS < 1) KS = 1;
     if (KS > 16) KS = 16;
     if (KS > K) KS = K;
-    SlstmSmem l = smem_layout(K, NOUT, BG, KS, UPC, bwd ? 2 : 3);
-    if (l.total > kSmemCap) return false;
-    out->BG = BG; out->CS = CS; out->UPC = UPC; out->KS = KS; out->CPT = CPT; out->lay = l;
-    return true;
+    if (CPT == 4 && bwd && KS > 4) KS = 4;
+    if (CPT == 4 && !bwd && KS > 8) KS = 8;
+    out->BG = BG; out->CS = CS; out->UPC = UPC; out->KS = KS; out->CPT = CPT;
+    if (bwd) {
+        out->blay = bw_layout(K, NOUTp, BG, KS, UPC, CS);
+        out->total = out->blay.total;
+    } else {
+        out->lay = smem_layout(K, NOUT, BG, KS, UPC, 3);
+        out->total = out->lay.total;
+    }
+    return out->total <= kSmemCap;
 }
 
 // Cluster size for a fixed batch group: the widest (<= 8, the portable limit) that keeps >= 8 units
@@ -918,19 +964,19 @@ static bool geometry_for(int BG, int B, int NH, int dhd, bool bwd, Geo* out) {
 // answer is cached per (kernel, device, cluster size, shared-memory size).
 template <int BG>
 static int coresident(bool bwd, const Geo& g, int* out) {
-    auto kern = bwd ? slstm_bw_cluster<BG> : slstm_fw_cluster<BG>;
+    const void* kern = bwd ? (const void*)slstm_bw_cluster<BG> : (const void*)slstm_fw_cluster<BG>;
     static std::atomic<unsigned long long> key_of[2][64];
     static std::atomic<int> val_of[2][64];
     int dev = 0;
     XL_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) dev = 0;
-    const unsigned long long key = ((unsigned long long)g.lay.total << 8) | (unsigned)g.CS;
+    const unsigned long long key = ((unsigned long long)g.total << 8) | (unsigned)g.CS;
     if (key_of[bwd][dev].load() == key) { *out = val_of[bwd][dev].load(); return XLSTM_OK; }
-    XL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.lay.total));
+    XL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.total));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)g.CS);
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = g.lay.total;
+    cfg.dynamicSmemBytes = g.total;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)g.CS;
@@ -942,7 +988,7 @@ static int coresident(bool bwd, const Geo& g, int* out) {
     XL_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
     if (getenv("XLSTM_DEBUG"))
         fprintf(stderr, "[xlstm] slstm %s: BG=%d CS=%d UPC=%d KS=%d CPT=%d smem=%zu clusters co-resident=%d\n", bwd ? "bw" : "fw",
-                BG, g.CS, g.UPC, g.KS, g.CPT, g.lay.total, n);
+                BG, g.CS, g.UPC, g.KS, g.CPT, g.total, n);
     val_of[bwd][dev].store(n);
     key_of[bwd][dev].store(key);
     *out = n;
@@ -951,12 +997,11 @@ static int coresident(bool bwd, const Geo& g, int* out) {
 
 template <int BG>
 static int launch(cudaStream_t st, bool bwd, const SlstmArgs& a, const Geo& g) {
-    auto kern = bwd ? slstm_bw_cluster<BG> : slstm_fw_cluster<BG>;
     int nbg = (a.B + BG - 1) / BG;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(a.NH * nbg * g.CS));
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = g.lay.total;
+    cfg.dynamicSmemBytes = g.total;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -965,7 +1010,8 @@ static int launch(cudaStream_t st, bool bwd, const SlstmArgs& a, const Geo& g) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    XL_CUDA(cudaLaunchKernelEx(&cfg, kern, a, g.lay));
+    if (bwd) XL_CUDA(cudaLaunchKernelEx(&cfg, slstm_bw_cluster<BG>, a, g.blay));
+    else XL_CUDA(cudaLaunchKernelEx(&cfg, slstm_fw_cluster<BG>, a, g.lay));
     count_launch();
     return XLSTM_OK;
 }
@@ -999,8 +1045,7 @@ static bool grid_geometry(int B, int NH, int dhd, bool bwd, GridGeo* out) {
         if (dhd % G) continue;
         const int UPC = dhd / G;
         const int K = bwd ? 4 * dhd : dhd, NOUT = bwd ? UPC : 4 * UPC, NOUTp = (NOUT + 1) & ~1;
-        int CPT = 2;
-        if (bwd && (NOUTp / 2) * 16 < kThreads) CPT = 1;
+        const int CPT = 2;
         const int ncols = NOUTp / CPT;
         int KS = kThreads / ncols;
         if (KS < 1) KS = 1;
