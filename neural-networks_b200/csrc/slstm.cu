@@ -1,4 +1,5 @@
-// sLSTM recurrent loop, forward and backward, as persistent thread-block-cluster kernels.
+// sLSTM recurrent loop, forward and backward, as persistent kernels: thread-block clusters for heads whose
+// recurrent slice fits a cluster's shared memory, grid-cooperative kernels (further down) for wider heads.
 //
 // The T-loop is a chain of dependent small mat-vecs, so it is latency-bound: the design
 // keeps everything a step needs on chip. A cluster of CS CTAs owns one (head, batch group);
@@ -9,9 +10,9 @@
 // per timestep is the only inter-CTA synchronisation; there is no grid-wide barrier and no
 // spin-wait. Heads (block-diagonal recurrence) and batch groups are independent clusters.
 //
-// The backward runs the same structure on the transposed slice: a CTA owns the rows of Wh
-// belonging to its units, the gate deltas of the whole head are what is broadcast, and
-// dh_{t-1} for its own units is what the mat-vec produces.
+// The backward keeps the columns of Wh that belong to a CTA's own units' gate deltas instead: its
+// mat-vec then needs only the deltas the CTA has just computed, yields a partial dh for every unit
+// of the head, and the CTAs exchange those partials (see slstm_bw_cluster).
 //
 // Math: src/nn2/slstm.rs:286-325, 399-423 with the GPU kernels' gate clamps
 // (src/gpu/cuda/slstm_fused.cu:132-142). Kernels replaced: src/gpu/cuda/slstm_coop.cu:103-515.
@@ -49,7 +50,7 @@ struct SlstmArgs {
     int dhd;                   // units per head
     int CS, UPC;               // cluster size, units per CTA
     int KS;                    // k-slices of the mat-vec
-    int CPT;                   // output columns per thread in the backward mat-vec (2 or 1)
+    int CPT;                   // output columns per thread in the mat-vec (4 or 2)
     long long* prof;           // development aid (profiling builds only)
     unsigned epoch;            // launch number, part of the tags of the grid kernels' flagged exchange
 };
@@ -74,8 +75,7 @@ static SlstmSmem smem_layout(int K, int NOUT, int BG, int KS, int UPC, int nstat
 // out[b][j] partial sums over a k-slice: part[(ks*BG + b)*NOUTp + j] = sum_{k in slice} xin[k*BG+b] * Ws[k*NOUTp+j].
 // CPT = 2: a thread owns a column pair and uses the packed fp32x2 FMA (one instruction per batch element and
 // row instead of two); CPT = 4: four columns per thread (one 16-byte weight load per row: the fewest
-// shared-memory wavefronts per FMA, for wide outputs); CPT = 1: one column per thread, for narrow outputs
-// where pairs would leave threads idle.
+// shared-memory wavefronts per FMA, for wide outputs).
 template <int BG, int CPT>
 __device__ __forceinline__ void matvec(const float* __restrict__ Ws, const float* __restrict__ xin,
                                        float* __restrict__ part, int K, int NOUTp, int KS) {
@@ -141,29 +141,6 @@ __device__ __forceinline__ void matvec(const float* __restrict__ Ws, const float
 #pragma unroll
             for (int b = 0; b < BG; ++b)
                 *reinterpret_cast<float2*>(part + ((size_t)ks * BG + b) * NOUTp + 2 * cp) = acc[b];
-        } else {
-            float acc[BG];
-#pragma unroll
-            for (int b = 0; b < BG; ++b) acc[b] = 0.f;
-#pragma unroll 4
-            for (int r = r0; r < r1; ++r) {
-                const float w = *wp;
-                if (BG % 4 == 0) {
-#pragma unroll
-                    for (int b4 = 0; b4 < BG / 4; ++b4) {
-                        const float4 x = *reinterpret_cast<const float4*>(xp + 4 * b4);
-                        acc[4 * b4 + 0] += x.x * w; acc[4 * b4 + 1] += x.y * w;
-                        acc[4 * b4 + 2] += x.z * w; acc[4 * b4 + 3] += x.w * w;
-                    }
-                } else {
-#pragma unroll
-                    for (int b = 0; b < BG; ++b) acc[b] += xp[b] * w;
-                }
-                wp += NOUTp;
-                xp += BG;
-            }
-#pragma unroll
-            for (int b = 0; b < BG; ++b) part[((size_t)ks * BG + b) * NOUTp + cp] = acc[b];
         }
     }
 }
@@ -928,8 +905,7 @@ static bool fits(int BG, int CS, int dhd, bool bwd, Geo* out) {
     // partial buffer affords, even though that leaves threads idle in the mat-vec (6.09 vs 6.44 us per backward
     // step at 4 x 256-unit heads); narrow outputs: column pairs
     int CPT = 2;
-    if (bwd && NOUTp % 4 == 0 && NOUTp >= 128) CPT = 4;
-    if (!bwd && NOUTp % 4 == 0 && NOUTp >= 128) CPT = 4;  // 4.77 vs 5.09 us per forward step at 4 x 256-unit heads
+    if (NOUTp % 4 == 0 && NOUTp >= 128) CPT = 4;  // forward 4.77 vs 5.09, backward 6.09 vs 6.44 us per step at 4 x 256-unit heads
     int ncols = NOUTp / CPT;
     int KS = kThreads / ncols;
     if (KS < 1) KS = 1;
