@@ -41,3 +41,25 @@ def test_head_shards_tile_the_cell_and_sum_to_the_full_projection():
     hl = heads // world
     partial = sum(hc[:, k * hl * dhv:(k + 1) * hl * dhv] @ parts[k]["w_out"] for k in range(world))
     assert np.allclose(partial + cell["b_out"], hc @ cell["w_out"] + cell["b_out"], rtol=1e-12, atol=1e-12)
+
+
+def test_package_weight_generator_matches_the_oracles_layout():
+    """bench.py draws its LM weights with the package's own generator (the product path may not import the
+    oracle); the dictionary it returns must have the oracle generator's keys and shapes, block by block."""
+    import importlib
+    from oracle import model as M
+    layers = importlib.import_module("neural-networks_b200.layers")
+    args = (50, 32, 3, 2, 16, 16, 88)
+    a = layers.init_lm_params(np.random.default_rng(0), *args, slstm_at=(1,), nh_s=2)
+    b = M.init_lm_params(np.random.default_rng(0), *args, slstm_at=(1,), nh_s=2)
+    assert a["table"].shape == b["table"].shape and a["gamma"].shape == b["gamma"].shape
+    assert len(a["blocks"]) == len(b["blocks"])
+    for x, y in zip(a["blocks"], b["blocks"]):
+        assert set(x) == set(y)
+        assert x["cell"]["kind"] == y["cell"]["kind"] and set(x["cell"]) == set(y["cell"])
+        for k in x:
+            if k != "cell":
+                assert np.shape(x[k]) == np.shape(y[k]), k
+        for k in x["cell"]:
+            if k != "kind":
+                assert np.shape(x["cell"][k]) == np.shape(y["cell"][k]), k
