@@ -109,6 +109,11 @@ int xlstm_mlstm_bw(void* stream, const xlstm_mlstm_shape* s, const void* q, cons
  *   state c,n,m,h [B,H]: read when carry!=0 (else zero), always written.
  *   slabs: nine [B,T,H] records in this order:
  *       c_prev, n_prev, i', f', c, n, z, o, h_prev   (src/gpu/ops.rs:2206-2256).
+ * Heads of up to 256 units run on thread-block clusters. Wider heads (dense H up to 1024, block-diagonal
+ * heads up to 512 units) run as ONE cooperative launch spanning the GPU, whose CTAs wait on one another
+ * with bounded polls (a timeout shows in xlstm_device_status); that path uses barrier words, a 2 MiB
+ * exchange array and (backward) a grow-only exchange buffer held by the library per device, so keep
+ * those calls on one stream per device, as the reference keeps all its calls. Anything wider returns 1.
  */
 typedef struct {
     float *c_prev, *n_prev, *ipr, *fpr, *c, *n, *zt, *ot, *h_prev;
