@@ -515,7 +515,7 @@ def main():
     ap.add_argument("--workload", default="mlstm", choices=["mlstm", "lm", "ops"],
                     help="mlstm: configs[1] layer kernel (headline); lm: training step; ops: the other hot-path kernels alone")
     ap.add_argument("--lm-blocks", type=int, default=0, help="override the LM depth (development)")
-    ap.add_argument("--lm-remat", type=int, default=4, help="blocks rematerialised in the full-width LM workload")
+    ap.add_argument("--lm-remat", type=int, default=2, help="blocks rematerialised in the full-width LM workload")
     ap.add_argument("--lm-full", action="store_true", help="LM workload at the full widths of configs[3] (d=2048, heads of 256 / 512)")
     args = ap.parse_args()
     if args.impl == "reference":
