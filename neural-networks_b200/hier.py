@@ -1,0 +1,357 @@
+"""The reference's three-stage hierarchical model (gpu::Hierarchical, src/gpu/hierarchical.rs) on this
+engine's blocks: the caller of the cells' carry API.
+
+  encoder   every word as one row of a [words, tmax] rectangle (chars, then the [W] token), words being the
+            batch axis: tied table -> blocks; e_w = the row at the [W] step. One rectangle per length group.
+  backbone  Linear(hc->wh) -> blocks over a window's words as one sequence -> Linear(wh->hc). Swept in
+            spans of the word axis: a span passes through all blocks with every cell's state carried in from
+            the span before it, and the backward unwinds the spans right to left with the cells' BPTT state
+            carried the other way. The arithmetic is that of one long call; only memory residency changes.
+  decoder   word w+1 as one row: slot 0 = the backbone's output at word w, slot k = table[char k-1]; blocks
+            -> RMSNorm -> bias-free fp32 head -> SoftCap -> masked cross-entropy scaled by 1/(valid rows of
+            the whole call). Forward and backward per length group.
+The encoder's backward re-runs each group's forward first (src/gpu/hierarchical.rs:1347-1407), so only one
+group's activations are ever resident.
+
+Beyond the reference: a call takes several windows with equally many words; their words share the encoder
+and decoder rectangles and the backbone runs them as a batch (the reference's backbone is batch 1).
+"""
+import numpy as np
+import torch
+
+from . import layers, ops
+
+BACKBONE_CHUNK = 512    # src/config.rs:96
+GROUP_MAX_ROWS = 2048   # src/config.rs:115
+
+
+class HierCfg:
+    """ModelCfg (src/gpu/hierarchical.rs:53-65). `small_heads`: heads of the encoder's and decoder's mLSTM
+    blocks (16 in the reference). `*_kinds`: a string of "s"/"m" per stage overriding the reference's
+    patterns (encoder and decoder alternate sLSTM, mLSTM; the backbone has an sLSTM at every eighth block)."""
+
+    def __init__(self, vocab, hc, wh, enc_blocks, bb_blocks, dec_blocks, heads, dqk, w_token, cap=30.0, small_heads=16,
+                 enc_kinds=None, bb_kinds=None, dec_kinds=None):
+        self.vocab, self.hc, self.wh = vocab, hc, wh
+        self.enc_blocks, self.bb_blocks, self.dec_blocks = enc_blocks, bb_blocks, dec_blocks
+        self.heads, self.dqk, self.w_token, self.cap, self.small_heads = heads, dqk, w_token, cap, small_heads
+        self.enc_kinds = enc_kinds or "".join("s" if i % 2 == 0 else "m" for i in range(enc_blocks))
+        self.bb_kinds = bb_kinds or "".join("s" if i % 8 == 0 else "m" for i in range(bb_blocks))
+        self.dec_kinds = dec_kinds or "".join("s" if i % 2 == 0 else "m" for i in range(dec_blocks))
+
+    def stage(self, name):
+        """(kinds, width, heads, dqk, dhv) of a stage's blocks."""
+        if name == "bb":
+            return self.bb_kinds, self.wh, self.heads, self.dqk, self.wh // self.heads
+        sh = self.small_heads
+        return (self.enc_kinds if name == "enc" else self.dec_kinds), self.hc, sh, self.hc // sh, self.hc // sh
+
+
+def up_of(hidden):
+    """SwiGLU inner width of a block, from its own width (src/gpu/hierarchical.rs:70-72)."""
+    return hidden * 8 // 3
+
+
+def init_hier_params(rng, cfg, std=0.02):
+    """Seeded N(0, std) host weights (norm gains 1) in the dictionary `Hierarchical` takes."""
+    def n(*shape):
+        return rng.standard_normal(shape, dtype=np.float32) * np.float32(std)
+
+    def blocks(name):
+        kinds, d, heads, dqk, dhv = cfg.stage(name)
+        sl = tuple(i for i, k in enumerate(kinds) if k == "s")
+        return layers.init_lm_params(rng, 1, d, len(kinds), heads, dqk, dhv, up_of(d), std=std, slstm_at=sl)["blocks"]
+
+    return dict(table=n(cfg.vocab, cfg.hc), enc=blocks("enc"), front_w=n(cfg.hc, cfg.wh), front_b=n(cfg.wh),
+                bb=blocks("bb"), back_w=n(cfg.wh, cfg.hc), back_b=n(cfg.hc), dec=blocks("dec"),
+                dec_gamma=np.ones(cfg.hc, np.float32), head_w=n(cfg.hc, cfg.vocab))
+
+
+def group_by_len(lens, no_group=False, cap=GROUP_MAX_ROWS):
+    """Word indices bucketed by the next power of two of their length, buckets in ascending order, each cut
+    into pieces of at most `cap` rows (rows = words x (longest word + 1); cap 0 = no cut), the pieces after
+    the first appended behind all buckets (src/gpu/hierarchical.rs:117-200). The order fixes the order in
+    which losses are summed and gradients scattered."""
+    if no_group:
+        return [list(range(len(lens)))]
+    key = lambda l: 1 << (max(l, 1) - 1).bit_length()
+    slots = {k: i for i, k in enumerate(sorted({key(l) for l in lens}))}
+    out = [[] for _ in slots]
+    for w, l in enumerate(lens):
+        out[slots[key(l)]].append(w)
+    if cap:
+        for g in range(len(slots)):
+            tmax = max(max(lens[w] for w in out[g]), 1)
+            per = max(cap // (tmax + 1), 1)
+            if len(out[g]) > per:
+                tail, out[g] = out[g][per:], out[g][:per]
+                out += [tail[i:i + per] for i in range(0, len(tail), per)]
+    return out
+
+
+def chunk_spans(n, chunk):
+    """[(start, len)] covering n rows in near-equal pieces of at most `chunk`; one span when chunk >= n
+    (src/gpu/hierarchical.rs:245-261)."""
+    if chunk >= n:
+        return [(0, n)]
+    pieces = -(-n // chunk)
+    base, extra = divmod(n, pieces)
+    out, c0 = [], 0
+    for i in range(pieces):
+        ln = base + (1 if i < extra else 0)
+        out.append((c0, ln))
+        c0 += ln
+    return out
+
+
+def _build_blocks(plist, d, heads, dqk, dhv, bf16, chunk):
+    t = lambda a: torch.as_tensor(np.asarray(a), dtype=torch.float32)
+    out = []
+    for bp in plist:
+        c = {k: (t(v) if k != "kind" else v) for k, v in bp["cell"].items()}
+        bpt = {k: t(v) for k, v in bp.items() if k != "cell"}
+        if c["kind"] == "mlstm":
+            out.append(layers.Block(layers.MLstm(c, heads, dqk, dhv, bf16=bf16, chunk=chunk), bpt, bf16=bf16))
+        else:
+            out.append(layers.Block(layers.SLstm(c, d, 1, bf16=bf16), bpt, post_norm=True, bf16=bf16))
+    return out
+
+
+class Hierarchical:
+    """gpu::Hierarchical (src/gpu/hierarchical.rs:460-1746): forward_backward over windows, then step."""
+
+    def __init__(self, params, cfg, bf16=False, chunk=64, bb_chunk=None, group_cap=None, no_group=False):
+        t = lambda a: torch.as_tensor(np.asarray(a), dtype=torch.float32)
+        self.cfg, self.bf16 = cfg, bf16
+        self.table = layers.Param(t(params["table"]), False)
+        self.enc = _build_blocks(params["enc"], *cfg.stage("enc")[1:], bf16, chunk)
+        self.front = layers.Linear(t(params["front_w"]), t(params["front_b"]), True, bf16)
+        self.bb = _build_blocks(params["bb"], *cfg.stage("bb")[1:], bf16, chunk)
+        self.back = layers.Linear(t(params["back_w"]), t(params["back_b"]), True, bf16)
+        self.dec = _build_blocks(params["dec"], *cfg.stage("dec")[1:], bf16, chunk)
+        self.dec_norm = layers.RmsNorm(t(params["dec_gamma"]))
+        # fp32 whatever the blocks run in: the softmax exponentiates the head's output
+        # (src/gpu/hierarchical.rs:626-635); bias-free, as the checkpoint stores it (:1797-1801)
+        self.head = layers.Param(t(params["head_w"]), False)
+        self.bb_chunk = bb_chunk      # None: BACKBONE_CHUNK; >= the window's words: one span
+        self.group_cap = group_cap    # None: GROUP_MAX_ROWS; 0: no cap
+        self.no_group = no_group      # every word in one rectangle per stage (the A/B baseline)
+        self.loss = torch.zeros((1,), dtype=torch.float32, device="cuda")
+        self.step_count = 0
+        self.last_rows = 0
+        self.last_word_loss = 0.0
+
+    def params(self):
+        out = [self.table]
+        for blk in self.enc:
+            out += blk.params()
+        out += self.front.params()
+        for blk in self.bb:
+            out += blk.params()
+        out += self.back.params()
+        for blk in self.dec:
+            out += blk.params()
+        return out + self.dec_norm.params() + [self.head]
+
+    def step(self, cfg):
+        """One AdamW update of every tensor through the batched queue (src/gpu/hierarchical.rs:1696-1746)."""
+        q = ops.AdamwQueue()
+        for p in self.params():
+            q.push(p.w, p.g, p.m, p.v, p.decay, p.wb)
+        q.flush(cfg, zero_grad=True)
+        self.step_count += 1
+
+    # ---- host-side index plans ----------------------------------------------------------------------------
+    def _cap(self):
+        return GROUP_MAX_ROWS if self.group_cap is None else self.group_cap
+
+    def _spans(self, dw):
+        c = BACKBONE_CHUNK if self.bb_chunk is None else self.bb_chunk
+        return chunk_spans(dw, dw if c == 0 else max(1, min(c, dw)))
+
+    @staticmethod
+    def _dev(a, dtype):
+        return torch.from_numpy(np.ascontiguousarray(a)).to("cuda", dtype=dtype, non_blocking=False)
+
+    def _enc_plan(self, word, N):
+        """Per group: (word rows, tmax, ids [n_g * tmax], readout rows) (src/gpu/hierarchical.rs:436-458)."""
+        lens = [len(word(i, 0)) for i in range(N)]
+        plan = []
+        for grp in group_by_len(lens, self.no_group, self._cap()):
+            tmax = max(lens[w] for w in grp) + 1
+            ids = np.zeros((len(grp), tmax), np.int64)
+            readout = np.zeros(len(grp), np.int64)
+            for i, w in enumerate(grp):
+                ids[i, :lens[w]] = word(w, 0)
+                ids[i, lens[w]] = self.cfg.w_token
+                readout[i] = i * tmax + lens[w]
+            plan.append((self._dev(grp, torch.int64), len(grp), tmax, self._dev(ids.reshape(-1), torch.int64),
+                         self._dev(readout, torch.int64)))
+        return plan
+
+    def _dec_plan(self, word, N, on):
+        """Per group the id lists of src/gpu/hierarchical.rs:329-364: slot-0 rows, char rows and ids, targets, mask."""
+        lens = [len(word(i, 1)) for i in range(N)]
+        plan = []
+        for grp in group_by_len(lens, self.no_group, self._cap()):
+            tmax = max(lens[w] for w in grp) + 1
+            rows = len(grp) * tmax
+            targets, mask = np.zeros(rows, np.int32), np.zeros(rows, np.int32)
+            char_rows, char_ids = [], []
+            for i, w in enumerate(grp):
+                cs, m = word(w, 1), lens[w]
+                char_rows += range(i * tmax + 1, i * tmax + m + 1)
+                char_ids += list(cs)
+                targets[i * tmax:i * tmax + m] = cs
+                targets[i * tmax + m] = self.cfg.w_token
+                mask[i * tmax:i * tmax + m + 1] = on(w)
+            plan.append(dict(words=self._dev(grp, torch.int64), n=len(grp), tmax=tmax,
+                             o_rows=self._dev(np.arange(len(grp)) * tmax, torch.int64),
+                             char_rows=self._dev(np.array(char_rows, np.int64), torch.int64),
+                             char_ids=self._dev(np.array(char_ids, np.int64), torch.int64),
+                             targets=self._dev(targets, torch.int32), mask=self._dev(mask, torch.int32)))
+        valid = sum((lens[w] + 1) * on(w) for w in range(N))
+        return plan, valid, sum(on(w) for w in range(N))
+
+    # ---- stages ---------------------------------------------------------------------------------------------
+    def _enc_stack(self, n_g, tmax, ids):
+        h = self.table.w.index_select(0, ids)
+        for blk in self.enc:
+            h = blk.forward(h, n_g, tmax)
+        return h
+
+    def _backbone_forward(self, e_w, Bw, dw):
+        """Chunk-major sweep (src/gpu/hierarchical.rs:959-1021). Returns o [Bw*dw, hc] and what the backward needs."""
+        wh, hc = self.cfg.wh, self.cfg.hc
+        bb_in = self.front.forward(e_w).view(Bw, dw, wh)
+        spans = self._spans(dw)
+        sweep = len(spans) > 1
+        o = torch.empty((Bw, dw, hc), dtype=torch.float32, device=e_w.device)
+        chunks, states = [], [None] * len(self.bb)
+        for c0, ln in spans:
+            blocks = [layers.shell(b) for b in self.bb] if sweep else self.bb
+            back = layers.shell(self.back) if sweep else self.back
+            h = bb_in[:, c0:c0 + ln].reshape(Bw * ln, wh)
+            for i, blk in enumerate(blocks):
+                cell = blk.cell
+                cell.sweep = sweep
+                if isinstance(cell, layers.MLstm):
+                    cell.carry, cell.dcarry = states[i], None
+                else:
+                    cell.state, cell.dstate = states[i], None
+                h = blk.forward(h, Bw, ln)
+                states[i] = cell.carry if isinstance(cell, layers.MLstm) else cell.state
+            o[:, c0:c0 + ln] = back.forward(h).view(Bw, ln, hc)
+            chunks.append((blocks, back))
+        return o.view(Bw * dw, hc), (spans, chunks, sweep)
+
+    def _backbone_backward(self, d_o, saved, Bw, dw):
+        """Spans right to left, each through all blocks, BPTT state handed leftwards (src/gpu/hierarchical.rs:1236-1295)."""
+        wh, hc = self.cfg.wh, self.cfg.hc
+        spans, chunks, sweep = saved
+        d_o = d_o.view(Bw, dw, hc)
+        d_in = torch.empty((Bw, dw, wh), dtype=torch.float32, device=d_o.device)
+        dstates = [None] * len(self.bb)
+        for (c0, ln), (blocks, back) in zip(reversed(spans), reversed(chunks)):
+            d = back.backward(d_o[:, c0:c0 + ln].reshape(Bw * ln, hc))
+            for i in range(len(blocks) - 1, -1, -1):
+                cell = blocks[i].cell
+                if isinstance(cell, layers.MLstm):
+                    cell.dcarry = dstates[i]
+                else:
+                    cell.dstate = dstates[i]
+                d = blocks[i].backward(d)
+                dstates[i] = cell.dcarry if isinstance(cell, layers.MLstm) else cell.dstate
+                blocks[i].release()
+            d_in[:, c0:c0 + ln] = d.view(Bw, ln, wh)
+        for blk in self.bb:  # leave the cells as plain training cells
+            blk.cell.sweep = False
+            if isinstance(blk.cell, layers.MLstm):
+                blk.cell.carry = blk.cell.dcarry = None
+            else:
+                blk.cell.state = blk.cell.dstate = None
+        return self.front.backward(d_in.view(Bw * dw, wh))
+
+    def _decode_groups(self, plan, o, inv):
+        """Forward and backward per length group; the loss accumulates on the device
+        (src/gpu/hierarchical.rs:1029-1132). Returns d_o [words, hc]."""
+        hc = self.cfg.hc
+        d_o = torch.zeros_like(o)
+        for g in plan:
+            n_g, tmax = g["n"], g["tmax"]
+            rows = n_g * tmax
+            dec_in = torch.zeros((rows, hc), dtype=torch.float32, device=o.device)
+            dec_in.index_copy_(0, g["o_rows"], o.index_select(0, g["words"]))
+            if g["char_rows"].numel():
+                dec_in.index_copy_(0, g["char_rows"], self.table.w.index_select(0, g["char_ids"]))
+            h = dec_in
+            for blk in self.dec:
+                h = blk.forward(h, n_g, tmax)
+            hdn = self.dec_norm.forward(h)
+            pre = torch.mm(hdn, self.head.w)
+            d_pre = pre  # the fused soft-cap + loss kernel writes the gradient over its input
+            ops.softcap_cross_entropy(pre, g["targets"], d_pre, self.loss, self.cfg.cap, mask=g["mask"], inv=inv)
+            self.head.g.addmm_(hdn.t(), d_pre)
+            d = self.dec_norm.backward(torch.mm(d_pre, self.head.w.t()))
+            for blk in reversed(self.dec):
+                d = blk.backward(d)
+                blk.release()
+            self.dec_norm.release()
+            # the decoder input's gradient goes to its two sources: slot 0 -> the backbone, char slots -> the table
+            d_o.index_copy_(0, g["words"], d.index_select(0, g["o_rows"]))
+            if g["char_rows"].numel():
+                ops.embedding_scatter_add(self.table.g, g["char_ids"], d.index_select(0, g["char_rows"]))
+        return d_o
+
+    def _encoder_backward(self, plan, d_e_w):
+        """Per group: forward again, then backward from the [W]-step rows (src/gpu/hierarchical.rs:1347-1407)."""
+        hc = self.cfg.hc
+        for words, n_g, tmax, ids, readout in plan:
+            self._enc_stack(n_g, tmax, ids)
+            d = torch.zeros((n_g * tmax, hc), dtype=torch.float32, device=d_e_w.device)
+            d.index_copy_(0, readout, d_e_w.index_select(0, words))
+            for blk in reversed(self.enc):
+                d = blk.backward(d)
+                blk.release()
+            ops.embedding_scatter_add(self.table.g, ids, d)
+
+    def forward_backward(self, windows, word_loss=None):
+        """windows: [(tokens, [(start, end), ...]), ...] with equally many words each; word 0 of a window is
+        encode-only, words 1.. are decoded. word_loss (per window, one flag per decoded word; None = all on)
+        keeps a word's rows out of the loss while the word is still encoded and decoded, as in supervised
+        fine-tuning on the response only (src/gpu/hierarchical.rs:698-720). Accumulates every gradient and
+        returns the mean cross-entropy over the unmasked decoder rows, read from the device once."""
+        nw = len(windows[0][1])
+        if any(len(w) != nw for _, w in windows):
+            raise ValueError("the windows of one call must hold equally many words")
+        dw, Bw = nw - 1, len(windows)
+        if dw < 1:
+            self.last_rows, self.last_word_loss = 0, 0.0
+            return 0.0
+        N = Bw * dw  # row i: window i // dw, word i % dw
+
+        def word(i, shift):
+            tok, words = windows[i // dw]
+            s, e = words[i % dw + shift]
+            return tok[s:e]
+
+        on = (lambda i: 1) if word_loss is None else (lambda i: int(bool(word_loss[i // dw][i % dw])))
+        enc_plan = self._enc_plan(word, N)
+        dec_plan, valid, scored = self._dec_plan(word, N, on)
+        inv = 1.0 / max(valid, 1)
+
+        e_w = torch.zeros((N, self.cfg.hc), dtype=torch.float32, device="cuda")
+        for words, n_g, tmax, ids, readout in enc_plan:
+            h = self._enc_stack(n_g, tmax, ids)
+            e_w.index_copy_(0, words, h.index_select(0, readout))
+            for blk in self.enc:  # the backward re-runs this group, nothing of it is read again
+                blk.release()
+        o, saved = self._backbone_forward(e_w, Bw, dw)
+        self.loss.zero_()
+        d_o = self._decode_groups(dec_plan, o, inv)
+        d_e_w = self._backbone_backward(d_o, saved, Bw, dw)
+        self._encoder_backward(enc_plan, d_e_w)
+        loss = float(self.loss.item())
+        self.last_rows = valid
+        self.last_word_loss = loss * valid / max(scored, 1)  # the same total re-averaged over words (:1124-1128)
+        return loss

@@ -11,6 +11,7 @@ pass that updates the weight, so it can never go stale) and q/k/v are stored as 
 Element-wise glue between the ops (gate activations, residual adds, embedding gather/scatter,
 soft-cap) is expressed with torch tensor ops.
 """
+import copy
 import math
 
 import torch
@@ -153,6 +154,8 @@ class MLstm:
         self.inv_sqrt = 1.0 / math.sqrt(dqk)
         self.carry = None  # (C, n, m) when a call continues the previous one
         self.stateful = False  # inference: keep the state a call ends with as the next call's carry
+        self.sweep = False  # training over a sequence cut into calls: `carry` in and out forwards, `dcarry` backwards
+        self.dcarry = None  # (dC, dn) from the call to the right
         self.shard_group = None  # head-sharded inference: process group whose ranks split the heads
 
     def forward(self, x, B, T, residual=None):
@@ -173,9 +176,11 @@ class MLstm:
         self.o = self.lo.forward(x)  # activated in place by the output-gate kernel below
         ig, fg = self.li.forward(x), self.lf.forward(x)
         self.core_in = (q, k, v, ig, fg)
-        self.fused = ops.mlstm_fused_fw(q, k, v, ig, fg, self.st, carry_in=self.carry, want_state=self.stateful,
+        keep = self.stateful or self.sweep
+        self.carry_in = self.carry  # the backward needs the state this call entered with
+        self.fused = ops.mlstm_fused_fw(q, k, v, ig, fg, self.st, carry_in=self.carry, want_state=keep,
                                         save_states=not self.stateful)
-        if self.stateful:
+        if keep:
             self.carry = self.fused.state
         self.yhat = self.hn.forward(self.fused.ytil.float() if self.bf16 else self.fused.ytil)
         hc = ops.ogate_forward(self.o, self.yhat, torch.bfloat16 if self.bf16 else torch.float32)
@@ -194,8 +199,11 @@ class MLstm:
         do_pre, d_yhat = ops.ogate_backward(d_hc, self.o, self.yhat, torch.bfloat16 if self.bf16 else torch.float32)
         d_ytil = self.hn.backward(d_yhat)
         q, k, v, ig, fg = self.core_in
-        dq, dk, dv, dig, dfg, _ = ops.mlstm_fused_bw(self.fused, q, k, v, ig, fg, d_ytil, self.st, carry_in=self.carry,
-                                                     want_dstate=False)
+        dq, dk, dv, dig, dfg, dstate = ops.mlstm_fused_bw(self.fused, q, k, v, ig, fg, d_ytil, self.st, carry_in=self.carry_in,
+                                                          dstate_in=self.dcarry if self.sweep else None,
+                                                          want_dstate=self.sweep)
+        if self.sweep:
+            self.dcarry = dstate
         dx = self.lq.backward(dq)
         self.lk.backward(dk.mul_(self.inv_sqrt), accum=dx)
         self.lv.backward(dv, accum=dx)
@@ -227,24 +235,32 @@ class SLstm:
         self.b = Param(p["bcat"], False)
         self.stateful = False  # inference: (c, n, m, h) persists from call to call
         self.state = None
+        self.sweep = False  # training over a sequence cut into calls: `state` forwards, `dstate` (dh, dc, dn) backwards
+        self.dstate = None
 
     def forward(self, x, B, T):
         H = self.H
         self.B, self.T, self.x = B, T, (_b16(x) if self.bf16 else x)
         self.g = _mm(self.x, self.wx.wb if self.bf16 else self.wx.w, self.bf16).view(B, T, 4 * H)
         self.slabs = ops.SlstmSlabs(B, T, H, x.device)
-        carry = self.stateful and self.state is not None
-        state = self.state if carry else tuple(torch.empty((B, H), dtype=torch.float32, device=x.device) for _ in range(4))
+        carry = (self.stateful or self.sweep) and self.state is not None
+        # a sweep's calls each keep their own copy: the loop updates the state in place
+        state = (tuple(t.clone() for t in self.state) if self.sweep else self.state) if carry else \
+            tuple(torch.empty((B, H), dtype=torch.float32, device=x.device) for _ in range(4))
         out = torch.empty((B, T, H), dtype=torch.float32, device=x.device)
         ops.slstm_fused_time(self.wh.w, self.g, self.b.w, state, out, self.slabs, nh=self.nh, carry=carry)
-        if self.stateful:
+        if self.stateful or self.sweep:
             self.state = state  # updated in place to the state after the last position
         return out.view(B * T, H)
 
     def backward(self, dy):
         B, T, H, nh = self.B, self.T, self.H, self.nh
-        ds = tuple(torch.empty((B, H), dtype=torch.float32, device=dy.device) for _ in range(3))
-        ops.slstm_fused_time_bwd(self.wh.w, dy.view(B, T, H).contiguous(), self.g, ds, self.slabs, nh=nh, carry=False)
+        bptt = self.sweep and self.dstate is not None
+        ds = tuple(t.clone() for t in self.dstate) if bptt else \
+            tuple(torch.empty((B, H), dtype=torch.float32, device=dy.device) for _ in range(3))
+        ops.slstm_fused_time_bwd(self.wh.w, dy.view(B, T, H).contiguous(), self.g, ds, self.slabs, nh=nh, carry=bptt)
+        if self.sweep:
+            self.dstate = ds  # now the gradient of the state this call entered with
         dg = self.g.view(B * T, 4 * H)  # the loop left the four gate deltas here
         dgn = _b16(dg) if self.bf16 else dg
         self.wx.g.add_(_mm(self.x.t(), dgn, self.bf16))
@@ -322,6 +338,18 @@ class Block:
             l.release()
         if self.post is not None:
             self.post.release()
+
+
+def shell(obj):
+    """A copy of a layer (or block) that shares every parameter with the original and owns its saved
+    activations: the same weights can then hold several calls' forward records at once, which a sweep over a
+    sequence cut into calls needs (all calls forward, then all calls backward, right to left). Gradients
+    accumulate into the shared parameters."""
+    new = copy.copy(obj)
+    for k, v in vars(obj).items():
+        if isinstance(v, (Linear, RmsNorm, MLstm, SLstm, Block)):
+            setattr(new, k, shell(v))
+    return new
 
 
 class Lm:

@@ -1,0 +1,150 @@
+"""The hierarchical window on the GPU against the CPU oracle, and the invariances the reference pins for it
+(src/gpu/hierarchical.rs:2051-2531): grouping by word length, the group row cap and the chunked backbone
+sweep are batching choices that must not change loss or gradients; repeated runs are bit-identical.
+fp32 bar against the oracle: 1e-4 rel-to-max for the loss and every gradient tensor. Batching variants are
+compared with each other at 2e-4 (two fp32 runs, each within the bar of the exact result). Tensors
+whose every element is below 1e-2 of the model's largest gradient element are measured against that floor.
+bf16 on the tensor-core path, chunked sweep against one long call: whole-gradient cosine >= 0.999 and every
+tensor within 2e-1 (the worst is the forget-gate projection, whose gradient is a cumulative difference of two
+nearly equal sums and moves by 0.13-0.16 with the placement of the chunk borders; every other tensor stays
+within 3e-2); the 2e-2 bar is held at the op level (tests/test_gpu_mlstm.py)."""
+import importlib
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import hier as OH
+
+pytestmark = pytest.mark.gpu
+
+
+def _mods():
+    return importlib.import_module("neural-networks_b200"), importlib.import_module("neural-networks_b200.hier")
+
+
+def _window(seed, lens, vocab):
+    r = np.random.default_rng(seed)
+    toks = r.integers(0, vocab - 1, sum(lens)).tolist()  # vocab-1 is the [W] token
+    words, s = [], 0
+    for l in lens:
+        words.append((s, s + l))
+        s += l
+    return toks, words
+
+
+def _cfg(H, **kw):
+    base = dict(vocab=12, hc=16, wh=24, enc_blocks=2, bb_blocks=3, dec_blocks=2, heads=2, dqk=8, w_token=11, small_heads=2)
+    base.update(kw)
+    return H.HierCfg(**base)
+
+
+def _grads(model, windows, word_loss=None):
+    loss = model.forward_backward(windows, word_loss)
+    g = [p.g.clone() for p in model.params()]
+    for p in model.params():
+        p.g.zero_()
+    return loss, g
+
+
+def _close(ga, gb, tol, floor_frac=1e-2, cos_min=None):
+    """Every tensor within tol of the reference, relative to the tensor's largest element, or to floor_frac of the
+    model's largest gradient element for a tensor that is smaller all over: a gate-bias gradient that is a
+    cancelling sum over thousands of rows carries the absolute error of its terms, not of its result."""
+    nb = [b.double().cpu().numpy() if torch.is_tensor(b) else b for b in gb]
+    na = [a.double().cpu().numpy() for a in ga]
+    floor = floor_frac * max(np.abs(b).max() for b in nb)
+    bad = []
+    for i, (a, b) in enumerate(zip(na, nb)):
+        e = np.abs(a - b).max() / max(np.abs(b).max(), floor)
+        if e > tol:
+            bad.append("gradient %d %s: rel-to-max %.3e (max |ref| %.3e)" % (i, b.shape, e, np.abs(b).max()))
+    assert not bad, "\n".join(bad)
+    if cos_min is not None:
+        dot = sum(float((a * b).sum()) for a, b in zip(na, nb))
+        cos = dot / np.sqrt(sum(float((a * a).sum()) for a in na) * sum(float((b * b).sum()) for b in nb))
+        assert cos >= cos_min, cos
+
+
+LENS_A = [2, 3, 1, 4, 7, 2, 5, 1, 3, 9, 2, 4, 6]
+LENS_B = [1, 2, 5, 2, 3, 3, 8, 1, 1, 4, 2, 6, 2]
+
+
+@pytest.mark.parametrize("masked", [False, True])
+def test_window_matches_oracle(masked):
+    xl, H = _mods()
+    cfg = _cfg(H)
+    p = OH.init_hier_params(np.random.default_rng(0), _cfg(OH), std=0.2)
+    wins = [_window(1, LENS_A, cfg.vocab), _window(2, LENS_B, cfg.vocab)]
+    wl = None
+    if masked:
+        r = np.random.default_rng(9)
+        wl = [list(r.integers(0, 2, len(LENS_A) - 1).astype(bool)) for _ in wins]
+    ref = OH.Hierarchical(p, _cfg(OH))
+    loss_ref = ref.forward_backward(wins, wl)
+    # every batching lever on: several length groups, a row cap that splits them, a backbone sweep of 5-word spans
+    m = H.Hierarchical(p, cfg, bb_chunk=5, group_cap=24)
+    loss, g = _grads(m, wins, wl)
+    assert xl._lib.lib.xlstm_device_status() == 0
+    assert m.last_rows == ref.last_rows
+    assert abs(loss - loss_ref) <= 1e-4 * max(1.0, abs(loss_ref)), (loss, loss_ref)
+    _close(g, [q.g for q in ref.params()], 1e-4)
+
+
+def test_grouping_cap_and_chunking_do_not_change_the_result():
+    xl, H = _mods()
+    cfg = _cfg(H)
+    p = H.init_hier_params(np.random.default_rng(3), cfg, std=0.2)
+    wins = [_window(4, LENS_A, cfg.vocab)]
+    base = H.Hierarchical(p, cfg, bb_chunk=0, no_group=True)  # one rectangle per stage, one backbone call
+    l0, g0 = _grads(base, wins)
+    for kw in (dict(bb_chunk=0, group_cap=0), dict(bb_chunk=0, group_cap=16), dict(bb_chunk=4, no_group=True),
+               dict(bb_chunk=1, group_cap=16)):
+        l1, g1 = _grads(H.Hierarchical(p, cfg, **kw), wins)
+        assert abs(l1 - l0) <= 2e-5 * max(1.0, abs(l0)), (kw, l1, l0)
+        _close(g1, g0, 2e-4)  # two fp32 runs, each within 1e-4 of the exact result
+    assert xl._lib.lib.xlstm_device_status() == 0
+
+
+def test_repeated_windows_are_bit_identical():
+    xl, H = _mods()
+    cfg = _cfg(H)
+    p = H.init_hier_params(np.random.default_rng(5), cfg, std=0.2)
+    wins = [_window(6, LENS_A, cfg.vocab), _window(7, LENS_B, cfg.vocab)]
+    m = H.Hierarchical(p, cfg, bb_chunk=4, group_cap=24)
+    l0, g0 = _grads(m, wins)
+    l1, g1 = _grads(m, wins)
+    assert l0 == l1
+    assert all(torch.equal(a, b) for a, b in zip(g0, g1))
+
+
+def test_bf16_sweep_across_tensor_core_calls_matches_one_long_call():
+    """Backbone spans of 96 words against the mLSTM's chunk of 64: every call runs more than one internal chunk
+    and the state crossing a call border is a scanned one (the reference's
+    backbone_chunked_matches_unchunked_multi_mlstm_chunk, src/gpu/hierarchical.rs:2250-2260)."""
+    xl, H = _mods()
+    cfg = _cfg(H, hc=32, wh=256, bb_blocks=2, bb_kinds="mm", heads=2, dqk=128, enc_blocks=1, dec_blocks=1)
+    p = H.init_hier_params(np.random.default_rng(8), cfg, std=0.2)
+    r = np.random.default_rng(10)
+    lens = r.integers(1, 6, 289).tolist()
+    wins = [_window(11, lens, cfg.vocab), _window(12, lens[::-1], cfg.vocab)]
+    l0, g0 = _grads(H.Hierarchical(p, cfg, bf16=True, bb_chunk=0), wins)
+    l1, g1 = _grads(H.Hierarchical(p, cfg, bf16=True, bb_chunk=96), wins)
+    assert xl._lib.lib.xlstm_device_status() == 0
+    assert abs(l1 - l0) <= 5e-3 * max(1.0, abs(l0)), (l1, l0)
+    _close(g1, g0, 2e-1, cos_min=0.999)
+
+
+def test_training_memorises_a_window():
+    xl, H = _mods()
+    cfg = _cfg(H)
+    p = H.init_hier_params(np.random.default_rng(13), cfg, std=0.1)
+    wins = [_window(14, LENS_A, cfg.vocab)]
+    m = H.Hierarchical(p, cfg, bb_chunk=4)
+    first = None
+    for t in range(1, 61):
+        loss = m.forward_backward(wins)
+        first = loss if first is None else first
+        m.step(xl.ops.AdamCfg(1e-2, 0.0, t=t))
+    assert loss < 0.5 * first, (first, loss)
+    assert m.step_count == 60
