@@ -379,6 +379,48 @@ def _slstm_pack(l, d, nh):
     return dict(kind="slstm", wx=wx, wh=wh, bcat=bcat)
 
 
+def _block_to_layer(bp, d, heads, dqk):
+    """One block of the parameter dictionary as the file's block layer (tag 14 mLSTM, tag 11 sLSTM)."""
+    c = bp["cell"]
+    up = np.asarray(bp["w_gate"]).shape[1]
+    l = dict(input=d, output=d, up_size=up, pre_norm1=bp["g1"], pre_norm2=bp["g2"])
+    for k in ("w_gate", "b_gate", "w_value", "b_value", "w_down", "b_down"):
+        l[k] = bp[k]
+    if c["kind"] == "mlstm":
+        if np.asarray(c["wv"]).shape[1] != d or np.asarray(c["wq"]).shape[1] != heads * dqk:
+            raise FormatError("the format needs heads * dhv == hidden and wq [hidden, heads * dqk]")
+        l["tag"] = TAG_MLSTM_BLOCK
+        l["cell.num_heads"], l["cell.dqk"], l["cell.head_norm"] = heads, dqk, c["gamma"]
+        for k in ("wq", "wk", "wv", "wo", "wi", "wf", "bq", "bk", "bv", "bo", "bi", "bf", "w_out", "b_out"):
+            l["cell." + k] = c[k]
+    else:
+        l["tag"] = TAG_SLSTM_BLOCK
+        l["post_cell_norm"] = bp["gpost"]
+        for k, v in _slstm_gates(c, d).items():
+            l["cell." + k] = v
+    return l
+
+
+def _layer_to_block(l, d, nh_s=1):
+    """Inverse of `_block_to_layer`. Returns (block dictionary, (heads, dqk) or None for an sLSTM block)."""
+    bp = dict(g1=l["pre_norm1"], g2=l["pre_norm2"])
+    for k in ("w_gate", "b_gate", "w_value", "b_value", "w_down", "b_down"):
+        bp[k] = l[k]
+    if l["tag"] == TAG_MLSTM_BLOCK:
+        shape = (int(l["cell.num_heads"]), int(l["cell.dqk"]))
+        cell = dict(kind="mlstm", gamma=l["cell.head_norm"])
+        for k in ("wq", "wk", "wv", "wo", "wi", "wf", "bq", "bk", "bv", "bo", "bi", "bf", "w_out", "b_out"):
+            cell[k] = l["cell." + k]
+    elif l["tag"] == TAG_SLSTM_BLOCK:
+        shape = None
+        cell = _slstm_pack(l, d, nh_s)
+        bp["gpost"] = l["post_cell_norm"]
+    else:
+        raise FormatError(f"layer tag {l['tag']} is not a block")
+    bp["cell"] = cell
+    return bp, shape
+
+
 def lm_to_container(params, heads, dqk, cap=30.0, head_w=None, head_b=None):
     """A flat container with the one section "model" (as `Sequential::save`, src/sequential.rs:90-94):
     Embedding, one block layer per block, RMSNorm, the head, SoftCap. A tied head (head_w None) is written as
@@ -387,25 +429,7 @@ def lm_to_container(params, heads, dqk, cap=30.0, head_w=None, head_b=None):
     table = np.asarray(params["table"], _F32)
     vocab, d = table.shape
     layers = [dict(tag=TAG_EMBEDDING, input=vocab, output=d, weights=table)]
-    for bp in params["blocks"]:
-        c = bp["cell"]
-        up = np.asarray(bp["w_gate"]).shape[1]
-        l = dict(input=d, output=d, up_size=up, pre_norm1=bp["g1"], pre_norm2=bp["g2"])
-        for k in ("w_gate", "b_gate", "w_value", "b_value", "w_down", "b_down"):
-            l[k] = bp[k]
-        if c["kind"] == "mlstm":
-            if np.asarray(c["wv"]).shape[1] != d or np.asarray(c["wq"]).shape[1] != heads * dqk:
-                raise FormatError("the format needs heads * dhv == hidden and wq [hidden, heads * dqk]")
-            l["tag"] = TAG_MLSTM_BLOCK
-            l["cell.num_heads"], l["cell.dqk"], l["cell.head_norm"] = heads, dqk, c["gamma"]
-            for k in ("wq", "wk", "wv", "wo", "wi", "wf", "bq", "bk", "bv", "bo", "bi", "bf", "w_out", "b_out"):
-                l["cell." + k] = c[k]
-        else:
-            l["tag"] = TAG_SLSTM_BLOCK
-            l["post_cell_norm"] = bp["gpost"]
-            for k, v in _slstm_gates(c, d).items():
-                l["cell." + k] = v
-        layers.append(l)
+    layers += [_block_to_layer(bp, d, heads, dqk) for bp in params["blocks"]]
     layers.append(dict(tag=TAG_NORM, input=d, output=d, gamma=params["gamma"]))
     if head_w is None:
         layers.append(dict(tag=TAG_LINEAR_NB, input=d, output=vocab, weights=np.ascontiguousarray(table.T)))
@@ -433,22 +457,12 @@ def lm_from_container(c, nh_s=1, section="model"):
         if tag in (TAG_MLSTM_BLOCK, TAG_SLSTM_BLOCK):
             if gamma is not None:
                 raise FormatError("a block after the final norm")
-            bp = dict(g1=l["pre_norm1"], g2=l["pre_norm2"])
-            for k in ("w_gate", "b_gate", "w_value", "b_value", "w_down", "b_down"):
-                bp[k] = l[k]
+            bp, shape = _layer_to_block(l, d, nh_s)
             info["up"] = int(l["up_size"])
-            if tag == TAG_MLSTM_BLOCK:
-                h, dqk = int(l["cell.num_heads"]), int(l["cell.dqk"])
-                if info["heads"] not in (None, h) or info["dqk"] not in (None, dqk):
+            if shape is not None:
+                if info["heads"] not in (None, shape[0]) or info["dqk"] not in (None, shape[1]):
                     raise FormatError("mLSTM blocks disagree on heads or dqk")
-                info.update(heads=h, dqk=dqk, dhv=d // h)
-                cell = dict(kind="mlstm", gamma=l["cell.head_norm"])
-                for k in ("wq", "wk", "wv", "wo", "wi", "wf", "bq", "bk", "bv", "bo", "bi", "bf", "w_out", "b_out"):
-                    cell[k] = l["cell." + k]
-            else:
-                cell = _slstm_pack(l, d, nh_s)
-                bp["gpost"] = l["post_cell_norm"]
-            bp["cell"] = cell
+                info.update(heads=shape[0], dqk=shape[1], dhv=d // shape[0])
             blocks.append(bp)
         elif tag == TAG_NORM:
             gamma = l["gamma"]
@@ -504,3 +518,121 @@ def load_lm(path, nh_s=1, **build_kw):
     params, info = lm_from_container(load(path), nh_s)
     return layers.build_lm(params, info["heads"] or 1, info["dqk"] or 1, info["dhv"] or 1, nh_s=nh_s, cap=info["cap"],
                            tied=info["tied"], head_w=info["head_w"], head_b=info["head_b"], **build_kw)
+
+
+# ---- the hierarchical model's parameter dictionary <-> a hierarchical container ------------------------------
+# Sections and their layers as the reference's GPU model exports them (src/gpu/hierarchical.rs:1750-1806):
+#   "encoder"      Embedding(tied table), encoder blocks
+#   "word_model"   Linear(hc -> wh), backbone blocks, Linear(wh -> hc)
+#   "char2_model"  decoder blocks, RMSNorm, bias-free head, SoftCap
+# The typed head carries vocab, context_size = hc (the backbone's output width, :1815-1817), the step count and
+# the data counters.
+
+def hier_to_container(params, cfg, step=0, seen=None):
+    """`cfg`: anything with vocab, hc, wh, heads, dqk, small_heads, cap (hier.HierCfg)."""
+    hc, wh, sh = cfg.hc, cfg.wh, cfg.small_heads
+    table = np.asarray(params["table"], _F32)
+    lin = lambda w, b: dict(tag=TAG_LINEAR, input=np.asarray(w).shape[0], output=np.asarray(w).shape[1],
+                            in_dim=np.asarray(w).shape[0], out_dim=np.asarray(w).shape[1], weights=w, biases=b)
+    enc = [dict(tag=TAG_EMBEDDING, input=cfg.vocab, output=hc, weights=table)]
+    enc += [_block_to_layer(bp, hc, sh, hc // sh) for bp in params["enc"]]
+    wm = [lin(params["front_w"], params["front_b"])]
+    wm += [_block_to_layer(bp, wh, cfg.heads, cfg.dqk) for bp in params["bb"]]
+    wm.append(lin(params["back_w"], params["back_b"]))
+    dec = [_block_to_layer(bp, hc, sh, hc // sh) for bp in params["dec"]]
+    dec.append(dict(tag=TAG_NORM, input=hc, output=hc, gamma=params["dec_gamma"]))
+    dec.append(dict(tag=TAG_LINEAR_NB, input=hc, output=cfg.vocab, weights=params["head_w"]))
+    dec.append(dict(tag=TAG_SOFT_CAP, input=cfg.vocab, output=cfg.vocab, cap=float(cfg.cap)))
+    meta = new_meta(cfg.vocab, hc, step, **(seen or {}))
+    return Container(KIND_HIERARCHICAL, meta).section("encoder", enc).section("word_model", wm).section("char2_model", dec)
+
+
+def hier_from_container(c):
+    """Inverse of `hier_to_container`, with the checks of the reference's loader (src/gpu/hierarchical.rs:1838-1935):
+    the encoder starts with an Embedding, the backbone starts and ends with a Linear, the decoder holds blocks, then
+    an RMSNorm, a bias-free projection and a SoftCap. Returns (params, info) with info = vocab, hc, wh, block
+    kinds per stage, heads, dqk, small_heads, cap, step, seen."""
+    if c.kind != KIND_HIERARCHICAL:
+        raise FormatError("not a hierarchical container")
+    sec = dict(c.sections)
+    for name in ("encoder", "word_model", "char2_model"):
+        if name not in sec:
+            raise FormatError(f"missing section {name!r}")
+    enc, wm, dec = sec["encoder"], sec["word_model"], sec["char2_model"]
+    if not enc or enc[0]["tag"] != TAG_EMBEDDING:
+        raise FormatError("encoder must start with an Embedding")
+    table = enc[0]["weights"]
+    vocab, hc = table.shape
+    if len(wm) < 2 or wm[0]["tag"] != TAG_LINEAR or wm[-1]["tag"] != TAG_LINEAR:
+        raise FormatError("backbone must start and end with a Linear")
+    wh = wm[0]["weights"].shape[1]
+    info = dict(vocab=vocab, hc=hc, wh=wh, heads=None, dqk=None, small_heads=None, cap=30.0, step=c.meta["step"],
+                seen=dict(c.meta["seen"]))
+
+    def stage(layers, d, small):
+        blocks, kinds = [], ""
+        for l in layers:
+            bp, shape = _layer_to_block(l, d)
+            kinds += "s" if shape is None else "m"
+            if shape is not None:
+                key = ("small_heads",) if small else ("heads", "dqk")
+                got = shape[:1] if small else shape
+                if any(info[k] not in (None, v) for k, v in zip(key, got)):
+                    raise FormatError("the mLSTM blocks of a stage disagree on heads or dqk")
+                info.update(zip(key, got))
+            blocks.append(bp)
+        return blocks, kinds
+
+    params = dict(table=table, front_w=wm[0]["weights"], front_b=wm[0]["biases"], back_w=wm[-1]["weights"],
+                  back_b=wm[-1]["biases"])
+    params["enc"], info["enc_kinds"] = stage(enc[1:], hc, True)
+    params["bb"], info["bb_kinds"] = stage(wm[1:-1], wh, False)
+    at = next((i for i, l in enumerate(dec) if l["tag"] == TAG_NORM), None)
+    if at is None:
+        raise FormatError("decoder is missing its RMSNorm")
+    params["dec"], info["dec_kinds"] = stage(dec[:at], hc, True)
+    params["dec_gamma"] = dec[at]["gamma"]
+    heads_ = [l for l in dec[at + 1:] if l["tag"] == TAG_LINEAR_NB]
+    if len(heads_) != 1:
+        raise FormatError("decoder is missing its head")
+    params["head_w"] = heads_[0]["weights"]
+    for l in dec[at + 1:]:
+        if l["tag"] == TAG_SOFT_CAP:
+            info["cap"] = float(l["cap"])
+    return params, info
+
+
+def export_hier_params(model):
+    """The host parameter dictionary of a live `hier.Hierarchical`."""
+    host = lambda p: p.w.detach().cpu().numpy()
+
+    class _Stack:  # the three block lists read like a flat model's
+        def __init__(self, blocks):
+            self.blocks, self.table, self.norm = blocks, model.table, model.dec_norm
+
+    out = dict(table=host(model.table), front_w=host(model.front.w), front_b=host(model.front.b),
+               back_w=host(model.back.w), back_b=host(model.back.b), dec_gamma=host(model.dec_norm.gamma),
+               head_w=host(model.head))
+    for name, blocks in (("enc", model.enc), ("bb", model.bb), ("dec", model.dec)):
+        out[name] = export_lm_params(_Stack(blocks))["blocks"]
+    return out
+
+
+def save_hier(path, model, seen=None):
+    """Writes a live hierarchical model as the container the reference's `Hierarchical::load` opens."""
+    save(path, hier_to_container(export_hier_params(model), model.cfg, step=model.step_count, seen=seen))
+
+
+def load_hier(path, w_token, **build_kw):
+    """Builds a `hier.Hierarchical` on the current GPU from a container; `w_token` comes from the caller, the
+    format does not store it (src/gpu/hierarchical.rs:1835-1838). AdamW moments start at zero."""
+    from . import hier
+
+    params, info = hier_from_container(load(path))
+    sh = info["small_heads"] or 16
+    cfg = hier.HierCfg(info["vocab"], info["hc"], info["wh"], len(params["enc"]), len(params["bb"]), len(params["dec"]),
+                       info["heads"] or 8, info["dqk"] or info["wh"] // 8, w_token, cap=info["cap"], small_heads=sh,
+                       enc_kinds=info["enc_kinds"], bb_kinds=info["bb_kinds"], dec_kinds=info["dec_kinds"])
+    model = hier.Hierarchical(params, cfg, **build_kw)
+    model.step_count = info["step"]
+    return model

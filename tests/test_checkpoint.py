@@ -230,3 +230,60 @@ def test_untied_head_round_trips_as_a_linear():
     q, info = ck.lm_from_container(c)
     assert _same(p, q) and not info["tied"]
     assert np.array_equal(info["head_w"], hw) and np.array_equal(info["head_b"], hb)
+
+
+# ---- hierarchical model -------------------------------------------------------------------------------------
+from oracle import hier as OH
+
+
+def _hier():
+    cfg = OH.HierCfg(vocab=12, hc=16, wh=24, enc_blocks=2, bb_blocks=3, dec_blocks=2, heads=2, dqk=8, w_token=11,
+                     cap=20.0, small_heads=2)
+    p = OH.init_hier_params(np.random.default_rng(4), cfg, std=0.3)
+    p = {k: ([dict(b, cell=dict(b["cell"])) for b in v] if isinstance(v, list) else np.asarray(v, np.float32)) for k, v in p.items()}
+    for k in ("enc", "bb", "dec"):
+        for b in p[k]:
+            for kk in list(b):
+                if kk != "cell":
+                    b[kk] = np.asarray(b[kk], np.float32)
+            b["cell"] = {kk: (vv if kk == "kind" else np.asarray(vv, np.float32)) for kk, vv in b["cell"].items()}
+    return cfg, p
+
+
+def test_hierarchical_parameters_survive_the_file_and_keep_the_references_section_layout():
+    cfg, p = _hier()
+    c = ck.hier_to_container(p, cfg, step=77, seen=dict(pretrain_chars=1000, pretrain_words=200))
+    assert [n for n, _ in c.sections] == ["encoder", "word_model", "char2_model"]
+    tags = {n: [l["tag"] for l in ls] for n, ls in c.sections}
+    assert tags == {"encoder": [7, 11, 14], "word_model": [12, 11, 14, 14, 12], "char2_model": [11, 14, 9, 3, 17]}
+    back = ck.loads(ck.dumps(c))
+    assert (back.meta["vocab_size"], back.meta["context_size"], back.meta["step"]) == (12, 16, 77)
+    assert back.meta["seen"]["pretrain_chars"] == 1000 and back.meta["seen"]["sft_words"] == 0
+    q, info = ck.hier_from_container(back)
+    assert _same(p, q)
+    assert (info["vocab"], info["hc"], info["wh"], info["heads"], info["dqk"], info["small_heads"], info["cap"]) == \
+        (12, 16, 24, 2, 8, 2, 20.0)
+    assert (info["enc_kinds"], info["bb_kinds"], info["dec_kinds"]) == ("sm", "smm", "sm")
+
+
+def test_hierarchical_loader_checks_the_stage_layout():
+    cfg, p = _hier()
+    c = ck.hier_to_container(p, cfg)
+    flat = ck.Container(ck.KIND_FLAT, sections=c.sections)
+    with pytest.raises(ck.FormatError, match="not a hierarchical"):
+        ck.hier_from_container(flat)
+    sections = dict(c.sections)
+    broken = ck.Container(ck.KIND_HIERARCHICAL, c.meta, [("encoder", sections["encoder"][1:]),
+                                                         ("word_model", sections["word_model"]),
+                                                         ("char2_model", sections["char2_model"])])
+    with pytest.raises(ck.FormatError, match="start with an Embedding"):
+        ck.hier_from_container(broken)
+    broken = ck.Container(ck.KIND_HIERARCHICAL, c.meta, [("encoder", sections["encoder"]),
+                                                         ("word_model", sections["word_model"][:-1]),
+                                                         ("char2_model", sections["char2_model"])])
+    with pytest.raises(ck.FormatError, match="start and end with a Linear"):
+        ck.hier_from_container(broken)
+    broken = ck.Container(ck.KIND_HIERARCHICAL, c.meta, [("encoder", sections["encoder"]),
+                                                         ("word_model", sections["word_model"])])
+    with pytest.raises(ck.FormatError, match="missing section 'char2_model'"):
+        ck.hier_from_container(broken)
