@@ -22,7 +22,11 @@ import torch
 from . import layers, ops
 
 BACKBONE_CHUNK = 512    # src/config.rs:96
-GROUP_MAX_ROWS = 2048   # src/config.rs:115
+# Row cap of one encoder/decoder rectangle. The reference's 2048 (src/config.rs:115) bounds the activations of a
+# 16 GB card; it is a batching choice that does not change results, and here it costs a factor of two in step
+# time at 16 x 8192 bytes (72 small rectangles per stage instead of one or two), so the default is sized for
+# 180 GB: a 131072-row rectangle of width 256 holds about 20 GB of activations.
+GROUP_MAX_ROWS = 131072
 
 
 class HierCfg:
@@ -67,26 +71,26 @@ def init_hier_params(rng, cfg, std=0.02):
                 dec_gamma=np.ones(cfg.hc, np.float32), head_w=n(cfg.hc, cfg.vocab))
 
 
-def group_by_len(lens, no_group=False, cap=GROUP_MAX_ROWS):
+def group_by_len(lens, no_group=False, cap=None):
     """Word indices bucketed by the next power of two of their length, buckets in ascending order, each cut
-    into pieces of at most `cap` rows (rows = words x (longest word + 1); cap 0 = no cut), the pieces after
-    the first appended behind all buckets (src/gpu/hierarchical.rs:117-200). The order fixes the order in
-    which losses are summed and gradients scattered."""
+    into pieces of at most `cap` rows (rows = words x (longest word + 1); cap 0 = no cut; None = GROUP_MAX_ROWS),
+    the pieces after the first appended behind all buckets (src/gpu/hierarchical.rs:117-200). The order fixes
+    the order in which losses are summed and gradients scattered."""
+    cap = GROUP_MAX_ROWS if cap is None else cap
+    lens = np.asarray(lens, np.int64)
     if no_group:
         return [list(range(len(lens)))]
-    key = lambda l: 1 << (max(l, 1) - 1).bit_length()
-    slots = {k: i for i, k in enumerate(sorted({key(l) for l in lens}))}
-    out = [[] for _ in slots]
-    for w, l in enumerate(lens):
-        out[slots[key(l)]].append(w)
+    l1 = np.maximum(lens, 1)
+    key = np.left_shift(1, np.ceil(np.log2(l1)).astype(np.int64))  # next power of two, exact for these sizes
+    out = [np.nonzero(key == k)[0] for k in np.unique(key)]
     if cap:
-        for g in range(len(slots)):
-            tmax = max(max(lens[w] for w in out[g]), 1)
-            per = max(cap // (tmax + 1), 1)
+        first = len(out)
+        for g in range(first):
+            per = max(cap // (int(l1[out[g]].max()) + 1), 1)
             if len(out[g]) > per:
                 tail, out[g] = out[g][per:], out[g][:per]
                 out += [tail[i:i + per] for i in range(0, len(tail), per)]
-    return out
+    return [g.tolist() for g in out]
 
 
 def chunk_spans(n, chunk):
@@ -173,45 +177,44 @@ class Hierarchical:
     def _dev(a, dtype):
         return torch.from_numpy(np.ascontiguousarray(a)).to("cuda", dtype=dtype, non_blocking=False)
 
-    def _enc_plan(self, word, N):
-        """Per group: (word rows, tmax, ids [n_g * tmax], readout rows) (src/gpu/hierarchical.rs:436-458)."""
-        lens = [len(word(i, 0)) for i in range(N)]
+    def _enc_plan(self, tok, start, lens):
+        """Per group: (word rows, n, tmax, ids [n * tmax], readout rows): the chars, then the [W] token, zero
+        padded (src/gpu/hierarchical.rs:436-458). tok: all windows' tokens; start, lens: per word."""
         plan = []
         for grp in group_by_len(lens, self.no_group, self._cap()):
-            tmax = max(lens[w] for w in grp) + 1
-            ids = np.zeros((len(grp), tmax), np.int64)
-            readout = np.zeros(len(grp), np.int64)
-            for i, w in enumerate(grp):
-                ids[i, :lens[w]] = word(w, 0)
-                ids[i, lens[w]] = self.cfg.w_token
-                readout[i] = i * tmax + lens[w]
+            grp = np.asarray(grp, np.int64)
+            L = lens[grp]
+            tmax = int(L.max()) + 1
+            k = np.arange(tmax)[None, :]
+            ids = np.where(k < L[:, None], tok[np.minimum(start[grp][:, None] + k, len(tok) - 1)], 0)
+            ids[np.arange(len(grp)), L] = self.cfg.w_token
+            readout = np.arange(len(grp)) * tmax + L
             plan.append((self._dev(grp, torch.int64), len(grp), tmax, self._dev(ids.reshape(-1), torch.int64),
                          self._dev(readout, torch.int64)))
         return plan
 
-    def _dec_plan(self, word, N, on):
-        """Per group the id lists of src/gpu/hierarchical.rs:329-364: slot-0 rows, char rows and ids, targets, mask."""
-        lens = [len(word(i, 1)) for i in range(N)]
+    def _dec_plan(self, tok, start, lens, on):
+        """Per group the id lists of src/gpu/hierarchical.rs:329-364: slot-0 rows, char rows and ids (slot k feeds
+        char k-1), targets (the chars, then [W]) and the loss mask. on: 0/1 per word."""
         plan = []
         for grp in group_by_len(lens, self.no_group, self._cap()):
-            tmax = max(lens[w] for w in grp) + 1
-            rows = len(grp) * tmax
-            targets, mask = np.zeros(rows, np.int32), np.zeros(rows, np.int32)
-            char_rows, char_ids = [], []
-            for i, w in enumerate(grp):
-                cs, m = word(w, 1), lens[w]
-                char_rows += range(i * tmax + 1, i * tmax + m + 1)
-                char_ids += list(cs)
-                targets[i * tmax:i * tmax + m] = cs
-                targets[i * tmax + m] = self.cfg.w_token
-                mask[i * tmax:i * tmax + m + 1] = on(w)
+            grp = np.asarray(grp, np.int64)
+            L = lens[grp]
+            tmax = int(L.max()) + 1
+            k = np.arange(tmax)[None, :]
+            chars = tok[np.minimum(start[grp][:, None] + k, len(tok) - 1)]
+            targets = np.where(k < L[:, None], chars, 0)
+            targets[np.arange(len(grp)), L] = self.cfg.w_token
+            mask = (k <= L[:, None]) * on[grp][:, None]
+            fed = (k >= 1) & (k <= L[:, None])          # slots that take the previous char, row-major
+            rows = (np.arange(len(grp))[:, None] * tmax + k)[fed]
+            prev = tok[np.minimum(start[grp][:, None] + k - 1, len(tok) - 1)][fed]
             plan.append(dict(words=self._dev(grp, torch.int64), n=len(grp), tmax=tmax,
                              o_rows=self._dev(np.arange(len(grp)) * tmax, torch.int64),
-                             char_rows=self._dev(np.array(char_rows, np.int64), torch.int64),
-                             char_ids=self._dev(np.array(char_ids, np.int64), torch.int64),
-                             targets=self._dev(targets, torch.int32), mask=self._dev(mask, torch.int32)))
-        valid = sum((lens[w] + 1) * on(w) for w in range(N))
-        return plan, valid, sum(on(w) for w in range(N))
+                             char_rows=self._dev(rows, torch.int64), char_ids=self._dev(prev, torch.int64),
+                             targets=self._dev(targets.reshape(-1), torch.int32),
+                             mask=self._dev(mask.reshape(-1), torch.int32)))
+        return plan, int(((lens + 1) * on).sum()), int(on.sum())
 
     # ---- stages ---------------------------------------------------------------------------------------------
     def _enc_stack(self, n_g, tmax, ids):
@@ -330,14 +333,18 @@ class Hierarchical:
             return 0.0
         N = Bw * dw  # row i: window i // dw, word i % dw
 
-        def word(i, shift):
-            tok, words = windows[i // dw]
-            s, e = words[i % dw + shift]
-            return tok[s:e]
-
-        on = (lambda i: 1) if word_loss is None else (lambda i: int(bool(word_loss[i // dw][i % dw])))
-        enc_plan = self._enc_plan(word, N)
-        dec_plan, valid, scored = self._dec_plan(word, N, on)
+        # all windows' tokens in one array; per row the start and length of the word it encodes and of the
+        # word it decodes (the next one)
+        tok = np.concatenate([np.asarray(t, np.int64).reshape(-1) for t, _ in windows] + [np.zeros(1, np.int64)])
+        base = np.cumsum([0] + [len(t) for t, _ in windows[:-1]])
+        se = np.stack([np.asarray(w, np.int64).reshape(nw, 2) + b for (_, w), b in zip(windows, base)])  # [Bw, nw, 2]
+        enc_start, enc_len = se[:, :-1, 0].reshape(-1), (se[:, :-1, 1] - se[:, :-1, 0]).reshape(-1)
+        dec_start, dec_len = se[:, 1:, 0].reshape(-1), (se[:, 1:, 1] - se[:, 1:, 0]).reshape(-1)
+        on = np.ones(N, np.int64) if word_loss is None else np.asarray(word_loss).astype(bool).astype(np.int64).reshape(-1)
+        if on.size != N:
+            raise ValueError("word_loss needs one flag per decoded word of every window")
+        enc_plan = self._enc_plan(tok, enc_start, enc_len)
+        dec_plan, valid, scored = self._dec_plan(tok, dec_start, dec_len, on)
         inv = 1.0 / max(valid, 1)
 
         e_w = torch.zeros((N, self.cfg.hc), dtype=torch.float32, device="cuda")
