@@ -503,6 +503,79 @@ def run_ops(args):
                       "peak": pk, "kernels": res, "gpu_launches": int(launches)}))
 
 
+def run_hier(args):
+    """Secondary workload: configs[4], one training step of the three-stage hierarchical model: bytes [16, 8192] in
+    words of 8, lower stacks 2 mLSTM blocks of width 256, backbone 8 mLSTM blocks of width 1024 (8 x 128), bf16 GEMM
+    operands, fp32 master weights, AdamW. The timed step starts from host token arrays (planning and id uploads
+    inside) and reads the loss back. One process per GPU, each its own replica and data (no gradient exchange is
+    wired for this model: replicas only)."""
+    import torch
+    import torch.distributed as dist
+    xl = importlib.import_module("neural-networks_b200")
+    H = importlib.import_module("neural-networks_b200.hier")
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    B, T, S = 16, 8192, 8
+    cfg = H.HierCfg(vocab=257, hc=256, wh=1024, enc_blocks=2, bb_blocks=8, dec_blocks=2, heads=8, dqk=128, w_token=256,
+                    small_heads=2, enc_kinds="mm", bb_kinds="m" * 8, dec_kinds="mm")
+    model = H.Hierarchical(H.init_hier_params(np.random.default_rng(0), cfg, std=0.02), cfg, bf16=True)
+    nparams = sum(q.w.numel() for q in model.params())
+    r = np.random.default_rng(1234 + rank)
+    words = [(i * S, (i + 1) * S) for i in range(T // S)]
+    wins = [(r.integers(0, 256, T), words) for _ in range(B)]
+    acfg = xl.ops.AdamCfg(1e-3, 0.1, t=0)
+
+    def step():
+        acfg.t += 1
+        loss = model.forward_backward(wins)  # reads the loss back
+        model.step(acfg)
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        loss = step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    l0 = xl._lib.lib.xlstm_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        loss = step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = xl._lib.lib.xlstm_launch_count() - l0
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.destroy_process_group()
+    ms /= args.steps
+    if rank == 0:
+        val = B * T * world / (ms * 1e-3)
+        ids_bytes = B * (T // S - 1) * (S + 1) * (8 + 8 + 4 + 4)  # encoder ids, decoder char ids, targets, mask (plus row lists)
+        print(json.dumps({
+            "metric": "train_bytes_per_s", "value": val, "unit": "bytes/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "hierarchical_train_step (configs[4]: bytes 16x8192 in words of 8, 2+2 blocks of 256, backbone 8 blocks of 1024 = 8x128)",
+                       "params": nparams, "parallelism": "replicas only (%d)" % world, "l2": "activations far larger than L2"},
+            "loss": loss, "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
+            "e2e": {"value": val, "unit": "bytes/s", "h2d_bytes_per_step": ids_bytes, "d2h_bytes_per_step": 4,
+                    "note": "the timed step already starts from host token arrays and reads the loss back"},
+            "gpu_launches": int(launches), "clocks": clocks}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -512,8 +585,9 @@ def main():
     ap.add_argument("--grad-dtype", default="f32", choices=["f32", "bf16"])
     ap.add_argument("--recompute", action="store_true", help="backward recomputes chunk-boundary states")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--workload", default="mlstm", choices=["mlstm", "lm", "ops"],
-                    help="mlstm: configs[1] layer kernel (headline); lm: training step; ops: the other hot-path kernels alone")
+    ap.add_argument("--workload", default="mlstm", choices=["mlstm", "lm", "ops", "hier"],
+                    help="mlstm: configs[1] layer kernel (headline); lm: training step; ops: the other hot-path kernels alone; "
+                         "hier: configs[4] hierarchical training step")
     ap.add_argument("--lm-blocks", type=int, default=0, help="override the LM depth (development)")
     ap.add_argument("--lm-remat", type=int, default=2, help="blocks rematerialised in the full-width LM workload")
     ap.add_argument("--lm-full", action="store_true", help="LM workload at the full widths of configs[3] (d=2048, heads of 256 / 512)")
@@ -524,6 +598,8 @@ def main():
         run_lm(args)
     elif args.workload == "ops":
         run_ops(args)
+    elif args.workload == "hier":
+        run_hier(args)
     else:
         run_ours(args)
 

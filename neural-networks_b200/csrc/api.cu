@@ -42,8 +42,10 @@ static int check_shape(const char* who, const xlstm_mlstm_shape* s) {
 static inline int eff_L(const xlstm_mlstm_shape* s) { return s->L < s->T ? s->L : s->T; }
 static inline int num_chunks(const xlstm_mlstm_shape* s) { int L = eff_L(s); return (s->T + L - 1) / L; }
 
+// The tensor-core kernels work on 64-row chunk tiles whatever T is: a sequence shorter than a chunk is one ragged
+// chunk (rows past T are zero-filled by the tensor map and never stored), so the requested L decides, not min(L, T).
 static inline bool use_tc(const xlstm_mlstm_shape* s) {
-    return !(s->flags & XLSTM_FORCE_SIMT) && mlstm_tc_supported(eff_L(s), s->dqk, s->dhv, s->dtype) && s->T >= 1;
+    return !(s->flags & XLSTM_FORCE_SIMT) && mlstm_tc_supported(s->L, s->dqk, s->dhv, s->dtype) && s->T >= 1;
 }
 
 // Chunk-state record of the CUDA-core path: C then n, each the state ENTERING a chunk, f32.

@@ -113,7 +113,8 @@ def test_declines_oversized_tile_without_launching():
 
 
 # ---- tensor-core path (dqk = dhv = 128, L = 64, bf16 storage; flags = 0 selects it) -----------
-@pytest.mark.parametrize("shape", [(1, 2, 64, 128, 128), (1, 2, 256, 128, 128), (2, 3, 200, 128, 128), (2, 2, 40, 128, 128)])
+@pytest.mark.parametrize("shape", [(1, 2, 64, 128, 128), (1, 2, 256, 128, 128), (2, 3, 200, 128, 128), (2, 2, 40, 128, 128),
+                                   (5, 2, 9, 128, 128), (8, 4, 1, 128, 128), (2, 1, 9, 256, 128)])
 @pytest.mark.parametrize("gdtype", [torch.float32, torch.bfloat16])
 def test_tensor_core_path_matches_oracle(shape, gdtype):
     from gpu_util import xl
