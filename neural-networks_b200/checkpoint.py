@@ -489,8 +489,10 @@ def export_lm_params(lm):
     host = lambda p: p.w.detach().cpu().numpy()
     blocks = []
     for blk in lm.blocks:
-        bp = dict(g1=host(blk.n1.gamma), g2=host(blk.n2.gamma), w_gate=host(blk.lg.w), b_gate=host(blk.lg.b),
-                  w_value=host(blk.lv.w), b_value=host(blk.lv.b), w_down=host(blk.ld.w), b_down=host(blk.ld.b))
+        u = blk.up  # the projections may be stored padded with zero columns / rows; the file holds the model's width
+        bp = dict(g1=host(blk.n1.gamma), g2=host(blk.n2.gamma), w_gate=host(blk.lg.w)[:, :u].copy(), b_gate=host(blk.lg.b)[:u].copy(),
+                  w_value=host(blk.lv.w)[:, :u].copy(), b_value=host(blk.lv.b)[:u].copy(), w_down=host(blk.ld.w)[:u].copy(),
+                  b_down=host(blk.ld.b))
         c = blk.cell
         if isinstance(c, layers.MLstm):
             cell = dict(kind="mlstm", w_out=host(c.lout.w), b_out=host(c.lout.b), gamma=host(c.hn.gamma))

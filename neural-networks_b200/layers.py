@@ -295,9 +295,17 @@ class Block:
         self.cell = cell
         self.n1, self.n2 = RmsNorm(p["g1"]), RmsNorm(p["g2"])
         self.post = RmsNorm(p["gpost"]) if post_norm else None
-        self.lg = Linear(p["w_gate"], p["b_gate"], True, bf16)
-        self.lv = Linear(p["w_value"], p["b_value"], True, bf16)
-        self.ld = Linear(p["w_down"], p["b_down"], True, bf16)
+        # The inner width as the model defines it (8h/3 in the reference's models: 682 at h = 256, 2730 at 1024).
+        # A bf16 operand whose rows are not a multiple of 16 bytes sends the library to its slow unaligned GEMMs,
+        # so in bf16 mode the three projections are stored padded to a multiple of 8 columns / rows of zeros. The
+        # padding is exact: SiLU(0) * 0 = 0 feeds zero rows of w_down, every gradient of a padded entry is zero
+        # and AdamW keeps a zero weight with a zero gradient at zero. `up` is what checkpoints see.
+        self.up = p["w_gate"].shape[1]
+        pad = (-self.up) % 8 if bf16 else 0
+        wide = lambda w: torch.nn.functional.pad(torch.as_tensor(w, dtype=torch.float32), (0, pad))
+        self.lg = Linear(wide(p["w_gate"]), wide(p["b_gate"]), True, bf16)
+        self.lv = Linear(wide(p["w_value"]), wide(p["b_value"]), True, bf16)
+        self.ld = Linear(torch.nn.functional.pad(torch.as_tensor(p["w_down"], dtype=torch.float32), (0, 0, 0, pad)), p["b_down"], True, bf16)
 
     def forward(self, x, B, T):
         if self.post is None:

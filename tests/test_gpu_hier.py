@@ -135,7 +135,17 @@ def test_bf16_sweep_across_tensor_core_calls_matches_one_long_call():
     lens = r.integers(1, 6, 289).tolist()
     wins = [_window(11, lens, cfg.vocab), _window(12, lens[::-1], cfg.vocab)]
     l0, g0 = _grads(H.Hierarchical(p, cfg, bf16=True, bb_chunk=0), wins)
-    l1, g1 = _grads(H.Hierarchical(p, cfg, bf16=True, bb_chunk=96), wins)
+    swept = H.Hierarchical(p, cfg, bf16=True, bb_chunk=96)
+    l1, g1 = _grads(swept, wins)
+    # bf16 blocks store the SwiGLU projections padded to a multiple of 8 columns (85 -> 88, 682 -> 688); what
+    # leaves the model has the model's own widths and values
+    ck = importlib.import_module("neural-networks_b200.checkpoint")
+    assert swept.enc[0].lg.w.w.shape[1] % 8 == 0 and swept.enc[0].up == H.up_of(cfg.hc) == 85
+    out = ck.export_hier_params(swept)
+    for name in ("enc", "bb", "dec"):
+        for a, b in zip(out[name], p[name]):
+            for k in ("w_gate", "b_gate", "w_value", "b_value", "w_down", "b_down"):
+                assert np.array_equal(a[k], b[k]), (name, k)
     assert xl._lib.lib.xlstm_device_status() == 0
     assert abs(l1 - l0) <= 5e-3 * max(1.0, abs(l0)), (l1, l0)
     _close(g1, g0, 2e-1, cos_min=0.999)
