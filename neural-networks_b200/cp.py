@@ -96,3 +96,19 @@ def dist_gather(group=None):
         return out
 
     return gather
+
+
+def enable(lm, rank, world, group=None, gather=None):
+    """Turns a model's mLSTM cells into context-parallel ones: every call then treats its [B, T] input as segment
+    `rank` of `world` of a sequence `world` times as long. Everything else in a block is position-wise and needs
+    nothing. Gradients of the parameters are partial sums over this rank's positions: add them over the ranks as
+    data parallelism does (`dp.attach`, whose loss scale 1/(B T world) is the whole sequence's). An sLSTM cell is
+    refused: its recurrence is not linear in its state, so there is no summary to fold; it needs the state handed
+    from rank to rank."""
+    from . import layers
+
+    g = gather if gather is not None else dist_gather(group)
+    for blk in lm.blocks:
+        if not isinstance(blk.cell, layers.MLstm):
+            raise ValueError("context parallelism covers mLSTM blocks; this model has an sLSTM block")
+        blk.cell.cp = (rank, world, g)

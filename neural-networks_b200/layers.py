@@ -16,7 +16,7 @@ import math
 
 import torch
 
-from . import ops
+from . import cp, ops
 
 
 class Param:
@@ -157,6 +157,7 @@ class MLstm:
         self.sweep = False  # training over a sequence cut into calls: `carry` in and out forwards, `dcarry` backwards
         self.dcarry = None  # (dC, dn) from the call to the right
         self.shard_group = None  # head-sharded inference: process group whose ranks split the heads
+        self.cp = None  # context parallelism: (rank, world, gather) when the sequence is cut over the ranks (cp.enable)
 
     def forward(self, x, B, T, residual=None):
         """residual: when given, the call returns residual + cell(x) (the block's first residual add, done inside
@@ -177,9 +178,12 @@ class MLstm:
         ig, fg = self.li.forward(x), self.lf.forward(x)
         self.core_in = (q, k, v, ig, fg)
         keep = self.stateful or self.sweep
-        self.carry_in = self.carry  # the backward needs the state this call entered with
-        self.fused = ops.mlstm_fused_fw(q, k, v, ig, fg, self.st, carry_in=self.carry, want_state=keep,
-                                        save_states=not self.stateful)
+        if self.cp is not None:  # this rank's segment inside the whole sequence: the carry comes from the ranks to the left
+            self.fused, self.carry_in = cp.forward(q, k, v, ig, fg, self.st, self.cp[0], self.cp[2])
+        else:
+            self.carry_in = self.carry  # the backward needs the state this call entered with
+            self.fused = ops.mlstm_fused_fw(q, k, v, ig, fg, self.st, carry_in=self.carry, want_state=keep,
+                                            save_states=not self.stateful)
         if keep:
             self.carry = self.fused.state
         self.yhat = self.hn.forward(self.fused.ytil.float() if self.bf16 else self.fused.ytil)
@@ -199,11 +203,15 @@ class MLstm:
         do_pre, d_yhat = ops.ogate_backward(d_hc, self.o, self.yhat, torch.bfloat16 if self.bf16 else torch.float32)
         d_ytil = self.hn.backward(d_yhat)
         q, k, v, ig, fg = self.core_in
-        dq, dk, dv, dig, dfg, dstate = ops.mlstm_fused_bw(self.fused, q, k, v, ig, fg, d_ytil, self.st, carry_in=self.carry_in,
-                                                          dstate_in=self.dcarry if self.sweep else None,
-                                                          want_dstate=self.sweep)
-        if self.sweep:
-            self.dcarry = dstate
+        if self.cp is not None:
+            dq, dk, dv, dig, dfg = cp.backward(self.fused, q, k, v, ig, fg, d_ytil, self.st, self.carry_in, *self.cp)
+        else:
+            dq, dk, dv, dig, dfg, dstate = ops.mlstm_fused_bw(self.fused, q, k, v, ig, fg, d_ytil, self.st,
+                                                              carry_in=self.carry_in,
+                                                              dstate_in=self.dcarry if self.sweep else None,
+                                                              want_dstate=self.sweep)
+            if self.sweep:
+                self.dcarry = dstate
         dx = self.lq.backward(dq)
         self.lk.backward(dk.mul_(self.inv_sqrt), accum=dx)
         self.lv.backward(dv, accum=dx)

@@ -114,3 +114,66 @@ def test_two_gpus_over_nccl(tmp_path):
     parts = [torch.load("%s.%d" % (out, r), weights_only=False) for r in range(2)]
     for i, n in enumerate(NAMES):
         assert rel_to_max(_join([p[i] for p in parts], B, T, 2), ref[n]) <= 2e-2, n
+
+
+class _ThreadRanks:
+    """W host threads as W ranks on one GPU: the exchange is a list behind a barrier. All kernels go to the same
+    stream in issue order and none waits on another, so this is a plain serialised run of the multi-rank code."""
+
+    def __init__(self, world):
+        import threading
+        self.world, self.slots, self.bar = world, [None] * world, threading.Barrier(world)
+
+    def gather_of(self, rank):
+        def gather(t):
+            self.slots[rank] = t
+            self.bar.wait()
+            out = list(self.slots)
+            self.bar.wait()
+            return out
+        return gather
+
+
+def test_language_model_over_three_segments_equals_the_whole_sequence():
+    """Every rank runs the same model on its third of each sequence; the summed losses and the summed parameter
+    gradients equal the single run on the whole sequences (fp32, 2e-4: two fp32 runs)."""
+    import threading
+    from gpu_util import xl
+    layers = importlib.import_module("neural-networks_b200.layers")
+    cp = importlib.import_module("neural-networks_b200.cp")
+    vocab, d, nb, heads, dqk, dhv, up, B, T, W = 40, 32, 2, 2, 8, 16, 48, 2, 48, 3
+    rng = np.random.default_rng(51)
+    p = layers.init_lm_params(rng, vocab, d, nb, heads, dqk, dhv, up, std=0.2)
+    ids = rng.integers(0, vocab, (B, T))
+    tg = np.roll(ids, -1, axis=1)
+    whole = layers.build_lm(p, heads, dqk, dhv, tied=True, chunk=8)
+    dev_ids = lambda a: torch.tensor(np.ascontiguousarray(a).reshape(-1), dtype=torch.int64, device="cuda")
+    dev_tg = lambda a: torch.tensor(np.ascontiguousarray(a).reshape(-1).astype(np.int32), device="cuda")
+    loss0 = whole.forward_backward(dev_ids(ids), dev_tg(tg), B, T).item()
+    ranks = _ThreadRanks(W)
+    models = [layers.build_lm(p, heads, dqk, dhv, tied=True, chunk=8) for _ in range(W)]
+    losses, errors = [None] * W, []
+
+    def run(r):
+        try:
+            cp.enable(models[r], r, W, gather=ranks.gather_of(r))
+            seg = slice(r * T // W, (r + 1) * T // W)
+            losses[r] = models[r].forward_backward(dev_ids(ids[:, seg]), dev_tg(tg[:, seg]), B, T // W, inv=1.0 / (B * T))
+        except Exception as e:  # a dead rank would leave the others at the barrier
+            errors.append(e)
+            ranks.bar.abort()
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(W)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    torch.cuda.synchronize()
+    assert xl._lib.lib.xlstm_device_status() == 0
+    assert abs(sum(l.item() for l in losses) - loss0) <= 2e-5 * abs(loss0)
+    gmax = max(float(q.g.abs().max()) for q in whole.params())
+    for i, q in enumerate(whole.params()):
+        total = sum(m.params()[i].g for m in models)
+        e = float((total - q.g).abs().max()) / max(float(q.g.abs().max()), 1e-2 * gmax)
+        assert e <= 2e-4, (i, tuple(q.g.shape), e)
