@@ -17,6 +17,7 @@ import argparse
 import ctypes
 import importlib
 import json
+import math
 import os
 import subprocess
 import sys
@@ -576,6 +577,69 @@ def run_hier(args):
             "gpu_launches": int(launches), "clocks": clocks}))
 
 
+def run_cp(args):
+    """Secondary workload: the configs[1] mLSTM layer kernel pair with ONE sequence set cut over the GPUs (context
+    parallelism): every rank holds a [16, 2048] segment of sequences world x 2048 long. Strong in the sequence,
+    weak per GPU; each rank runs two forward and two backward passes plus two all-gathers of segment summaries."""
+    import torch
+    import torch.distributed as dist
+    xl = importlib.import_module("neural-networks_b200")
+    cp = importlib.import_module("neural-networks_b200.cp")
+    ops = xl.ops
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    c = CFG
+    B, H, T, dqk, dhv = c["B"], c["H"], c["T"], c["dqk"], c["dhv"]
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    rnd = lambda *sh: torch.randn(sh, device="cuda", generator=g)
+    q, k, v = (rnd(B * T, H * d).to(torch.bfloat16) for d in (dqk, dqk, dhv))
+    k = (k.float() / math.sqrt(dqk)).to(torch.bfloat16)
+    ig, fg, dy = rnd(B * T, H), rnd(B * T, H) + 3.0, rnd(B * T, H * dhv)
+    st = ops.MlstmShape(B, H, T, dqk, dhv, c["L"], torch.bfloat16, torch.float32)
+    gather = cp.dist_gather() if world > 1 else (lambda t: [t])
+
+    def step():
+        fused, carry = cp.forward(q, k, v, ig, fg, st, rank, gather) if world > 1 else \
+            (ops.mlstm_fused_fw(q, k, v, ig, fg, st, save_states=True, want_state=False), None)
+        return cp.backward(fused, q, k, v, ig, fg, dy, st, carry, rank, world, gather)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    l0 = xl._lib.lib.xlstm_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = xl._lib.lib.xlstm_launch_count() - l0
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.destroy_process_group()
+    ms /= args.steps
+    if rank == 0:
+        print(json.dumps({
+            "metric": "mlstm_layer_tokens_per_s", "value": B * T * world / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "mlstm_layer_fwd_bwd, sequences of %d positions cut over %d GPUs (B16 H8 S2048 per GPU, dqk128 dv128 chunk64)" % (T * world, world),
+                       "parallelism": "cp%d (segment summaries all-gathered, carry folded, BPTT state suffix-summed)" % world,
+                       "l2": "tensors larger than L2"},
+            "gpu_launches": int(launches)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -585,9 +649,9 @@ def main():
     ap.add_argument("--grad-dtype", default="f32", choices=["f32", "bf16"])
     ap.add_argument("--recompute", action="store_true", help="backward recomputes chunk-boundary states")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--workload", default="mlstm", choices=["mlstm", "lm", "ops", "hier"],
+    ap.add_argument("--workload", default="mlstm", choices=["mlstm", "lm", "ops", "hier", "cp"],
                     help="mlstm: configs[1] layer kernel (headline); lm: training step; ops: the other hot-path kernels alone; "
-                         "hier: configs[4] hierarchical training step")
+                         "hier: configs[4] hierarchical training step; cp: the layer kernel with sequences cut over the GPUs")
     ap.add_argument("--lm-blocks", type=int, default=0, help="override the LM depth (development)")
     ap.add_argument("--lm-remat", type=int, default=2, help="blocks rematerialised in the full-width LM workload")
     ap.add_argument("--lm-full", action="store_true", help="LM workload at the full widths of configs[3] (d=2048, heads of 256 / 512)")
@@ -600,6 +664,8 @@ def main():
         run_ops(args)
     elif args.workload == "hier":
         run_hier(args)
+    elif args.workload == "cp":
+        run_cp(args)
     else:
         run_ours(args)
 
