@@ -30,6 +30,11 @@ def _flat(parts):
     return torch.cat([p.reshape(p.shape[0], -1) for p in parts], dim=1)
 
 
+def _log_forget_sum(fg, st):
+    """F = sum over the segment of log sigmoid(f), [BH, 1] (summed in fp64: T terms of either sign of rounding)."""
+    return torch.nn.functional.logsigmoid(fg).view(st.b, st.t, st.h).sum(dim=1, dtype=torch.float64).float().reshape(st.bh(), 1)
+
+
 def segment_summary(q, k, v, ig, fg, st):
     """[BH, dhv*dqk + dqk + 2]: the segment's own (C_s, n_s, M_s) and F, one row per (batch, head)."""
     bh = st.bh()
@@ -38,8 +43,7 @@ def segment_summary(q, k, v, ig, fg, st):
              torch.zeros((bh, st.dqk), dtype=torch.float32, device=dev),
              torch.full((bh,), NO_HISTORY, dtype=torch.float32, device=dev))
     own = ops.mlstm_fused_fw(q, k, v, ig, fg, st, carry_in=empty, save_states=False, want_state=True).state
-    F = torch.nn.functional.logsigmoid(fg.view(st.b, st.t, st.h).double()).sum(dim=1).float().reshape(bh, 1)
-    return _flat([own[0], own[1], own[2].reshape(bh, 1), F])
+    return _flat([own[0], own[1], own[2].reshape(bh, 1), _log_forget_sum(fg, st)])
 
 
 def fold(summaries, rank, st):
@@ -61,8 +65,11 @@ def fold(summaries, rank, st):
 
 def forward(q, k, v, ig, fg, st, rank, gather):
     """The fused forward of this rank's segment inside the whole sequence. Returns (fused, carry_in)."""
-    carry = fold(gather(segment_summary(q, k, v, ig, fg, st)), rank, st)
-    return ops.mlstm_fused_fw(q, k, v, ig, fg, st, carry_in=carry, save_states=True, want_state=True), carry
+    mine = segment_summary(q, k, v, ig, fg, st)
+    carry = fold(gather(mine), rank, st)
+    fused = ops.mlstm_fused_fw(q, k, v, ig, fg, st, carry_in=carry, save_states=True, want_state=True)
+    fused.log_forget_sum = mine[:, -1:]  # the backward's transport factor needs it again
+    return fused, carry
 
 
 def backward(fused, q, k, v, ig, fg, d_ytil, st, carry, rank, world, gather):
@@ -72,7 +79,7 @@ def backward(fused, q, k, v, ig, fg, d_ytil, st, carry, rank, world, gather):
         return ops.mlstm_fused_bw(fused, q, k, v, ig, fg, d_ytil, st, carry_in=carry, want_dstate=False)[:5]
     # the local term: what this segment's own outputs send into its carry
     own = ops.mlstm_fused_bw(fused, q, k, v, ig, fg, d_ytil, st, carry_in=carry, want_dstate=True)
-    F = torch.nn.functional.logsigmoid(fg.view(st.b, st.t, st.h).double()).sum(dim=1).float().reshape(bh, 1)
+    F = fused.log_forget_sum if hasattr(fused, "log_forget_sum") else _log_forget_sum(fg, st)
     m_in = carry[2].reshape(bh, 1) if carry is not None else torch.zeros_like(F)
     t = torch.exp(F + m_in - fused.state[2].reshape(bh, 1))
     parts = gather(_flat([own[5][0], own[5][1], t]))
