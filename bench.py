@@ -508,8 +508,8 @@ def run_hier(args):
     """Secondary workload: configs[4], one training step of the three-stage hierarchical model: bytes [16, 8192] in
     words of 8, lower stacks 2 mLSTM blocks of width 256, backbone 8 mLSTM blocks of width 1024 (8 x 128), bf16 GEMM
     operands, fp32 master weights, AdamW. The timed step starts from host token arrays (planning and id uploads
-    inside) and reads the loss back. One process per GPU, each its own replica and data (no gradient exchange is
-    wired for this model: replicas only)."""
+    inside) and reads the loss back. One process per GPU, each its own windows; gradients are summed over the ranks
+    in three buckets (decoder, backbone, encoder + table) as the window's backward completes them."""
     import torch
     import torch.distributed as dist
     xl = importlib.import_module("neural-networks_b200")
@@ -527,12 +527,12 @@ def run_hier(args):
     words = [(i * S, (i + 1) * S) for i in range(T // S)]
     wins = [(r.integers(0, 256, T), words) for _ in range(B)]
     acfg = xl.ops.AdamCfg(1e-3, 0.1, t=0)
+    dp = importlib.import_module("neural-networks_b200.dp")
+    buckets = dp.attach_hier(model)
 
     def step():
         acfg.t += 1
-        loss = model.forward_backward(wins)  # reads the loss back
-        model.step(acfg)
-        return loss
+        return dp.train_step_hier(model, buckets, wins, acfg)  # reads the loss back
 
     def barrier():
         if world > 1:
@@ -570,7 +570,7 @@ def run_hier(args):
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "hierarchical_train_step (configs[4]: bytes 16x8192 in words of 8, 2+2 blocks of 256, backbone 8 blocks of 1024 = 8x128)",
-                       "params": nparams, "parallelism": "replicas only (%d)" % world, "l2": "activations far larger than L2"},
+                       "params": nparams, "parallelism": "dp%d (gradient all-reduce per stage, overlapped with the window's backward)" % world, "l2": "activations far larger than L2"},
             "loss": loss, "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
             "e2e": {"value": val, "unit": "bytes/s", "h2d_bytes_per_step": ids_bytes, "d2h_bytes_per_step": 4,
                     "note": "the timed step already starts from host token arrays and reads the loss back"},

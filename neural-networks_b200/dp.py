@@ -73,3 +73,30 @@ def train_step(lm, buckets, ids, targets, B, T, cfg):
     buckets.wait()
     lm.step(cfg)
     return loss
+
+
+def attach_hier(model, group=None):
+    """Buckets for a `hier.Hierarchical`: decoder stage, backbone stage, encoder stage + tied table, each reduced
+    as soon as its part of the window's backward is done. The loss normaliser becomes the valid decoder rows of
+    all ranks (the ranks' windows differ in length), one small all-reduce per call."""
+    buckets = GradBuckets(model.stage_params(), group)
+    model.on_stage_backward = buckets.reduce_async
+
+    def rows_of_all_ranks(valid):
+        if buckets.world() == 1:
+            return valid
+        t = torch.tensor([valid], dtype=torch.int64, device=model.loss.device)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+        return int(t.item())
+
+    model.rows_of_all_ranks = rows_of_all_ranks
+    return buckets
+
+
+def train_step_hier(model, buckets, windows, cfg, word_loss=None):
+    """One data-parallel step of the hierarchical model: every rank its own windows, gradients summed, identical
+    AdamW everywhere. Returns this rank's share of the global mean loss."""
+    loss = model.forward_backward(windows, word_loss)
+    buckets.wait()
+    model.step(cfg)
+    return loss

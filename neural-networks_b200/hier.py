@@ -144,6 +144,19 @@ class Hierarchical:
         self.step_count = 0
         self.last_rows = 0
         self.last_word_loss = 0.0
+        # data parallelism (dp.attach_hier): called with 0, 1, 2 when the decoder's, the backbone's and the
+        # encoder's (and the table's) gradients are complete; `rows_of_all_ranks(valid)` returns the call's valid
+        # decoder rows summed over the ranks, the loss normaliser of the global batch
+        self.on_stage_backward = None
+        self.rows_of_all_ranks = None
+
+    def stage_params(self):
+        """The parameters in the order their gradients complete in a backward: decoder stage, backbone stage,
+        encoder stage with the tied table (which both the decoder and the encoder write)."""
+        dec = [q for blk in self.dec for q in blk.params()] + self.dec_norm.params() + [self.head]
+        bb = self.back.params() + [q for blk in self.bb for q in blk.params()] + self.front.params()
+        enc = [q for blk in self.enc for q in blk.params()] + [self.table]
+        return [dec, bb, enc]
 
     def params(self):
         out = [self.table]
@@ -323,7 +336,8 @@ class Hierarchical:
         encode-only, words 1.. are decoded. word_loss (per window, one flag per decoded word; None = all on)
         keeps a word's rows out of the loss while the word is still encoded and decoded, as in supervised
         fine-tuning on the response only (src/gpu/hierarchical.rs:698-720). Accumulates every gradient and
-        returns the mean cross-entropy over the unmasked decoder rows, read from the device once."""
+        returns the mean cross-entropy over the unmasked decoder rows, read from the device once (under data
+        parallelism: this rank's share of the global mean; the ranks' values add up to it)."""
         nw = len(windows[0][1])
         if any(len(w) != nw for _, w in windows):
             raise ValueError("the windows of one call must hold equally many words")
@@ -345,7 +359,8 @@ class Hierarchical:
             raise ValueError("word_loss needs one flag per decoded word of every window")
         enc_plan = self._enc_plan(tok, enc_start, enc_len)
         dec_plan, valid, scored = self._dec_plan(tok, dec_start, dec_len, on)
-        inv = 1.0 / max(valid, 1)
+        total = valid if self.rows_of_all_ranks is None else self.rows_of_all_ranks(valid)
+        inv = 1.0 / max(total, 1)
 
         e_w = torch.zeros((N, self.cfg.hc), dtype=torch.float32, device="cuda")
         for words, n_g, tmax, ids, readout in enc_plan:
@@ -355,9 +370,13 @@ class Hierarchical:
                 blk.release()
         o, saved = self._backbone_forward(e_w, Bw, dw)
         self.loss.zero_()
+        done = self.on_stage_backward or (lambda i: None)
         d_o = self._decode_groups(dec_plan, o, inv)
+        done(0)
         d_e_w = self._backbone_backward(d_o, saved, Bw, dw)
+        done(1)
         self._encoder_backward(enc_plan, d_e_w)
+        done(2)
         loss = float(self.loss.item())
         self.last_rows = valid
         self.last_word_loss = loss * valid / max(scored, 1)  # the same total re-averaged over words (:1124-1128)

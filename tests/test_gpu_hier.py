@@ -186,3 +186,50 @@ def test_trained_model_reloads_from_its_container_to_the_same_loss(tmp_path):
     got, gg = _grads(again, wins)
     assert got == want
     assert all(torch.equal(a, b) for a, b in zip(gg, gw))
+
+
+def _dp_rank(rank, world, port, out):
+    import os
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    xl, H = _mods()
+    dp = importlib.import_module("neural-networks_b200.dp")
+    cfg = _cfg(H)
+    p = H.init_hier_params(np.random.default_rng(21), cfg, std=0.2)
+    wins = _dp_windows(cfg)
+    m = H.Hierarchical(p, cfg, bb_chunk=4)
+    buckets = dp.attach_hier(m)
+    loss = m.forward_backward(wins[2 * rank:2 * rank + 2])
+    buckets.wait()
+    torch.cuda.synchronize()
+    torch.save((loss, [q.g.cpu() for q in m.params()]), "%s.%d" % (out, rank))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _dp_windows(cfg):
+    lens = [LENS_A, LENS_B, LENS_B[::-1], [3] * len(LENS_A)]  # different valid-row counts on the two ranks
+    return [_window(30 + i, l, cfg.vocab) for i, l in enumerate(lens)]
+
+
+def test_two_gpu_data_parallel_gradients_equal_one_gpu_on_all_windows(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import socket
+    import torch.multiprocessing as mp
+    xl, H = _mods()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = str(tmp_path / "dp")
+    mp.spawn(_dp_rank, args=(2, port, out), nprocs=2, join=True)
+    cfg = _cfg(H)
+    p = H.init_hier_params(np.random.default_rng(21), cfg, std=0.2)
+    one = H.Hierarchical(p, cfg, bb_chunk=4)
+    loss, g = _grads(one, _dp_windows(cfg))
+    parts = [torch.load("%s.%d" % (out, r), weights_only=False) for r in range(2)]
+    assert abs(parts[0][0] + parts[1][0] - loss) <= 2e-5 * loss  # the ranks' shares add up to the global mean
+    for r in range(2):
+        _close([t.cuda() for t in parts[r][1]], g, 2e-4)
