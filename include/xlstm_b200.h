@@ -87,6 +87,14 @@ int xlstm_mlstm_fw(void* stream, const xlstm_mlstm_shape* s, const void* q, cons
                    float* psiv, float* qnv, void* saved, float* out_C, float* out_n,
                    float* out_m, void* workspace, size_t workspace_bytes);
 
+/* The state a call would end in, without its outputs: the recurrence over (C, n, m) alone, about half a
+ * forward's time. New (the reference has no such entry): context parallelism summarises a segment with it
+ * before the carry from the ranks to its left is known. Arguments as in xlstm_mlstm_fw; out_* required. */
+int xlstm_mlstm_final_state(void* stream, const xlstm_mlstm_shape* s, const void* q, const void* k,
+                            const void* v, const float* ig, const float* fg, const float* carry_C,
+                            const float* carry_n, const float* carry_m, float* out_C, float* out_n,
+                            float* out_m);
+
 /* Backward with the stabiliser held constant. d_ytil [B*T,H*dhv] at `gdtype`;
  * carry_dC [BH,dhv,dqk], carry_dn [BH,dqk] f32: gradient w.r.t. the state this call left
  * (NULL = zero), out_dC/out_dn: gradient w.r.t. the state it entered with (optional).

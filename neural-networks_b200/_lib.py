@@ -45,6 +45,7 @@ SIGNATURES = {
     "xlstm_mlstm_fw_workspace_bytes": (_sz, [_shape_p]),
     "xlstm_mlstm_bw_workspace_bytes": (_sz, [_shape_p, _i]),
     "xlstm_mlstm_fw": (_i, [_vp, _shape_p] + [_vp] * 17 + [_sz]),
+    "xlstm_mlstm_final_state": (_i, [_vp, _shape_p] + [_vp] * 11),
     "xlstm_mlstm_bw": (_i, [_vp, _shape_p] + [_vp] * 24 + [_sz]),
     "xlstm_slstm_fw": (_i, [_vp] * 9 + [ctypes.POINTER(SlstmSlabs), _i, _i, _i, _i, _i, _u]),
     "xlstm_slstm_bw": (_i, [_vp] * 7 + [ctypes.POINTER(SlstmSlabs), _i, _i, _i, _i, _i, _u]),

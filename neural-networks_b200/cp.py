@@ -42,7 +42,7 @@ def segment_summary(q, k, v, ig, fg, st):
     empty = (torch.zeros((bh, st.dhv, st.dqk), dtype=torch.float32, device=dev),
              torch.zeros((bh, st.dqk), dtype=torch.float32, device=dev),
              torch.full((bh,), NO_HISTORY, dtype=torch.float32, device=dev))
-    own = ops.mlstm_fused_fw(q, k, v, ig, fg, st, carry_in=empty, save_states=False, want_state=True).state
+    own = ops.mlstm_final_state(q, k, v, ig, fg, st, carry_in=empty)
     return _flat([own[0], own[1], own[2].reshape(bh, 1), _log_forget_sum(fg, st)])
 
 

@@ -117,6 +117,23 @@ extern "C" int xlstm_mlstm_fw(void* stream, const xlstm_mlstm_shape* s, const vo
     return mlstm_fw_simt_launch((cudaStream_t)stream, a, s->dtype);
 }
 
+extern "C" int xlstm_mlstm_final_state(void* stream, const xlstm_mlstm_shape* s, const void* q, const void* k, const void* v,
+                                       const float* ig, const float* fg, const float* carry_C, const float* carry_n,
+                                       const float* carry_m, float* out_C, float* out_n, float* out_m) {
+    int rc = check_shape("mlstm_final_state", s);
+    if (rc) return rc;
+    XL_CHECK_ARG(q && k && v && ig && fg && out_C && out_n && out_m, "mlstm_final_state: null pointer");
+    XL_CHECK_ARG((carry_C != nullptr) == (carry_n != nullptr) && (carry_C != nullptr) == (carry_m != nullptr),
+                 "mlstm_final_state: carry C, n, m must be given together");
+    MlstmFwArgs a = {};
+    a.q = q; a.k = k; a.v = v; a.ig = ig; a.fg = fg; a.cC = carry_C; a.cn = carry_n; a.cm = carry_m;
+    a.oC = out_C; a.on = out_n; a.om = out_m;
+    a.B = s->B; a.H = s->H; a.T = s->T; a.dqk = s->dqk; a.dhv = s->dhv; a.L = eff_L(s); a.NC = num_chunks(s);
+    a.states_only = 1;
+    if (use_tc(s)) return mlstm_fw_tc_launch((cudaStream_t)stream, a, nullptr, nullptr, 0);
+    return mlstm_fw_simt_launch((cudaStream_t)stream, a, s->dtype);
+}
+
 extern "C" int xlstm_mlstm_bw(void* stream, const xlstm_mlstm_shape* s, const void* q, const void* k, const void* v,
                               const float* ig, const float* fg, const float* carry_C, const float* carry_n,
                               const float* carry_m, const void* ytil, const float* msv, const float* psiv,

@@ -74,6 +74,20 @@ def mlstm_fused_fw(qh, kh, vh, igh, fgh, st, carry_in=None, save_states=True, wa
     return MlstmFused(ytil, msv, psiv, qnv, saved, state)
 
 
+def mlstm_final_state(qh, kh, vh, igh, fgh, st, carry_in=None):
+    """The (C, n, m) a fused forward would end in, from the state recurrence alone (no outputs, no record)."""
+    dev = qh.device
+    bh = st.bh()
+    state = (torch.empty((bh, st.dhv, st.dqk), dtype=torch.float32, device=dev),
+             torch.empty((bh, st.dqk), dtype=torch.float32, device=dev),
+             torch.empty((bh,), dtype=torch.float32, device=dev))
+    cC, cn, cm = carry_in if carry_in is not None else (None, None, None)
+    check(lib.xlstm_mlstm_final_state(_stream(), ctypes.byref(st.c), _ptr(qh), _ptr(kh), _ptr(vh), _ptr(igh), _ptr(fgh),
+                                      _ptr(cC), _ptr(cn), _ptr(cm), _ptr(state[0]), _ptr(state[1]), _ptr(state[2])),
+          "mlstm_final_state")
+    return state
+
+
 def mlstm_fused_bw(fused, qh, kh, vh, igh, fgh, d_ytil, st, carry_in=None, dstate_in=None, want_dstate=True):
     """ops::mlstm_fused_bw (src/gpu/ops.rs:4546-4707). dstate_in = (dC, dn) from the call to the right.
     Returns (dq, dk, dv, dig, dfg, (dC, dn))."""

@@ -177,3 +177,23 @@ def test_wide_heads_with_carry_and_recompute():
     got, ref = _run((B, H, T, dqk, dhv), 64, torch.bfloat16, torch.float32, carry=carry, dstate=dstate, save_states=False)
     assert xl._lib.lib.xlstm_device_status() == 0, xl._lib.lib.xlstm_last_error()
     _assert_close(got, ref, 2e-2, FW + BW)
+
+
+@pytest.mark.parametrize("shape,L,dtype", [((2, 2, 70, 8, 12), 16, torch.float32), ((2, 2, 150, 128, 128), 64, torch.bfloat16),
+                                           ((1, 2, 130, 256, 128), 64, torch.bfloat16), ((3, 2, 9, 128, 128), 64, torch.bfloat16)])
+def test_final_state_alone_equals_the_forwards_final_state(shape, L, dtype):
+    """The states-only entry point walks the same recurrence as the forward: bit-identical (C, n, m), with a carry."""
+    from gpu_util import ops, dev, mlstm_inputs, xl
+    B, H, T, dqk, dhv = shape
+    q, k, v, ig, fg, _ = mlstm_inputs(*shape, seed=61, bf16=dtype == torch.bfloat16)
+    r = np.random.default_rng(62)
+    carry = tuple(dev(a) for a in (r.standard_normal((B * H, dhv, dqk)), r.standard_normal((B * H, dqk)), r.standard_normal((B * H,))))
+    st = ops.MlstmShape(B, H, T, dqk, dhv, L, dtype, torch.float32)
+    args = (dev(q, dtype), dev(k, dtype), dev(v, dtype), dev(ig), dev(fg), st)
+    for cin in (None, carry):
+        full = ops.mlstm_fused_fw(*args, carry_in=cin, save_states=False, want_state=True).state
+        alone = ops.mlstm_final_state(*args, carry_in=cin)
+        torch.cuda.synchronize()
+        assert xl._lib.lib.xlstm_device_status() == 0
+        for a, b in zip(alone, full):
+            assert torch.equal(a, b)
