@@ -62,7 +62,10 @@ int xlstm_device_status(void);
  */
 typedef struct {
     int B, H, T, dqk, dhv;
-    int L;          /* chunk length (blocking only: results do not depend on it) */
+    int L;          /* chunk length (blocking only: results do not depend on it). L = 64 with bf16 storage and
+                       dqk, dhv multiples of 128 up to 512 selects the tensor-core kernels, for every T >= 1: a
+                       sequence shorter than a chunk is one ragged chunk. Everything else runs on the CUDA-core
+                       kernels with min(L, T) as the chunk. */
     int dtype;      /* storage of q, k, v, ytil                (MlstmShape + SlabBuf width) */
     int gdtype;     /* storage of d_ytil, dq, dk, dv            (reference: always f32) */
     unsigned flags;
