@@ -164,6 +164,9 @@ def test_training_memorises_a_window():
         m.step(xl.ops.AdamCfg(1e-2, 0.0, t=t))
     assert loss < 0.5 * first, (first, loss)
     assert m.step_count == 60
+    # the data-parallel buckets are built from stage_params(): every parameter exactly once
+    staged = [q for stage in m.stage_params() for q in stage]
+    assert sorted(map(id, staged)) == sorted(map(id, m.params())) and len(set(map(id, staged))) == len(staged)
 
 
 def test_trained_model_reloads_from_its_container_to_the_same_loss(tmp_path):
