@@ -140,15 +140,20 @@ int xlstm_slstm_bw(void* stream, const float* wh, const float* dy, float* g, flo
 
 /* ---- grouped RMSNorm -----------------------------------------------------------------------
  * Replaces ops::rms_norm_forward_into / rms_norm_backward_into (src/gpu/ops.rs:1601-1685).
- * x,y [rows,F] f32; gamma [F]; inv_rms [rows*F/group]. x_hat may be NULL (the backward
- * rebuilds it from x and inv_rms). */
-int xlstm_rmsnorm_fw(void* stream, const float* x, const float* gamma, float* y,
+ * x,y [rows,F]; gamma [F] f32; inv_rms [rows*F/group] f32. x_hat (f32) may be NULL (the backward
+ * rebuilds it from x and inv_rms). x may be stored as bf16 (the mLSTM core's output feeding the
+ * head-wise norm) and y may be written as bf16 where only GEMMs consume it: the casts the reference
+ * launches around the norm (src/gpu/cuda/bf16_cast.cu:22-60) happen inside it. */
+int xlstm_rmsnorm_fw(void* stream, const void* x, int x_dtype, const float* gamma, void* y, int y_dtype,
                      float* inv_rms, float* x_hat, int rows, int F, int group, float eps);
 size_t xlstm_rmsnorm_bw_workspace_bytes(int rows, int F);
-/* dgamma [F] is ACCUMULATED into (+=), by a fixed-order two-stage column sum. */
-int xlstm_rmsnorm_bw(void* stream, const float* dy, const float* x, const float* inv_rms,
-                     const float* gamma, float* dx, float* dgamma, int rows, int F, int group,
-                     void* workspace, size_t workspace_bytes);
+/* dgamma [F] is ACCUMULATED into (+=), by a fixed-order two-stage column sum. dy f32; x at x_dtype;
+ * dx at dx_dtype. residual (f32 [rows,F], or NULL) is added to dx: the gradient that reaches the same
+ * tensor through the block's skip connection (the reference adds it with a pass of its own,
+ * src/gpu/block.rs:856-909). */
+int xlstm_rmsnorm_bw(void* stream, const float* dy, const void* x, int x_dtype, const float* inv_rms,
+                     const float* gamma, const float* residual, void* dx, int dx_dtype, float* dgamma,
+                     int rows, int F, int group, void* workspace, size_t workspace_bytes);
 
 /* ---- softmax cross-entropy, forward + backward in one pass ---------------------------------
  * Replaces ops::softmax_cross_entropy and masked_softmax_ce_u32_into (src/gpu/ops.rs:
@@ -193,8 +198,10 @@ int xlstm_swiglu_fw(void* stream, const float* gate_pre, const float* value, con
 int xlstm_swiglu_bw(void* stream, const float* d_mixed, const float* gate_pre, const float* value,
                     const float* bias_gate, const float* bias_value, int cols, void* d_gate, void* d_value,
                     int out_dtype, size_t n);
-/* o <- sigmoid(o) in place; hc = o * yhat */
-int xlstm_ogate_fw(void* stream, float* o, const float* yhat, void* hc, int out_dtype, size_t n);
+/* o <- sigmoid(o + bias) in place; hc = o * yhat. bias ([cols], or NULL) is the output-gate projection's
+ * bias, folded in here like the SwiGLU biases above. */
+int xlstm_ogate_fw(void* stream, float* o, const float* yhat, const float* bias, int cols, void* hc, int out_dtype,
+                   size_t n);
 /* do_pre = d_hc * yhat * o * (1 - o) with o the activated gate; d_yhat = d_hc * o (fp32) */
 int xlstm_ogate_bw(void* stream, const float* d_hc, const float* o, const float* yhat, void* do_pre,
                    int out_dtype, float* d_yhat, size_t n);
@@ -202,6 +209,17 @@ int xlstm_ogate_bw(void* stream, const float* d_hc, const float* o, const float*
  * operands of an fp32-accurate product run as six bf16 tensor-core GEMMs (the fp32 head of gpu::Lm,
  * src/gpu/lm.rs:84-163, which the reference runs as a cublasSgemm). No reference counterpart. */
 int xlstm_split3_bf16(void* stream, const float* x, void* hi, void* mid, void* lo, size_t n);
+
+/* Bias gradient of a projection, with the narrowing of the same tensor for the two weight-side GEMMs folded in
+ * (replaces add_col_sum, src/gpu/cuda/common.cu:49-124, and a cast, src/gpu/cuda/bf16_cast.cu:22-60):
+ * acc[c] += scale * sum_r x[r][c] (fixed summation order, no float atomics); if out_bf16 is not NULL,
+ * out_bf16[r][c] = bf16(scale * x[r][c]). x [rows, cols] at x_dtype. */
+size_t xlstm_colsum_workspace_bytes(int rows, int cols);
+int xlstm_colsum_narrow(void* stream, const void* x, int x_dtype, int rows, int cols, float scale, void* out_bf16,
+                        float* acc, void* workspace, size_t workspace_bytes);
+/* out[r][c] = bias[c] (+ residual[r][c] when given): the seed a projection's GEMM accumulates into with beta = 1
+ * (broadcast_row / broadcast_row_resid, src/gpu/cuda/common.cu:20-48). f32, [rows, cols]. */
+int xlstm_bias_rows(void* stream, const float* residual, const float* bias, float* out, int rows, int cols);
 
 /* Embedding backward without float atomics (replaces embedding_scatter_add / embedding_scatter_merge,
  * src/gpu/cuda/common.cu:127-168): table_g[id] += sum of the rows d[pos] with ids[pos] == id, in ascending
@@ -229,6 +247,31 @@ typedef struct {
 
 int xlstm_adamw_multi(void* stream, const xlstm_adamw_desc* descs, int n, float lr,
                       float beta1, float beta2, float eps, float bc1, float bc2, int zero_grad);
+
+/* ---- data-parallel gradient buckets over NCCL --------------------------------------------------
+ * No counterpart in the reference, which trains on one GPU (src/gpu/mod.rs:134); this is what a host
+ * that runs one replica per GPU calls around its backward pass and in front of AdamwQueue::flush
+ * (src/gpu/hierarchical.rs:1696-1746). Gradients live in flat fp32 buckets the caller owns. NCCL is
+ * bound at run time (libnccl.so.2; a copy the process already holds is reused). State is per device:
+ * make the device current first, and keep the calls for one device on one host thread.
+ *   xlstm_dp_unique_id:  rank 0 obtains the 128-byte id and hands it to every rank (any host channel).
+ *   xlstm_dp_init:       collective over the ranks; creates the communicator for the current device.
+ *   xlstm_dp_init_comm:  adopt a communicator (ncclComm_t) the host already has; never destroyed here.
+ *   xlstm_dp_bucket_register: returns the bucket's index (>= 0) or a negative error.
+ *   xlstm_dp_bucket_start: call when everything enqueued on producer_stream so far has written the
+ *       bucket; a SUM all-reduce (in place, fp32) is ordered behind that point on a library-owned
+ *       high-priority stream and runs while producer_stream carries on with the layers below.
+ *   xlstm_dp_wait:       `stream` waits for every reduction started since the last wait.
+ * With the loss scaled by 1 / (rows * ranks) on every rank the summed gradient is the gradient of the
+ * global mean loss. Plain NCCL collectives only. */
+int xlstm_dp_unique_id(void* out128);
+int xlstm_dp_init(int nranks, int rank, const void* unique_id128);
+int xlstm_dp_init_comm(void* nccl_comm);
+int xlstm_dp_world(void); /* ranks of the current device's communicator, 0 if none */
+int xlstm_dp_bucket_register(float* grads, size_t n);
+int xlstm_dp_bucket_start(int index, void* producer_stream);
+int xlstm_dp_wait(void* stream);
+int xlstm_dp_shutdown(void);
 
 #ifdef __cplusplus
 }

@@ -49,20 +49,31 @@ SIGNATURES = {
     "xlstm_mlstm_bw": (_i, [_vp, _shape_p] + [_vp] * 24 + [_sz]),
     "xlstm_slstm_fw": (_i, [_vp] * 9 + [ctypes.POINTER(SlstmSlabs), _i, _i, _i, _i, _i, _u]),
     "xlstm_slstm_bw": (_i, [_vp] * 7 + [ctypes.POINTER(SlstmSlabs), _i, _i, _i, _i, _i, _u]),
-    "xlstm_rmsnorm_fw": (_i, [_vp] * 6 + [_i, _i, _i, _f]),
+    "xlstm_rmsnorm_fw": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _f]),
     "xlstm_rmsnorm_bw_workspace_bytes": (_sz, [_i, _i]),
-    "xlstm_rmsnorm_bw": (_i, [_vp] * 7 + [_i, _i, _i, _vp, _sz]),
+    "xlstm_rmsnorm_bw": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _sz]),
     "xlstm_ce_workspace_bytes": (_sz, [_i]),
     "xlstm_ce_fw_bw": (_i, [_vp] * 6 + [_i, _i, _f, _vp, _sz]),
     "xlstm_ce_fw_bw_noalloc": (_i, [_vp] * 6 + [_i, _i, _f]),
     "xlstm_softcap_ce_fw_bw": (_i, [_vp] * 6 + [_i, _i, _f, _f, _vp, _sz]),
     "xlstm_swiglu_fw": (_i, [_vp] * 5 + [_i, _vp, _i, _sz]),
     "xlstm_swiglu_bw": (_i, [_vp] * 6 + [_i, _vp, _vp, _i, _sz]),
-    "xlstm_ogate_fw": (_i, [_vp] * 4 + [_i, _sz]),
+    "xlstm_ogate_fw": (_i, [_vp] * 4 + [_i, _vp, _i, _sz]),
     "xlstm_ogate_bw": (_i, [_vp] * 5 + [_i, _vp, _sz]),
+    "xlstm_colsum_workspace_bytes": (_sz, [_i, _i]),
+    "xlstm_colsum_narrow": (_i, [_vp, _vp, _i, _i, _i, _f, _vp, _vp, _vp, _sz]),
+    "xlstm_bias_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i]),
     "xlstm_embedding_scatter_add": (_i, [_vp] * 5 + [_i, _i]),
     "xlstm_split3_bf16": (_i, [_vp] * 5 + [_sz]),
     "xlstm_adamw_multi": (_i, [_vp, ctypes.POINTER(AdamwDesc), _i, _f, _f, _f, _f, _f, _f, _i]),
+    "xlstm_dp_unique_id": (_i, [_vp]),
+    "xlstm_dp_init": (_i, [_i, _i, _vp]),
+    "xlstm_dp_init_comm": (_i, [_vp]),
+    "xlstm_dp_world": (_i, []),
+    "xlstm_dp_bucket_register": (_i, [_vp, _sz]),
+    "xlstm_dp_bucket_start": (_i, [_i, _vp]),
+    "xlstm_dp_wait": (_i, [_vp]),
+    "xlstm_dp_shutdown": (_i, []),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

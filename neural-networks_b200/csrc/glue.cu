@@ -118,14 +118,15 @@ __global__ void __launch_bounds__(256) swiglu_bw_k(const float* __restrict__ d, 
     }
 }
 
-// o <- sigmoid(o) in place (kept for the backward), hc = o * yhat
+// o <- sigmoid(o + bias) in place (kept for the backward), hc = o * yhat
 template <typename OT>
-__global__ void __launch_bounds__(256) ogate_fw_k(float* __restrict__ o, const float* __restrict__ yhat, OT* __restrict__ hc,
-                                                  size_t n, int vec) {
+__global__ void __launch_bounds__(256) ogate_fw_k(float* __restrict__ o, const float* __restrict__ yhat,
+                                                  const float* __restrict__ bias, int cols, OT* __restrict__ hc, size_t n, int vec) {
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (vec) {
         const size_t n4 = n / 4, i0 = (size_t)blockIdx.x * (256 * kUnroll) + threadIdx.x;
         float4 a[kUnroll], y[kUnroll];
+        const unsigned col0 = (unsigned)((4 * i0) % (size_t)cols);
 #pragma unroll
         for (int k = 0; k < kUnroll; ++k) {
             const size_t j = i0 + 256 * k;
@@ -135,14 +136,14 @@ __global__ void __launch_bounds__(256) ogate_fw_k(float* __restrict__ o, const f
         for (int k = 0; k < kUnroll; ++k) {
             const size_t j = i0 + 256 * k;
             if (j >= n4) continue;
-            float4 t = a[k];
+            float4 t = add4(a[k], bias4(bias, col_of(col0, k, cols)));
             t.x = stable_sigmoid(t.x); t.y = stable_sigmoid(t.y); t.z = stable_sigmoid(t.z); t.w = stable_sigmoid(t.w);
             reinterpret_cast<float4*>(o)[j] = t;
             st4(hc, j, make_float4(t.x * y[k].x, t.y * y[k].y, t.z * y[k].z, t.w * y[k].w));
         }
     } else {
         if (i >= n) return;
-        const float a = stable_sigmoid(o[i]);
+        const float a = stable_sigmoid(o[i] + bias1(bias, i, cols));
         o[i] = a;
         st1(hc, i, a * yhat[i]);
     }
@@ -234,6 +235,106 @@ __global__ void __launch_bounds__(256) split3_k(const float* __restrict__ x, bf1
     }
 }
 
+// ---- column sums (bias gradients) with the narrowing of the same tensor folded in -------------------------------
+// partial[part][c] = sum over the part's rows of x[r][c]; out[r][c] = bf16(scale * x[r][c]) when asked for.
+// A CTA covers 128 columns (32 threads x 4) and eight row lanes; the lanes are combined in lane order and the
+// parts in part order by the merge kernel: fixed summation order, no float atomics (the reference's add_col_sum is
+// deterministic the same way, src/gpu/cuda/common.cu:49-124).
+__device__ __forceinline__ float4 ld4(const bf16* p, size_t i4) {
+    const uint2 u = __ldcs(reinterpret_cast<const uint2*>(p) + i4);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_narrow_k(const T* __restrict__ x, bf16* __restrict__ out, float* __restrict__ partial,
+                                                       int rows, int cols, float scale, int rows_per_part) {
+    __shared__ float4 sacc[8][32];
+    const int cq = threadIdx.x & 31, rl = threadIdx.x >> 5;
+    const int c0 = blockIdx.x * 128 + 4 * cq;
+    const int r0 = blockIdx.y * rows_per_part, r1 = min(rows, r0 + rows_per_part);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c0 < cols) {
+        const size_t c4 = (size_t)c0 / 4, row4 = (size_t)cols / 4;
+        int r = r0 + rl;
+        for (; r + 8 < r1; r += 16) {  // two rows in flight
+            const float4 v0 = ld4(x, (size_t)r * row4 + c4), v1 = ld4(x, (size_t)(r + 8) * row4 + c4);
+            acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
+            acc.x += v1.x; acc.y += v1.y; acc.z += v1.z; acc.w += v1.w;
+            if (out) {
+                st4(out, (size_t)r * row4 + c4, make_float4(v0.x * scale, v0.y * scale, v0.z * scale, v0.w * scale));
+                st4(out, (size_t)(r + 8) * row4 + c4, make_float4(v1.x * scale, v1.y * scale, v1.z * scale, v1.w * scale));
+            }
+        }
+        for (; r < r1; r += 8) {
+            const float4 v0 = ld4(x, (size_t)r * row4 + c4);
+            acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
+            if (out) st4(out, (size_t)r * row4 + c4, make_float4(v0.x * scale, v0.y * scale, v0.z * scale, v0.w * scale));
+        }
+    }
+    sacc[rl][cq] = acc;
+    __syncthreads();
+    if (threadIdx.x < 32 && c0 < cols) {
+        float4 t = sacc[0][cq];
+#pragma unroll
+        for (int l = 1; l < 8; ++l) { const float4 u = sacc[l][cq]; t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w; }
+        *reinterpret_cast<float4*>(partial + (size_t)blockIdx.y * cols + c0) = make_float4(t.x * scale, t.y * scale, t.z * scale, t.w * scale);
+    }
+}
+// any width / alignment: one thread per column
+template <typename T>
+__global__ void __launch_bounds__(128) colsum_narrow_gen_k(const T* __restrict__ x, bf16* __restrict__ out, float* __restrict__ partial,
+                                                           int rows, int cols, float scale, int rows_per_part) {
+    const int c = blockIdx.x * 128 + threadIdx.x;
+    if (c >= cols) return;
+    const int r0 = blockIdx.y * rows_per_part, r1 = min(rows, r0 + rows_per_part);
+    float acc = 0.f;
+    for (int r = r0; r < r1; ++r) {
+        const float v = ldf(x, (size_t)r * cols + c);
+        acc += v;
+        if (out) out[(size_t)r * cols + c] = __float2bfloat16_rn(v * scale);
+    }
+    partial[(size_t)blockIdx.y * cols + c] = acc * scale;
+}
+__global__ void colsum_parts_merge_k(const float* __restrict__ partial, float* __restrict__ acc, int nparts, int cols) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float s = 0.f;
+    for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * cols + c];
+    acc[c] += s;
+}
+static int colsum_parts(int rows, int cols) {
+    const int tiles = (cols + 127) / 128;
+    int want = (sm_count() * 4 + tiles - 1) / tiles;
+    const int maxp = (rows + 15) / 16;
+    if (want > maxp) want = maxp;
+    return want < 1 ? 1 : want;
+}
+
+// out[r][c] = (residual ? residual[r][c] : 0) + bias[c]: the seed a GEMM with beta = 1 accumulates into
+// (broadcast_row / broadcast_row_resid, src/gpu/cuda/common.cu:20-48).
+__global__ void __launch_bounds__(256) bias_rows_k(const float* __restrict__ residual, const float* __restrict__ bias,
+                                                   float* __restrict__ out, size_t n, int cols, int vec) {
+    if (vec) {
+        const size_t n4 = n / 4, i0 = (size_t)blockIdx.x * (256 * kUnroll) + threadIdx.x;
+        float4 r[kUnroll];
+        const unsigned col0 = (unsigned)((4 * i0) % (size_t)cols);
+#pragma unroll
+        for (int k = 0; k < kUnroll; ++k) {
+            const size_t j = i0 + 256 * k;
+            r[k] = (residual && j < n4) ? ld4(residual, j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int k = 0; k < kUnroll; ++k) {
+            const size_t j = i0 + 256 * k;
+            if (j < n4) reinterpret_cast<float4*>(out)[j] = add4(r[k], bias4(bias, col_of(col0, k, cols)));
+        }
+    } else {
+        const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+        if (i < n) out[i] = (residual ? residual[i] : 0.f) + bias[i % (size_t)cols];
+    }
+}
+
 static inline int can_vec(size_t n, std::initializer_list<const void*> ptrs) {
     if (n % 4) return 0;
     for (const void* p : ptrs)
@@ -294,13 +395,16 @@ extern "C" int xlstm_swiglu_bw(void* stream, const float* d_mixed, const float* 
     return XLSTM_OK;
 }
 
-extern "C" int xlstm_ogate_fw(void* stream, float* o, const float* yhat, void* hc, int out_dtype, size_t n) {
+extern "C" int xlstm_ogate_fw(void* stream, float* o, const float* yhat, const float* bias, int cols, void* hc, int out_dtype,
+                              size_t n) {
     XL_CHECK_ARG(o && yhat && hc, "ogate_fw: null pointer");
+    XL_CHECK_ARG(!bias || (cols > 0 && n % (size_t)cols == 0), "ogate_fw: a bias needs cols > 0 dividing n");
     GLUE_CHECK("ogate_fw")
     cudaStream_t st = (cudaStream_t)stream;
-    const int vec = can_vec(n, {o, yhat, hc});
-    if (out_dtype == XLSTM_BF16) ogate_fw_k<bf16><<<blocks_for(n, vec), 256, 0, st>>>(o, yhat, (bf16*)hc, n, vec);
-    else ogate_fw_k<float><<<blocks_for(n, vec), 256, 0, st>>>(o, yhat, (float*)hc, n, vec);
+    const int vec = can_vec(n, {o, yhat, hc}) && bias_vec_ok(bias, nullptr, cols);
+    if (cols <= 0) cols = 1;
+    if (out_dtype == XLSTM_BF16) ogate_fw_k<bf16><<<blocks_for(n, vec), 256, 0, st>>>(o, yhat, bias, cols, (bf16*)hc, n, vec);
+    else ogate_fw_k<float><<<blocks_for(n, vec), 256, 0, st>>>(o, yhat, bias, cols, (float*)hc, n, vec);
     XL_LAUNCH_OK("ogate_fw");
     return XLSTM_OK;
 }
@@ -333,5 +437,52 @@ extern "C" int xlstm_split3_bf16(void* stream, const float* x, void* hi, void* m
     const int vec = can_vec(n, {x}) && !(((uintptr_t)hi | (uintptr_t)mid | (uintptr_t)lo) & 7);
     split3_k<<<blocks_for(n, vec), 256, 0, (cudaStream_t)stream>>>(x, (bf16*)hi, (bf16*)mid, (bf16*)lo, n, vec);
     XL_LAUNCH_OK("split3_bf16");
+    return XLSTM_OK;
+}
+
+extern "C" size_t xlstm_colsum_workspace_bytes(int rows, int cols) {
+    if (rows <= 0 || cols <= 0) return 0;
+    return (size_t)colsum_parts(rows, cols) * cols * sizeof(float);
+}
+
+extern "C" int xlstm_colsum_narrow(void* stream, const void* x, int x_dtype, int rows, int cols, float scale, void* out_bf16,
+                                   float* acc, void* workspace, size_t workspace_bytes) {
+    XL_CHECK_ARG(x && acc, "colsum_narrow: null pointer");
+    XL_CHECK_ARG(rows >= 0 && cols > 0, "colsum_narrow: bad shape %d x %d", rows, cols);
+    XL_CHECK_ARG(x_dtype == XLSTM_F32 || x_dtype == XLSTM_BF16, "colsum_narrow: unknown storage type");
+    if (rows == 0) return XLSTM_OK;
+    const size_t need = xlstm_colsum_workspace_bytes(rows, cols);
+    if (!workspace || workspace_bytes < need) {
+        set_error("colsum_narrow: workspace of %zu B is smaller than the %zu B required", workspace_bytes, need);
+        return XLSTM_ERR_WORKSPACE;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    float* partial = (float*)workspace;
+    int nparts = colsum_parts(rows, cols);
+    const int rpp = (rows + nparts - 1) / nparts;
+    nparts = (rows + rpp - 1) / rpp;
+    const bool vec = cols % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)out_bf16 & 7) && !((uintptr_t)partial & 15);
+    const dim3 grid((cols + 127) / 128, nparts);
+    if (vec) {
+        if (x_dtype == XLSTM_F32) colsum_narrow_k<float><<<grid, 256, 0, st>>>((const float*)x, (bf16*)out_bf16, partial, rows, cols, scale, rpp);
+        else colsum_narrow_k<bf16><<<grid, 256, 0, st>>>((const bf16*)x, (bf16*)out_bf16, partial, rows, cols, scale, rpp);
+    } else {
+        if (x_dtype == XLSTM_F32) colsum_narrow_gen_k<float><<<grid, 128, 0, st>>>((const float*)x, (bf16*)out_bf16, partial, rows, cols, scale, rpp);
+        else colsum_narrow_gen_k<bf16><<<grid, 128, 0, st>>>((const bf16*)x, (bf16*)out_bf16, partial, rows, cols, scale, rpp);
+    }
+    XL_LAUNCH_OK("colsum_narrow");
+    colsum_parts_merge_k<<<(cols + 127) / 128, 128, 0, st>>>(partial, acc, nparts, cols);
+    XL_LAUNCH_OK("colsum_parts_merge");
+    return XLSTM_OK;
+}
+
+extern "C" int xlstm_bias_rows(void* stream, const float* residual, const float* bias, float* out, int rows, int cols) {
+    XL_CHECK_ARG(bias && out, "bias_rows: null pointer");
+    XL_CHECK_ARG(rows >= 0 && cols > 0, "bias_rows: bad shape %d x %d", rows, cols);
+    const size_t n = (size_t)rows * cols;
+    if (n == 0) return XLSTM_OK;
+    const int vec = can_vec(n, {residual, out}) && bias_vec_ok(bias, nullptr, cols);
+    bias_rows_k<<<blocks_for(n, vec), 256, 0, (cudaStream_t)stream>>>(residual, bias, out, n, cols, vec);
+    XL_LAUNCH_OK("bias_rows");
     return XLSTM_OK;
 }

@@ -57,9 +57,6 @@ bool tc_make_map2(CUtensorMap* m, const void* base, uint64_t rows, int W, int bo
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-static long long* g_prof = nullptr;
-extern "C" void xlstm_debug_set_prof(void* p) { g_prof = (long long*)p; }
-long long* tc_debug_prof() { return g_prof; }
 int* tc_status_ptr() {
     // resolved once per device: the lookup is a driver call, too slow for every launch
     static std::atomic<int*> cached[64];

@@ -874,11 +874,14 @@ size_t mlstm_tc_bw_workspace_bytes(int B, int H, int T, int dqk, int dhv) {
 template <typename GT, typename OT, bool WIDE>
 static int bw_launch_kernel(cudaStream_t st, const bw::Params& p, int ctas) {
     using namespace bw;
-    static bool attr_set = false;  // one flag per instantiation
+    // the opt-in to large dynamic shared memory is a per-device function attribute: one flag per device and instantiation
+    static std::atomic<bool> attr_set[64];
     const size_t smem = Smem::total + 1024;
-    if (!attr_set) {
+    int dev = 0;
+    XL_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
         XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<GT, OT, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set = true;
+        if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
     mlstm_bw_tc<GT, OT, WIDE><<<ctas, kThreads, smem, st>>>(p);
     XL_LAUNCH_OK("mlstm_bw_tc");

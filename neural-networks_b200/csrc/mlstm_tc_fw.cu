@@ -23,7 +23,6 @@ namespace xl {
 using namespace tc;
 
 int* tc_status_ptr();
-long long* tc_debug_prof();
 bool tc_make_map3(CUtensorMap* m, const void* base, int B, int T, int W);
 bool tc_make_map2(CUtensorMap* m, const void* base, uint64_t rows, int W, int box_rows);
 
@@ -558,12 +557,15 @@ int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved, void*
     p.states_only = a.states_only;
     p.status = tc_status_ptr();
     if (!p.status) { set_error("mlstm_fw: cannot resolve the device status word"); return XLSTM_ERR_CUDA; }
-    static bool attr_set = false;
+    // the opt-in to large dynamic shared memory is a per-device function attribute: one flag per device
+    static std::atomic<bool> attr_set[64];
     const size_t smem = Smem::total + 1024;
-    if (!attr_set) {
+    int dev = 0;
+    XL_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
         XL_CUDA(cudaFuncSetAttribute(mlstm_fw_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         XL_CUDA(cudaFuncSetAttribute(mlstm_fw_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set = true;
+        if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
     if (nsub == 1) mlstm_fw_tc<false><<<a.B * a.H, kThreads, smem, st>>>(p);
     else mlstm_fw_tc<true><<<a.B * a.H * nsub, kThreads, smem, st>>>(p);

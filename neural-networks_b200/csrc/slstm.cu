@@ -51,7 +51,6 @@ struct SlstmArgs {
     int CS, UPC;               // cluster size, units per CTA
     int KS;                    // k-slices of the mat-vec
     int CPT;                   // output columns per thread in the mat-vec (4 or 2)
-    long long* prof;           // development aid (profiling builds only)
     unsigned epoch;            // launch number, part of the tags of the grid kernels' flagged exchange
 };
 
@@ -218,14 +217,7 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
         for (int q = 0; q < 4; ++q)
             bias[p][q] = (it < NI) ? a.bcat[q * H + hd * dhd + cr * UPC + it % UPC] : 0.f;
     }
-#ifdef XL_TC_PROFILE
-    long long tprev = clock64(), pacc[6] = {0, 0, 0, 0, 0, 0};
-#define SPROF(i) { long long tn = clock64(); pacc[i] += tn - tprev; tprev = tn; }
-#else
-#define SPROF(i)
-#endif
     for (int t = 0; t < T; ++t) {
-        SPROF(0)
         // issue this step's global reads early; they land while the mat-vec runs
         float gpre[kPF][4];
 #pragma unroll
@@ -240,7 +232,6 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
                 }
             }
         }
-        SPROF(1)
         // this CTA's own previous h (a saved record), read before peers may overwrite the buffer
         float hprev[kPF];
 #pragma unroll
@@ -251,9 +242,7 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
         if (a.CPT == 4) matvec<BG, 4>(Ws, xin, part, K, NOUTp, a.KS);
         else matvec<BG, 2>(Ws, xin, part, K, NOUTp, a.KS);
         if (NI <= kPF * kThreads) cluster_arrive();  // done reading the exchange buffer
-        SPROF(2)
         __syncthreads();
-        SPROF(3)
         auto cell = [&](int it, const float* gin, const float* bs, float hp) {
             const int b = it / UPC, ul = it % UPC;
             float hh = 0.f;
@@ -307,20 +296,13 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_cluster(SlstmArgs a, SlstmS
             for (int q = 0; q < 4; ++q) bs[q] = a.bcat[q * H + hd * dhd + cr * UPC + ul];
             cell(it, gin, bs, xin[(size_t)(cr * UPC + ul) * BG + b]);
         }
-        SPROF(4)
         __syncthreads();
         if (NI > kPF * kThreads) cluster_arrive();  // wide CTAs read their previous h inside the cell
         cluster_wait();                               // every CTA is done reading: the buffer may be overwritten
         broadcast<BG>(cluster, stage, xin, CS, UPC, 1, UPC, 0, cr * UPC);
-        SPROF(5)
         cluster_arrive();
         cluster_wait();                               // the new h of the whole head is visible
     }
-#ifdef XL_TC_PROFILE
-    if (blockIdx.x == 0 && tid == 0 && a.prof)
-        for (int i = 0; i < 6; ++i) a.prof[i] = pacc[i];
-#endif
-#undef SPROF
     // final state
     for (int it = tid; it < NI; it += kThreads) {
         int b = it / UPC, ul = it % UPC;
@@ -1003,8 +985,12 @@ static int coresident_any(int BG, bool bwd, const Geo& g, int* out) {
     }
 }
 
-long long* tc_debug_prof();
 int* tc_status_ptr();
+
+// Launch counter of the flagged exchange, one per device and shared by every instantiation of the grid kernels
+// (they all tag words in the one exchange array). Twelve bits of it go into the tags; when they wrap, the array
+// is cleared first, so a word left by an earlier launch can never carry the tag a later launch polls for.
+static unsigned g_ll_epoch[64];
 
 struct GridGeo {
     int BG, G, UPC, KS, CPT;
@@ -1046,7 +1032,6 @@ static int launch_grid(cudaStream_t st, bool bwd, SlstmArgs a, const GridGeo& g)
     static std::atomic<unsigned long long> key_of[2][64];
     static GridSync* sync_of[64];
     static uint2* ll_of[64];
-    static unsigned epoch_of[64];
     int dev = 0;
     XL_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) dev = 0;
@@ -1077,7 +1062,12 @@ static int launch_grid(cudaStream_t st, bool bwd, SlstmArgs a, const GridGeo& g)
     int* status = tc_status_ptr();
     if (!status) return XLSTM_ERR_CUDA;
     uint2* ll = ll_of[dev];
-    a.epoch = (++epoch_of[dev]) & 0xfffu;
+    unsigned epoch = ++g_ll_epoch[dev];
+    if ((epoch & 0xfffu) == 0) {
+        XL_CUDA(cudaMemsetAsync(ll, 0, sizeof(g_slstm_ll), st));
+        epoch = ++g_ll_epoch[dev];
+    }
+    a.epoch = epoch & 0xfffu;
     void* args[5] = {&a, &lay, &gs, &status, &ll};
     XL_CUDA(cudaLaunchCooperativeKernel(kern, dim3((unsigned)grid), dim3(kThreads), args, g.lay.total, st));
     count_launch();
@@ -1194,7 +1184,6 @@ static int run_grid(cudaStream_t st, bool bwd, const SlstmArgs& a) {
 // it (12, 16) while the clusters it needs exceed what can be resident at once: a second wave of
 // clusters doubles the time of a latency-bound loop, a wider batch group costs far less.
 static int run(cudaStream_t st, bool bwd, SlstmArgs a) {
-    a.prof = tc_debug_prof();
     const int cand[6] = {1, 2, 4, 8, 12, 16};
     int first = 0;
     for (int i = 3; i >= 0; --i)

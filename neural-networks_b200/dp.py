@@ -9,16 +9,28 @@ blocks below it are still computing. With the loss scaled by 1 / (rows * world) 
 summed gradient is the gradient of the global mean loss, so N ranks reproduce one rank on the
 concatenated batch.
 
-Works on any torch.distributed backend (NCCL on GPUs; gloo in the CPU tests of the bucket logic).
+On GPUs the buckets go through the library's own entry points (xlstm_dp_*, include/xlstm_b200.h): the
+communicator is created inside libxlstm_b200.so from a unique id that rank 0 hands out over torch.distributed,
+each bucket's all-reduce is ordered behind the backward pass on the library's side stream, and the optimizer's
+stream waits for them before AdamW. On CPU tensors (the gloo tests of the bucket logic) the same class issues
+torch.distributed all-reduces.
 """
+import importlib
+
 import torch
 import torch.distributed as dist
 
 
+def _native_lib():
+    return importlib.import_module("neural-networks_b200")._lib
+
+
 class GradBuckets:
-    def __init__(self, groups, group=None):
+    def __init__(self, groups, group=None, native=None):
         """`groups`: list of lists of objects with `.w` (parameter) and `.g` (gradient) tensors. The
-        gradients are re-homed into one flat buffer per group; `.g` becomes a view into it."""
+        gradients are re-homed into one flat buffer per group; `.g` becomes a view into it.
+        `native`: reduce through xlstm_dp_* (default: whenever the gradients are CUDA tensors, the default
+        process group is NCCL and there is more than one rank)."""
         self.pg = group
         self.flat = []
         self.handles = []
@@ -37,6 +49,39 @@ class GradBuckets:
                 p.g = view
                 off += k
             self.flat.append(buf)
+        on_gpu = any(b is not None and b.is_cuda for b in self.flat)
+        if native is None:
+            native = on_gpu and group is None and self.world() > 1 and dist.get_backend() == "nccl"
+        self.native = bool(native)
+        self.index = [None] * len(self.flat)
+        self.exposed = None  # (event before, event after) of the last wait(), when `time_wait` is set
+        self.time_wait = False
+        if self.native:
+            self._init_native()
+
+    def _init_native(self):
+        L = _native_lib()
+        lib = L.lib
+        world, rank = self.world(), dist.get_rank()
+        if lib.xlstm_dp_world() == 0:
+            uid = torch.zeros(128, dtype=torch.uint8)
+            if rank == 0:
+                L.check(lib.xlstm_dp_unique_id(uid.data_ptr()), "dp_unique_id")
+            dev = uid.cuda()
+            dist.broadcast(dev, src=0)
+            uid = dev.cpu()
+            L.check(lib.xlstm_dp_init(world, rank, uid.data_ptr()), "dp_init")
+        elif lib.xlstm_dp_world() != world:
+            raise L.XlstmError("xlstm_dp: the library's communicator has %d ranks, the process group %d" % (lib.xlstm_dp_world(), world))
+        for i, buf in enumerate(self.flat):
+            if buf is None:
+                continue
+            if buf.dtype != torch.float32:
+                raise L.XlstmError("xlstm_dp buckets are fp32")
+            idx = lib.xlstm_dp_bucket_register(buf.data_ptr(), buf.numel())
+            if idx < 0:
+                L.check(idx, "dp_bucket_register")
+            self.index[i] = idx
 
     def world(self):
         return dist.get_world_size(self.pg) if dist.is_available() and dist.is_initialized() else 1
@@ -45,13 +90,34 @@ class GradBuckets:
         """Start the SUM all-reduce of bucket i (call when its gradients are complete)."""
         if self.world() == 1 or self.flat[i] is None:
             return
+        if self.native:
+            L = _native_lib()
+            L.check(L.lib.xlstm_dp_bucket_start(self.index[i], torch.cuda.current_stream().cuda_stream), "dp_bucket_start")
+            return
         self.handles.append(dist.all_reduce(self.flat[i], op=dist.ReduceOp.SUM, group=self.pg, async_op=True))
 
     def wait(self):
-        """Block the current stream until every started reduction has finished."""
+        """Make the current stream wait until every started reduction has finished."""
+        timed = self.time_wait and any(b is not None and b.is_cuda for b in self.flat)
+        if timed:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        if self.native and self.world() > 1:
+            L = _native_lib()
+            L.check(L.lib.xlstm_dp_wait(torch.cuda.current_stream().cuda_stream), "dp_wait")
         for h in self.handles:
             h.wait()
         self.handles = []
+        if timed:
+            e1.record()
+            self.exposed = (e0, e1)
+
+    def exposed_ms(self):
+        """Device time the stream spent stalled in the last wait() (needs `time_wait`; synchronises)."""
+        if self.exposed is None:
+            return 0.0
+        self.exposed[1].synchronize()
+        return self.exposed[0].elapsed_time(self.exposed[1])
 
 
 def attach(lm, group=None):
@@ -71,6 +137,9 @@ def train_step(lm, buckets, ids, targets, B, T, cfg):
     loss = lm.forward_backward(ids, targets, B, T, inv=1.0 / (B * T * world))
     buckets.reduce_async(len(lm.blocks))
     buckets.wait()
+    if getattr(lm, "check_status", False):  # waits for the backward pass; raises before the update is applied
+        from . import ops
+        ops.device_status_check()
     lm.step(cfg)
     return loss
 
@@ -96,7 +165,10 @@ def attach_hier(model, group=None):
 def train_step_hier(model, buckets, windows, cfg, word_loss=None):
     """One data-parallel step of the hierarchical model: every rank its own windows, gradients summed, identical
     AdamW everywhere. Returns this rank's share of the global mean loss."""
-    loss = model.forward_backward(windows, word_loss)
+    loss = model.forward_backward(windows, word_loss)  # reads the loss back: the backward pass has finished
     buckets.wait()
+    if getattr(model, "check_status", False):
+        from . import ops
+        ops.device_status_check()
     model.step(cfg)
     return loss

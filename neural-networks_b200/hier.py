@@ -148,6 +148,7 @@ class Hierarchical:
         # encoder's (and the table's) gradients are complete; `rows_of_all_ranks(valid)` returns the call's valid
         # decoder rows summed over the ranks, the loss normaliser of the global batch
         self.on_stage_backward = None
+        self.check_status = True  # a step raises, before AdamW, if a kernel gave up on a bounded device-side wait
         self.rows_of_all_ranks = None
 
     def stage_params(self):

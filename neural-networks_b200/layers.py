@@ -8,8 +8,10 @@ Plain projections are library GEMMs (torch.matmul -> cuBLAS/cuBLASLt), as they a
 reference (src/gpu/ops.rs:186-441). Parameters of record are fp32; with `bf16=True` GEMM operands
 are narrowed to bf16 (the per-layer bf16 weight shadow is written by the AdamW kernel in the same
 pass that updates the weight, so it can never go stale) and q/k/v are stored as bf16.
-Element-wise glue between the ops (gate activations, residual adds, embedding gather/scatter,
-soft-cap) is expressed with torch tensor ops.
+In bf16 mode the element-wise glue between the GEMMs runs in the library too (SwiGLU, output gate, bias
+gradients fused with the narrowing of the same tensor, residual gradients inside the norm's backward, bias +
+residual seeds of the output GEMMs); what is left to torch tensor ops is the embedding gather, the sort in
+front of the embedding scatter, and the fp32 reference mode of the small parity models.
 """
 import copy
 import math
@@ -82,28 +84,39 @@ class Linear:
             return torch.addmm(self.b.w.to(torch.bfloat16), self.x, w, beta=scale, alpha=scale)
         assert scale == 1.0, "scale is folded only into the narrowed epilogue"
         if residual is not None:
-            out = torch.add(residual, self.b.w)
+            out = ops.bias_rows(self.b.w, residual.shape[0], residual)
             if self.bf16:
                 return torch.addmm(out, self.x, w, out_dtype=torch.float32, out=out)
             return out.addmm_(self.x, w)
         y = _mm(self.x, w, self.bf16)
         return y.add_(self.b.w) if bias else y
 
-    def backward(self, dy, need_dx=True, accum=None):
-        """Accumulates dW, db; returns dx, added into `accum` (inside the GEMM, beta = 1) when one is given."""
-        self.b.g.add_(dy.sum(dim=0, dtype=torch.float32))
+    def backward(self, dy, need_dx=True, accum=None, scale=1.0):
+        """Accumulates dW, db; returns dx, added into `accum` (inside the GEMM, beta = 1) when one is given.
+        `scale`: the gradient that reaches this layer is scale * dy (the 1/sqrt(dqk) of the key projection)."""
         if self.bf16:
-            dy = _b16(dy)  # narrowed once for both products
-            torch.addmm(self.w.g, self.x.t(), dy, out_dtype=torch.float32, out=self.w.g)
-        else:
-            self.w.g.addmm_(self.x.t(), dy)
+            # bias gradient and the narrowing of dy for both products in one pass over dy; a dy that arrives in
+            # bf16 is only summed, and the scale rides in the GEMMs' alpha
+            was_narrow = dy.dtype == torch.bfloat16
+            dy = ops.colsum_narrow(dy, self.b.g, scale, narrow=not was_narrow)
+            alpha = scale if was_narrow else 1.0
+            torch.addmm(self.w.g, self.x.t(), dy, out_dtype=torch.float32, out=self.w.g, alpha=alpha)
+            if not need_dx:
+                return None
+            wt = self.w.wb.t()
+            if accum is None:
+                dx = torch.mm(dy, wt, out_dtype=torch.float32)
+                return dx if alpha == 1.0 else dx.mul_(alpha)
+            return torch.addmm(accum, dy, wt, out_dtype=torch.float32, out=accum, alpha=alpha)
+        if scale != 1.0:
+            dy = dy * scale
+        self.b.g.add_(dy.sum(dim=0, dtype=torch.float32))
+        self.w.g.addmm_(self.x.t(), dy)
         if not need_dx:
             return None
-        wt = (self.w.wb if self.bf16 else self.w.w).t()
+        wt = self.w.w.t()
         if accum is None:
-            return _mm(dy, wt, self.bf16)
-        if self.bf16:
-            return torch.addmm(accum, dy, wt, out_dtype=torch.float32, out=accum)
+            return torch.mm(dy, wt)
         return accum.addmm_(dy, wt)
 
     def params(self):
@@ -120,17 +133,19 @@ class RmsNorm:
         self.gamma = Param(gamma, False)
         self.group = group or gamma.numel()
 
-    def forward(self, x):
+    def forward(self, x, out_dtype=torch.float32):
+        """x fp32 or bf16; the result in `out_dtype` (bf16 where only GEMMs consume it)."""
         self.x = x
         rows, f = x.shape
-        y = torch.empty_like(x)
+        y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
         self.inv = torch.empty((rows * (f // self.group),), dtype=torch.float32, device=x.device)
         ops.rms_norm_forward_into(x, self.gamma.w, self.group, y, self.inv)
         return y
 
-    def backward(self, dy):
-        dx = torch.empty_like(dy)
-        ops.rms_norm_backward_into(dy, self.x, self.inv, self.gamma.w, self.group, dx, self.gamma.g)
+    def backward(self, dy, residual=None, out_dtype=torch.float32):
+        """Returns dx (+ residual, the gradient arriving over the skip connection, added in the same pass)."""
+        dx = torch.empty(dy.shape, dtype=out_dtype, device=dy.device)
+        ops.rms_norm_backward_into(dy, self.x, self.inv, self.gamma.w, self.group, dx, self.gamma.g, residual=residual)
         return dx
 
     def params(self):
@@ -145,8 +160,13 @@ class MLstm:
     RMSNorm -> output gate -> output projection. `p` holds wq,wk [in,H*dqk], wv,wo [in,H*dhv],
     wi,wf [in,H], their biases, w_out [d,d], b_out, gamma [d]."""
 
-    def __init__(self, p, heads, dqk, dhv, bf16=False, chunk=64):
+    def __init__(self, p, heads, dqk, dhv, bf16=False, chunk=64, recompute_states=False, grad_bf16=None):
+        """recompute_states: training keeps no chunk-state record; the backward rebuilds the chunk-boundary states
+        (the reference stores them for every chunk, src/gpu/ops.rs:3955-3967). grad_bf16 (default: as bf16): the
+        core's gradient I/O (d_ytil in; dq, dk, dv out) is bf16, the width the GEMMs on either side consume."""
         self.h, self.dqk, self.dhv, self.bf16, self.chunk = heads, dqk, dhv, bf16, chunk
+        self.recompute_states = recompute_states
+        self.grad_bf16 = bf16 if grad_bf16 is None else (grad_bf16 and bf16)
         mk = lambda n: Linear(p["w" + n], p["b" + n], True, bf16)
         self.lq, self.lk, self.lv, self.lo, self.li, self.lf = (mk(n) for n in "qkvoif")
         self.lout = Linear(p["w_out"], p["b_out"], True, bf16)
@@ -163,7 +183,8 @@ class MLstm:
         """residual: when given, the call returns residual + cell(x) (the block's first residual add, done inside
         the output projection's GEMM)."""
         sdt = torch.bfloat16 if self.bf16 else torch.float32
-        self.st = ops.MlstmShape(B, self.h, T, self.dqk, self.dhv, self.chunk, sdt, torch.float32)
+        self.st = ops.MlstmShape(B, self.h, T, self.dqk, self.dhv, self.chunk, sdt,
+                                 torch.bfloat16 if self.grad_bf16 else torch.float32)
         if self.bf16:
             x = _b16(x)  # one narrowing feeds all six projections
         if self.bf16:  # bf16 q, k, v straight from the GEMM epilogue (bias and the 1/sqrt(dqk) of k folded in)
@@ -174,7 +195,7 @@ class MLstm:
             q = self.lq.forward(x)
             k = self.lk.forward(x).mul_(self.inv_sqrt)
             v = self.lv.forward(x)
-        self.o = self.lo.forward(x)  # activated in place by the output-gate kernel below
+        self.o = self.lo.forward(x, bias=False)  # bias added and activated in place by the output-gate kernel below
         ig, fg = self.li.forward(x), self.lf.forward(x)
         self.core_in = (q, k, v, ig, fg)
         keep = self.stateful or self.sweep
@@ -183,11 +204,11 @@ class MLstm:
         else:
             self.carry_in = self.carry  # the backward needs the state this call entered with
             self.fused = ops.mlstm_fused_fw(q, k, v, ig, fg, self.st, carry_in=self.carry, want_state=keep,
-                                            save_states=not self.stateful)
+                                            save_states=not (self.stateful or self.recompute_states))
         if keep:
             self.carry = self.fused.state
-        self.yhat = self.hn.forward(self.fused.ytil.float() if self.bf16 else self.fused.ytil)
-        hc = ops.ogate_forward(self.o, self.yhat, torch.bfloat16 if self.bf16 else torch.float32)
+        self.yhat = self.hn.forward(self.fused.ytil)  # reads the core's bf16 output as it is
+        hc = ops.ogate_forward(self.o, self.yhat, torch.bfloat16 if self.bf16 else torch.float32, bias=self.lo.b.w)
         if self.shard_group is None:
             return self.lout.forward(hc, residual=residual)
         # heads are split over the group's ranks: W_out's rows are too, and the partial products are summed
@@ -201,7 +222,7 @@ class MLstm:
     def backward(self, dy):
         d_hc = self.lout.backward(dy)
         do_pre, d_yhat = ops.ogate_backward(d_hc, self.o, self.yhat, torch.bfloat16 if self.bf16 else torch.float32)
-        d_ytil = self.hn.backward(d_yhat)
+        d_ytil = self.hn.backward(d_yhat, out_dtype=torch.bfloat16 if self.grad_bf16 else torch.float32)
         q, k, v, ig, fg = self.core_in
         if self.cp is not None:
             dq, dk, dv, dig, dfg = cp.backward(self.fused, q, k, v, ig, fg, d_ytil, self.st, self.carry_in, *self.cp)
@@ -213,7 +234,7 @@ class MLstm:
             if self.sweep:
                 self.dcarry = dstate
         dx = self.lq.backward(dq)
-        self.lk.backward(dk.mul_(self.inv_sqrt), accum=dx)
+        self.lk.backward(dk, accum=dx, scale=self.inv_sqrt)
         self.lv.backward(dv, accum=dx)
         self.lo.backward(do_pre, accum=dx)
         self.li.backward(dig, accum=dx)
@@ -270,9 +291,13 @@ class SLstm:
         if self.sweep:
             self.dstate = ds  # now the gradient of the state this call entered with
         dg = self.g.view(B * T, 4 * H)  # the loop left the four gate deltas here
-        dgn = _b16(dg) if self.bf16 else dg
-        self.wx.g.add_(_mm(self.x.t(), dgn, self.bf16))
-        self.b.g.add_(dg.sum(dim=0))
+        if self.bf16:
+            dgn = ops.colsum_narrow(dg, self.b.g)  # bias gradient and the bf16 copy in one pass
+            torch.addmm(self.wx.g, self.x.t(), dgn, out_dtype=torch.float32, out=self.wx.g)
+        else:
+            dgn = dg
+            self.wx.g.addmm_(self.x.t(), dgn)
+            self.b.g.add_(dg.sum(dim=0))
         hp = self.slabs.t["h_prev"].view(B * T, H)
         if nh == 1:
             self.wh.g.add_(_mm(hp.t(), dgn, self.bf16))
@@ -316,13 +341,12 @@ class Block:
         self.ld = Linear(torch.nn.functional.pad(torch.as_tensor(p["w_down"], dtype=torch.float32), (0, 0, 0, pad)), p["b_down"], True, bf16)
 
     def forward(self, x, B, T):
+        nd_in = torch.bfloat16 if self.lg.bf16 else torch.float32  # the norms feed GEMMs only: narrowed as they are written
         if self.post is None:
-            z = self.cell.forward(self.n1.forward(x), B, T, residual=x)
+            z = self.cell.forward(self.n1.forward(x, nd_in), B, T, residual=x)
         else:
-            z = x + self.post.forward(self.cell.forward(self.n1.forward(x), B, T))
-        zn = self.n2.forward(z)
-        if self.lg.bf16:
-            zn = _b16(zn)
+            z = x + self.post.forward(self.cell.forward(self.n1.forward(x, nd_in), B, T))
+        zn = self.n2.forward(z, nd_in)
         # the two projections without their biases: the SwiGLU kernels add them (forward and backward)
         self.gate_pre, self.value = self.lg.forward(zn, bias=False), self.lv.forward(zn, bias=False)
         nd = torch.bfloat16 if self.ld.bf16 else torch.float32
@@ -335,9 +359,9 @@ class Block:
                                               self.lg.b.w, self.lv.b.w)
         d_zn = self.lg.backward(d_gate)
         self.lv.backward(d_value, accum=d_zn)
-        d_z = self.n2.backward(d_zn).add_(dy)
+        d_z = self.n2.backward(d_zn, residual=dy)
         d_c = self.post.backward(d_z) if self.post is not None else d_z
-        return self.n1.backward(self.cell.backward(d_c)).add_(d_z)
+        return self.n1.backward(self.cell.backward(d_c), residual=d_z)
 
     def params(self):
         out = self.n1.params() + self.cell.params() + self.n2.params()
@@ -388,6 +412,9 @@ class Lm:
         self.cap = cap
         self.loss = torch.zeros((1,), dtype=torch.float32, device="cuda")
         self.on_block_backward = None  # hook(i) called when block i's gradients are complete
+        # train_step waits for the backward pass and raises if a kernel gave up on a bounded device-side wait, before
+        # AdamW consumes the gradients; set False for a host that must stay fully asynchronous
+        self.check_status = True
         self.remat = set(range(len(blocks))) if remat is True else set(remat or ())
         self.head_rows = head_rows
         # head_split: the fp32 head products (row-chunked path) run as six bf16 tensor-core GEMMs on
@@ -491,6 +518,8 @@ class Lm:
 
     def train_step(self, ids, targets, B, T, cfg):
         loss = self.forward_backward(ids, targets, B, T)
+        if self.check_status:
+            ops.device_status_check()
         self.step(cfg)
         return loss
 
@@ -522,7 +551,7 @@ def init_lm_params(rng, vocab, d, n_blocks, heads, dqk, dhv, up, std=0.02, slstm
 
 
 def build_lm(params, heads, dqk, dhv, nh_s=1, cap=30.0, tied=True, head_w=None, head_b=None, bf16=False, chunk=64,
-             remat=False, head_rows=0, head_split=False):
+             remat=False, head_rows=0, head_split=False, recompute_states=False, grad_bf16=None):
     """Builds an Lm from the host parameter dictionary `oracle.model.init_lm_params` produces."""
     t = lambda a: torch.as_tensor(a, dtype=torch.float32)
     d = params["table"].shape[1]
@@ -531,7 +560,8 @@ def build_lm(params, heads, dqk, dhv, nh_s=1, cap=30.0, tied=True, head_w=None, 
         c = {k_: (t(v_) if k_ != "kind" else v_) for k_, v_ in bp["cell"].items()}
         bpt = {k_: t(v_) for k_, v_ in bp.items() if k_ != "cell"}
         if c["kind"] == "mlstm":
-            blocks.append(Block(MLstm(c, heads, dqk, dhv, bf16=bf16, chunk=chunk), bpt, bf16=bf16))
+            blocks.append(Block(MLstm(c, heads, dqk, dhv, bf16=bf16, chunk=chunk, recompute_states=recompute_states,
+                                      grad_bf16=grad_bf16), bpt, bf16=bf16))
         else:
             blocks.append(Block(SLstm(c, d, nh_s, bf16=bf16), bpt, post_norm=True, bf16=bf16))
     return Lm(t(params["table"]), blocks, t(params["gamma"]), None if head_w is None else t(head_w),

@@ -14,6 +14,48 @@ from ._lib import lib, check
 
 _DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
 
+# ---- optional per-op device timing (benchmarks): CUDA events around the calls of the named ops -----------------------
+_timing = None
+
+
+def timing_start(names=None):
+    """From now on every call of an op in `names` (all ops when None) is bracketed by two CUDA events on the current
+    stream. Costs two event records per call; nothing is synchronised until timing_stop()."""
+    global _timing
+    _timing = {"names": None if names is None else set(names), "ev": {}}
+
+
+def timing_stop():
+    """Stops the recording and returns {op name: [milliseconds of each call]} (synchronises the device)."""
+    global _timing
+    t, _timing = _timing, None
+    if t is None:
+        return {}
+    torch.cuda.synchronize()
+    return {k: [a.elapsed_time(b) for a, b in v] for k, v in t["ev"].items()}
+
+
+def timed(name):
+    """Decorator (also usable on library GEMM wrappers in a benchmark): records the op's device time while timing is on."""
+    def wrap(fn):
+        def inner(*a, **kw):
+            t = _timing
+            if t is None or (t["names"] is not None and name not in t["names"]):
+                return fn(*a, **kw)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(*a, **kw)
+            e1.record()
+            t["ev"].setdefault(name, []).append((e0, e1))
+            return out
+        inner.__name__, inner.__doc__, inner.__wrapped__ = fn.__name__, fn.__doc__, fn
+        return inner
+    return wrap
+
+
+def _dt(t):
+    return _DT[t]
+
 
 def _ptr(t):
     if t is None:
@@ -50,6 +92,7 @@ class MlstmFused:
         self.ytil, self.msv, self.psiv, self.qnv, self.saved, self.state = ytil, msv, psiv, qnv, saved, state
 
 
+@timed("mlstm_fused_fw")
 def mlstm_fused_fw(qh, kh, vh, igh, fgh, st, carry_in=None, save_states=True, want_state=True):
     """ops::mlstm_fused_fw (src/gpu/ops.rs:4380-4537). carry_in = (C [BH,dhv,dqk], n [BH,dqk], m [BH])."""
     dev = qh.device
@@ -74,6 +117,7 @@ def mlstm_fused_fw(qh, kh, vh, igh, fgh, st, carry_in=None, save_states=True, wa
     return MlstmFused(ytil, msv, psiv, qnv, saved, state)
 
 
+@timed("mlstm_final_state")
 def mlstm_final_state(qh, kh, vh, igh, fgh, st, carry_in=None):
     """The (C, n, m) a fused forward would end in, from the state recurrence alone (no outputs, no record)."""
     dev = qh.device
@@ -88,6 +132,7 @@ def mlstm_final_state(qh, kh, vh, igh, fgh, st, carry_in=None):
     return state
 
 
+@timed("mlstm_fused_bw")
 def mlstm_fused_bw(fused, qh, kh, vh, igh, fgh, d_ytil, st, carry_in=None, dstate_in=None, want_dstate=True):
     """ops::mlstm_fused_bw (src/gpu/ops.rs:4546-4707). dstate_in = (dC, dn) from the call to the right.
     Returns (dq, dk, dv, dig, dfg, (dC, dn))."""
@@ -125,6 +170,7 @@ class SlstmSlabs:
         self.c = _lib.SlstmSlabs(*[self.t[n].data_ptr() for n in SLSTM_SLAB_NAMES])
 
 
+@timed("slstm_fused_time")
 def slstm_fused_time(wh, g, bcat, state, out, slabs, nh=1, carry=False):
     """ops::slstm_fused_time (src/gpu/ops.rs:2787-2880). state = (c, n, m, h), each [B,H], updated in place.
     Raises Declined (nothing launched) where the reference would return false."""
@@ -135,6 +181,7 @@ def slstm_fused_time(wh, g, bcat, state, out, slabs, nh=1, carry=False):
                              ctypes.byref(slabs.c), b, h, nh, t, int(carry), 0), "slstm_fused_time")
 
 
+@timed("slstm_fused_time_bwd")
 def slstm_fused_time_bwd(wh, dy, g, dstate, slabs, nh=1, carry=False):
     """ops::slstm_fused_time_bwd (src/gpu/ops.rs:2712-2777). dstate = (dh, dc, dn), each [B,H], updated in place."""
     b, t, h4 = g.shape
@@ -144,22 +191,56 @@ def slstm_fused_time_bwd(wh, dy, g, dstate, slabs, nh=1, carry=False):
                              ctypes.byref(slabs.c), b, h, nh, t, int(carry), 0), "slstm_fused_time_bwd")
 
 
+@timed("rms_norm_forward_into")
 def rms_norm_forward_into(x, gamma, group, out, inv_rms, x_hat=None, eps=1e-6):
-    """ops::rms_norm_forward_into (src/gpu/ops.rs:1601-1640)."""
+    """ops::rms_norm_forward_into (src/gpu/ops.rs:1601-1640). x may be fp32 or bf16; `out` fp32 or bf16."""
     rows, f = x.shape
-    check(lib.xlstm_rmsnorm_fw(_stream(), _ptr(x), _ptr(gamma), _ptr(out), _ptr(inv_rms), _ptr(x_hat), rows, f, group,
-                               eps), "rms_norm_forward_into")
+    check(lib.xlstm_rmsnorm_fw(_stream(), _ptr(x), _dt(x.dtype), _ptr(gamma), _ptr(out), _dt(out.dtype), _ptr(inv_rms),
+                               _ptr(x_hat), rows, f, group, eps), "rms_norm_forward_into")
 
 
-def rms_norm_backward_into(dy, x, inv_rms, gamma, group, dx, dgamma):
-    """ops::rms_norm_backward_into + the dgamma column sum (src/gpu/ops.rs:1642-1685). dgamma is accumulated."""
+@timed("rms_norm_backward_into")
+def rms_norm_backward_into(dy, x, inv_rms, gamma, group, dx, dgamma, residual=None):
+    """ops::rms_norm_backward_into + the dgamma column sum (src/gpu/ops.rs:1642-1685). dgamma is accumulated;
+    `residual` (fp32, same shape) is added to dx in the same pass; x fp32 or bf16, dx fp32 or bf16."""
     rows, f = dy.shape
     wsb = lib.xlstm_rmsnorm_bw_workspace_bytes(rows, f)
     ws = torch.empty((max(wsb, 1),), dtype=torch.uint8, device=dy.device)
-    check(lib.xlstm_rmsnorm_bw(_stream(), _ptr(dy), _ptr(x), _ptr(inv_rms), _ptr(gamma), _ptr(dx), _ptr(dgamma), rows, f,
-                               group, _ptr(ws), wsb), "rms_norm_backward_into")
+    check(lib.xlstm_rmsnorm_bw(_stream(), _ptr(dy), _ptr(x), _dt(x.dtype), _ptr(inv_rms), _ptr(gamma), _ptr(residual),
+                               _ptr(dx), _dt(dx.dtype), _ptr(dgamma), rows, f, group, _ptr(ws), wsb), "rms_norm_backward_into")
 
 
+@timed("colsum_narrow")
+def colsum_narrow(x, acc, scale=1.0, narrow=True):
+    """acc += scale * x.sum(0) (a projection's bias gradient, add_col_sum of src/gpu/cuda/common.cu:49-124) and, with
+    `narrow`, the bf16 copy of scale * x that the two weight-side GEMMs consume, in the same pass. Returns the
+    bf16 tensor (x itself when it is bf16 already and scale == 1)."""
+    rows, cols = x.shape
+    out = None
+    if narrow and (x.dtype != torch.bfloat16 or scale != 1.0):
+        out = torch.empty((rows, cols), dtype=torch.bfloat16, device=x.device)
+    wsb = lib.xlstm_colsum_workspace_bytes(rows, cols)
+    ws = torch.empty((max(wsb, 1),), dtype=torch.uint8, device=x.device)
+    check(lib.xlstm_colsum_narrow(_stream(), _ptr(x), _dt(x.dtype), rows, cols, float(scale), _ptr(out), _ptr(acc), _ptr(ws), wsb),
+          "colsum_narrow")
+    return out if out is not None else x
+
+
+@timed("bias_rows")
+def bias_rows(bias, rows, residual=None):
+    """broadcast_row / broadcast_row_resid (src/gpu/cuda/common.cu:20-48): a new [rows, cols] fp32 tensor holding
+    bias (+ residual), the seed an output projection's GEMM accumulates into."""
+    out = torch.empty((rows, bias.numel()), dtype=torch.float32, device=bias.device)
+    check(lib.xlstm_bias_rows(_stream(), _ptr(residual), _ptr(bias), _ptr(out), rows, bias.numel()), "bias_rows")
+    return out
+
+
+def device_status_check():
+    """Waits for the work enqueued so far and raises if a kernel gave up on a bounded device-side wait."""
+    check(lib.xlstm_device_status(), "device status")
+
+
+@timed("softmax_cross_entropy")
 def softmax_cross_entropy(logits, targets, dlogits, loss_accum, mask=None, inv=None):
     """ops::softmax_cross_entropy / masked_softmax_ce_u32_into (src/gpu/ops.rs:1689-1714, 3567-3618).
     targets/mask are int32 tensors holding u32 values; loss_accum is a 1-element f32 device tensor (+=)."""
@@ -172,6 +253,7 @@ def softmax_cross_entropy(logits, targets, dlogits, loss_accum, mask=None, inv=N
                              inv, _ptr(ws), wsb), "softmax_cross_entropy")
 
 
+@timed("softcap_cross_entropy")
 def softcap_cross_entropy(pre_logits, targets, d_pre, loss_accum, cap, mask=None, inv=None):
     """Soft-cap (softcap_forward/backward, src/gpu/cuda/common.cu:4-12) fused into the loss: the loss of
     cap*tanh(pre/cap) and its gradient with respect to `pre_logits` (d_pre may alias pre_logits)."""
@@ -184,10 +266,7 @@ def softcap_cross_entropy(pre_logits, targets, d_pre, loss_accum, cap, mask=None
                                      rows, c, inv, float(cap), _ptr(ws), wsb), "softcap_cross_entropy")
 
 
-def _dt(t):
-    return _DT[t]
-
-
+@timed("swiglu_forward")
 def swiglu_forward(gate_pre, value, out_dtype=torch.float32, bias_gate=None, bias_value=None):
     """swiglu_forward (src/gpu/cuda/block.cu:6-29): SiLU(gate_pre + bias_gate) * (value + bias_value), optionally
     narrowed to bf16. The biases are the two projections' (both or neither), folded in here."""
@@ -197,6 +276,7 @@ def swiglu_forward(gate_pre, value, out_dtype=torch.float32, bias_gate=None, bia
     return out
 
 
+@timed("swiglu_backward")
 def swiglu_backward(d_mixed, gate_pre, value, out_dtype=torch.float32, bias_gate=None, bias_value=None):
     """swiglu_backward: (d_gate_pre, d_value), optionally narrowed to bf16 for the GEMMs that consume them."""
     dg = torch.empty(gate_pre.shape, dtype=out_dtype, device=gate_pre.device)
@@ -206,13 +286,17 @@ def swiglu_backward(d_mixed, gate_pre, value, out_dtype=torch.float32, bias_gate
     return dg, dv
 
 
-def ogate_forward(o, yhat, out_dtype=torch.float32):
-    """ogate_fwd (src/gpu/cuda/mlstm_ops.cu:147-153): o <- sigmoid(o) in place; returns o * yhat."""
+@timed("ogate_forward")
+def ogate_forward(o, yhat, out_dtype=torch.float32, bias=None):
+    """ogate_fwd (src/gpu/cuda/mlstm_ops.cu:147-153): o <- sigmoid(o + bias) in place; returns o * yhat. `bias` is the
+    gate projection's, folded in here when its GEMM ran without one."""
     hc = torch.empty(o.shape, dtype=out_dtype, device=o.device)
-    check(lib.xlstm_ogate_fw(_stream(), _ptr(o), _ptr(yhat), _ptr(hc), _dt(out_dtype), o.numel()), "ogate_forward")
+    check(lib.xlstm_ogate_fw(_stream(), _ptr(o), _ptr(yhat), _ptr(bias), o.shape[-1], _ptr(hc), _dt(out_dtype), o.numel()),
+          "ogate_forward")
     return hc
 
 
+@timed("ogate_backward")
 def ogate_backward(d_hc, o, yhat, out_dtype=torch.float32):
     """ogate_bwd (src/gpu/cuda/mlstm_ops.cu:400-407): (do_pre [out_dtype], d_yhat [fp32])."""
     do_pre = torch.empty(o.shape, dtype=out_dtype, device=o.device)
@@ -222,6 +306,7 @@ def ogate_backward(d_hc, o, yhat, out_dtype=torch.float32):
     return do_pre, d_yhat
 
 
+@timed("split3_bf16")
 def split3_bf16(x):
     """fp32 tensor -> (hi, mid, lo) bf16 tensors with hi + mid + lo == x to 24 bits, in one pass."""
     x = x.contiguous()
@@ -230,6 +315,7 @@ def split3_bf16(x):
     return hi, mid, lo
 
 
+@timed("embedding_scatter_add")
 def embedding_scatter_add(table_g, ids, d):
     """embedding_scatter_add (src/gpu/cuda/common.cu:127-168): table_g[ids[p]] += d[p], summed in position
     order for each token (deterministic; the sort is a library call, the accumulation is the kernel)."""
@@ -259,6 +345,10 @@ class AdamwQueue:
     def flush(self, cfg, zero_grad=True):
         if not self.items:
             return
+        return self._flush(cfg, zero_grad)
+
+    @timed("adamw_multi")
+    def _flush(self, cfg, zero_grad):
         n = len(self.items)
         arr = (_lib.AdamwDesc * n)()
         for i, (p, g, m, v, decay, pb) in enumerate(self.items):

@@ -15,6 +15,10 @@ import numpy as np
 
 from . import oracle as O
 
+# Arithmetic width of everything built from this module. float64 is the low-noise comparison target the parity tests
+# use; the benchmark's CPU legs set float32, the width of the reference's own CPU layers (src/nn2), before building.
+DT = np.float64
+
 
 class AdamState:
     def __init__(self, p):
@@ -26,13 +30,13 @@ class Param:
     """A parameter with its gradient accumulator and AdamW moments."""
 
     def __init__(self, value, decay):
-        self.w = np.array(value, dtype=np.float64)
+        self.w = np.array(value, dtype=DT)
         self.g = np.zeros_like(self.w)
         self.decay = decay
         self.st = AdamState(self.w)
 
     def step(self, lr, wd, t):
-        self.w, self.st.m, self.st.v = O.adamw(self.w, self.g, self.st.m, self.st.v, lr, wd if self.decay else 0.0, t)
+        self.w, self.st.m, self.st.v = O.adamw(self.w, self.g, self.st.m, self.st.v, lr, wd if self.decay else 0.0, t, dtype=DT)
         self.g[...] = 0.0
 
 
@@ -60,11 +64,11 @@ class RmsNorm:
         self.group = group or len(gamma)
 
     def forward(self, x):
-        y, self.xh, self.inv = O.rmsnorm_fw(x, self.gamma.w, self.group)
+        y, self.xh, self.inv = O.rmsnorm_fw(x, self.gamma.w, self.group, dtype=DT)
         return y
 
     def backward(self, dy):
-        dx, dg = O.rmsnorm_bw(dy, self.xh, self.inv, self.gamma.w, self.group)
+        dx, dg = O.rmsnorm_bw(dy, self.xh, self.inv, self.gamma.w, self.group, dtype=DT)
         self.gamma.g += dg
         return dx
 
@@ -73,7 +77,7 @@ class RmsNorm:
 
 
 def sigmoid(x):
-    return 1.0 / (1.0 + np.exp(-x))
+    return 1.0 / (1.0 + np.exp(-x))  # numpy keeps the array's width (DT)
 
 
 class MLstm:
@@ -95,7 +99,7 @@ class MLstm:
         self.o = sigmoid(self.lo.forward(x))
         ig, fg = self.li.forward(x), self.lf.forward(x)
         self.core_in = (q, k, v, ig, fg)
-        fw = O.mlstm_core_fw(q, k, v, ig, fg, B, self.h, T, self.dqk, self.dhv)
+        fw = O.mlstm_core_fw(q, k, v, ig, fg, B, self.h, T, self.dqk, self.dhv, dtype=DT)
         self.yhat = self.hn.forward(fw["ytil"])
         self.hc = self.o * self.yhat
         return self.lout.forward(self.hc)
@@ -105,7 +109,7 @@ class MLstm:
         do_pre = d_hc * self.yhat * self.o * (1.0 - self.o)
         d_ytil = self.hn.backward(d_hc * self.o)
         q, k, v, ig, fg = self.core_in
-        g = O.mlstm_core_bw(q, k, v, ig, fg, d_ytil, self.B, self.h, self.T, self.dqk, self.dhv)
+        g = O.mlstm_core_bw(q, k, v, ig, fg, d_ytil, self.B, self.h, self.T, self.dqk, self.dhv, dtype=DT)
         dx = self.lq.backward(g["dq"])
         dx += self.lk.backward(g["dk"] * self.inv_sqrt)
         dx += self.lv.backward(g["dv"])
@@ -134,12 +138,12 @@ class SLstm:
     def forward(self, x, B, T):
         self.B, self.T, self.x = B, T, x
         g = (x @ self.wx.w).reshape(B, T, 4 * self.H)
-        self.fw = O.slstm_fw(self.wh.w, g, self.b.w, B, self.H, self.nh, T)
+        self.fw = O.slstm_fw(self.wh.w, g, self.b.w, B, self.H, self.nh, T, dtype=DT)
         return self.fw["out"].reshape(B * T, self.H)
 
     def backward(self, dy):
         B, T, H, nh = self.B, self.T, self.H, self.nh
-        bw = O.slstm_bw(self.wh.w, dy.reshape(B, T, H), self.fw, B, H, nh, T)
+        bw = O.slstm_bw(self.wh.w, dy.reshape(B, T, H), self.fw, B, H, nh, T, dtype=DT)
         dg = bw["dg"].reshape(B * T, 4 * H)
         self.wx.g += self.x.T @ dg
         self.b.g += dg.sum(axis=0)
@@ -245,7 +249,7 @@ class Lm:
 
     def train_step(self, ids, targets, B, T, lr, wd, t):
         logits = self.forward(ids, B, T)
-        loss, dlogits = O.softmax_ce(logits, targets)
+        loss, dlogits = O.softmax_ce(logits, targets, dtype=DT)
         self.backward(dlogits)
         grads = [p.g.copy() for p in self.params()]
         for p in self.params():

@@ -175,3 +175,69 @@ def test_adamw_single_and_batched(wd):
         assert rel_to_max(host(dM[i]), M[i]) <= 1e-6 and rel_to_max(host(dV[i]), V[i]) <= 1e-6
         assert torch.equal(dP[i], sP[i])  # batched == per-tensor, bit for bit
         assert torch.equal(dPb[i], dP[i].to(torch.bfloat16))  # the bf16 shadow is the RNE cast of the new weight
+
+
+@pytest.mark.parametrize("rows,F,group", [(64, 2048, 256), (33, 1024, 1024), (5, 12, 4), (7, 300, 300)])
+def test_rmsnorm_bf16_storage_and_residual(rows, F, group):
+    """The norm reading a bf16 tensor (the mLSTM core's output), writing bf16 (what only GEMMs consume), and the
+    backward adding the skip connection's gradient in the same pass: each equals the fp32 op applied to the
+    bf16-rounded operand, to bf16 rounding of the result where the result is bf16."""
+    from gpu_util import ops, dev, host, rel_to_max, bf16_round
+    r = np.random.default_rng(3)
+    f32 = lambda a: a.astype(np.float32).astype(np.float64)
+    x = bf16_round(r.standard_normal((rows, F)) * 2); gamma = f32(1 + 0.1 * r.standard_normal(F))
+    dy = f32(r.standard_normal((rows, F))); res = f32(r.standard_normal((rows, F)))
+    y, xh, inv = O.rmsnorm_fw(x, gamma, group)
+    dx, dgam = O.rmsnorm_bw(dy, xh, inv, gamma, group)
+    xb, g_ = dev(x, torch.bfloat16), dev(gamma)
+    inv_ = torch.empty((rows * (F // group),), device="cuda")
+    for ydt, tol in ((torch.float32, 1e-4), (torch.bfloat16, 8e-3)):
+        out = torch.empty((rows, F), dtype=ydt, device="cuda")
+        ops.rms_norm_forward_into(xb, g_, group, out, inv_)
+        assert rel_to_max(host(out), y) <= tol
+    for ddt, tol in ((torch.float32, 1e-4), (torch.bfloat16, 8e-3)):
+        dgam_ = torch.zeros(F, device="cuda")
+        dxo = torch.empty((rows, F), dtype=ddt, device="cuda")
+        ops.rms_norm_backward_into(dev(dy), xb, inv_, g_, group, dxo, dgam_, residual=dev(res))
+        assert rel_to_max(host(dxo), dx + res) <= tol
+        assert rel_to_max(host(dgam_), dgam) <= 1e-4
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 4), (37, 8), (1000, 2048), (4096, 5464), (333, 130), (64, 7)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_colsum_narrow(rows, cols, dtype):
+    """Bias gradient (fixed-order column sum, accumulated) and the bf16 copy of the scaled tensor in one pass."""
+    from gpu_util import ops, dev, host, rel_to_max, bf16_round
+    r = np.random.default_rng(4)
+    x = r.standard_normal((rows, cols)) + 0.3
+    x = bf16_round(x) if dtype == torch.bfloat16 else x.astype(np.float32).astype(np.float64)
+    base = r.standard_normal(cols).astype(np.float32).astype(np.float64)
+    for scale, narrow in ((1.0, True), (0.125, True), (0.5, False)):
+        acc = dev(base)
+        xd = dev(x, dtype)
+        out = ops.colsum_narrow(xd, acc, scale, narrow=narrow)
+        assert rel_to_max(host(acc), base + scale * x.sum(0)) <= 1e-5
+        if not narrow or (dtype == torch.bfloat16 and scale == 1.0):
+            assert out is xd
+        else:
+            assert out.dtype == torch.bfloat16
+            assert torch.equal(out, (xd.float() * scale).to(torch.bfloat16))
+        again = dev(base)
+        ops.colsum_narrow(xd, again, scale, narrow=narrow)
+        assert torch.equal(acc, again)  # fixed summation order
+
+
+@pytest.mark.parametrize("rows,cols", [(3, 5), (128, 2048), (77, 12)])
+def test_bias_rows_and_ogate_bias(rows, cols):
+    from gpu_util import ops, dev, host
+    r = np.random.default_rng(5)
+    f32 = lambda a: a.astype(np.float32)
+    b, res = f32(r.standard_normal(cols)), f32(r.standard_normal((rows, cols)))
+    assert torch.equal(ops.bias_rows(dev(b), rows), dev(np.broadcast_to(b, (rows, cols)).copy()))
+    assert torch.equal(ops.bias_rows(dev(b), rows, dev(res)), dev(res + b))
+    o, y = f32(r.standard_normal((rows, cols))), f32(r.standard_normal((rows, cols)))
+    od = dev(o)
+    hc = ops.ogate_forward(od, dev(y), torch.float32, bias=dev(b))
+    sig = 1.0 / (1.0 + np.exp(-(o.astype(np.float64) + b)))
+    assert np.abs(host(od) - sig).max() <= 1e-6
+    assert np.abs(host(hc) - sig * y).max() <= 1e-5
