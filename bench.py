@@ -1,17 +1,23 @@
 #!/usr/bin/env python
 """Benchmark of the xLSTM hot path on B200.
 
-Default workload: the mLSTM layer kernel, forward + backward, at B=16 H=8 S=2048
-d_qk=d_v=128 chunk 64, q/k/v bf16 ~N(0,1) (k pre-scaled by 1/sqrt(d_qk), the contract of the
-op), gate logits fp32 (input N(0,1), forget N(3,1)), zero initial state, upstream grad N(0,1).
-One "step" is one forward + backward over that batch. With N GPUs every rank runs the same
-per-GPU batch (the path shards over batch with no data-path collective): weak scaling.
+Default workload (every N): one data-parallel TRAINING STEP of the xLSTM language model of BASELINE.json configs[3] at
+its own widths: 24 blocks (one sLSTM per 8, the rest mLSTM), d = 2048, mLSTM 8 heads x 256, sLSTM 4 heads x 512, vocab
+50304, bf16 GEMM operands with fp32 master weights, AdamW, per-GPU batch 8 x 4096 of uniform-random token ids. A step
+starts from pinned HOST token ids and ends with the loss read back on the host, so the device-timed `value` (train
+tokens/s, whole job) and `e2e` are the same measurement. With N GPUs every rank holds a replica and its own batch
+(weak scaling); gradients are summed with one NCCL all-reduce per block, started through the library's xlstm_dp_*
+entry points the moment the block's backward is done and waited for in front of AdamW.
 
-Prints ONE JSON line (rank 0). `value` is device-timed with inputs resident in HBM; `e2e` is
-the same step through the public op API starting from pinned HOST buffers, host<->device
-copies inside the timed region. `--impl reference` times the CPU restatement of the
-reference's layer math (the reference itself is a Rust crate that cannot be built here) on
-the host cores, on a bounded sample of the same workload.
+The same JSON line carries: `mlstm_fwd_bwd_tflops` (the configs[1] mLSTM layer kernel pair, B16 H8 S2048 d128 chunk 64,
+measured in this process before the model is built), `roofline` (the mLSTM backward op at the model's shape, CUDA
+events around every call inside the timed steps), `kernels` (device time of every library op and of the library GEMMs
+in one extra instrumented step), `cpu_baseline` (N = 1), and for N > 1 `allreduce_exposed_ms` and `dp_parity_max_rel`
+(a small model's N-rank gradients against one rank on the concatenated batch, checked before the timed region).
+
+`--impl reference` times the CPU restatement of the reference's layers (the reference is a Rust crate that cannot be
+built here) on the host cores, on a fixed sample of the same workload; the line states the sample and the
+extrapolation. `--workload mlstm|ops|hier|cp` run the secondary workloads.
 """
 import argparse
 import ctypes
@@ -119,63 +125,225 @@ def make_inputs(cfg, seed):
     return q, k, v, ig, fg, dy
 
 
-def cpu_sample(seconds_target=15.0, threads=None):
-    """Times the CPU restatement (f32) on a slice of the workload: Bs sequences of the full length."""
+def _limit_threads(n):
+    """Context manager: BLAS and OpenMP pools limited to n threads (None = leave as they are)."""
+    import contextlib
+    if n is None:
+        return contextlib.nullcontext()
+    from threadpoolctl import threadpool_limits
+    return threadpool_limits(limits=n)
+
+
+MLSTM_CPU_SEQS = 8  # sequences (of the 16) in the all-core CPU sample of the configs[1] kernel pair: fixed, not core-count dependent
+
+
+def cpu_mlstm_sample(seqs=MLSTM_CPU_SEQS, threads=None):
+    """Times the CPU restatement (f32) of the configs[1] kernel pair on `seqs` sequences of the full length."""
     from oracle import oracle as O
     cfg = dict(CFG)
-    ncores = os.cpu_count() or 1
-    threads = threads or min(ncores, 64)  # each worker holds ~134 MB of per-step records
-    os.environ["OMP_NUM_THREADS"] = str(threads)
-    Bs = max(1, min(cfg["B"], (4 * threads + cfg["H"] - 1) // cfg["H"]))
-    cfg["B"] = Bs
+    cfg["B"] = seqs
     q, k, v, ig, fg, dy = make_inputs(cfg, 0)
     args = (cfg["B"], cfg["H"], cfg["T"], cfg["dqk"], cfg["dhv"])
-    t0 = time.perf_counter()
-    O.mlstm_core_fw(q, k, v, ig, fg, *args, dtype=np.float32)
-    O.mlstm_core_bw(q, k, v, ig, fg, dy, *args, dtype=np.float32)
-    dt = time.perf_counter() - t0
+    with _limit_threads(threads):
+        t0 = time.perf_counter()
+        O.mlstm_core_fw(q, k, v, ig, fg, *args, dtype=np.float32)
+        O.mlstm_core_bw(q, k, v, ig, fg, dy, *args, dtype=np.float32)
+        dt = time.perf_counter() - t0
     f, b = flops_fwd_bwd(**cfg)
-    return dict(seconds=dt, flops=f + b, tokens=Bs * cfg["T"], Bs=Bs, threads=threads)
+    return dict(seconds=dt, flops=f + b, tokens=seqs * cfg["T"], seqs=seqs, threads=threads or (os.cpu_count() or 1))
+
+
+# ---- the LM workload (configs[3]) -----------------------------------------------------------------------------------
+LM_CFG_FULL = dict(vocab=50304, d=2048, blocks=24, heads=8, dqk=256, dhv=256, slstm_every=8, slstm_heads=4, B=8, T=4096)
+# development stand-in with the same structure at half the width (`--lm-reduced`)
+LM_CFG_REDUCED = dict(vocab=50304, d=1024, blocks=24, heads=8, dqk=128, dhv=128, slstm_every=8, slstm_heads=4, B=8, T=4096)
+LM_CPU_SAMPLE = dict(B=8, T=64)       # all-core CPU sample: sequences x positions run through one block of each kind + the head
+LM_CPU_SAMPLE_1CORE = dict(B=1, T=64)
+
+
+def lm_cfg(args):
+    c = dict(LM_CFG_REDUCED if args.lm_reduced else LM_CFG_FULL)
+    if args.lm_blocks:
+        c["blocks"] = args.lm_blocks
+    c["up"] = (8 * c["d"] // 3 + 7) // 8 * 8
+    c["slstm_at"] = tuple(i for i in range(c["blocks"]) if i % c["slstm_every"] == 0)
+    return c
+
+
+def lm_config_dict(args, world):
+    """The `config` object of the LM line: identical for the engine's arm and the reference arm."""
+    c = lm_cfg(args)
+    return {"workload": "xlstm_lm_train_step (configs[3]%s: %d blocks, sLSTM at %s, d=%d, mLSTM %dx%d, sLSTM %dx%d, vocab %d, AdamW)"
+                        % (" widths" if not args.lm_reduced else " structure, reduced widths", c["blocks"], list(c["slstm_at"]), c["d"],
+                           c["heads"], c["dqk"], c["slstm_heads"], c["d"] // c["slstm_heads"], c["vocab"]),
+            "per_gpu_batch": [c["B"], c["T"]], "global_batch_tokens": c["B"] * c["T"] * world,
+            "parallelism": "dp%d (one NCCL gradient all-reduce per block through xlstm_dp_*, overlapped with backward)" % world,
+            "chunk_states": "recomputed in backward" if args.recompute else "saved by forward",
+            "rematerialised_blocks": args.lm_remat, "l2": "activations far larger than L2"}
+
+
+def lm_param_count(c):
+    d, up, H = c["d"], c["up"], c["heads"]
+    ffn = 3 * d * up + 2 * up + d + 2 * d  # gate, value, down (+ biases) and the two norm gains
+    m = 2 * (d * H * c["dqk"] + H * c["dqk"]) + 2 * (d * H * c["dhv"] + H * c["dhv"]) + 2 * (d * H + H) + d * d + d + d
+    dh = d // c["slstm_heads"]
+    s_ = d * 4 * d + c["slstm_heads"] * dh * 4 * dh + 4 * d + d  # wx, wh, bias, post-norm gain
+    ns = len(c["slstm_at"])
+    return c["vocab"] * d + d + (c["blocks"] - ns) * (m + ffn) + ns * (s_ + ffn), m + ffn, s_ + ffn
+
+
+def _cpu_lm_params(rng, c):
+    """Seeded N(0, 0.02) f32 host weights of one sLSTM block, one mLSTM block and the table at the model's widths, in the
+    dictionary layout the CPU restatement's `build_lm` takes (numpy only: the CPU legs never load the engine)."""
+    d, up, H, dqk, dhv, nh = c["d"], c["up"], c["heads"], c["dqk"], c["dhv"], c["slstm_heads"]
+    n = lambda *shape: rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02)
+    one = lambda k: np.ones(k, np.float32)
+    ffn = lambda: dict(g1=one(d), g2=one(d), w_gate=n(d, up), b_gate=n(up), w_value=n(d, up), b_value=n(up), w_down=n(up, d), b_down=n(d))
+    dh = d // nh
+    sblk = dict(ffn(), gpost=one(d), cell=dict(kind="slstm", wx=n(d, 4 * d), wh=n(nh, dh, 4 * dh), bcat=n(4 * d)))
+    mblk = dict(ffn(), cell=dict(kind="mlstm", wq=n(d, H * dqk), wk=n(d, H * dqk), wv=n(d, H * dhv), wo=n(d, H * dhv), wi=n(d, H),
+                                 wf=n(d, H), bq=n(H * dqk), bk=n(H * dqk), bv=n(H * dhv), bo=n(H * dhv), bi=n(H), bf=n(H),
+                                 w_out=n(d, d), b_out=n(d), gamma=one(d)))
+    return dict(table=n(c["vocab"], d), blocks=[sblk, mblk], gamma=one(d))
+
+
+_cpu_lm_cache = {}
+
+
+def cpu_lm_sample(args, sample, threads=None):
+    """Times the CPU restatement (f32, the width of the reference's src/nn2 layers) of the LM's three kinds of work at
+    the model's full widths on a small batch: one sLSTM block, one mLSTM block, and embedding + final norm + tied fp32
+    head + soft-cap + cross-entropy, each forward + backward, plus AdamW over one block's tensors. The full model's
+    step on the full per-GPU batch is extrapolated: every per-token cost scales with the token count, AdamW with the
+    parameter count. Returns the pieces and the extrapolated step."""
+    from oracle import model as M
+    from oracle import oracle as O
+    c = lm_cfg(args)
+    B, T = sample["B"], sample["T"]
+    rows = B * T
+    M.DT = np.float32
+    try:
+        if "lm" not in _cpu_lm_cache:
+            _cpu_lm_cache["lm"] = M.build_lm(_cpu_lm_params(np.random.default_rng(0), c), c["heads"], c["dqk"], c["dhv"],
+                                             nh_s=c["slstm_heads"], tied=True)
+        lm = _cpu_lm_cache["lm"]
+        ids = np.random.default_rng(1).integers(0, c["vocab"], (B, T + 1))
+        x_ids, tg = ids[:, :-1].reshape(-1), ids[:, 1:].reshape(-1)
+        with _limit_threads(threads):
+            x = lm.table.w[x_ids]
+            t = {}
+            t0 = time.perf_counter(); y_s = lm.blocks[0].forward(x, B, T); t["slstm_fw"] = time.perf_counter() - t0
+            t0 = time.perf_counter(); y_m = lm.blocks[1].forward(y_s, B, T); t["mlstm_fw"] = time.perf_counter() - t0
+            t0 = time.perf_counter()
+            normed = lm.norm.forward(y_m)
+            pre = normed @ lm.table.w.T
+            logits = lm.cap * np.tanh(pre / lm.cap)
+            loss, dlogits = O.softmax_ce(logits, tg, dtype=np.float32)
+            d_pre = dlogits * (1.0 - (logits / lm.cap) ** 2)
+            lm.table.g += d_pre.T @ normed
+            d = lm.norm.backward(d_pre @ lm.table.w)
+            t["head"] = time.perf_counter() - t0
+            t0 = time.perf_counter(); d = lm.blocks[1].backward(d); t["mlstm_bw"] = time.perf_counter() - t0
+            t0 = time.perf_counter(); d = lm.blocks[0].backward(d); t["slstm_bw"] = time.perf_counter() - t0
+            t0 = time.perf_counter(); np.add.at(lm.table.g, x_ids, d); t["embed_bw"] = time.perf_counter() - t0
+            t0 = time.perf_counter()
+            nstep = 0
+            for q in lm.blocks[1].params():
+                q.step(1e-3, 0.1, 1); nstep += q.w.size
+            t["adamw"] = time.perf_counter() - t0
+    finally:
+        M.DT = np.float64
+    total, _, _ = lm_param_count(c)
+    nm, ns = c["blocks"] - len(c["slstm_at"]), len(c["slstm_at"])
+    per_rows = nm * (t["mlstm_fw"] + t["mlstm_bw"]) + ns * (t["slstm_fw"] + t["slstm_bw"]) + t["head"] + t["embed_bw"]
+    full_rows = c["B"] * c["T"]
+    step_s = per_rows * (full_rows / rows) + t["adamw"] * (total / nstep)
+    measured_s = sum(t.values())
+    return dict(pieces=t, rows=rows, measured_s=measured_s, step_s=step_s, tokens_per_s=full_rows / step_s, loss=float(loss),
+                threads=threads or (os.cpu_count() or 1),
+                formula="step = (%d/%d rows) * (%d*(mlstm_fw+bw) + %d*(slstm_fw+bw) + head + embed_bw) + adamw * (%d/%d params)"
+                        % (full_rows, rows, nm, ns, total, nstep))
+
+
+def lm_cpu_baseline(args, with_one_core=True):
+    s = cpu_lm_sample(args, LM_CPU_SAMPLE)
+    out = {"value": s["tokens_per_s"], "unit": "tokens/s", "cores": s["threads"], "kind": "port",
+           "sample": "f32 CPU restatement of the reference's layers at the model's full widths: one mLSTM block, one sLSTM block and "
+                     "embedding + norm + tied head + soft-cap + CE, forward + backward + AdamW, on %d sequences x %d positions "
+                     "(%.1f s measured); %s" % (LM_CPU_SAMPLE["B"], LM_CPU_SAMPLE["T"], s["measured_s"], s["formula"]),
+           "seconds_measured": s["measured_s"], "extrapolated_step_s": s["step_s"], "pieces_s": s["pieces"]}
+    if with_one_core:
+        s1 = cpu_lm_sample(args, LM_CPU_SAMPLE_1CORE, threads=1)
+        out["one_core"] = {"value": s1["tokens_per_s"], "unit": "tokens/s", "cores": 1,
+                           "sample": "same pieces on %d x %d, BLAS and OpenMP limited to one thread (%.1f s measured)"
+                                     % (LM_CPU_SAMPLE_1CORE["B"], LM_CPU_SAMPLE_1CORE["T"], s1["measured_s"])}
+    return out, s
 
 
 def run_reference(args):
+    """The reference arm: the CPU restatement on the host cores (rank 0 only), same config / metric / unit as the engine's arm."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    times = []
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    if args.workload == "mlstm":
+        times = []
+        for i in range(args.warmup + args.steps):
+            s = cpu_mlstm_sample()
+            if i >= args.warmup:
+                times.append(s["seconds"])
+        t = float(np.mean(times))
+        val = s["flops"] / t / 1e12
+        one = cpu_mlstm_sample(seqs=1, threads=1)
+        sample = "%d of 16 sequences x 2048 positions x 8 heads, recurrent f32 restatement, OpenMP over (batch, head)" % s["seqs"]
+        line = {"impl": "reference", "metric": "mlstm_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": mlstm_config_dict(args, world),
+                "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": s["threads"], "kind": "port", "sample": sample,
+                                 "one_core": {"value": one["flops"] / one["seconds"] / 1e12, "unit": "TFLOP/s", "cores": 1,
+                                              "sample": "1 of 16 sequences, one thread"}},
+                "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+    vals, secs = [], []
     for i in range(args.warmup + args.steps):
-        s = cpu_sample()
+        s = cpu_lm_sample(args, LM_CPU_SAMPLE)
         if i >= args.warmup:
-            times.append(s["seconds"])
-    t = float(np.mean(times))
-    val = s["flops"] / t / 1e12
-    line = {
-        "impl": "reference", "metric": "mlstm_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "mlstm_layer_fwd_bwd B16 H8 S2048 dqk128 dv128 chunk64 (configs[1])",
-                   "sample": "B=%d of 16 sequences, full length" % s["Bs"]},
-        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": s["threads"], "kind": "port",
-                         "sample": "%d of 16 sequences x 2048 positions x 8 heads, recurrent f32 oracle, OpenMP over (batch, head)" % s["Bs"]},
-        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "tokens_per_s": s["tokens"] / t,
-    }
+            vals.append(s["tokens_per_s"]); secs.append(s["measured_s"])
+    val = float(np.mean(vals))
+    cb, _ = lm_cpu_baseline(args, with_one_core=True)
+    cb["value"] = val
+    line = {"impl": "reference", "metric": "train_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(np.mean(secs)) * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": lm_config_dict(args, world),
+            "cpu_baseline": cb,
+            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "each step runs the fixed sample (ms_per_step is the sample's wall time); value is the full model's "
+                    "tokens/s on the full per-GPU batch extrapolated from it on one host (the reference has no multi-GPU path)"}
     print(json.dumps(line))
 
 
-def run_ours(args):
+def mlstm_config_dict(args, world):
+    cfg = CFG
+    gb = 2 if args.grad_dtype == "bf16" else 4
+    bf, bb = algorithmic_bytes(cfg["B"], cfg["H"], cfg["T"], cfg["dqk"], cfg["dhv"], gb)
+    return {"workload": "mlstm_layer_fwd_bwd B16 H8 S2048 dqk128 dv128 chunk64 (configs[1])", "per_gpu_batch": cfg["B"],
+            "grad_dtype": args.grad_dtype, "chunk_states": "recomputed in backward" if args.recompute else "saved by forward",
+            "l2": "inputs (%.0f MB) larger than L2" % ((bf + bb) / 1e6), "parallelism": "dp%d (batch shards, no collective)" % world}
+
+
+def _dist_env():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def measure_mlstm_pair(args, steps, warmup=3, with_e2e=False):
+    """The configs[1] kernel pair on this rank's GPU: device-timed steps with inputs resident (CUDA events around the
+    whole run and around each op), optionally the same step end to end from pinned host buffers. Returns a dict of
+    this rank's figures (no collectives)."""
     import torch
-    import torch.distributed as dist
     xl = importlib.import_module("neural-networks_b200")
     ops = xl.ops
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world, local = _dist_env()
     cfg = dict(CFG)
     gd = torch.bfloat16 if args.grad_dtype == "bf16" else torch.float32
     st = ops.MlstmShape(cfg["B"], cfg["H"], cfg["T"], cfg["dqk"], cfg["dhv"], cfg["L"], torch.bfloat16, gd, 0)
@@ -187,192 +355,224 @@ def run_ours(args):
     torch.cuda.synchronize()
     q, k, v, ig, fg, dy = dev_in
 
-    marks = []  # (before forward, between, after backward) events of every timed step
-
-    def step(timed=False):
-        if timed:
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-            marks.append(ev)
-            ev[0].record()
+    def step():
         fused = ops.mlstm_fused_fw(q, k, v, ig, fg, st, save_states=not args.recompute, want_state=False)
-        if timed:
-            ev[1].record()
-        g = ops.mlstm_fused_bw(fused, q, k, v, ig, fg, dy, st, want_dstate=False)
-        if timed:
-            ev[2].record()
-        return fused, g
+        return fused, ops.mlstm_fused_bw(fused, q, k, v, ig, fg, dy, st, want_dstate=False)
+
+    for _ in range(max(warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    launches0 = xl._lib.lib.xlstm_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ops.timing_start(("mlstm_fused_fw", "mlstm_fused_bw"))
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    per_op = ops.timing_stop()  # synchronises
+    ms_per_step = e0.elapsed_time(e1) / steps
+    launches = xl._lib.lib.xlstm_launch_count() - launches0
+    # the device runs behind the host here, so the gap between an op's two events is its kernels and nothing else
+    fw_t, bw_t = float(np.median(per_op["mlstm_fused_fw"])), float(np.median(per_op["mlstm_fused_bw"]))
+    ff, fb = flops_fwd_bwd(**cfg)
+    gb = 2 if gd == torch.bfloat16 else 4
+    bf, bb = algorithmic_bytes(cfg["B"], cfg["H"], cfg["T"], cfg["dqk"], cfg["dhv"], gb)
+    pk = peaks()
+    out = dict(ms_per_step=ms_per_step, fw_ms=fw_t, bw_ms=bw_t, flops=ff + fb, bytes_fw=bf, bytes_bw=bb, launches=int(launches),
+               tflops=(ff + fb) / (ms_per_step * 1e-3) / 1e12, tokens=cfg["B"] * cfg["T"],
+               bw_gbs=bb / (bw_t * 1e-3) / 1e9, fw_gbs=bf / (fw_t * 1e-3) / 1e9, peaks=pk)
+    if with_e2e:
+        # Every step copies its inputs from pinned host memory, runs forward + backward through `ops`, and copies every
+        # result back to pinned host memory; all of it is inside the timed region. The three stages run on three
+        # streams with double-buffered device inputs, so step i+1's upload and step i-1's download overlap step i
+        # (PCIe is full duplex): steady state is the slower of the two copy directions, not their sum.
+        s_in, s_out, s_cmp = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+        dbuf = [[torch.empty(t.shape, dtype=t.dtype, device="cuda") for t in host_in] for _ in range(2)]
+        state = {"outs_host": None, "free": [None, None]}
+
+        def e2e_run(nsteps):
+            last_out = None
+            for i in range(nsteps):
+                j = i & 1
+                with torch.cuda.stream(s_in):
+                    if state["free"][j] is not None:
+                        s_in.wait_event(state["free"][j])
+                    for dst, src in zip(dbuf[j], host_in):
+                        dst.copy_(src, non_blocking=True)
+                    ev_in = torch.cuda.Event(); ev_in.record(s_in)
+                s_cmp.wait_event(ev_in)
+                d = dbuf[j]
+                fused = ops.mlstm_fused_fw(d[0], d[1], d[2], d[3], d[4], st, save_states=not args.recompute, want_state=False)
+                g = ops.mlstm_fused_bw(fused, d[0], d[1], d[2], d[3], d[4], d[5], st, want_dstate=False)
+                res = [fused.ytil, g[0], g[1], g[2], g[3], g[4]]
+                ev_c = torch.cuda.Event(); ev_c.record(s_cmp)
+                state["free"][j] = ev_c
+                if state["outs_host"] is None:
+                    state["outs_host"] = [[torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res] for _ in range(2)]
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_c)
+                    for h, r in zip(state["outs_host"][j], res):
+                        r.record_stream(s_out)
+                        h.copy_(r, non_blocking=True)
+                    last_out = torch.cuda.Event(); last_out.record(s_out)
+            s_cmp.wait_event(last_out)  # the timed region ends when the last result is on the host
+
+        e2e_steps = max(2, min(steps, 6))
+        e2e_run(2)
+        torch.cuda.synchronize()
+        e0.record()
+        e2e_run(e2e_steps)
+        e1.record()
+        torch.cuda.synchronize()
+        out["e2e_ms"] = e0.elapsed_time(e1) / e2e_steps
+        out["h2d"] = sum(t.numel() * t.element_size() for t in host_in)
+        out["d2h"] = sum(t.numel() * t.element_size() for t in state["outs_host"][0])
+    return out
+
+
+def mlstm_pair_summary(m):
+    """The sub-object the LM line carries for the configs[1] kernel pair."""
+    pk = m["peaks"]
+    return {"value": m["tflops"], "unit": "TFLOP/s", "workload": "mlstm_layer_fwd_bwd B16 H8 S2048 dqk128 dv128 chunk64 (configs[1]), this rank",
+            "ms_per_step": m["ms_per_step"], "frac_of_bf16_peak": m["tflops"] / pk["tensor"],
+            "forward": {"launch_ms": m["fw_ms"], "algorithmic_bytes": m["bytes_fw"], "achieved_gbs": m["fw_gbs"], "frac_of_hbm_peak": m["fw_gbs"] / pk["hbm"]},
+            "backward": {"launch_ms": m["bw_ms"], "algorithmic_bytes": m["bytes_bw"], "achieved_gbs": m["bw_gbs"], "frac_of_hbm_peak": m["bw_gbs"] / pk["hbm"]},
+            "tokens_per_s": m["tokens"] / (m["ms_per_step"] * 1e-3), "peak_source": pk["src"]}
+
+
+def run_mlstm(args):
+    """Secondary workload: the configs[1] kernel pair as the whole line (device-timed, end to end from pinned host buffers,
+    CPU baseline)."""
+    import torch
+    import torch.distributed as dist
+    rank, world, local = _dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    m = measure_mlstm_pair(args, args.steps, args.warmup, with_e2e=True)
+    clocks = sampler.stop() if rank == 0 else None
+    ms, e2e_ms = m["ms_per_step"], m["e2e_ms"]
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0].item()), float(t[1].item())
+    if rank == 0:
+        pk = m["peaks"]
+        value = m["flops"] * world / (ms * 1e-3) / 1e12
+        line = {"metric": "mlstm_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "bf16", "data": "synthetic", "config": mlstm_config_dict(args, world),
+                "tokens_per_s": m["tokens"] * world / (ms * 1e-3), "frac_of_bf16_peak": value / world / pk["tensor"],
+                "roofline": {"kernel": "mlstm backward", "bound": "hbm", "achieved": m["bw_gbs"], "peak": pk["hbm"], "unit": "GB/s",
+                             "frac": m["bw_gbs"] / pk["hbm"], "traffic": None, "peak_source": pk["src"],
+                             "algorithmic_bytes": m["bytes_bw"], "launch_ms": m["bw_ms"],
+                             "forward": {"achieved": m["fw_gbs"], "frac": m["fw_gbs"] / pk["hbm"], "algorithmic_bytes": m["bytes_fw"],
+                                         "launch_ms": m["fw_ms"], "traffic": None}},
+                "e2e": {"value": m["flops"] * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": m["h2d"],
+                        "d2h_bytes_per_step": m["d2h"], "ms_per_step": e2e_ms},
+                "gpu_launches": m["launches"], "clocks": clocks}
+        if world == 1 and not args.no_cpu:
+            cpu = cpu_mlstm_sample()
+            one = cpu_mlstm_sample(seqs=1, threads=1)
+            line["cpu_baseline"] = {"value": cpu["flops"] / cpu["seconds"] / 1e12, "unit": "TFLOP/s", "cores": cpu["threads"], "kind": "port",
+                                    "seconds": cpu["seconds"],
+                                    "sample": "%d of 16 sequences x 2048 positions x 8 heads, recurrent f32 restatement, OpenMP over (batch, head)" % cpu["seqs"],
+                                    "one_core": {"value": one["flops"] / one["seconds"] / 1e12, "unit": "TFLOP/s", "cores": 1,
+                                                 "sample": "1 of 16 sequences, one thread"}}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def mlstm_op_bytes(B, H, T, dqk, dhv, gbytes):
+    """Compulsory HBM traffic of the fused forward and backward ops at a shape (chunk states excluded)."""
+    return algorithmic_bytes(B, H, T, dqk, dhv, gbytes)
+
+
+DP_CHECK_CFG = dict(vocab=64, d=256, blocks=2, heads=2, dqk=128, dhv=128, up=256, B=2, T=128)
+
+
+def dp_parity_check(world, rank):
+    """A small bf16 model's gradients after the bucketed all-reduce over `world` ranks against one rank on the
+    concatenated batch (same kernels per sequence; only the fp32 summation order over the batch differs). Returns the
+    largest error relative to each tensor's largest gradient, maximised over tensors and ranks."""
+    import torch
+    import torch.distributed as dist
+    layers = importlib.import_module("neural-networks_b200.layers")
+    dp = importlib.import_module("neural-networks_b200.dp")
+    c = DP_CHECK_CFG
+
+    def build():
+        p = layers.init_lm_params(np.random.default_rng(0), c["vocab"], c["d"], c["blocks"], c["heads"], c["dqk"], c["dhv"], c["up"], std=0.05)
+        return layers.build_lm(p, c["heads"], c["dqk"], c["dhv"], tied=True, bf16=True)
+
+    ids = torch.tensor(np.random.default_rng(7).integers(0, c["vocab"], (world * c["B"], c["T"] + 1)), device="cuda")
+    lm = build()
+    buckets = dp.attach(lm)
+    mine = ids[rank * c["B"]:(rank + 1) * c["B"]]
+    lm.forward_backward(mine[:, :-1].reshape(-1), mine[:, 1:].reshape(-1).to(torch.int32), c["B"], c["T"], inv=1.0 / (c["B"] * c["T"] * world))
+    buckets.reduce_async(len(lm.blocks))
+    buckets.wait()
+    one = build()
+    one.forward_backward(ids[:, :-1].reshape(-1), ids[:, 1:].reshape(-1).to(torch.int32), world * c["B"], c["T"])
+    worst = 0.0
+    for a, b in zip(lm.params(), one.params()):
+        scale = max(b.g.abs().max().item(), 1e-12)
+        worst = max(worst, (a.g - b.g).abs().max().item() / scale)
+    t = torch.tensor([worst], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item()), bool(buckets.native)
+
+
+def run_lm(args):
+    """Default workload: the data-parallel training step of the configs[3] language model (see the module docstring)."""
+    import torch
+    import torch.distributed as dist
+    xl = importlib.import_module("neural-networks_b200")
+    layers = importlib.import_module("neural-networks_b200.layers")
+    dp = importlib.import_module("neural-networks_b200.dp")
+    ops = xl.ops
+    rank, world, local = _dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
+    # ---- the configs[1] kernel pair, in this process, before the model takes the memory ---------------------------------
+    pair = measure_mlstm_pair(args, 20, 3) if not args.no_pair else None
+    torch.cuda.empty_cache()
+    # ---- multi-GPU correctness carried in the record: N-rank gradients against one rank -------------------------------
+    parity = dp_parity_check(world, rank) if world > 1 else None
 
-    # ---- device-timed steps (inputs resident) -------------------------------------------
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    launches0 = xl._lib.lib.xlstm_launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step(timed=True)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    launches = xl._lib.lib.xlstm_launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
-    if world > 1:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms_per_step = ms / args.steps
-
-    # ---- per-kernel durations for the roofline: CUDA events around each op inside the timed region above.
-    # The device runs behind the host there, so the gap between two marks is the op's kernels and nothing else.
-    fw_t = float(np.median([m[0].elapsed_time(m[1]) for m in marks]))
-    bw_t = float(np.median([m[1].elapsed_time(m[2]) for m in marks]))
-
-    # ---- end to end from pinned host buffers ----------------------------------------------
-    # Every step copies its inputs from pinned host memory, runs forward + backward through `ops`, and copies every
-    # result back to pinned host memory; all of it is inside the timed region. The three stages run on three
-    # streams with double-buffered device inputs, so step i+1's upload and step i-1's download overlap step i
-    # (PCIe is full duplex): steady state is the slower of the two copy directions, not their sum.
-    s_in, s_out, s_cmp = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
-    dbuf = [[torch.empty(t.shape, dtype=t.dtype, device="cuda") for t in host_in] for _ in range(2)]
-    outs_host = None
-    free_ev = [None, None]  # compute finished reading device-input set j
-
-    def e2e_run(nsteps):
-        nonlocal outs_host
-        last_out = None
-        for i in range(nsteps):
-            j = i & 1
-            with torch.cuda.stream(s_in):
-                if free_ev[j] is not None:
-                    s_in.wait_event(free_ev[j])
-                for dst, src in zip(dbuf[j], host_in):
-                    dst.copy_(src, non_blocking=True)
-                ev_in = torch.cuda.Event(); ev_in.record(s_in)
-            s_cmp.wait_event(ev_in)
-            d = dbuf[j]
-            fused = ops.mlstm_fused_fw(d[0], d[1], d[2], d[3], d[4], st, save_states=not args.recompute, want_state=False)
-            g = ops.mlstm_fused_bw(fused, d[0], d[1], d[2], d[3], d[4], d[5], st, want_dstate=False)
-            res = [fused.ytil, g[0], g[1], g[2], g[3], g[4]]
-            ev_c = torch.cuda.Event(); ev_c.record(s_cmp)
-            free_ev[j] = ev_c
-            if outs_host is None:
-                outs_host = [[torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res] for _ in range(2)]
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_c)
-                for h, r in zip(outs_host[j], res):
-                    r.record_stream(s_out)
-                    h.copy_(r, non_blocking=True)
-                last_out = torch.cuda.Event(); last_out.record(s_out)
-        s_cmp.wait_event(last_out)  # the timed region ends when the last result is on the host
-
-    e2e_steps = max(2, min(args.steps, 6))
-    e2e_run(2)
-    barrier()
-    e0.record()
-    e2e_run(e2e_steps)
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([e2e_ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_ms /= e2e_steps
-    h2d = sum(t.numel() * t.element_size() for t in host_in)
-    d2h = sum(t.numel() * t.element_size() for t in outs_host[0])
-
-    if rank == 0:
-        ff, fb = flops_fwd_bwd(**cfg)
-        gb = 2 if gd == torch.bfloat16 else 4
-        bf, bb = algorithmic_bytes(cfg["B"], cfg["H"], cfg["T"], cfg["dqk"], cfg["dhv"], gb)
-        pk = peaks()
-        tokens = cfg["B"] * cfg["T"]
-        value = (ff + fb) * world / (ms_per_step * 1e-3) / 1e12
-        achieved = bb / (bw_t * 1e-3) / 1e9
-        # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of this workload at its default
-        # settings (profiles/mlstm_tc_cfg2.md); includes the 138 MB chunk-state record, which the algorithmic bytes
-        # leave out. Other settings were not captured.
-        default_cfg = args.grad_dtype == "f32" and not args.recompute and cfg["B"] == 16
-        traffic = {"bw": 545305088 + 368029952, "fw": 203553280 + 163480320} if default_cfg else {"bw": None, "fw": None}
-        cpu = cpu_sample() if world == 1 and not args.no_cpu else None
-        line = {
-            "metric": "mlstm_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "mlstm_layer_fwd_bwd B16 H8 S2048 dqk128 dv128 chunk64 (configs[1])",
-                       "per_gpu_batch": cfg["B"], "grad_dtype": args.grad_dtype,
-                       "chunk_states": "recomputed in backward" if args.recompute else "saved by forward",
-                       "l2": "inputs (%.0f MB) larger than L2" % ((bf + bb) / 1e6), "parallelism": "dp%d (batch shards, no collective)" % world},
-            "tokens_per_s": tokens * world / (ms_per_step * 1e-3),
-            "frac_of_bf16_peak": value / world / pk["tensor"],
-            "roofline": {"kernel": "mlstm backward", "bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
-                         "frac": achieved / pk["hbm"], "traffic": traffic["bw"], "peak_source": pk["src"],
-                         "algorithmic_bytes": bb, "launch_ms": bw_t,
-                         "forward": {"achieved": bf / (fw_t * 1e-3) / 1e9, "frac": bf / (fw_t * 1e-3) / 1e9 / pk["hbm"],
-                                     "algorithmic_bytes": bf, "launch_ms": fw_t, "traffic": traffic["fw"]}},
-            "e2e": {"value": (ff + fb) * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-            "gpu_launches": int(launches),
-            "clocks": clocks,
-        }
-        if cpu is not None:
-            line["cpu_baseline"] = {"value": cpu["flops"] / cpu["seconds"] / 1e12, "unit": "TFLOP/s", "cores": cpu["threads"],
-                                    "kind": "port", "seconds": cpu["seconds"],
-                                    "sample": "%d of 16 sequences x 2048 positions x 8 heads, recurrent f32 oracle, OpenMP over (batch, head)" % cpu["Bs"]}
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
-
-
-LM_CFG = dict(vocab=50304, d=1024, blocks=24, heads=8, dqk=128, dhv=128, slstm_every=8, slstm_heads=4, B=8, T=4096)
-# configs[3] at its own widths: d = 2048, mLSTM 8 heads x 256, sLSTM 4 heads x 512
-LM_CFG_FULL = dict(vocab=50304, d=2048, blocks=24, heads=8, dqk=256, dhv=256, slstm_every=8, slstm_heads=4, B=8, T=4096)
-
-
-def run_lm(args):
-    """Secondary workload: a data-parallel training step of an xLSTM LM with configs[3]'s structure
-    (24 blocks, one sLSTM per 8, vocab 50304, per-GPU batch 8 x 4096, bf16 GEMM operands, fp32 master
-    weights, AdamW) at d = 1024 with mLSTM heads of 128 and sLSTM heads of 256 -- the widths the
-    kernels cover today (configs[3] itself asks for d = 2048 with heads of 256 / 512)."""
-    import torch
-    import torch.distributed as dist
-    xl = importlib.import_module("neural-networks_b200")
-    layers = importlib.import_module("neural-networks_b200.layers")
-    dp = importlib.import_module("neural-networks_b200.dp")
-    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    c = dict(LM_CFG_FULL if args.lm_full else LM_CFG)
-    if args.lm_blocks:
-        c["blocks"] = args.lm_blocks
-    up = (8 * c["d"] // 3 + 7) // 8 * 8
+    c = lm_cfg(args)
     rng = np.random.default_rng(0)  # identical replicas on every rank
-    slstm_at = tuple(i for i in range(c["blocks"]) if i % c["slstm_every"] == 0)
-    p = layers.init_lm_params(rng, c["vocab"], c["d"], c["blocks"], c["heads"], c["dqk"], c["dhv"], up, std=0.02, slstm_at=slstm_at,
-                         nh_s=c["slstm_heads"])
-    # full widths: the first `--lm-remat` mLSTM blocks keep only their input and re-run their forward in the
-    # backward, so that 24 blocks fit in HBM; sLSTM blocks (the long sequential loops) are never re-run
-    remat = [i for i in range(c["blocks"]) if i not in slstm_at][:args.lm_remat] if args.lm_full else ()
-    # (the reduced model needs none); the head runs row-chunked with fp32-accurate split-bf16 products in both
-    lm = layers.build_lm(p, c["heads"], c["dqk"], c["dhv"], nh_s=c["slstm_heads"], tied=True, bf16=True,
-                         remat=remat, head_rows=4096, head_split=True)
+    p = layers.init_lm_params(rng, c["vocab"], c["d"], c["blocks"], c["heads"], c["dqk"], c["dhv"], c["up"], std=0.02,
+                              slstm_at=c["slstm_at"], nh_s=c["slstm_heads"])
+    # the first `--lm-remat` mLSTM blocks keep only their input and re-run their forward in the backward, so that 24
+    # blocks of activations fit in HBM; sLSTM blocks (the long sequential loops) are never re-run. The head runs
+    # row-chunked with fp32-accurate split-bf16 products.
+    remat = [i for i in range(c["blocks"]) if i not in c["slstm_at"]][:args.lm_remat] if not args.lm_reduced else ()
+    lm = layers.build_lm(p, c["heads"], c["dqk"], c["dhv"], nh_s=c["slstm_heads"], tied=True, bf16=True, remat=remat,
+                         head_rows=4096, head_split=True, recompute_states=args.recompute)
+    del p
     nparams = sum(q.w.numel() for q in lm.params())
     buckets = dp.attach(lm)
     B, T = c["B"], c["T"]
     g = torch.Generator().manual_seed(1234 + rank)
     host_ids = torch.randint(0, c["vocab"], (B, T + 1), generator=g).pin_memory()
-    cfg = xl.ops.AdamCfg(1e-3, 0.1, t=0)
+    cfg = ops.AdamCfg(1e-3, 0.1, t=0)
 
     def step():
         cfg.t += 1
@@ -381,57 +581,107 @@ def run_lm(args):
         tg = d[:, 1:].reshape(-1).to(torch.int32)
         return dp.train_step(lm, buckets, ids, tg, B, T, cfg)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
+    loss_step1 = None
+    for i in range(max(args.warmup, 3)):
         loss = step()
+        if i == 0:
+            loss_step1 = float(loss.item()) * world  # each rank holds its share of the global mean
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    buckets.time_wait = world > 1
+    exposed = []
     l0 = xl._lib.lib.xlstm_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ops.timing_start(("mlstm_fused_fw", "mlstm_fused_bw", "slstm_fused_time", "slstm_fused_time_bwd"))
     barrier()
     e0.record()
     for _ in range(args.steps):
         loss = step()
         lv = loss.item()  # the step's result read back on the host, as a training loop does
+        if world > 1:
+            exposed.append(buckets.exposed_ms())
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
     launches = xl._lib.lib.xlstm_launch_count() - l0
+    per_op = ops.timing_stop()
     clocks = sampler.stop() if rank == 0 else None
+    buckets.time_wait = False
+    exposed_ms = float(np.mean(exposed)) if exposed else 0.0
     if world > 1:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        t = torch.tensor([ms, exposed_ms, lv], device="cuda")
+        mx = t.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = t.clone(); dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, exposed_ms, lv = float(mx[0].item()), float(mx[1].item()), float(sm[2].item())
     ms /= args.steps
+
+    # ---- one extra instrumented step: device time of every library op and of the library GEMMs ---------------------------
+    kernels = None
+    if not args.no_kernels:
+        saved = (torch.mm, torch.addmm, torch.bmm)
+        torch.mm, torch.addmm, torch.bmm = (ops.timed("library_gemm")(f) for f in saved)
+        try:
+            ops.timing_start(None)
+            es0, es1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            es0.record()
+            step().item()
+            es1.record()
+            table = ops.timing_stop()
+        finally:
+            torch.mm, torch.addmm, torch.bmm = saved
+        step_ms = es0.elapsed_time(es1)
+        kernels = {k: {"calls": len(v), "ms": float(np.sum(v))} for k, v in sorted(table.items())}
+        acc = sum(v["ms"] for v in kernels.values())
+        kernels["other (eager element-wise, copies, gaps)"] = {"calls": None, "ms": max(step_ms - acc, 0.0)}
+        kernels["instrumented_step_ms"] = step_ms
+    barrier()
+
     if rank == 0:
         tokens = B * T
         pk = peaks()
+        val = tokens * world / (ms * 1e-3)
+        gbytes = 2  # bf16 gradient I/O of the core in bf16 mode
+        bfw, bbw = mlstm_op_bytes(B, c["heads"], T, c["dqk"], c["dhv"], gbytes)
+        bw_calls = per_op.get("mlstm_fused_bw", [])
+        fw_calls = per_op.get("mlstm_fused_fw", [])
+        bw_ms = float(np.mean(bw_calls)) if bw_calls else None
+        fw_ms = float(np.mean(fw_calls)) if fw_calls else None
+        ff, fb = flops_fwd_bwd(B, c["heads"], T, c["dqk"], c["dhv"], 64)
+        roof = {"kernel": "mlstm backward op at the model's shape (B%d H%d S%d dqk%d dv%d chunk 64, bf16 gradient I/O)" % (B, c["heads"], T, c["dqk"], c["dhv"]),
+                "bound": "hbm", "achieved": bbw / (bw_ms * 1e-3) / 1e9 if bw_ms else None, "peak": pk["hbm"], "unit": "GB/s",
+                "frac": bbw / (bw_ms * 1e-3) / 1e9 / pk["hbm"] if bw_ms else None, "traffic": None, "peak_source": pk["src"],
+                "algorithmic_bytes": bbw, "launch_ms": bw_ms, "launches_timed": len(bw_calls),
+                "tflops": fb / (bw_ms * 1e-3) / 1e12 if bw_ms else None,
+                "forward": {"launch_ms": fw_ms, "algorithmic_bytes": bfw, "achieved": bfw / (fw_ms * 1e-3) / 1e9 if fw_ms else None,
+                            "frac": bfw / (fw_ms * 1e-3) / 1e9 / pk["hbm"] if fw_ms else None, "launches_timed": len(fw_calls),
+                            "tflops": ff / (fw_ms * 1e-3) / 1e12 if fw_ms else None}}
+        sl = {k: float(np.mean(per_op[k])) * 1e3 / T for k in ("slstm_fused_time", "slstm_fused_time_bwd") if per_op.get(k)}
         sustained = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))).get("bf16_tflops_sustained", pk["tensor"]) \
             if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else 1400.0
-        flops = 6.0 * nparams * tokens
-        val = tokens * world / (ms * 1e-3)
+        dense = 6.0 * nparams * tokens / (ms * 1e-3) / 1e12
         line = {"metric": "train_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": ("xlstm_lm_train_step (configs[3] widths: d=%d, mLSTM %dx%d, sLSTM %dx%d)" if args.lm_full else
-                                        "xlstm_lm_train_step (reduced stand-in for configs[3]: d=%d, mLSTM %dx%d, sLSTM %dx%d)")
-                                       % (c["d"], c["heads"], c["dqk"], c["slstm_heads"], c["d"] // c["slstm_heads"]),
-                           "blocks": c["blocks"], "vocab": c["vocab"], "params": nparams, "per_gpu_batch": [B, T],
-                           "parallelism": "dp%d (gradient all-reduce per block, overlapped with backward)" % world,
-                           "l2": "activations far larger than L2"},
-                "loss": lv, "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
-                "roofline": {"kernel": "whole step (6*P*tokens dense FLOPs)", "bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12,
-                             "peak": sustained, "unit": "TFLOP/s", "frac": flops / (ms * 1e-3) / 1e12 / sustained, "traffic": None,
-                             "peak_source": pk["src"] + " (sustained)"},
+                "dtype": "bf16", "data": "synthetic", "config": lm_config_dict(args, world),
+                "params": nparams, "loss_step1": loss_step1, "loss_expected_at_init": math.log(c["vocab"]), "loss": lv,
+                "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
+                "roofline": roof,
+                "slstm_us_per_timestep": sl,
+                "dense_equivalent": {"tflops_per_gpu": dense, "frac_of_sustained_bf16_peak": dense / sustained, "formula": "6 * params * tokens / step time"},
                 "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": host_ids.numel() * 8, "d2h_bytes_per_step": 4,
-                        "note": "the timed step already starts from pinned host ids and reads the loss back"},
+                        "note": "the timed step starts from pinned host ids and reads the loss back: value and e2e are the same measurement"},
                 "gpu_launches": int(launches), "clocks": clocks}
+        if kernels is not None:
+            line["kernels"] = kernels
+        if pair is not None:
+            line["mlstm_fwd_bwd_tflops"] = mlstm_pair_summary(pair)
+        if world > 1:
+            line["allreduce_exposed_ms"] = exposed_ms
+            line["dp_parity_max_rel"] = parity[0]
+            line["dp_native_buckets"] = parity[1]
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"], _ = lm_cpu_baseline(args)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -643,18 +893,21 @@ def run_cp(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--grad-dtype", default="f32", choices=["f32", "bf16"])
-    ap.add_argument("--recompute", action="store_true", help="backward recomputes chunk-boundary states")
+    ap.add_argument("--workload", default="lm", choices=["lm", "mlstm", "ops", "hier", "cp"],
+                    help="lm: data-parallel training step of the configs[3] model (headline); mlstm: the configs[1] layer kernel pair; "
+                         "ops: the other hot-path kernels alone; hier: configs[4] hierarchical training step; cp: the layer kernel "
+                         "with sequences cut over the GPUs")
+    ap.add_argument("--grad-dtype", default="f32", choices=["f32", "bf16"], help="mlstm workload: width of d_ytil, dq, dk, dv")
+    ap.add_argument("--recompute", action="store_true", help="backward recomputes chunk-boundary states instead of reading a saved record")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--workload", default="mlstm", choices=["mlstm", "lm", "ops", "hier", "cp"],
-                    help="mlstm: configs[1] layer kernel (headline); lm: training step; ops: the other hot-path kernels alone; "
-                         "hier: configs[4] hierarchical training step; cp: the layer kernel with sequences cut over the GPUs")
+    ap.add_argument("--no-pair", action="store_true", help="lm workload: skip the configs[1] kernel-pair measurement")
+    ap.add_argument("--no-kernels", action="store_true", help="lm workload: skip the instrumented step behind `kernels`")
     ap.add_argument("--lm-blocks", type=int, default=0, help="override the LM depth (development)")
-    ap.add_argument("--lm-remat", type=int, default=2, help="blocks rematerialised in the full-width LM workload")
-    ap.add_argument("--lm-full", action="store_true", help="LM workload at the full widths of configs[3] (d=2048, heads of 256 / 512)")
+    ap.add_argument("--lm-remat", type=int, default=2, help="mLSTM blocks rematerialised in the LM workload")
+    ap.add_argument("--lm-reduced", action="store_true", help="LM workload at half width (d=1024, heads of 128 / 256): development stand-in")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -667,7 +920,7 @@ def main():
     elif args.workload == "cp":
         run_cp(args)
     else:
-        run_ours(args)
+        run_mlstm(args)
 
 
 if __name__ == "__main__":
