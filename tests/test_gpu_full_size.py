@@ -65,13 +65,13 @@ def test_mlstm_full_size_sample_against_oracle_carry_and_linearity(B, H, T, d, h
     f0 = ops.mlstm_fused_fw(*(half(a, 0) for a in (q, k, v, ig, fg)), sth)
     f1 = ops.mlstm_fused_fw(*(half(a, 1) for a in (q, k, v, ig, fg)), sth, carry_in=f0.state)
     y2 = torch.cat([f0.ytil.view(B, Th, -1), f1.ytil.view(B, Th, -1)], dim=1).reshape(B * T, -1)
-    assert float((y2.float() - fused.ytil.float()).abs().max()) <= 3e-2 * float(fused.ytil.float().abs().max())
+    assert float((y2.float() - fused.ytil.float()).abs().max()) <= 2e-2 * float(fused.ytil.float().abs().max())
     g1 = ops.mlstm_fused_bw(f1, *(half(a, 1) for a in (q, k, v, ig, fg)), half(dy, 1), sth, carry_in=f0.state)
     g0 = ops.mlstm_fused_bw(f0, *(half(a, 0) for a in (q, k, v, ig, fg)), half(dy, 0), sth, dstate_in=g1[5])
     for i, name in enumerate(("dq", "dk", "dv", "dig", "dfg")):
         joined = torch.cat([g0[i].view(B, Th, -1), g1[i].view(B, Th, -1)], dim=1).reshape(B * T, -1)
         whole = grads[i].view(B * T, -1)
-        assert float((joined - whole).abs().max()) <= 3e-2 * float(whole.abs().max()), name
+        assert float((joined - whole).abs().max()) <= 2e-2 * float(whole.abs().max()), name
 
     # (3) the backward is linear in dy
     dy2 = _gen((B * T, H * d), 7)

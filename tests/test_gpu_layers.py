@@ -122,3 +122,24 @@ def test_split_bf16_product_is_fp32_accurate():
     e_split = float((got.double() - ref).abs().max()) / scale
     e_plain = float((plain.double() - ref).abs().max()) / scale
     assert e_split <= max(2.0 * e_plain, 2e-6), (e_split, e_plain)
+
+
+def test_recomputed_chunk_states_leave_the_step_bit_identical():
+    """`recompute_states`: training keeps no chunk-state record and the backward rebuilds the chunk-boundary
+    states (the reference stores them for every chunk, src/gpu/ops.rs:3955-3967). Loss and every gradient of a
+    two-block bf16 LM on the tensor-core cells are bit-identical with the switch on."""
+    layers = importlib.import_module("neural-networks_b200.layers")
+    vocab, d, nb, heads, dqk, dhv, up, B, T = 64, 256, 2, 2, 128, 128, 680, 2, 200
+    rng = np.random.default_rng(11)
+    p = M.init_lm_params(rng, vocab, d, nb, heads, dqk, dhv, up, std=0.05)
+    ids = torch.tensor(rng.integers(0, vocab, B * T), dtype=torch.int64, device="cuda")
+    tg = torch.tensor(rng.integers(0, vocab, B * T).astype(np.int32), device="cuda")
+    out = []
+    for rec in (False, True):
+        lm = layers.build_lm(p, heads, dqk, dhv, tied=True, bf16=True, recompute_states=rec)
+        loss = lm.forward_backward(ids, tg, B, T).item()
+        assert all((blk.cell.fused is None) for blk in lm.blocks)  # released after the backward
+        out.append((loss, [q.g.clone() for q in lm.params()]))
+    assert out[0][0] == out[1][0]
+    for i, (a, b) in enumerate(zip(out[0][1], out[1][1])):
+        assert torch.equal(a, b), i

@@ -197,3 +197,48 @@ def test_final_state_alone_equals_the_forwards_final_state(shape, L, dtype):
         assert xl._lib.lib.xlstm_device_status() == 0
         for a, b in zip(alone, full):
             assert torch.equal(a, b)
+
+
+def test_caller_buffers_reused_across_shapes_with_stale_contents():
+    """The boundary's ownership rule (caller allocates every buffer, possibly larger than the shape and holding
+    stale data; the callee writes every element of its outputs; src/gpu/buf.rs:24-30, and the reference's own
+    pooled-buffer test src/gpu/slstm.rs:1615-1647): one set of oversized, NaN-poisoned output, record and
+    workspace buffers serves calls of three different shapes in a row, and each call's results are bit-identical
+    to the same call on fresh exact-size buffers."""
+    import ctypes
+    from gpu_util import ops, xl
+    lib, L = xl._lib.lib, xl._lib
+    shapes = [(2, 2, 200, 128, 128), (1, 4, 64, 128, 128), (2, 1, 130, 256, 256), (2, 2, 200, 128, 128)]
+    big = 1 << 26  # bytes per pooled buffer
+    pool = {n: torch.empty(big, dtype=torch.uint8, device="cuda") for n in
+            ("ytil", "msv", "psiv", "qnv", "saved", "ws", "dq", "dk", "dv", "dig", "dfg", "wsb")}
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    for (B, H, T, dqk, dhv) in shapes:
+        st = ops.MlstmShape(B, H, T, dqk, dhv, 64, torch.bfloat16, torch.float32)
+        rnd = lambda *s: torch.randn(s, device="cuda", generator=gen)
+        q, v = rnd(B * T, H * dqk).to(torch.bfloat16), rnd(B * T, H * dhv).to(torch.bfloat16)
+        k = (rnd(B * T, H * dqk) / dqk ** 0.5).to(torch.bfloat16)
+        ig, fg, dy = rnd(B * T, H), rnd(B * T, H) + 3.0, rnd(B * T, H * dhv)
+        fused = ops.mlstm_fused_fw(q, k, v, ig, fg, st, want_state=False)
+        want = ops.mlstm_fused_bw(fused, q, k, v, ig, fg, dy, st, want_dstate=False)
+        for t in pool.values():
+            t.view(torch.float32).fill_(float("nan"))
+        wsf = lib.xlstm_mlstm_fw_workspace_bytes(ctypes.byref(st.c))
+        assert lib.xlstm_mlstm_saved_bytes(ctypes.byref(st.c)) <= big and wsf <= big
+        stream = torch.cuda.current_stream().cuda_stream
+        L.check(lib.xlstm_mlstm_fw(stream, ctypes.byref(st.c), p(q), p(k), p(v), p(ig), p(fg), None, None, None, p(pool["ytil"]),
+                                   p(pool["msv"]), p(pool["psiv"]), p(pool["qnv"]), p(pool["saved"]), None, None, None,
+                                   p(pool["ws"]), big), "fw")
+        L.check(lib.xlstm_mlstm_bw(stream, ctypes.byref(st.c), p(q), p(k), p(v), p(ig), p(fg), None, None, None, p(pool["ytil"]),
+                                   p(pool["msv"]), p(pool["psiv"]), p(pool["qnv"]), p(pool["saved"]), p(dy), None, None,
+                                   p(pool["dq"]), p(pool["dk"]), p(pool["dv"]), p(pool["dig"]), p(pool["dfg"]), None, None,
+                                   p(pool["wsb"]), big), "bw")
+        torch.cuda.synchronize()
+        n = B * T
+        got_y = pool["ytil"].view(torch.bfloat16)[:n * H * dhv].view(n, H * dhv)
+        assert torch.equal(got_y, fused.ytil)
+        for name, ref in zip(("dq", "dk", "dv", "dig", "dfg"), want[:5]):
+            got = pool[name].view(torch.float32)[:ref.numel()].view(ref.shape)
+            assert torch.equal(got, ref), name
+        assert xl._lib.lib.xlstm_device_status() == 0

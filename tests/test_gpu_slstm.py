@@ -98,3 +98,12 @@ def test_bit_repeatable():
     b, _ = _case(8, 256, 4, 20, seed=3)
     for k in a:
         assert np.array_equal(a[k], b[k]), k
+
+
+def test_grid_kernels_alternating_batch_sizes_and_very_short_sequences():
+    """The grid kernels' flagged exchange tags every word with a launch number and a step. Calls that alternate
+    between batch sizes (different kernel instantiations writing the same exchange array) and run for only two or
+    three steps must never accept a word an earlier launch left behind: every call equals the oracle."""
+    for i, (B, T) in enumerate([(8, 3), (4, 2), (8, 2), (4, 3), (8, 3), (2, 2)]):
+        got, ref = _case(B, 1024, 1, T, seed=40 + i)
+        _check(got, ref)
