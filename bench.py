@@ -771,7 +771,9 @@ def run_hier(args):
     B, T, S = 16, 8192, 8
     cfg = H.HierCfg(vocab=257, hc=256, wh=1024, enc_blocks=2, bb_blocks=8, dec_blocks=2, heads=8, dqk=128, w_token=256,
                     small_heads=2, enc_kinds="mm", bb_kinds="m" * 8, dec_kinds="mm")
-    model = H.Hierarchical(H.init_hier_params(np.random.default_rng(0), cfg, std=0.02), cfg, bf16=True)
+    # configs[4] asks for chunk-state recomputation: on unless --hier-saved-states
+    recompute = not args.hier_saved_states
+    model = H.Hierarchical(H.init_hier_params(np.random.default_rng(0), cfg, std=0.02), cfg, bf16=True, recompute_states=recompute)
     nparams = sum(q.w.numel() for q in model.params())
     r = np.random.default_rng(1234 + rank)
     words = [(i * S, (i + 1) * S) for i in range(T // S)]
@@ -797,6 +799,7 @@ def run_hier(args):
         sampler.start()
     l0 = xl._lib.lib.xlstm_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    xl.ops.timing_start(("mlstm_fused_fw", "mlstm_fused_bw"))
     barrier()
     e0.record()
     for _ in range(args.steps):
@@ -804,6 +807,7 @@ def run_hier(args):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
+    per_op = xl.ops.timing_stop()
     launches = xl._lib.lib.xlstm_launch_count() - l0
     clocks = sampler.stop() if rank == 0 else None
     if world > 1:
@@ -813,6 +817,17 @@ def run_hier(args):
         dist.destroy_process_group()
     ms /= args.steps
     if rank == 0:
+        pk = peaks()
+        sustained = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))).get("bf16_tflops_sustained", pk["tensor"]) \
+            if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else 1400.0
+        # dense-equivalent work of a step: 6 x (a stage's parameters) x (the rows that stage processes)
+        words = B * (T // S)
+        stage_rows = {"enc": words * (S + 1), "bb": words, "dec": (words - B) * (S + 1)}
+        stage_params = {"enc": sum(q.w.numel() for b_ in model.enc for q in b_.params()),
+                        "bb": sum(q.w.numel() for b_ in model.bb for q in b_.params()) + sum(q.w.numel() for l in (model.front, model.back) for q in l.params()),
+                        "dec": sum(q.w.numel() for b_ in model.dec for q in b_.params())}
+        dense = sum(6.0 * stage_params[k] * stage_rows[k] for k in stage_rows) / (ms * 1e-3) / 1e12
+        mcore_ms = (sum(per_op.get("mlstm_fused_fw", [])) + sum(per_op.get("mlstm_fused_bw", []))) / args.steps
         val = B * T * world / (ms * 1e-3)
         ids_bytes = B * (T // S - 1) * (S + 1) * (8 + 8 + 4 + 4)  # encoder ids, decoder char ids, targets, mask (plus row lists)
         print(json.dumps({
@@ -820,8 +835,12 @@ def run_hier(args):
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "hierarchical_train_step (configs[4]: bytes 16x8192 in words of 8, 2+2 blocks of 256, backbone 8 blocks of 1024 = 8x128)",
-                       "params": nparams, "parallelism": "dp%d (gradient all-reduce per stage, overlapped with the window's backward)" % world, "l2": "activations far larger than L2"},
+                       "params": nparams, "parallelism": "dp%d (gradient all-reduce per stage, overlapped with the window's backward)" % world, "l2": "activations far larger than L2",
+                       "chunk_states": "recomputed in backward" if recompute else "saved by forward"},
             "loss": loss, "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
+            "roofline": {"kernel": "whole step, dense-equivalent work (6 x stage parameters x stage rows)", "bound": "tensor", "achieved": dense,
+                         "peak": sustained, "unit": "TFLOP/s", "frac": dense / sustained, "traffic": None, "peak_source": pk["src"] + " (sustained)",
+                         "mlstm_core_ms_per_step": mcore_ms, "mlstm_core_share": mcore_ms / ms},
             "e2e": {"value": val, "unit": "bytes/s", "h2d_bytes_per_step": ids_bytes, "d2h_bytes_per_step": 4,
                     "note": "the timed step already starts from host token arrays and reads the loss back"},
             "gpu_launches": int(launches), "clocks": clocks}))
@@ -880,14 +899,25 @@ def run_cp(args):
         dist.destroy_process_group()
     ms /= args.steps
     if rank == 0:
-        print(json.dumps({
+        line = {
             "metric": "mlstm_layer_tokens_per_s", "value": B * T * world / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "mlstm_layer_fwd_bwd, sequences of %d positions cut over %d GPUs (B16 H8 S2048 per GPU, dqk128 dv128 chunk64)" % (T * world, world),
                        "parallelism": "cp%d (segment summaries all-gathered, carry folded, BPTT state suffix-summed)" % world,
                        "l2": "tensors larger than L2"},
-            "gpu_launches": int(launches)}))
+            "gpu_launches": int(launches)}
+        bf, bb = algorithmic_bytes(B, H, T, dqk, dhv, 4)
+        pk = peaks()
+        gbs = (bf + bb) / (ms * 1e-3) / 1e9
+        line["roofline"] = {"kernel": "forward + backward of one segment, everything a rank runs for it (summary pass, exchanges, fold included)",
+                            "bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"], "traffic": None,
+                            "peak_source": pk["src"], "algorithmic_bytes": bf + bb}
+        if world == 1 and not args.no_cpu:
+            cpu = cpu_mlstm_sample()
+            line["cpu_baseline"] = {"value": cpu["tokens"] / cpu["seconds"], "unit": "tokens/s", "cores": cpu["threads"], "kind": "port",
+                                    "sample": "%d of 16 sequences x 2048 positions x 8 heads, recurrent f32 restatement, OpenMP over (batch, head)" % cpu["seqs"]}
+        print(json.dumps(line))
 
 
 def main():
@@ -905,6 +935,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-pair", action="store_true", help="lm workload: skip the configs[1] kernel-pair measurement")
     ap.add_argument("--no-kernels", action="store_true", help="lm workload: skip the instrumented step behind `kernels`")
+    ap.add_argument("--hier-saved-states", action="store_true", help="hier workload: keep the chunk-state records instead of recomputing them")
     ap.add_argument("--lm-blocks", type=int, default=0, help="override the LM depth (development)")
     ap.add_argument("--lm-remat", type=int, default=2, help="mLSTM blocks rematerialised in the LM workload")
     ap.add_argument("--lm-reduced", action="store_true", help="LM workload at half width (d=1024, heads of 128 / 256): development stand-in")

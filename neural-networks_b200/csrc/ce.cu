@@ -181,6 +181,65 @@ __global__ void __launch_bounds__(256) ce_row_warp(const float* __restrict__ log
     }
 }
 
+// ---- narrow rows, streamed: a CTA owns R consecutive rows (R a multiple of 4, so the block starts on a
+// 16-byte boundary whatever C is), brings the whole R x C block into shared memory with 128-bit coalesced
+// loads, lets each warp work on rows of the on-chip copy, and writes the gradient block back with 128-bit
+// stores. A byte vocabulary (C = 256 or 257) then moves at streaming speed instead of one 1 KB row per warp
+// with 4-byte accesses.
+template <bool CAP>
+__global__ void __launch_bounds__(256) ce_rows_block(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
+                                                     const uint32_t* __restrict__ mask, float* __restrict__ dlogits,
+                                                     float* __restrict__ row_loss, int rows, int C, int R, float inv, float cap) {
+    const float icap = CAP ? 1.f / cap : 0.f;
+    extern __shared__ __align__(16) float sblk[];  // [R][C]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nblocks = (rows + R - 1) / R;
+    for (int blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
+        const int r0 = blk * R, nr = min(R, rows - r0);
+        const size_t base = (size_t)r0 * C;
+        const int n = nr * C, n4 = n / 4;
+        const float4* src4 = reinterpret_cast<const float4*>(logits + base);
+        for (int i = threadIdx.x; i < n4; i += 256) reinterpret_cast<float4*>(sblk)[i] = __ldcs(src4 + i);
+        for (int i = 4 * n4 + threadIdx.x; i < n; i += 256) sblk[i] = logits[base + i];
+        __syncthreads();
+        for (int rr = warp; rr < nr; rr += 8) {
+            float* z = sblk + (size_t)rr * C;
+            const int r = r0 + rr;
+            if (mask && !mask[r]) {
+                for (int j = lane; j < C; j += 32) z[j] = 0.f;
+                if (lane == 0) row_loss[r] = 0.f;
+                continue;
+            }
+            float mx = -INFINITY;
+            for (int j = lane; j < C; j += 32) {
+                const float t = capped<CAP>(z[j], cap, icap);
+                if (CAP) z[j] = t;
+                mx = fmaxf(mx, t);
+            }
+            mx = warp_max(mx);
+            float sum = 0.f;
+            for (int j = lane; j < C; j += 32) sum += __expf(z[j] - mx);
+            sum = warp_sum(sum);
+            const float is = 1.f / sum;
+            const uint32_t tg = targets[r];
+            float pt = 0.f;
+            for (int j = lane; j < C; j += 32) {
+                const float t = z[j];
+                float pr = __expf(t - mx) * is;
+                if ((uint32_t)j == tg) { pt = pr; pr -= 1.f; }
+                z[j] = through_cap<CAP>(pr * inv, t, icap);
+            }
+            pt = warp_sum(pt);
+            if (lane == 0) row_loss[r] = -logf(fmaxf(pt, 1e-30f));
+        }
+        __syncthreads();
+        float4* dst4 = reinterpret_cast<float4*>(dlogits + base);
+        for (int i = threadIdx.x; i < n4; i += 256) __stcs(dst4 + i, reinterpret_cast<const float4*>(sblk)[i]);
+        for (int i = 4 * n4 + threadIdx.x; i < n; i += 256) dlogits[base + i] = sblk[i];
+        __syncthreads();
+    }
+}
+
 // *loss_accum += inv * sum(row_loss), one CTA, fixed order.
 __global__ void __launch_bounds__(1024) ce_loss_reduce(const float* __restrict__ row_loss, float* loss_accum, int rows, float inv) {
     __shared__ float red[32];
@@ -209,7 +268,23 @@ static int ce_run(void* stream, const float* logits, const uint32_t* targets, co
     }
     cudaStream_t st = (cudaStream_t)stream;
     float* row_loss = (float*)workspace;
-    if (C <= 1024) {
+    const bool aligned16 = !(((uintptr_t)logits | (uintptr_t)dlogits) & 15);
+    if (C <= 1024 && rows >= 64 && aligned16) {
+        // R rows per CTA: a multiple of 4 (block starts stay 16-byte aligned), at most 32 KB of shared memory
+        int R = (32 * 1024) / (C * (int)sizeof(float));
+        R = R >= 32 ? 32 : (R >= 4 ? R / 4 * 4 : 4);
+        const size_t smem = (size_t)R * C * sizeof(float);
+        static std::atomic<bool> attr_set[2][64];
+        int dev = 0;
+        XL_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || !attr_set[CAP][dev].load(std::memory_order_acquire)) {
+            XL_CUDA(cudaFuncSetAttribute(ce_rows_block<CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+            if (dev >= 0 && dev < 64) attr_set[CAP][dev].store(true, std::memory_order_release);
+        }
+        const int nblocks = (rows + R - 1) / R, maxb = sm_count() * 6;
+        ce_rows_block<CAP><<<nblocks < maxb ? nblocks : maxb, 256, smem, st>>>(logits, targets, mask, dlogits, row_loss, rows, C, R, inv, cap);
+        XL_LAUNCH_OK("ce_rows_block");
+    } else if (C <= 1024) {
         int wpb = 8;
         int nb = (rows + wpb - 1) / wpb, maxb = sm_count() * 8;
         int grid = nb < maxb ? nb : maxb;

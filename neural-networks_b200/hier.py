@@ -108,14 +108,14 @@ def chunk_spans(n, chunk):
     return out
 
 
-def _build_blocks(plist, d, heads, dqk, dhv, bf16, chunk):
+def _build_blocks(plist, d, heads, dqk, dhv, bf16, chunk, recompute_states=False):
     t = lambda a: torch.as_tensor(np.asarray(a), dtype=torch.float32)
     out = []
     for bp in plist:
         c = {k: (t(v) if k != "kind" else v) for k, v in bp["cell"].items()}
         bpt = {k: t(v) for k, v in bp.items() if k != "cell"}
         if c["kind"] == "mlstm":
-            out.append(layers.Block(layers.MLstm(c, heads, dqk, dhv, bf16=bf16, chunk=chunk), bpt, bf16=bf16))
+            out.append(layers.Block(layers.MLstm(c, heads, dqk, dhv, bf16=bf16, chunk=chunk, recompute_states=recompute_states), bpt, bf16=bf16))
         else:
             out.append(layers.Block(layers.SLstm(c, d, 1, bf16=bf16), bpt, post_norm=True, bf16=bf16))
     return out
@@ -124,15 +124,16 @@ def _build_blocks(plist, d, heads, dqk, dhv, bf16, chunk):
 class Hierarchical:
     """gpu::Hierarchical (src/gpu/hierarchical.rs:460-1746): forward_backward over windows, then step."""
 
-    def __init__(self, params, cfg, bf16=False, chunk=64, bb_chunk=None, group_cap=None, no_group=False):
+    def __init__(self, params, cfg, bf16=False, chunk=64, bb_chunk=None, group_cap=None, no_group=False, recompute_states=False):
+        """recompute_states: the mLSTM cells keep no chunk-state record; their backward rebuilds the chunk-boundary states."""
         t = lambda a: torch.as_tensor(np.asarray(a), dtype=torch.float32)
         self.cfg, self.bf16 = cfg, bf16
         self.table = layers.Param(t(params["table"]), False)
-        self.enc = _build_blocks(params["enc"], *cfg.stage("enc")[1:], bf16, chunk)
+        self.enc = _build_blocks(params["enc"], *cfg.stage("enc")[1:], bf16, chunk, recompute_states)
         self.front = layers.Linear(t(params["front_w"]), t(params["front_b"]), True, bf16)
-        self.bb = _build_blocks(params["bb"], *cfg.stage("bb")[1:], bf16, chunk)
+        self.bb = _build_blocks(params["bb"], *cfg.stage("bb")[1:], bf16, chunk, recompute_states)
         self.back = layers.Linear(t(params["back_w"]), t(params["back_b"]), True, bf16)
-        self.dec = _build_blocks(params["dec"], *cfg.stage("dec")[1:], bf16, chunk)
+        self.dec = _build_blocks(params["dec"], *cfg.stage("dec")[1:], bf16, chunk, recompute_states)
         self.dec_norm = layers.RmsNorm(t(params["dec_gamma"]))
         # fp32 whatever the blocks run in: the softmax exponentiates the head's output
         # (src/gpu/hierarchical.rs:626-635); bias-free, as the checkpoint stores it (:1797-1801)
@@ -203,8 +204,12 @@ class Hierarchical:
             ids = np.where(k < L[:, None], tok[np.minimum(start[grp][:, None] + k, len(tok) - 1)], 0)
             ids[np.arange(len(grp)), L] = self.cfg.w_token
             readout = np.arange(len(grp)) * tmax + L
+            # rows that hold a char or the [W] token; the padding behind them carries zero gradient and is kept out
+            # of the embedding scatter (all of it would land on id 0 and be summed by a single CTA)
+            live = np.flatnonzero((k <= L[:, None]).reshape(-1))
+            live_dev = None if live.size == ids.size else self._dev(live, torch.int64)
             plan.append((self._dev(grp, torch.int64), len(grp), tmax, self._dev(ids.reshape(-1), torch.int64),
-                         self._dev(readout, torch.int64)))
+                         self._dev(readout, torch.int64), live_dev))
         return plan
 
     def _dec_plan(self, tok, start, lens, on):
@@ -323,14 +328,17 @@ class Hierarchical:
     def _encoder_backward(self, plan, d_e_w):
         """Per group: forward again, then backward from the [W]-step rows (src/gpu/hierarchical.rs:1347-1407)."""
         hc = self.cfg.hc
-        for words, n_g, tmax, ids, readout in plan:
+        for words, n_g, tmax, ids, readout, live in plan:
             self._enc_stack(n_g, tmax, ids)
             d = torch.zeros((n_g * tmax, hc), dtype=torch.float32, device=d_e_w.device)
             d.index_copy_(0, readout, d_e_w.index_select(0, words))
             for blk in reversed(self.enc):
                 d = blk.backward(d)
                 blk.release()
-            ops.embedding_scatter_add(self.table.g, ids, d)
+            if live is None:
+                ops.embedding_scatter_add(self.table.g, ids, d)
+            else:
+                ops.embedding_scatter_add(self.table.g, ids.index_select(0, live), d.index_select(0, live))
 
     def forward_backward(self, windows, word_loss=None):
         """windows: [(tokens, [(start, end), ...]), ...] with equally many words each; word 0 of a window is
@@ -364,7 +372,7 @@ class Hierarchical:
         inv = 1.0 / max(total, 1)
 
         e_w = torch.zeros((N, self.cfg.hc), dtype=torch.float32, device="cuda")
-        for words, n_g, tmax, ids, readout in enc_plan:
+        for words, n_g, tmax, ids, readout, _live in enc_plan:
             h = self._enc_stack(n_g, tmax, ids)
             e_w.index_copy_(0, words, h.index_select(0, readout))
             for blk in self.enc:  # the backward re-runs this group, nothing of it is read again
