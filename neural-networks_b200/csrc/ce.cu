@@ -181,62 +181,86 @@ __global__ void __launch_bounds__(256) ce_row_warp(const float* __restrict__ log
     }
 }
 
-// ---- narrow rows, streamed: a CTA owns R consecutive rows (R a multiple of 4, so the block starts on a
-// 16-byte boundary whatever C is), brings the whole R x C block into shared memory with 128-bit coalesced
-// loads, lets each warp work on rows of the on-chip copy, and writes the gradient block back with 128-bit
-// stores. A byte vocabulary (C = 256 or 257) then moves at streaming speed instead of one 1 KB row per warp
-// with 4-byte accesses.
-template <bool CAP>
-__global__ void __launch_bounds__(256) ce_rows_block(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
-                                                     const uint32_t* __restrict__ mask, float* __restrict__ dlogits,
-                                                     float* __restrict__ row_loss, int rows, int C, int R, float inv, float cap) {
+// ---- narrow rows whose width is a multiple of 4 (a byte vocabulary, C = 256): one warp per PAIR of rows, 128-bit
+// accesses, both rows' loads in flight before either is reduced.
+template <int V4, bool CAP>
+__global__ void __launch_bounds__(256) ce_row_warp4(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
+                                                    const uint32_t* __restrict__ mask, float* __restrict__ dlogits,
+                                                    float* __restrict__ row_loss, int rows, int C, float inv, float cap) {
     const float icap = CAP ? 1.f / cap : 0.f;
-    extern __shared__ __align__(16) float sblk[];  // [R][C]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int nblocks = (rows + R - 1) / R;
-    for (int blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
-        const int r0 = blk * R, nr = min(R, rows - r0);
-        const size_t base = (size_t)r0 * C;
-        const int n = nr * C, n4 = n / 4;
-        const float4* src4 = reinterpret_cast<const float4*>(logits + base);
-        for (int i = threadIdx.x; i < n4; i += 256) reinterpret_cast<float4*>(sblk)[i] = __ldcs(src4 + i);
-        for (int i = 4 * n4 + threadIdx.x; i < n; i += 256) sblk[i] = logits[base + i];
-        __syncthreads();
-        for (int rr = warp; rr < nr; rr += 8) {
-            float* z = sblk + (size_t)rr * C;
-            const int r = r0 + rr;
-            if (mask && !mask[r]) {
-                for (int j = lane; j < C; j += 32) z[j] = 0.f;
+    const int lane = threadIdx.x & 31;
+    const int wglobal = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int wstride = gridDim.x * (blockDim.x >> 5);
+    const int n4 = C / 4;
+    for (int r0 = 2 * wglobal; r0 < rows; r0 += 2 * wstride) {
+        float4 v[2][V4];
+        bool live[2];
+        uint32_t tg[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int r = r0 + e;
+            live[e] = r < rows && !(mask && !mask[r]);
+            tg[e] = live[e] ? targets[r] : 0u;
+            const float4* z4 = reinterpret_cast<const float4*>(logits + (size_t)r * C);
+#pragma unroll
+            for (int i = 0; i < V4; ++i) {
+                const int j = i * 32 + lane;
+                v[e][i] = (live[e] && j < n4) ? __ldcs(z4 + j) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int r = r0 + e;
+            if (r >= rows) break;
+            float4* d4 = reinterpret_cast<float4*>(dlogits + (size_t)r * C);
+            if (!live[e]) {
+#pragma unroll
+                for (int i = 0; i < V4; ++i) {
+                    const int j = i * 32 + lane;
+                    if (j < n4) __stcs(d4 + j, make_float4(0.f, 0.f, 0.f, 0.f));
+                }
                 if (lane == 0) row_loss[r] = 0.f;
                 continue;
             }
             float mx = -INFINITY;
-            for (int j = lane; j < C; j += 32) {
-                const float t = capped<CAP>(z[j], cap, icap);
-                if (CAP) z[j] = t;
-                mx = fmaxf(mx, t);
+#pragma unroll
+            for (int i = 0; i < V4; ++i) {
+                if (CAP) {
+                    v[e][i].x = capped<CAP>(v[e][i].x, cap, icap); v[e][i].y = capped<CAP>(v[e][i].y, cap, icap);
+                    v[e][i].z = capped<CAP>(v[e][i].z, cap, icap); v[e][i].w = capped<CAP>(v[e][i].w, cap, icap);
+                }
+                mx = fmaxf(mx, fmaxf(fmaxf(v[e][i].x, v[e][i].y), fmaxf(v[e][i].z, v[e][i].w)));
             }
             mx = warp_max(mx);
             float sum = 0.f;
-            for (int j = lane; j < C; j += 32) sum += __expf(z[j] - mx);
+            float4 ex[V4];
+#pragma unroll
+            for (int i = 0; i < V4; ++i) {  // exp(-inf) = 0 for the padding (capped(-inf) = -cap is masked by j < n4 below)
+                const bool in = i * 32 + lane < n4;
+                ex[i].x = in ? __expf(v[e][i].x - mx) : 0.f; ex[i].y = in ? __expf(v[e][i].y - mx) : 0.f;
+                ex[i].z = in ? __expf(v[e][i].z - mx) : 0.f; ex[i].w = in ? __expf(v[e][i].w - mx) : 0.f;
+                sum += (ex[i].x + ex[i].y) + (ex[i].z + ex[i].w);
+            }
             sum = warp_sum(sum);
             const float is = 1.f / sum;
-            const uint32_t tg = targets[r];
             float pt = 0.f;
-            for (int j = lane; j < C; j += 32) {
-                const float t = z[j];
-                float pr = __expf(t - mx) * is;
-                if ((uint32_t)j == tg) { pt = pr; pr -= 1.f; }
-                z[j] = through_cap<CAP>(pr * inv, t, icap);
+#pragma unroll
+            for (int i = 0; i < V4; ++i) {
+                const int j = i * 32 + lane;
+                if (j >= n4) continue;
+                float4 o = make_float4(ex[i].x * is, ex[i].y * is, ex[i].z * is, ex[i].w * is);
+                const uint32_t base = 4u * j;
+                if (tg[e] == base) { pt = o.x; o.x -= 1.f; }
+                else if (tg[e] == base + 1u) { pt = o.y; o.y -= 1.f; }
+                else if (tg[e] == base + 2u) { pt = o.z; o.z -= 1.f; }
+                else if (tg[e] == base + 3u) { pt = o.w; o.w -= 1.f; }
+                o.x = through_cap<CAP>(o.x * inv, v[e][i].x, icap); o.y = through_cap<CAP>(o.y * inv, v[e][i].y, icap);
+                o.z = through_cap<CAP>(o.z * inv, v[e][i].z, icap); o.w = through_cap<CAP>(o.w * inv, v[e][i].w, icap);
+                __stcs(d4 + j, o);
             }
             pt = warp_sum(pt);
             if (lane == 0) row_loss[r] = -logf(fmaxf(pt, 1e-30f));
         }
-        __syncthreads();
-        float4* dst4 = reinterpret_cast<float4*>(dlogits + base);
-        for (int i = threadIdx.x; i < n4; i += 256) __stcs(dst4 + i, reinterpret_cast<const float4*>(sblk)[i]);
-        for (int i = 4 * n4 + threadIdx.x; i < n; i += 256) dlogits[base + i] = sblk[i];
-        __syncthreads();
     }
 }
 
@@ -269,21 +293,16 @@ static int ce_run(void* stream, const float* logits, const uint32_t* targets, co
     cudaStream_t st = (cudaStream_t)stream;
     float* row_loss = (float*)workspace;
     const bool aligned16 = !(((uintptr_t)logits | (uintptr_t)dlogits) & 15);
-    if (C <= 1024 && rows >= 64 && aligned16) {
-        // R rows per CTA: a multiple of 4 (block starts stay 16-byte aligned), at most 32 KB of shared memory
-        int R = (32 * 1024) / (C * (int)sizeof(float));
-        R = R >= 32 ? 32 : (R >= 4 ? R / 4 * 4 : 4);
-        const size_t smem = (size_t)R * C * sizeof(float);
-        static std::atomic<bool> attr_set[2][64];
-        int dev = 0;
-        XL_CUDA(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64 || !attr_set[CAP][dev].load(std::memory_order_acquire)) {
-            XL_CUDA(cudaFuncSetAttribute(ce_rows_block<CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-            if (dev >= 0 && dev < 64) attr_set[CAP][dev].store(true, std::memory_order_release);
-        }
-        const int nblocks = (rows + R - 1) / R, maxb = sm_count() * 6;
-        ce_rows_block<CAP><<<nblocks < maxb ? nblocks : maxb, 256, smem, st>>>(logits, targets, mask, dlogits, row_loss, rows, C, R, inv, cap);
-        XL_LAUNCH_OK("ce_rows_block");
+    if (C <= 1024 && C % 4 == 0 && aligned16) {
+        const int pairs = (rows + 1) / 2, nb = (pairs + 7) / 8, maxb = sm_count() * 8;
+        const int grid = nb < maxb ? nb : maxb;
+#define RUN4(V) ce_row_warp4<V, CAP><<<grid, 256, 0, st>>>(logits, targets, mask, dlogits, row_loss, rows, C, inv, cap)
+        if (C <= 128) RUN4(1);
+        else if (C <= 256) RUN4(2);
+        else if (C <= 512) RUN4(4);
+        else RUN4(8);
+#undef RUN4
+        XL_LAUNCH_OK("ce_row_warp4");
     } else if (C <= 1024) {
         int wpb = 8;
         int nb = (rows + wpb - 1) / wpb, maxb = sm_count() * 8;
