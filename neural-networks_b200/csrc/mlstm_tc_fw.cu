@@ -515,12 +515,15 @@ size_t mlstm_tc_fw_workspace_bytes(int B, int H, int T, int dqk, int dhv) {
     return align_up((size_t)nq * B * T * H * dhv * sizeof(float), 256) + align_up((size_t)nq * B * H * T * sizeof(float), 256);
 }
 
+int mlstm_fw_ws_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved);  // 128 x 128 heads: the warp-specialised kernel
+
 int mlstm_fw_tc_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved, void* workspace, size_t workspace_bytes) {
     using namespace fw;
     if (((uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.ytil | (uintptr_t)saved) & 15) {
         set_error("mlstm_fw (tensor-core path): q, k, v, ytil and the state record must be 16-byte aligned");
         return XLSTM_ERR_ARG;
     }
+    if (a.dqk == D && a.dhv == D) return mlstm_fw_ws_launch(st, a, saved);  // heads wider than 128 run below as sub-heads
     Params p = {};
     p.nq = a.dqk / D; p.nv = a.dhv / D;
     const int nsub = p.nq * p.nv;
