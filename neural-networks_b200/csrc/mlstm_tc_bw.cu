@@ -573,15 +573,24 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             tmem_ld16(tS + lane_base + 16 * cq, s);
             tmem_ld16(tDds + lane_base + 16 * cq, dd);
             tmem_ld_wait();
-            if (lane < 16) {
+            {
+                // branch-free and on all lanes (lanes 16-31 hold no rows of an M = 64 tile; their values are not stored):
+                // the causal mask goes into the exponent's argument, exp(-inf) = 0
                 const float rt = Gc->rowt[srow], dq_t = sdqn[srow];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int j = 16 * cq + i;
-                    const float dbar = (j <= srow) ? __expf(rt + Gc->colt[j]) : 0.f;
-                    s[i] *= dbar;
-                    dd[i] = dbar * (dd[i] + dq_t);
+                for (int i4 = 0; i4 < 4; ++i4) {
+                    const float4 c4 = *reinterpret_cast<const float4*>(Gc->colt + 16 * cq + 4 * i4);
+                    const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = 4 * i4 + e, j = 16 * cq + i;
+                        const float dbar = __expf((j <= srow) ? rt + cc[e] : -INFINITY);
+                        s[i] *= dbar;
+                        dd[i] = dbar * (dd[i] + dq_t);
+                    }
                 }
+            }
+            if (lane < 16) {
                 put_row<2>(sDS, srow, 2 * cq, s);
                 put_row<2>(sdS, srow, 2 * cq, dd);
             }

@@ -327,16 +327,24 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_tc(const __grid_constant
             float s[16];
             tmem_ld16(tS + lane_base + 16 * cq, s);
             tmem_ld_wait();
-            if (lane < 16) {
+            float rs = 0.f;
+            {
+                // branch-free and on all lanes (lanes 16-31 hold no rows of an M = 64 tile; their values are not stored)
                 const float rt = Gc->rowt[srow];
-                float rs = 0.f;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int j = 16 * cq + i;
-                    const float dbar = (j <= srow) ? __expf(rt + Gc->colt[j]) : 0.f;
-                    s[i] *= dbar;
-                    rs += s[i];
+                for (int i4 = 0; i4 < 4; ++i4) {
+                    const float4 c4 = *reinterpret_cast<const float4*>(Gc->colt + 16 * cq + 4 * i4);
+                    const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = 4 * i4 + e, j = 16 * cq + i;
+                        const float dbar = __expf((j <= srow) ? rt + cc[e] : -INFINITY);
+                        s[i] *= dbar;
+                        rs += s[i];
+                    }
                 }
+            }
+            if (lane < 16) {
                 *reinterpret_cast<uint4*>(sP + swz(srow, 2 * cq)) = pack8(s);
                 *reinterpret_cast<uint4*>(sP + swz(srow, 2 * cq + 1)) = pack8(s + 8);
                 rpart[cq * L + srow] = rs;

@@ -9,12 +9,12 @@
 // Only the state recurrence C_k -> (MMA) -> state pass -> C_{k+1} is sequential.
 //
 //   warps 0-3   C group   state pass: C (TMEM, fp32) -> bf16 operand copy (+ record, + final state), x next decay
-//   warps 4-7   H group   output epilogue: (Hi + b He) / psi -> bf16 tile in shared memory -> TMA store
+//   warps 4-7   H group   q.n and psi, then the output epilogue: (Hi + b He) / psi -> bf16 tile -> TMA store
 //   warps 8-15  S group   S epilogue: P = Dbar . S (bf16 tile) and its row sums; the a-scaled copy of V one chunk ahead
 //   warp 16     loads     TMA loads of Q, K, V two chunks ahead; gate vectors (cumulative log-sigmoid, stabiliser chain)
 //   warp 17     MMA       every tcgen05.mma, issued from the converged warp
-//   warp 18     q.n       q_t . n, normaliser psi, the per-position scalars the backward reads
-//   warp 19     n         n_{k+1} = g n_k + sum_j a_j k_j
+//   warps 18-19 n         n_{k+1} = g n_k + sum_j a_j k_j (half of the rows each; warp 19 carries the chain)
+// (q_t . n, the normaliser psi and the per-position scalars the backward reads are the H group's, ahead of its epilogue)
 //
 // Every wait is bounded; a wait that runs out raises the CTA's abort flag, every role leaves its loop (their own
 // waits run out or see the flag), tensor memory is freed and the code of the first failed wait goes to the device
@@ -82,7 +82,7 @@ enum Bar {
     kCReady = 18,    // state pass done: bf16 copy in shared memory, C in TMEM scaled for the chunk
     kHFull = 19,     // [2] Hi (and He) accumulators written
     kHFree = 21,     // [2] output epilogue of the chunk finished (q.n, 1/psi and the gate vectors no longer needed either)
-    kPsi = 23,       // [2] 1/psi of the chunk's positions written
+    kNPart = 23,     // [2] the first half of the n update's row sum written
     kNReady = 25,    // [2] n entering the chunk written
     kNFree = 27,     // [2] q.n of the chunk no longer needs n
     kNumBars = 29
@@ -97,7 +97,7 @@ struct Smem {
     static constexpr uint32_t gates = yt + 2 * kTileBytes;                 // ring of gate vectors
     static constexpr uint32_t nvec = gates + kGateRing * sizeof(Gates);    // 2 x n [128]
     static constexpr uint32_t rpart = nvec + 2 * D * 4;                    // row-sum halves [2][2][64]
-    static constexpr uint32_t ipsi = rpart + 2 * 2 * L * 4;                // 1/psi [2][64]
+    static constexpr uint32_t ipsi = rpart + 2 * 2 * L * 4 + 2 * D * 4;    // 1/psi [2][64] (behind the n partials [2][128])
     static constexpr uint32_t bars = ipsi + 2 * L * 4;
     static constexpr uint32_t misc = bars + kNumBars * 8;                  // tmem slot, abort flag
     static constexpr uint32_t total = misc + 32;
@@ -207,9 +207,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
 
     if (tid == 0) {
         // arrivals per phase. A stage's tiles are released by the MMA warp's commit, the eight S-group warps (they
-        // read V), the n warp (K) and, with outputs, the q.n warp (Q).
-        const uint32_t e = full ? 11u : 10u;
-        const uint32_t cnt[kNumBars] = {1, 1, e, e, 1, 1, 1, 1, 1, 1, 8, 8, 8, 8, 8, 8, 1, 1, 4, 1, 1, 4, 4, 1, 1, 1, 1, 1, 1};
+        // read V), the two n warps (K) and, with outputs, the four H-group warps (Q).
+        const uint32_t e = full ? 15u : 11u;
+        const uint32_t cnt[kNumBars] = {1, 1, e, e, 1, 1, 1, 1, 1, 1, 8, 8, 8, 8, 8, 8, 1, 1, 4, 1, 1, 4, 4, 1, 1, 1, 1, 4, 4};
         for (int i = 0; i < kNumBars; ++i) mbar_init(&bars[i], cnt[i]);
         *abort_flag = 0;
         fence_mbar_init();
@@ -456,23 +456,52 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
         }
         if (tid == 0) tma_store_wait_all();
     } else if (warp < 8) {
-        // ================= H group: output epilogue ================================================================
-        const int hx = tid - 128;                     // feature v of this thread
+        // ================= H group: q.n and psi, then the output epilogue =========================================
+        const int hx = tid - 128;                     // feature v of this thread in the epilogue
         const uint32_t lane_base = (uint32_t)(32 * (warp - 4)) << 16;
         const uint32_t xoff = (uint32_t)(hx >> 6) * kBoxBytes + (hx & 7) * 2, xch8 = (hx & 63) >> 3;
+        const int qt = hx >> 1, qhf = hx & 1;         // q.n: position qt, columns 64 * qhf .. + 63 (two threads per position)
         for (int k = 0; full && k < NC; ++k) {
             const int s = k & 1;
-            bool bad = !wait_or_abort(&bars[kHFull + s], (uint32_t)((k >> 1) & 1), abort_flag);
-            if (!bad) bad = !wait_or_abort(&bars[kGates + (k & 3)], (uint32_t)((k >> 2) & 1), abort_flag);
-            if (!bad) bad = !wait_or_abort(&bars[kPsi + s], (uint32_t)((k >> 1) & 1), abort_flag);
+            const int t0 = k * L, Lc = min(L, p.T - t0);
+            const Gates* Gc = &G[k & 3];
+            bool bad = !wait_or_abort(&bars[kGates + (k & 3)], (uint32_t)((k >> 2) & 1), abort_flag);
+            if (!bad) bad = !wait_or_abort(&bars[kFull + s], (uint32_t)((k >> 1) & 1), abort_flag);
+            if (!bad) bad = !wait_or_abort(&bars[kNReady + s], (uint32_t)((k >> 1) & 1), abort_flag);
+            float acc = 0.f;
+            if (!bad) {
+                const unsigned char* sQ = sm + Smem::tiles + (uint32_t)s * 3 * kTileBytes + (uint32_t)qhf * kBoxBytes;
+                const float* nn = nvec + s * D + 64 * qhf;
+#pragma unroll 2
+                for (int cb = 0; cb < 8; ++cb) {
+                    const float4 n0 = *reinterpret_cast<const float4*>(nn + 8 * cb), n1 = *reinterpret_cast<const float4*>(nn + 8 * cb + 4);
+                    const uint4 v4 = *reinterpret_cast<const uint4*>(sQ + swz(qt, cb));
+                    const float2 f0 = unpack_bf16(v4.x), f1 = unpack_bf16(v4.y), f2 = unpack_bf16(v4.z), f3 = unpack_bf16(v4.w);
+                    acc += f0.x * n0.x + f0.y * n0.y + f1.x * n0.z + f1.y * n0.w + f2.x * n1.x + f2.y * n1.y + f3.x * n1.z + f3.y * n1.w;
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            if (lane == 0) { mbar_arrive(&bars[kNFree + s]); mbar_arrive(&bars[kEmpty + s]); }  // done with n and the Q tile
+            if (!bad) bad = !wait_or_abort(&bars[kPFull + s], (uint32_t)((k >> 1) & 1), abort_flag);
+            if (!bad && qhf == 0) {
+                const float qn = rpart[(s * 2 + 0) * L + qt] + rpart[(s * 2 + 1) * L + qt] + Gc->b[qt] * acc;
+                const float mt = Gc->m[qt];
+                const float psi = fmaxf(fabsf(qn), expf(-mt));
+                sipsi[s * L + qt] = 1.f / psi;
+                if (qt < Lc) {
+                    const size_t o = (size_t)bh * p.T + t0 + qt;
+                    p.msv[o] = mt; p.psiv[o] = psi; p.qnv[o] = qn;
+                }
+            }
+            if (!bad) bad = !wait_or_abort(&bars[kHFull + s], (uint32_t)((k >> 1) & 1), abort_flag);
             // the store of two chunks ago has finished reading this output buffer
             if (hx == 0) tma_store_wait_read1();
+            // one answer for the whole group; the barrier also publishes 1/psi to the group
             if (named_barrier_or(2, 128, bad || *abort_flag != 0)) {
                 if (*abort_flag == 0) *abort_flag = 51;
                 break;
             }
             tc_fence_after();
-            const Gates* Gc = &G[k & 3];
             const float* ips = sipsi + s * L;
             unsigned char* ydst = sm + Smem::yt + (uint32_t)s * kTileBytes + xoff;
 #pragma unroll 1
@@ -505,61 +534,22 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
             if (lane == 0) mbar_arrive(&bars[kHFree + s]);
         }
         if (hx == 0) tma_store_wait_all();
-    } else if (warp == 18) {
-        // ================= q.n, psi ===================================================================================
-        for (int k = 0; full && k < NC; ++k) {
-            const int s = k & 1;
-            const int t0 = k * L, Lc = min(L, p.T - t0);
-            WS_WAIT_GATES(k, 61)
-            WS_WAIT2(kFull, k, 62)
-            WS_WAIT2(kNReady, k, 63)
-            const Gates* Gc = &G[k & 3];
-            const unsigned char* sQ = sm + Smem::tiles + (uint32_t)s * 3 * kTileBytes;
-            const float* nn = nvec + s * D;
-            float acc[2] = {0.f, 0.f};  // positions lane and lane + 32
-#pragma unroll 4
-            for (int cb = 0; cb < 16; ++cb) {
-                const float4 n0 = *reinterpret_cast<const float4*>(nn + 8 * cb), n1 = *reinterpret_cast<const float4*>(nn + 8 * cb + 4);
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const uint4 v4 = *reinterpret_cast<const uint4*>(sQ + (cb >> 3) * kBoxBytes + swz(lane + 32 * e, cb & 7));
-                    const float2 f0 = unpack_bf16(v4.x), f1 = unpack_bf16(v4.y), f2 = unpack_bf16(v4.z), f3 = unpack_bf16(v4.w);
-                    acc[e] += f0.x * n0.x + f0.y * n0.y + f1.x * n0.z + f1.y * n0.w + f2.x * n1.x + f2.y * n1.y + f3.x * n1.z + f3.y * n1.w;
-                }
-            }
-            __syncwarp();
-            if (lane == 0) { mbar_arrive(&bars[kNFree + s]); mbar_arrive(&bars[kEmpty + s]); }
-            WS_WAIT2(kPFull, k, 64)
-            float ip[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int t = lane + 32 * e;
-                const float qn = rpart[(s * 2 + 0) * L + t] + rpart[(s * 2 + 1) * L + t] + Gc->b[t] * acc[e];
-                const float mt = Gc->m[t];
-                const float psi = fmaxf(fabsf(qn), expf(-mt));
-                ip[e] = 1.f / psi;
-                if (t < Lc) {
-                    const size_t o = (size_t)bh * p.T + t0 + t;
-                    p.msv[o] = mt; p.psiv[o] = psi; p.qnv[o] = qn;
-                }
-            }
-            if (k >= 2) WS_WAIT2(kHFree, k - 2, 65)   // the epilogue of two chunks ago has read its 1/psi
-            sipsi[s * L + lane] = ip[0];
-            sipsi[s * L + lane + 32] = ip[1];
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars[kPsi + s]);
-        }
-    } else if (warp == 19) {
-        // ================= n chain ===================================================================================
+    } else if (warp == 18 || warp == 19) {
+        // ================= n chain: n_{k+1} = g n_k + sum_j a_j k_j, rows 0-31 by warp 18, rows 32-63 and the chain by 19 ===
+        const bool chain = warp == 19;
         const int c = 4 * lane;  // features c .. c + 3
-        float nv[4];
+        float* npart = rpart + 2 * 2 * L;  // [2][128] partial sums of warp 18 (behind the row-sum halves)
+        float nv[4] = {0.f, 0.f, 0.f, 0.f};
+        if (chain) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) nv[i] = p.cn ? p.cn[(size_t)bh * D + c + i] : 0.f;
-        if (full) *reinterpret_cast<float4*>(nvec + c) = make_float4(nv[0], nv[1], nv[2], nv[3]);
-        if (p.savedn) *reinterpret_cast<float4*>(p.savedn + ((size_t)bh * (NC + 1) + 0) * D + c) = make_float4(nv[0], nv[1], nv[2], nv[3]);
-        __syncwarp();
-        if (full && lane == 0) mbar_arrive(&bars[kNReady + 0]);
+            for (int i = 0; i < 4; ++i) nv[i] = p.cn ? p.cn[(size_t)bh * D + c + i] : 0.f;
+            if (full) *reinterpret_cast<float4*>(nvec + c) = make_float4(nv[0], nv[1], nv[2], nv[3]);
+            if (p.savedn) *reinterpret_cast<float4*>(p.savedn + ((size_t)bh * (NC + 1) + 0) * D + c) = make_float4(nv[0], nv[1], nv[2], nv[3]);
+            __syncwarp();
+            if (full && lane == 0) mbar_arrive(&bars[kNReady + 0]);
+        }
         const uint32_t koff = (uint32_t)(lane >> 4) * kBoxBytes + (lane & 1) * 8, kch = (lane & 15) >> 1;
+        const int j0 = chain ? 32 : 0;
         int k = 0;
         for (; k < NC; ++k) {
             const int s = k & 1;
@@ -568,16 +558,26 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
             const Gates* Gc = &G[k & 3];
             const unsigned char* sK = sm + Smem::tiles + (uint32_t)s * 3 * kTileBytes + kTileBytes + koff;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
-            for (int j = 0; j < L; ++j) {
+#pragma unroll 4
+            for (int j = j0; j < j0 + 32; ++j) {
                 const uint2 v2 = *reinterpret_cast<const uint2*>(sK + swz(j, kch));
                 const float aj = Gc->a[j];
                 const float2 f0 = unpack_bf16(v2.x), f1 = unpack_bf16(v2.y);
                 acc[0] += aj * f0.x; acc[1] += aj * f0.y; acc[2] += aj * f1.x; acc[3] += aj * f1.y;
             }
+            if (!chain) {
+                // the chain warp read this buffer two chunks ago before it released that chunk's tiles, and this chunk's
+                // tiles could only land after that release
+                *reinterpret_cast<float4*>(npart + s * D + c) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(&bars[kNPart + s]); mbar_arrive(&bars[kEmpty + s]); }
+                continue;
+            }
+            WS_WAIT2(kNPart, k, 74)
+            const float4 pp = *reinterpret_cast<const float4*>(npart + s * D + c);
             const float g = Gc->g;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) nv[i] = g * nv[i] + acc[i];
+            nv[0] = g * nv[0] + (pp.x + acc[0]); nv[1] = g * nv[1] + (pp.y + acc[1]);
+            nv[2] = g * nv[2] + (pp.z + acc[2]); nv[3] = g * nv[3] + (pp.w + acc[3]);
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars[kEmpty + s]);
             if (p.savedn) *reinterpret_cast<float4*>(p.savedn + ((size_t)bh * (NC + 1) + k + 1) * D + c) = make_float4(nv[0], nv[1], nv[2], nv[3]);
@@ -589,7 +589,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
                 if (lane == 0) mbar_arrive(&bars[kNReady + s1]);
             }
         }
-        if (k == NC && p.on) *reinterpret_cast<float4*>(p.on + (size_t)bh * D + c) = make_float4(nv[0], nv[1], nv[2], nv[3]);
+        if (chain && k == NC && p.on) *reinterpret_cast<float4*>(p.on + (size_t)bh * D + c) = make_float4(nv[0], nv[1], nv[2], nv[3]);
     }
 
     // ---- every role ends here -----------------------------------------------------------------------------------------
