@@ -159,7 +159,7 @@ __device__ __forceinline__ float gates_compute(const Params& p, int b, int h, in
 
 // Bounded wait that also gives up when another role has raised the CTA's abort flag.
 // Called by all 32 lanes of a warp; the answer is the same on every lane, so a role never splits a warp on it.
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __noinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     bool ok = false;
     for (int i = 0; i < kWaitBudget; ++i) {
         if (mbar_try_wait(bar, parity)) { ok = true; break; }
@@ -261,42 +261,37 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
             }
             mma_commit_w(&bars[kSFull + (c & 1)]);
         };
-        bool live = true;
-        if (full) {
-            do {
-                live = false;
-                WS_WAIT2(kFull, 0, 21)
-                tc_fence_after();
-                issue_S(0);
-                live = true;
-            } while (false);
-        }
-        for (int k = 0; live && k < NC; ++k) {
+        // iteration k: the state products of chunk k, S of chunk k + 1, then P V of chunk k; k = -1 only issues S of chunk 0.
+        // One call site for each group of instructions: the kernel's code size matters (seven roles share the
+        // instruction caches).
+        for (int k = full ? -1 : 0; k < NC; ++k) {
             const int s = k & 1;
             const uint32_t aQ = aTiles + (uint32_t)s * 3 * kTileBytes, aK = aQ + kTileBytes, aV = aK + kTileBytes;
             const uint32_t aVa = aVa0 + (uint32_t)s * kTileBytes;
-            WS_WAIT1(kCReady, k, 22)
-            if (full) {
-                if (k >= 2) WS_WAIT2(kHFree, k - 2, 23)
+            if (k >= 0) {
+                WS_WAIT1(kCReady, k, 22)
+                if (full) {
+                    if (k >= 2) WS_WAIT2(kHFree, k - 2, 23)
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {  // He^T[v,t] = sum_c C[v,c] Q[t,c]
+                        const uint32_t ko = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
+                        const uint32_t kc = (ks >> 2) * kStateBox + (ks & 3) * 32;
+                        mma_ss_w(tHe + 64 * s, desc_at(dK_, aC + kc), desc_at(dK_, aQ + ko), id_kk, ks > 0);
+                    }
+                } else {
+                    WS_WAIT2(kFull, k, 24)
+                }
+                WS_WAIT2(kAVFull, k, 25)
                 tc_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {  // He^T[v,t] = sum_c C[v,c] Q[t,c]
-                    const uint32_t ko = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
-                    const uint32_t kc = (ks >> 2) * kStateBox + (ks & 3) * 32;
-                    mma_ss_w(tHe + 64 * s, desc_at(dK_, aC + kc), desc_at(dK_, aQ + ko), id_kk, ks > 0);
+                for (int ks = 0; ks < 4; ++ks)  // C += (a.V)^T K : M = v, N = c, K = j in 4 steps of 16 rows
+                    mma_ss_w(tC, desc_at(dM1, aVa + ks * 2048), desc_at(dM1, aK + ks * 2048), id_mm128, 1);
+                mma_commit_w(&bars[kCDone + s]);
+                if (!full) {
+                    mma_commit_w(&bars[kEmpty + s]);
+                    continue;
                 }
-            } else {
-                WS_WAIT2(kFull, k, 24)
-            }
-            WS_WAIT2(kAVFull, k, 25)
-            tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)  // C += (a.V)^T K : M = v, N = c, K = j in 4 steps of 16 rows
-                mma_ss_w(tC, desc_at(dM1, aVa + ks * 2048), desc_at(dM1, aK + ks * 2048), id_mm128, 1);
-            mma_commit_w(&bars[kCDone + s]);
-            if (!full) {
-                mma_commit_w(&bars[kEmpty + s]);
-                continue;
             }
             if (k + 1 < NC) {
                 WS_WAIT2(kFull, k + 1, 26)
@@ -304,6 +299,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
                 tc_fence_after();
                 issue_S(k + 1);
             }
+            if (k < 0) continue;
             WS_WAIT2(kPFull, k, 28)
             tc_fence_after();
             const uint32_t aP = aP0 + (uint32_t)s * kBoxBytes;
@@ -347,10 +343,12 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
             if (lane == 0) { mbar_arrive(&bars[kAVFull + s]); mbar_arrive(&bars[kEmpty + s]); }
             return true;
         };
-        bool live = scaled_v(0);
-        for (int k = 0; live && k < NC; ++k) {
+        // iteration k: the S epilogue of chunk k (none for k = -1), then the scaled V of chunk k + 1. One call site each:
+        // the kernel's code size matters (seven roles share the instruction caches)
+        bool live = true;
+        for (int k = -1; live && k < NC; ++k) {
             const int s = k & 1;
-            if (full) {
+            if (full && k >= 0) {
                 WS_WAIT2(kSFull, k, 34)
                 tc_fence_after();
                 float sv[32];
