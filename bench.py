@@ -530,6 +530,65 @@ def dp_parity_check(world, rank):
     return float(t.item()), bool(buckets.native)
 
 
+def head_sharding_check(world, rank):
+    """Greedy decoding with every mLSTM block's heads split over the `world` ranks (one all-reduce of the W_out partials
+    per block) against the same model unsharded on this rank: identical token ids, logits within 1e-4."""
+    import torch
+    import torch.distributed as dist
+    layers = importlib.import_module("neural-networks_b200.layers")
+    infer = importlib.import_module("neural-networks_b200.infer")
+    heads = max(4, world)
+    vocab, dh, nb, up, B, Tp, n_new = 61, 16, 2, 176, 2, 9, 6
+    d = heads * dh
+    p = layers.init_lm_params(np.random.default_rng(13), vocab, d, nb, heads, dh, dh, up, std=0.1, slstm_at=(1,), nh_s=2)
+    prompt = torch.tensor(np.random.default_rng(8).integers(0, vocab, (B, Tp)), device="cuda")
+    lm = infer.build_lm_head_sharded(p, heads, dh, dh, rank, world, nh_s=2, tied=True)
+    ids, logits = infer.greedy_decode(lm, prompt, n_new)
+    one = layers.build_lm(p, heads, dh, dh, nh_s=2, tied=True)
+    ids1, logits1 = infer.greedy_decode(one, prompt, n_new)
+    same = float(torch.equal(ids, ids1))
+    err = float((logits - logits1).abs().max()) / max(float(logits1.abs().max()), 1e-30)
+    t = torch.tensor([1.0 - same, err], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"ids_equal": bool(t[0].item() == 0.0), "logits_max_rel": float(t[1].item()), "heads": heads}
+
+
+def context_parallel_check(world, rank):
+    """The mLSTM layer kernel pair with each sequence cut into `world` segments, one per rank (segment summaries
+    all-gathered over NCCL, carry folded, BPTT state suffix-summed) against the whole sequence run on this rank
+    (bf16 tensor-core path). Returns the largest error relative to each tensor's largest element over
+    ytil, dq, dk, dv, di, df of this rank's segment, maximised over ranks."""
+    import torch
+    import torch.distributed as dist
+    xl = importlib.import_module("neural-networks_b200")
+    cp = importlib.import_module("neural-networks_b200.cp")
+    ops = xl.ops
+    B, H, Ts, d = 2, 2, 128, 128
+    T = Ts * world
+    g = torch.Generator(device="cuda").manual_seed(43)
+    rnd = lambda *sh: torch.randn(sh, device="cuda", generator=g)
+    q, k, v = (rnd(B, T, H * d).to(torch.bfloat16) for _ in range(3))
+    k = (k.float() / math.sqrt(d)).to(torch.bfloat16)
+    ig, fg, dy = rnd(B, T, H), rnd(B, T, H) + 3.0, rnd(B, T, H * d)
+    whole = ops.MlstmShape(B, H, T, d, d, 64, torch.bfloat16, torch.float32)
+    flat = lambda a: a.reshape(B * a.shape[1], -1).contiguous()
+    fw = ops.mlstm_fused_fw(flat(q), flat(k), flat(v), flat(ig), flat(fg), whole, want_state=False)
+    ref = [fw.ytil.float()] + [a.float() for a in ops.mlstm_fused_bw(fw, flat(q), flat(k), flat(v), flat(ig), flat(fg), flat(dy), whole, want_dstate=False)[:5]]
+    seg = lambda a: flat(a[:, rank * Ts:(rank + 1) * Ts])
+    st = ops.MlstmShape(B, H, Ts, d, d, 64, torch.bfloat16, torch.float32)
+    gather = cp.dist_gather()
+    fused, carry = cp.forward(seg(q), seg(k), seg(v), seg(ig), seg(fg), st, rank, gather)
+    grads = cp.backward(fused, seg(q), seg(k), seg(v), seg(ig), seg(fg), seg(dy), st, carry, rank, world, gather)
+    got = [fused.ytil.float()] + [a.float() for a in grads[:5]]
+    worst = 0.0
+    for a, r in zip(got, ref):
+        r = r.view(B, T, -1)[:, rank * Ts:(rank + 1) * Ts].reshape(B * Ts, -1)
+        worst = max(worst, float((a - r).abs().max()) / max(float(r.abs().max()), 1e-30))
+    t = torch.tensor([worst], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
 def run_lm(args):
     """Default workload: the data-parallel training step of the configs[3] language model (see the module docstring)."""
     import torch
@@ -555,6 +614,8 @@ def run_lm(args):
     torch.cuda.empty_cache()
     # ---- multi-GPU correctness carried in the record: N-rank gradients against one rank -------------------------------
     parity = dp_parity_check(world, rank) if world > 1 else None
+    shard_check = head_sharding_check(world, rank) if world > 1 else None
+    cp_check = context_parallel_check(world, rank) if world > 1 else None
 
     c = lm_cfg(args)
     rng = np.random.default_rng(0)  # identical replicas on every rank
@@ -680,6 +741,9 @@ def run_lm(args):
             line["allreduce_exposed_ms"] = exposed_ms
             line["dp_parity_max_rel"] = parity[0]
             line["dp_native_buckets"] = parity[1]
+            # the multi-GPU paths a one-GPU test box cannot show, checked here before the timed region
+            line["head_sharded_inference_check"] = shard_check
+            line["context_parallel_max_rel"] = cp_check
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"], _ = lm_cpu_baseline(args)
         print(json.dumps(line))
