@@ -126,12 +126,10 @@ def make_inputs(cfg, seed):
 
 
 def _limit_threads(n):
-    """Context manager: BLAS and OpenMP pools limited to n threads (None = leave as they are)."""
-    import contextlib
-    if n is None:
-        return contextlib.nullcontext()
+    """Context manager: BLAS and OpenMP pools set to n threads; None = every host core, set explicitly because a
+    launcher may have exported OMP_NUM_THREADS=1 for its ranks (torch.distributed.run does)."""
     from threadpoolctl import threadpool_limits
-    return threadpool_limits(limits=n)
+    return threadpool_limits(limits=n if n is not None else (os.cpu_count() or 1))
 
 
 MLSTM_CPU_SEQS = 8  # sequences (of the 16) in the all-core CPU sample of the configs[1] kernel pair: fixed, not core-count dependent
