@@ -606,6 +606,32 @@ static GridSmem grid_layout(int K, int NOUTp, int BG, int KS, int UPC, int Bp, i
     return l;
 }
 
+// The same product for the geometry in which every thread owns exactly one (column pair, k-slice of 32 rows) item
+// for the whole call: its 64 weights stay in registers across the timesteps, so a step reads only the staged vector
+// from shared memory (half the shared-memory wavefronts of the loop above and no weight-load latency in it).
+template <int BG>
+__device__ __forceinline__ void matvec_reg2(const float2 (&w)[32], const float* __restrict__ xin, float* __restrict__ part,
+                                            int NOUTp, int cp, int ks) {
+    static_assert(BG % 4 == 0, "register mat-vec takes batch groups of 4, 8, ...");
+    float2 acc[BG];
+#pragma unroll
+    for (int b = 0; b < BG; ++b) acc[b] = make_float2(0.f, 0.f);
+    const float* xp = xin + (size_t)ks * 32 * BG;
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+#pragma unroll
+        for (int b4 = 0; b4 < BG / 4; ++b4) {
+            const float4 x = *reinterpret_cast<const float4*>(xp + r * BG + 4 * b4);
+            acc[4 * b4 + 0] = __ffma2_rn(make_float2(x.x, x.x), w[r], acc[4 * b4 + 0]);
+            acc[4 * b4 + 1] = __ffma2_rn(make_float2(x.y, x.y), w[r], acc[4 * b4 + 1]);
+            acc[4 * b4 + 2] = __ffma2_rn(make_float2(x.z, x.z), w[r], acc[4 * b4 + 2]);
+            acc[4 * b4 + 3] = __ffma2_rn(make_float2(x.w, x.w), w[r], acc[4 * b4 + 3]);
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < BG; ++b) *reinterpret_cast<float2*>(part + ((size_t)ks * BG + b) * NOUTp + 2 * cp) = acc[b];
+}
+
 template <int BG, bool LL>
 __global__ void __launch_bounds__(kThreads) slstm_fw_grid(SlstmArgs a, GridSmem lay, GridSync* gs, int* status, uint2* ll) {
     const int G = a.CS, UPC = a.UPC, dhd = a.dhd, H = a.H, T = a.T, B = a.B;
@@ -647,6 +673,15 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_grid(SlstmArgs a, GridSmem 
     }
     bool ok = true;
     if (tid == 0) s_flag = 1;
+    // register-resident weights where the mat-vec's item map is one item of 32 rows per thread (block-diagonal heads of
+    // 512 units over 32 CTAs: 64 columns, 16 k-slices)
+    const bool wreg_on = BG % 4 == 0 && a.CPT == 2 && (NOUT / 2) * a.KS == kThreads && K == 32 * a.KS;
+    const int mv_cp = tid % (NOUT / 2), mv_ks = tid / (NOUT / 2);
+    float2 wreg[32];
+    if (wreg_on) {
+#pragma unroll
+        for (int r = 0; r < 32; ++r) wreg[r] = *reinterpret_cast<const float2*>(Ws + (size_t)(mv_ks * 32 + r) * NOUT + 2 * mv_cp);
+    }
     __syncthreads();
     for (int t = 0; t < T && ok; ++t) {
         float gpre[4] = {0.f, 0.f, 0.f, 0.f};
@@ -668,7 +703,8 @@ __global__ void __launch_bounds__(kThreads) slstm_fw_grid(SlstmArgs a, GridSmem 
             }
             __syncthreads();
             if (LL && !s_flag) { ok = false; break; }
-            if (a.CPT == 4) matvec<BG, 4>(Ws, xin, part, K, NOUT, a.KS);
+            if (BG % 4 == 0 && wreg_on) matvec_reg2<(BG % 4 == 0 ? BG : 4)>(wreg, xin, part, NOUT, mv_cp, mv_ks);
+            else if (a.CPT == 4) matvec<BG, 4>(Ws, xin, part, K, NOUT, a.KS);
             else matvec<BG, 2>(Ws, xin, part, K, NOUT, a.KS);
             __syncthreads();
             for (int gi = tid; gi < B * UPC; gi += kThreads) {  // global item b*UPC + ul; this sub-group's only
