@@ -177,7 +177,9 @@ def lm_config_dict(args, world):
             "per_gpu_batch": [c["B"], c["T"]], "global_batch_tokens": c["B"] * c["T"] * world,
             "parallelism": "dp%d (one NCCL gradient all-reduce per block through xlstm_dp_*, overlapped with backward)" % world,
             "chunk_states": "recomputed in backward" if args.recompute else "saved by forward",
-            "rematerialised_blocks": args.lm_remat, "l2": "activations far larger than L2"}
+            "rematerialised_blocks": args.lm_remat,
+            "head": "fp32 logits; operands as bf16 triples, %d tensor-core products per GEMM" % args.lm_head_terms,
+            "l2": "activations far larger than L2"}
 
 
 def lm_param_count(c):
@@ -619,12 +621,12 @@ def run_lm(args):
     rng = np.random.default_rng(0)  # identical replicas on every rank
     p = layers.init_lm_params(rng, c["vocab"], c["d"], c["blocks"], c["heads"], c["dqk"], c["dhv"], c["up"], std=0.02,
                               slstm_at=c["slstm_at"], nh_s=c["slstm_heads"])
-    # the first `--lm-remat` mLSTM blocks keep only their input and re-run their forward in the backward, so that 24
-    # blocks of activations fit in HBM; sLSTM blocks (the long sequential loops) are never re-run. The head runs
-    # row-chunked with fp32-accurate split-bf16 products.
+    # the first `--lm-remat` mLSTM blocks keep only their input and re-run their forward in the backward (a memory
+    # lever: none is needed at 8 x 4096 per GPU); sLSTM blocks (the long sequential loops) are never re-run. The head runs
+    # row-chunked on split-bf16 operands (`--lm-head-terms`: 6 = fp32-accurate, 3 = 16 bits per operand).
     remat = [i for i in range(c["blocks"]) if i not in c["slstm_at"]][:args.lm_remat] if not args.lm_reduced else ()
     lm = layers.build_lm(p, c["heads"], c["dqk"], c["dhv"], nh_s=c["slstm_heads"], tied=True, bf16=True, remat=remat,
-                         head_rows=4096, head_split=True, recompute_states=args.recompute)
+                         head_rows=4096, head_split=args.lm_head_terms, recompute_states=args.recompute)
     del p
     nparams = sum(q.w.numel() for q in lm.params())
     buckets = dp.attach(lm)
@@ -999,7 +1001,10 @@ def main():
     ap.add_argument("--no-kernels", action="store_true", help="lm workload: skip the instrumented step behind `kernels`")
     ap.add_argument("--hier-saved-states", action="store_true", help="hier workload: keep the chunk-state records instead of recomputing them")
     ap.add_argument("--lm-blocks", type=int, default=0, help="override the LM depth (development)")
-    ap.add_argument("--lm-remat", type=int, default=2, help="mLSTM blocks rematerialised in the LM workload")
+    ap.add_argument("--lm-remat", type=int, default=0,
+                    help="mLSTM blocks rematerialised in the LM workload (0: all 24 blocks' activations fit, 127 GB peak)")
+    ap.add_argument("--lm-head-terms", type=int, default=3, choices=(3, 6),
+                    help="LM head GEMMs: bf16 products per fp32 product (6: fp32-accurate; 3: 16 significand bits per operand)")
     ap.add_argument("--lm-reduced", action="store_true", help="LM workload at half width (d=1024, heads of 128 / 256): development stand-in")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -192,12 +192,14 @@ int xlstm_ce_fw_bw_noalloc(void* stream, const float* logits, const uint32_t* ta
 /* out = SiLU(gate_pre + bias_gate) * (value + bias_value). The biases ([cols] each, or both NULL) are the
  * gate/value projections' biases, folded in here so that those GEMMs need no bias pass (the reference seeds
  * the GEMM output with broadcast_row, src/gpu/cuda/common.cu:20-48); element i is in column i % cols. */
-int xlstm_swiglu_fw(void* stream, const float* gate_pre, const float* value, const float* bias_gate,
+int xlstm_swiglu_fw(void* stream, const void* gate_pre, const void* value, int in_dtype, const float* bias_gate,
                     const float* bias_value, int cols, void* out, int out_dtype, size_t n);
-/* with g = gate_pre + bias_gate, v = value + bias_value: d_gate = d_mixed * v * SiLU'(g); d_value = d_mixed * SiLU(g) */
-int xlstm_swiglu_bw(void* stream, const float* d_mixed, const float* gate_pre, const float* value,
-                    const float* bias_gate, const float* bias_value, int cols, void* d_gate, void* d_value,
-                    int out_dtype, size_t n);
+/* with g = gate_pre + bias_gate, v = value + bias_value: d_gate = d_mixed * v * SiLU'(g); d_value = d_mixed * SiLU(g).
+ * in_dtype is the width of gate_pre / value (a bf16 layer takes them narrow straight from its GEMMs' epilogues),
+ * d_dtype that of d_mixed; bf16 inputs need bf16 outputs. */
+int xlstm_swiglu_bw(void* stream, const void* d_mixed, int d_dtype, const void* gate_pre, const void* value,
+                    int in_dtype, const float* bias_gate, const float* bias_value, int cols, void* d_gate,
+                    void* d_value, int out_dtype, size_t n);
 /* o <- sigmoid(o + bias) in place; hc = o * yhat. bias ([cols], or NULL) is the output-gate projection's
  * bias, folded in here like the SwiGLU biases above. */
 int xlstm_ogate_fw(void* stream, float* o, const float* yhat, const float* bias, int cols, void* hc, int out_dtype,

@@ -56,8 +56,8 @@ SIGNATURES = {
     "xlstm_ce_fw_bw": (_i, [_vp] * 6 + [_i, _i, _f, _vp, _sz]),
     "xlstm_ce_fw_bw_noalloc": (_i, [_vp] * 6 + [_i, _i, _f]),
     "xlstm_softcap_ce_fw_bw": (_i, [_vp] * 6 + [_i, _i, _f, _f, _vp, _sz]),
-    "xlstm_swiglu_fw": (_i, [_vp] * 5 + [_i, _vp, _i, _sz]),
-    "xlstm_swiglu_bw": (_i, [_vp] * 6 + [_i, _vp, _vp, _i, _sz]),
+    "xlstm_swiglu_fw": (_i, [_vp] * 3 + [_i, _vp, _vp, _i, _vp, _i, _sz]),
+    "xlstm_swiglu_bw": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _sz]),
     "xlstm_ogate_fw": (_i, [_vp] * 4 + [_i, _vp, _i, _sz]),
     "xlstm_ogate_bw": (_i, [_vp] * 5 + [_i, _vp, _sz]),
     "xlstm_colsum_workspace_bytes": (_sz, [_i, _i]),

@@ -26,9 +26,32 @@ __device__ __forceinline__ void st4(bf16* p, size_t i4, float4 v) {
 __device__ __forceinline__ void st1(float* p, size_t i, float v) { p[i] = v; }
 __device__ __forceinline__ void st1(bf16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 __device__ __forceinline__ float4 ld4(const float* p, size_t i4) { return __ldcs(reinterpret_cast<const float4*>(p) + i4); }
+__device__ __forceinline__ float4 ld4(const bf16* p, size_t i4) {
+    const uint2 r = __ldcs(reinterpret_cast<const uint2*>(p) + i4);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ float ld1(const float* p, size_t i) { return p[i]; }
+__device__ __forceinline__ float ld1(const bf16* p, size_t i) { return __bfloat162float(p[i]); }
 
+// The sigmoid of a kernel whose results leave as bf16: one ex2 and one rcp on the special-function unit instead of the
+// library exponential and an IEEE division (relative error below 1e-6, a five-hundredth of the bf16 rounding that
+// follows), branch-free. The fp32-output kernels keep the reference's branch-stable form (stable_sigmoid).
+__device__ __forceinline__ float fast_sigmoid(float x) {
+    const float e = __expf(-fabsf(x));
+    const float r = __fdividef(1.f, 1.f + e);
+    return x >= 0.f ? r : e * r;
+}
+template <typename OT>
+__device__ __forceinline__ float sigmoid_for(float x) {
+    if constexpr (sizeof(OT) == 2) return fast_sigmoid(x);
+    else return stable_sigmoid(x);
+}
+
+template <typename OT>
 __device__ __forceinline__ float silu_f(float x, float* sig) {
-    const float s = stable_sigmoid(x);
+    const float s = sigmoid_for<OT>(x);
     *sig = s;
     return x * s;
 }
@@ -45,8 +68,8 @@ __device__ __forceinline__ float bias1(const float* b, size_t i, int cols) { ret
 __device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
 
 // out = SiLU(gate + bg) * (value + bv)
-template <typename OT>
-__global__ void __launch_bounds__(256) swiglu_fw_k(const float* __restrict__ gate, const float* __restrict__ value,
+template <typename IT, typename OT>
+__global__ void __launch_bounds__(256) swiglu_fw_k(const IT* __restrict__ gate, const IT* __restrict__ value,
                                                    const float* __restrict__ bg, const float* __restrict__ bv, int cols,
                                                    OT* __restrict__ out, size_t n, int vec) {
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
@@ -67,24 +90,24 @@ __global__ void __launch_bounds__(256) swiglu_fw_k(const float* __restrict__ gat
             if (j >= n4) continue;
             const unsigned c = col_of(col0, k, cols);
             const float4 gg = add4(g[k], bias4(bg, c)), vv = add4(v[k], bias4(bv, c));
-            st4(out, j, make_float4(silu_f(gg.x, &s) * vv.x, silu_f(gg.y, &s) * vv.y, silu_f(gg.z, &s) * vv.z, silu_f(gg.w, &s) * vv.w));
+            st4(out, j, make_float4(silu_f<OT>(gg.x, &s) * vv.x, silu_f<OT>(gg.y, &s) * vv.y, silu_f<OT>(gg.z, &s) * vv.z, silu_f<OT>(gg.w, &s) * vv.w));
         }
     } else {
         if (i >= n) return;
-        st1(out, i, silu_f(gate[i] + bias1(bg, i, cols), &s) * (value[i] + bias1(bv, i, cols)));
+        st1(out, i, silu_f<OT>(ld1(gate, i) + bias1(bg, i, cols), &s) * (ld1(value, i) + bias1(bv, i, cols)));
     }
 }
 
 // d_gate = d * value * SiLU'(gate), d_value = d * SiLU(gate);  SiLU'(x) = s (1 + x (1 - s))
-template <typename OT>
-__global__ void __launch_bounds__(256) swiglu_bw_k(const float* __restrict__ d, const float* __restrict__ gate,
-                                                   const float* __restrict__ value, const float* __restrict__ bg,
+template <typename DT, typename IT, typename OT>
+__global__ void __launch_bounds__(256) swiglu_bw_k(const DT* __restrict__ d, const IT* __restrict__ gate,
+                                                   const IT* __restrict__ value, const float* __restrict__ bg,
                                                    const float* __restrict__ bv, int cols, OT* __restrict__ d_gate,
                                                    OT* __restrict__ d_value, size_t n, int vec) {
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     auto one = [](float dd, float g, float v, float* dg, float* dv) {
         float s;
-        const float act = silu_f(g, &s);
+        const float act = silu_f<OT>(g, &s);
         *dg = dd * v * (s * (1.f + g * (1.f - s)));
         *dv = dd * act;
     };
@@ -112,7 +135,7 @@ __global__ void __launch_bounds__(256) swiglu_bw_k(const float* __restrict__ d, 
     } else {
         if (i >= n) return;
         float dg, dv;
-        one(d[i], gate[i] + bias1(bg, i, cols), value[i] + bias1(bv, i, cols), &dg, &dv);
+        one(ld1(d, i), ld1(gate, i) + bias1(bg, i, cols), ld1(value, i) + bias1(bv, i, cols), &dg, &dv);
         st1(d_gate, i, dg);
         st1(d_value, i, dv);
     }
@@ -137,13 +160,13 @@ __global__ void __launch_bounds__(256) ogate_fw_k(float* __restrict__ o, const f
             const size_t j = i0 + 256 * k;
             if (j >= n4) continue;
             float4 t = add4(a[k], bias4(bias, col_of(col0, k, cols)));
-            t.x = stable_sigmoid(t.x); t.y = stable_sigmoid(t.y); t.z = stable_sigmoid(t.z); t.w = stable_sigmoid(t.w);
+            t.x = sigmoid_for<OT>(t.x); t.y = sigmoid_for<OT>(t.y); t.z = sigmoid_for<OT>(t.z); t.w = sigmoid_for<OT>(t.w);
             reinterpret_cast<float4*>(o)[j] = t;
             st4(hc, j, make_float4(t.x * y[k].x, t.y * y[k].y, t.z * y[k].z, t.w * y[k].w));
         }
     } else {
         if (i >= n) return;
-        const float a = stable_sigmoid(o[i] + bias1(bias, i, cols));
+        const float a = sigmoid_for<OT>(o[i] + bias1(bias, i, cols));
         o[i] = a;
         st1(hc, i, a * yhat[i]);
     }
@@ -240,12 +263,6 @@ __global__ void __launch_bounds__(256) split3_k(const float* __restrict__ x, bf1
 // A CTA covers 128 columns (32 threads x 4) and eight row lanes; the lanes are combined in lane order and the
 // parts in part order by the merge kernel: fixed summation order, no float atomics (the reference's add_col_sum is
 // deterministic the same way, src/gpu/cuda/common.cu:49-124).
-__device__ __forceinline__ float4 ld4(const bf16* p, size_t i4) {
-    const uint2 u = __ldcs(reinterpret_cast<const uint2*>(p) + i4);
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
-    return make_float4(a.x, a.y, b.x, b.y);
-}
 template <typename T>
 __global__ void __launch_bounds__(256) colsum_narrow_k(const T* __restrict__ x, bf16* __restrict__ out, float* __restrict__ partial,
                                                        int rows, int cols, float scale, int rows_per_part) {
@@ -359,38 +376,51 @@ static inline int bias_vec_ok(const float* bg, const float* bv, int cols) {
     return cols % 4 == 0 && !((uintptr_t)bg & 15) && !((uintptr_t)bv & 15);
 }
 
-extern "C" int xlstm_swiglu_fw(void* stream, const float* gate_pre, const float* value, const float* bias_gate,
+extern "C" int xlstm_swiglu_fw(void* stream, const void* gate_pre, const void* value, int in_dtype, const float* bias_gate,
                                const float* bias_value, int cols, void* out, int out_dtype, size_t n) {
     XL_CHECK_ARG(gate_pre && value && out, "swiglu_fw: null pointer");
     XL_CHECK_ARG((!bias_gate && !bias_value) || (cols > 0 && n % (size_t)cols == 0), "swiglu_fw: biases need cols > 0 dividing n");
+    XL_CHECK_ARG(in_dtype == XLSTM_F32 || in_dtype == XLSTM_BF16, "swiglu_fw: in_dtype");
     GLUE_CHECK("swiglu_fw")
     cudaStream_t st = (cudaStream_t)stream;
     const int vec = can_vec(n, {gate_pre, value, out}) && bias_vec_ok(bias_gate, bias_value, cols);
     if (cols <= 0) cols = 1;
     const unsigned nb = vec ? (unsigned)((n / 4 + 256 * kUnrollFw - 1) / (256 * kUnrollFw)) : blocks_for(n, 0);
-    if (out_dtype == XLSTM_BF16)
-        swiglu_fw_k<bf16><<<nb, 256, 0, st>>>(gate_pre, value, bias_gate, bias_value, cols, (bf16*)out, n, vec);
-    else
-        swiglu_fw_k<float><<<nb, 256, 0, st>>>(gate_pre, value, bias_gate, bias_value, cols, (float*)out, n, vec);
+    const bool ib = in_dtype == XLSTM_BF16, ob = out_dtype == XLSTM_BF16;
+#define XL_SWIGLU_FW(IT, OT) \
+    swiglu_fw_k<IT, OT><<<nb, 256, 0, st>>>((const IT*)gate_pre, (const IT*)value, bias_gate, bias_value, cols, (OT*)out, n, vec)
+    if (ib && ob) XL_SWIGLU_FW(bf16, bf16);
+    else if (ib) XL_SWIGLU_FW(bf16, float);
+    else if (ob) XL_SWIGLU_FW(float, bf16);
+    else XL_SWIGLU_FW(float, float);
+#undef XL_SWIGLU_FW
     XL_LAUNCH_OK("swiglu_fw");
     return XLSTM_OK;
 }
 
-extern "C" int xlstm_swiglu_bw(void* stream, const float* d_mixed, const float* gate_pre, const float* value,
-                               const float* bias_gate, const float* bias_value, int cols, void* d_gate, void* d_value,
-                               int out_dtype, size_t n) {
+extern "C" int xlstm_swiglu_bw(void* stream, const void* d_mixed, int d_dtype, const void* gate_pre, const void* value,
+                               int in_dtype, const float* bias_gate, const float* bias_value, int cols, void* d_gate,
+                               void* d_value, int out_dtype, size_t n) {
     XL_CHECK_ARG(d_mixed && gate_pre && value && d_gate && d_value, "swiglu_bw: null pointer");
     XL_CHECK_ARG((!bias_gate && !bias_value) || (cols > 0 && n % (size_t)cols == 0), "swiglu_bw: biases need cols > 0 dividing n");
+    XL_CHECK_ARG((in_dtype == XLSTM_F32 || in_dtype == XLSTM_BF16) && (d_dtype == XLSTM_F32 || d_dtype == XLSTM_BF16),
+                 "swiglu_bw: in_dtype / d_dtype");
     GLUE_CHECK("swiglu_bw")
     cudaStream_t st = (cudaStream_t)stream;
     const int vec = can_vec(n, {d_mixed, gate_pre, value, d_gate, d_value}) && bias_vec_ok(bias_gate, bias_value, cols);
     if (cols <= 0) cols = 1;
-    if (out_dtype == XLSTM_BF16)
-        swiglu_bw_k<bf16><<<blocks_for(n, vec), 256, 0, st>>>(d_mixed, gate_pre, value, bias_gate, bias_value, cols, (bf16*)d_gate,
-                                                              (bf16*)d_value, n, vec);
-    else
-        swiglu_bw_k<float><<<blocks_for(n, vec), 256, 0, st>>>(d_mixed, gate_pre, value, bias_gate, bias_value, cols, (float*)d_gate,
-                                                               (float*)d_value, n, vec);
+    const unsigned nb = blocks_for(n, vec);
+    const bool db = d_dtype == XLSTM_BF16, ib = in_dtype == XLSTM_BF16, ob = out_dtype == XLSTM_BF16;
+#define XL_SWIGLU_BW(DT, IT, OT)                                                                                          \
+    swiglu_bw_k<DT, IT, OT><<<nb, 256, 0, st>>>((const DT*)d_mixed, (const IT*)gate_pre, (const IT*)value, bias_gate, bias_value, \
+                                                cols, (OT*)d_gate, (OT*)d_value, n, vec)
+    // narrow inputs come with narrow outputs (a bf16 layer); the fp32 layer is fp32 throughout, with the outputs' width free
+    if (db && ib && ob) XL_SWIGLU_BW(bf16, bf16, bf16);
+    else if (!db && ib && ob) XL_SWIGLU_BW(float, bf16, bf16);
+    else if (!db && !ib && ob) XL_SWIGLU_BW(float, float, bf16);
+    else if (!db && !ib && !ob) XL_SWIGLU_BW(float, float, float);
+    else XL_CHECK_ARG(false, "swiglu_bw: this combination of widths is not built (bf16 inputs need bf16 outputs)");
+#undef XL_SWIGLU_BW
     XL_LAUNCH_OK("swiglu_bw");
     return XLSTM_OK;
 }

@@ -52,15 +52,20 @@ def _split3(a):
     return ops.split3_bf16(a)
 
 
-def _mm_split(a3, b3, accum=None):
-    """fp32-accurate product of two fp32 matrices given as bf16 triples: the six partial products whose
-    weight is above 2^-24 run on the bf16 tensor cores with fp32 accumulation, smallest terms first, each
-    accumulated into the result inside its GEMM (beta = 1). `accum`: add the product into this tensor."""
+def _mm_split(a3, b3, accum=None, terms=6, into=None):
+    """Product of two fp32 matrices given as bf16 triples, on the bf16 tensor cores with fp32 accumulation, smallest
+    terms first, each accumulated into the result inside its GEMM (beta = 1). terms=6: every partial product whose
+    weight is above 2^-24 (fp32-accurate). terms=3: hi*hi + hi*mid + mid*hi, 16 significand bits per operand (the
+    dropped terms weigh 2^-16: 64 times finer than the TF32 mode the reference offers for its fp32 GEMMs,
+    src/gpu/mod.rs:192-231) at half the cost. `accum`: add the product into this tensor; `into`: write it over this one."""
     (ah, am, al), (bh, bm, bl) = a3, b3
-    out = torch.mm(al, bh, out_dtype=torch.float32) if accum is None else \
-        torch.addmm(accum, al, bh, out_dtype=torch.float32, out=accum)
-    for x, y in ((ah, bl), (am, bm), (am, bh), (ah, bm), (ah, bh)):
-        torch.addmm(out, x, y, out_dtype=torch.float32, out=out)
+    pairs = ((al, bh), (ah, bl), (am, bm), (am, bh), (ah, bm), (ah, bh)) if terms == 6 else ((am, bh), (ah, bm), (ah, bh))
+    out = accum
+    for x, y in pairs:
+        if out is None:
+            out = torch.mm(x, y, out_dtype=torch.float32) if into is None else torch.mm(x, y, out_dtype=torch.float32, out=into)
+        else:
+            torch.addmm(out, x, y, out_dtype=torch.float32, out=out)
     return out
 
 
@@ -81,6 +86,9 @@ class Linear:
         self.x = _b16(x) if self.bf16 else x
         w = self.w.wb if self.bf16 else self.w.w
         if narrow and self.bf16:
+            if not bias:
+                assert scale == 1.0
+                return torch.mm(self.x, w)
             return torch.addmm(self.b.w.to(torch.bfloat16), self.x, w, beta=scale, alpha=scale)
         assert scale == 1.0, "scale is folded only into the narrowed epilogue"
         if residual is not None:
@@ -91,9 +99,10 @@ class Linear:
         y = _mm(self.x, w, self.bf16)
         return y.add_(self.b.w) if bias else y
 
-    def backward(self, dy, need_dx=True, accum=None, scale=1.0):
+    def backward(self, dy, need_dx=True, accum=None, scale=1.0, narrow_dx=False):
         """Accumulates dW, db; returns dx, added into `accum` (inside the GEMM, beta = 1) when one is given.
-        `scale`: the gradient that reaches this layer is scale * dy (the 1/sqrt(dqk) of the key projection)."""
+        `scale`: the gradient that reaches this layer is scale * dy (the 1/sqrt(dqk) of the key projection).
+        `narrow_dx` (bf16 layers, no `accum`): dx as bf16 from the GEMM epilogue, for an element-wise consumer."""
         if self.bf16:
             # bias gradient and the narrowing of dy for both products in one pass over dy; a dy that arrives in
             # bf16 is only summed, and the scale rides in the GEMMs' alpha
@@ -105,7 +114,7 @@ class Linear:
                 return None
             wt = self.w.wb.t()
             if accum is None:
-                dx = torch.mm(dy, wt, out_dtype=torch.float32)
+                dx = torch.mm(dy, wt) if narrow_dx else torch.mm(dy, wt, out_dtype=torch.float32)
                 return dx if alpha == 1.0 else dx.mul_(alpha)
             return torch.addmm(accum, dy, wt, out_dtype=torch.float32, out=accum, alpha=alpha)
         if scale != 1.0:
@@ -324,6 +333,10 @@ class Block:
     """gpu::Block<C> (src/gpu/block.rs:435-1185): z = x + [post](cell(norm1 x));
     y = z + down(SiLU(gate(norm2 z)) * value(norm2 z))."""
 
+    # bf16 layers keep the SwiGLU pre-activations and the gradient of its output as bf16, written by the GEMM
+    # epilogues (half the traffic and half the saved bytes); False keeps them fp32 between bf16 GEMMs
+    narrow_ffn = True
+
     def __init__(self, cell, p, post_norm=False, bf16=False):
         self.cell = cell
         self.n1, self.n2 = RmsNorm(p["g1"]), RmsNorm(p["g2"])
@@ -348,13 +361,15 @@ class Block:
             z = x + self.post.forward(self.cell.forward(self.n1.forward(x, nd_in), B, T))
         zn = self.n2.forward(z, nd_in)
         # the two projections without their biases: the SwiGLU kernels add them (forward and backward)
-        self.gate_pre, self.value = self.lg.forward(zn, bias=False), self.lv.forward(zn, bias=False)
+        # (bf16 layers: straight from the GEMM epilogues as bf16, which is also what the backward keeps)
+        nf = self.narrow_ffn
+        self.gate_pre, self.value = self.lg.forward(zn, bias=False, narrow=nf), self.lv.forward(zn, bias=False, narrow=nf)
         nd = torch.bfloat16 if self.ld.bf16 else torch.float32
         mixed = ops.swiglu_forward(self.gate_pre, self.value, nd, self.lg.b.w, self.lv.b.w)
         return self.ld.forward(mixed, residual=z)
 
     def backward(self, dy):
-        d_mixed = self.ld.backward(dy)
+        d_mixed = self.ld.backward(dy, narrow_dx=self.ld.bf16 and self.narrow_ffn)
         d_gate, d_value = ops.swiglu_backward(d_mixed, self.gate_pre, self.value, torch.bfloat16 if self.lg.bf16 else torch.float32,
                                               self.lg.b.w, self.lv.b.w)
         d_zn = self.lg.backward(d_gate)
@@ -417,9 +432,10 @@ class Lm:
         self.check_status = True
         self.remat = set(range(len(blocks))) if remat is True else set(remat or ())
         self.head_rows = head_rows
-        # head_split: the fp32 head products (row-chunked path) run as six bf16 tensor-core GEMMs on
-        # 3-way split operands, which keeps fp32 accuracy (see _mm_split) at several times the SIMT rate
-        self.head_split = head_split
+        # head_split: the fp32 head products (row-chunked path) run as bf16 tensor-core GEMMs on 3-way split
+        # operands (see _mm_split): True or 6 keeps fp32 accuracy with six products, 3 keeps 16 bits per operand
+        self.head_split = 6 if head_split is True else int(head_split or 0)
+        assert self.head_split in (0, 3, 6)
         assert not head_rows or tied, "the row-chunked head is implemented for the tied head"
 
     def forward_hidden(self, ids, B, T):
@@ -501,15 +517,15 @@ class Lm:
             hi = min(rows, lo + self.head_rows)
             if self.head_split:
                 n3 = _split3(normed[lo:hi])
-                pre = _mm_split(n3, w3t)
+                pre = _mm_split(n3, w3t, terms=self.head_split)
             else:
                 pre = torch.mm(normed[lo:hi], wt)
             d_pre = pre  # the fused soft-cap + loss kernel writes the gradient over its input
             ops.softcap_cross_entropy(pre, targets[lo:hi], d_pre, self.loss, self.cap, inv=inv)
             if self.head_split:
                 d3 = _split3(d_pre)
-                _mm_split(tuple(p.t() for p in d3), n3, accum=self.table.g)
-                d_n[lo:hi] = _mm_split(d3, w3)
+                _mm_split(tuple(p.t() for p in d3), n3, accum=self.table.g, terms=self.head_split)
+                _mm_split(d3, w3, terms=self.head_split, into=d_n[lo:hi])
             else:
                 self.table.g.addmm_(d_pre.t(), normed[lo:hi])
                 torch.mm(d_pre, self.table.w, out=d_n[lo:hi])

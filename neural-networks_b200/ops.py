@@ -269,20 +269,24 @@ def softcap_cross_entropy(pre_logits, targets, d_pre, loss_accum, cap, mask=None
 @timed("swiglu_forward")
 def swiglu_forward(gate_pre, value, out_dtype=torch.float32, bias_gate=None, bias_value=None):
     """swiglu_forward (src/gpu/cuda/block.cu:6-29): SiLU(gate_pre + bias_gate) * (value + bias_value), optionally
-    narrowed to bf16. The biases are the two projections' (both or neither), folded in here."""
+    narrowed to bf16. The biases are the two projections' (both or neither), folded in here. gate_pre / value: fp32, or
+    bf16 as a bf16 layer's GEMM epilogues write them."""
+    assert gate_pre.dtype == value.dtype
     out = torch.empty(gate_pre.shape, dtype=out_dtype, device=gate_pre.device)
-    check(lib.xlstm_swiglu_fw(_stream(), _ptr(gate_pre), _ptr(value), _ptr(bias_gate), _ptr(bias_value), gate_pre.shape[-1],
-                              _ptr(out), _dt(out_dtype), gate_pre.numel()), "swiglu_forward")
+    check(lib.xlstm_swiglu_fw(_stream(), _ptr(gate_pre), _ptr(value), _dt(gate_pre.dtype), _ptr(bias_gate), _ptr(bias_value),
+                              gate_pre.shape[-1], _ptr(out), _dt(out_dtype), gate_pre.numel()), "swiglu_forward")
     return out
 
 
 @timed("swiglu_backward")
 def swiglu_backward(d_mixed, gate_pre, value, out_dtype=torch.float32, bias_gate=None, bias_value=None):
     """swiglu_backward: (d_gate_pre, d_value), optionally narrowed to bf16 for the GEMMs that consume them."""
+    assert gate_pre.dtype == value.dtype
     dg = torch.empty(gate_pre.shape, dtype=out_dtype, device=gate_pre.device)
     dv = torch.empty(gate_pre.shape, dtype=out_dtype, device=gate_pre.device)
-    check(lib.xlstm_swiglu_bw(_stream(), _ptr(d_mixed), _ptr(gate_pre), _ptr(value), _ptr(bias_gate), _ptr(bias_value),
-                              gate_pre.shape[-1], _ptr(dg), _ptr(dv), _dt(out_dtype), gate_pre.numel()), "swiglu_backward")
+    check(lib.xlstm_swiglu_bw(_stream(), _ptr(d_mixed), _dt(d_mixed.dtype), _ptr(gate_pre), _ptr(value), _dt(gate_pre.dtype),
+                              _ptr(bias_gate), _ptr(bias_value), gate_pre.shape[-1], _ptr(dg), _ptr(dv), _dt(out_dtype),
+                              gate_pre.numel()), "swiglu_backward")
     return dg, dv
 
 

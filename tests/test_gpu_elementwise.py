@@ -102,9 +102,23 @@ def test_swiglu_and_output_gate_glue(n, out_dtype):
     dg, dv = ops.swiglu_backward(dev(d), dev(g), dev(v), out_dtype)
     assert close(host(dg.float()), d * v * sig * (1.0 + g * (1.0 - sig)))
     assert close(host(dv.float()), d * g * sig)
+    # bf16 pre-activations (a bf16 layer's GEMM epilogues) and, in the backward, a bf16 upstream gradient: exact on
+    # the rounded inputs
+    gn, vn, dn = (dev(a).to(torch.bfloat16) for a in (g, v, d))
+    g_, v_, d_ = (host(a.float()).astype(np.float64) for a in (gn, vn, dn))
+    s_ = 1.0 / (1.0 + np.exp(-g_))
+    assert close(host(ops.swiglu_forward(gn, vn, out_dtype).float()), g_ * s_ * v_)
+    if out_dtype == torch.bfloat16:
+        for dd, dref in ((dn, d_), (dev(d), d)):
+            dg, dv = ops.swiglu_backward(dd, gn, vn, out_dtype)
+            assert close(host(dg.float()), dref * v_ * s_ * (1.0 + g_ * (1.0 - s_)))
+            assert close(host(dv.float()), dref * g_ * s_)
+    else:
+        with pytest.raises(Exception):
+            ops.swiglu_backward(dn, gn, vn, out_dtype)
     o = dev(g)
     hc = ops.ogate_forward(o, dev(y), out_dtype)
-    assert np.abs(host(o) - sig).max() <= 1e-6
+    assert np.abs(host(o) - sig).max() <= (1e-6 if out_dtype == torch.float32 else 2e-6)  # bf16 layers: SFU sigmoid
     assert close(host(hc.float()), sig * y)
     do_pre, d_yhat = ops.ogate_backward(dev(d), o, dev(y), out_dtype)
     assert close(host(do_pre.float()), d * y * sig * (1.0 - sig))

@@ -93,11 +93,12 @@ def test_remat_is_exact_and_row_chunked_head_agrees():
     ids = torch.tensor(rng.integers(0, vocab, B * T), dtype=torch.int64, device="cuda")
     tg = torch.tensor(rng.integers(0, vocab, B * T).astype(np.int32), device="cuda")
     out = []
-    for kw in (dict(), dict(remat=True), dict(remat=[0, 2], head_rows=64), dict(head_rows=64, head_split=True)):
+    for kw in (dict(), dict(remat=True), dict(remat=[0, 2], head_rows=64), dict(head_rows=64, head_split=True),
+               dict(head_rows=64, head_split=3)):
         lm = layers.build_lm(p, heads, dqk, dhv, nh_s=2, tied=True, **kw)
         loss = lm.forward_backward(ids, tg, B, T).item()
         out.append((loss, [q.g.clone() for q in lm.params()]))
-    (l0, g0), (l1, g1), (l2, g2), (l3, g3) = out
+    (l0, g0), (l1, g1), (l2, g2), (l3, g3), (l4, g4) = out
     assert l0 == l1
     for i, (a, b) in enumerate(zip(g0, g1)):
         assert torch.equal(a, b), i
@@ -106,6 +107,10 @@ def test_remat_is_exact_and_row_chunked_head_agrees():
         assert abs(l0 - l) <= 1e-6 * abs(l0)
         for i, (a, b) in enumerate(zip(g0, g)):
             assert float((a - b).abs().max()) <= 2e-5 * float(a.abs().max()) + 1e-6 * gmax, i
+    # the three-product head: operands cut at 16 bits, so the bar is the fp32 parity bar, not round-off
+    assert abs(l0 - l4) <= 1e-5 * abs(l0)
+    for i, (a, b) in enumerate(zip(g0, g4)):
+        assert float((a - b).abs().max()) <= 1e-4 * float(a.abs().max()) + 1e-5 * gmax, i
 
 
 def test_split_bf16_product_is_fp32_accurate():
@@ -122,6 +127,13 @@ def test_split_bf16_product_is_fp32_accurate():
     e_split = float((got.double() - ref).abs().max()) / scale
     e_plain = float((plain.double() - ref).abs().max()) / scale
     assert e_split <= max(2.0 * e_plain, 2e-6), (e_split, e_plain)
+    # three products (hi*hi + hi*mid + mid*hi): 16 bits per operand, far inside TF32's 10 and bf16's 8
+    got3 = layers._mm_split(layers._split3(a), layers._split3(b), terms=3)
+    e3 = float((got3.double() - ref).abs().max()) / scale
+    tf32 = float(((a.double() * (1 + 2.0 ** -11)) @ b.double() - ref).abs().max()) / scale  # one TF32 half-ulp on a
+    assert e3 <= 1e-5 and e3 < tf32, (e3, tf32)
+    into = torch.empty_like(got3)
+    assert layers._mm_split(layers._split3(a), layers._split3(b), terms=3, into=into) is into and torch.equal(into, got3)
 
 
 def test_recomputed_chunk_states_leave_the_step_bit_identical():
