@@ -894,6 +894,13 @@ def run_hier(args):
         mcore_ms = (sum(per_op.get("mlstm_fused_fw", [])) + sum(per_op.get("mlstm_fused_bw", []))) / args.steps
         val = B * T * world / (ms * 1e-3)
         ids_bytes = B * (T // S - 1) * (S + 1) * (8 + 8 + 4 + 4)  # encoder ids, decoder char ids, targets, mask (plus row lists)
+        cpu = None
+        if not args.no_cpu:
+            _limit_threads(None)
+            v, dt = cpu_hier_sample()
+            cpu = {"value": v, "unit": "bytes/s", "cores": os.cpu_count(), "kind": "port",
+                   "sample": "CPU restatement of the reference's hierarchical model at configs[4]'s widths (float64 numpy), one window of "
+                             "512 bytes in words of 8: forward + backward + AdamW (%.1f s)" % dt}
         print(json.dumps({
             "metric": "train_bytes_per_s", "value": val, "unit": "bytes/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -907,7 +914,26 @@ def run_hier(args):
                          "mlstm_core_ms_per_step": mcore_ms, "mlstm_core_share": mcore_ms / ms},
             "e2e": {"value": val, "unit": "bytes/s", "h2d_bytes_per_step": ids_bytes, "d2h_bytes_per_step": 4,
                     "note": "the timed step already starts from host token arrays and reads the loss back"},
-            "gpu_launches": int(launches), "clocks": clocks}))
+            "gpu_launches": int(launches), "clocks": clocks, "cpu_baseline": cpu}))
+
+
+def cpu_hier_sample(seed=0, nbytes=512, S=8):
+    """The CPU restatement of the hierarchical model at configs[4]'s widths on one short window (`nbytes` bytes in
+    words of S): forward, backward and AdamW. Every stage's cost is linear in the bytes it sees, so bytes/s of the
+    sample is the figure for the full batch. Returns (bytes_per_s, seconds)."""
+    from oracle import hier as OH
+    cfg = OH.HierCfg(vocab=257, hc=256, wh=1024, enc_blocks=2, bb_blocks=8, dec_blocks=2, heads=8, dqk=128, w_token=256,
+                     small_heads=2, enc_kinds="mm", bb_kinds="m" * 8, dec_kinds="mm")
+    model = OH.Hierarchical(OH.init_hier_params(np.random.default_rng(seed), cfg, std=0.02), cfg)
+    r = np.random.default_rng(seed + 1)
+    wins = [(r.integers(0, 256, nbytes), [(i * S, (i + 1) * S) for i in range(nbytes // S)])]
+    model.forward_backward(wins)  # first call: allocations, BLAS start-up
+    t0 = time.perf_counter()
+    model.forward_backward(wins)
+    for q in model.params():
+        q.step(1e-3, 0.1, 1)
+    dt = time.perf_counter() - t0
+    return nbytes / dt, dt
 
 
 def run_cp(args):
