@@ -275,6 +275,9 @@ class SLstm:
         self.state = None
         self.sweep = False  # training over a sequence cut into calls: `state` forwards, `dstate` (dh, dc, dn) backwards
         self.dstate = None
+        # hook() called right before the backward time loop is launched: a long, latency-bound kernel that leaves the
+        # memory system and twenty SMs idle, so a data-parallel step starts its pending all-reduces here
+        self.before_time_loop = None
 
     def forward(self, x, B, T):
         H = self.H
@@ -296,6 +299,8 @@ class SLstm:
         bptt = self.sweep and self.dstate is not None
         ds = tuple(t.clone() for t in self.dstate) if bptt else \
             tuple(torch.empty((B, H), dtype=torch.float32, device=dy.device) for _ in range(3))
+        if self.before_time_loop is not None:
+            self.before_time_loop()
         ops.slstm_fused_time_bwd(self.wh.w, dy.view(B, T, H).contiguous(), self.g, ds, self.slabs, nh=nh, carry=bptt)
         if self.sweep:
             self.dstate = ds  # now the gradient of the state this call entered with

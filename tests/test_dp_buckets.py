@@ -62,3 +62,71 @@ def test_single_process_is_noop():
     b.reduce_async(0)
     b.wait()
     assert torch.all(g[0][0].g == 3.0)
+
+
+def test_all_reduces_gather_at_the_slstm_time_loops():
+    """`attach` on a model with sLSTM blocks: a block's all-reduce is held until the next sLSTM backward time loop is
+    launched (or the pass ends); without sLSTM blocks every block starts its own at once."""
+    sys.path.insert(0, ROOT)
+    dp = importlib.import_module("neural-networks_b200.dp")
+    layers = importlib.import_module("neural-networks_b200.layers")
+
+    class Rec:
+        def __init__(self, groups, group=None):
+            self.started, self.n = [], len(groups)
+
+        def reduce_async(self, i):
+            self.started.append(i)
+
+    class Blk:
+        def __init__(self, cell):
+            self.cell = cell
+
+        def params(self):
+            return []
+
+    class Norm:
+        def params(self):
+            return []
+
+    class FakeLm:
+        def __init__(self, kinds):
+            self.blocks = [Blk(object.__new__(layers.SLstm) if k == "s" else object()) for k in kinds]
+            for b in self.blocks:
+                if isinstance(b.cell, layers.SLstm):
+                    b.cell.before_time_loop = None
+            self.table, self.norm, self.head, self.on_block_backward = object(), Norm(), None, None
+
+    def backward(lm, buckets):
+        log = []
+        for i in range(len(lm.blocks) - 1, -1, -1):
+            cell = lm.blocks[i].cell
+            if isinstance(cell, layers.SLstm) and cell.before_time_loop is not None:
+                cell.before_time_loop()
+                log.append(("loop %d" % i, list(buckets.started)))
+            lm.on_block_backward(i)
+        getattr(buckets, "reduce_async_deferred", buckets.reduce_async)(len(lm.blocks))
+        return log
+
+    real = dp.GradBuckets
+    dp.GradBuckets = Rec
+    try:
+        lm = FakeLm("smmsmm")
+        b = dp.attach(lm)
+        log = backward(lm, b)
+        # at block 3's loop: blocks 5, 4 start; at block 0's loop: 3, 2, 1; then 0 and the table's bucket
+        assert log == [("loop 3", [5, 4]), ("loop 0", [5, 4, 3, 2, 1])], log
+        assert b.started == [5, 4, 3, 2, 1, 0, 6]
+        lm = FakeLm("mmsm")  # the bottom block is not an sLSTM block: what is pending goes out with block 0
+        b = dp.attach(lm)
+        log = backward(lm, b)
+        assert log == [("loop 2", [3])] and b.started == [3, 2, 1, 0, 4], (log, b.started)
+        lm = FakeLm("mmm")
+        b = dp.attach(lm)
+        assert backward(lm, b) == [] and b.started == [2, 1, 0, 3]
+        lm = FakeLm("smm")
+        b = dp.attach(lm, gather_at_slstm=False)
+        backward(lm, b)
+        assert b.started == [2, 1, 0, 3] and lm.blocks[0].cell.before_time_loop is None
+    finally:
+        dp.GradBuckets = real
