@@ -823,8 +823,10 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_grid_ps(SlstmArgs a, GridSm
         for (int sg = 0; sg < nsub; ++sg) {
             const int b0 = sg * BG;
             // gate deltas of the own units for this sub-group: to g (the record) and to shared memory (the operand)
-            for (int e = tid; e < K * BG; e += kThreads) xin[e] = 0.f;  // entries past the batch end stay zero
-            __syncthreads();
+            if (B % BG != 0) {  // a ragged last sub-group: entries past the batch end stay zero (otherwise all are rewritten)
+                for (int e = tid; e < K * BG; e += kThreads) xin[e] = 0.f;
+                __syncthreads();
+            }
             for (int gi = tid; gi < B * UPC; gi += kThreads) {
                 const int it = gi - b0 * UPC;
                 if (it < 0 || it >= BG * UPC) continue;

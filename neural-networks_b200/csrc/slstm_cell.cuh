@@ -35,15 +35,23 @@ struct SlstmBwCell {
 __device__ __forceinline__ SlstmBwCell slstm_cell_bw(float d_h, float o, float c, float n, float f, float i, float z,
                                                       float c_prev, float n_prev, float f_pre, float dc_in,
                                                       float dn_in) {
+    // One reciprocal of n serves the three quotients, and the quotients and the sigmoid go through the hardware
+    // approximations like the forward cell's (relative error ~1e-6): with IEEE divisions and the library exponential
+    // this chain was 1.7 k of a 12.6 k-cycle step of the grid kernel.
     SlstmBwCell r;
-    r.dob = d_h * (c / n) * o * (1.f - o);
-    const float d_c = d_h * o / n + dc_in;
-    const float d_n = d_h * o * (-c) / (n * n) + dn_in;
+    const float rn = __fdividef(1.f, n);
+    const float hn = c * rn;  // c / n
+    const float dho = d_h * o;
+    r.dob = dho * hn * (1.f - o);
+    const float d_c = dho * rn + dc_in;
+    const float d_n = dn_in - dho * hn * rn;
     const float d_f_gate = d_c * c_prev + d_n * n_prev;
     const float d_i_gate = d_c * z + d_n;
     r.dz = d_c * i * (1.f - z * z);
     r.di = d_i_gate * i;
-    r.df = d_f_gate * f * (1.f - stable_sigmoid(f_pre));
+    const float e = __expf(-fabsf(f_pre));          // 1 - sigmoid(f_pre) = sigmoid(-f_pre), branch-free
+    const float rs = __fdividef(1.f, 1.f + e);
+    r.df = d_f_gate * f * (f_pre >= 0.f ? e * rs : rs);
     r.dc = d_c * f;
     r.dn = d_n * f;
     return r;
