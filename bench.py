@@ -323,11 +323,33 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def mlstm_cfg(args):
+    """configs[1], or the shape `--mlstm-shape B,H,S,d` asks for (kernel studies: e.g. 2,8,4096,256 is a quarter of the
+    batch the configs[3] model hands its mLSTM core)."""
+    cfg = dict(CFG)
+    shape = getattr(args, "mlstm_shape", None)
+    if shape:
+        B, H, T, d = (int(x) for x in shape.split(","))
+        cfg.update(B=B, H=H, T=T, dqk=d, dhv=d)
+    return cfg
+
+
+# DRAM bytes per launch (read + written) from one ncu capture of each kernel at configs[1], fp32 gradients, states saved
+MLSTM_TRAFFIC = {"fw": 203.5e6 + 163.4e6, "bw": 545.4e6 + 366.3e6}
+# The configs[3] model's core ops (B8 H8 S4096, heads of 256 as four 128 x 128 sub-heads, bf16 gradients, states
+# saved): DRAM bytes of every kernel of one op call, captured at a quarter of the batch (B = 2) and multiplied by four
+# (each kernel's traffic is proportional to the batch). Backward: row-dot pass 67.1 MB, sub-head kernel 328.5 + 366.0 MB
+# (the fp32 partial planes are its writes), three plane sums 3 x 140 MB; forward: sub-head kernel 101.3 + 212.3 MB,
+# combine 140.8 MB. 4.4 and 3.4 times the algorithmic bytes: the price of the sub-head decomposition.
+LM_CORE_TRAFFIC = {"fw": 4 * 454.4e6, "bw": 4 * 1183.7e6}
+
+
 def mlstm_config_dict(args, world):
-    cfg = CFG
+    cfg = mlstm_cfg(args)
     gb = 2 if args.grad_dtype == "bf16" else 4
     bf, bb = algorithmic_bytes(cfg["B"], cfg["H"], cfg["T"], cfg["dqk"], cfg["dhv"], gb)
-    return {"workload": "mlstm_layer_fwd_bwd B16 H8 S2048 dqk128 dv128 chunk64 (configs[1])", "per_gpu_batch": cfg["B"],
+    name = "mlstm_layer_fwd_bwd B%d H%d S%d dqk%d dv%d chunk%d" % (cfg["B"], cfg["H"], cfg["T"], cfg["dqk"], cfg["dhv"], cfg["L"])
+    return {"workload": name + (" (configs[1])" if cfg == CFG else ""), "per_gpu_batch": cfg["B"],
             "grad_dtype": args.grad_dtype, "chunk_states": "recomputed in backward" if args.recompute else "saved by forward",
             "l2": "inputs (%.0f MB) larger than L2" % ((bf + bb) / 1e6), "parallelism": "dp%d (batch shards, no collective)" % world}
 
@@ -344,7 +366,7 @@ def measure_mlstm_pair(args, steps, warmup=3, with_e2e=False):
     xl = importlib.import_module("neural-networks_b200")
     ops = xl.ops
     rank, world, local = _dist_env()
-    cfg = dict(CFG)
+    cfg = mlstm_cfg(args)
     gd = torch.bfloat16 if args.grad_dtype == "bf16" else torch.float32
     st = ops.MlstmShape(cfg["B"], cfg["H"], cfg["T"], cfg["dqk"], cfg["dhv"], cfg["L"], torch.bfloat16, gd, 0)
     hq, hk, hv, hig, hfg, hdy = make_inputs(cfg, 1000 + rank)
@@ -380,7 +402,8 @@ def measure_mlstm_pair(args, steps, warmup=3, with_e2e=False):
     pk = peaks()
     out = dict(ms_per_step=ms_per_step, fw_ms=fw_t, bw_ms=bw_t, flops=ff + fb, bytes_fw=bf, bytes_bw=bb, launches=int(launches),
                tflops=(ff + fb) / (ms_per_step * 1e-3) / 1e12, tokens=cfg["B"] * cfg["T"],
-               bw_gbs=bb / (bw_t * 1e-3) / 1e9, fw_gbs=bf / (fw_t * 1e-3) / 1e9, peaks=pk)
+               bw_gbs=bb / (bw_t * 1e-3) / 1e9, fw_gbs=bf / (fw_t * 1e-3) / 1e9, peaks=pk,
+               traffic=MLSTM_TRAFFIC if (cfg == CFG and args.grad_dtype == "f32" and not args.recompute) else {"fw": None, "bw": None})
     if with_e2e:
         # Every step copies its inputs from pinned host memory, runs forward + backward through `ops`, and copies every
         # result back to pinned host memory; all of it is inside the timed region. The three stages run on three
@@ -435,8 +458,10 @@ def mlstm_pair_summary(m):
     pk = m["peaks"]
     return {"value": m["tflops"], "unit": "TFLOP/s", "workload": "mlstm_layer_fwd_bwd B16 H8 S2048 dqk128 dv128 chunk64 (configs[1]), this rank",
             "ms_per_step": m["ms_per_step"], "frac_of_bf16_peak": m["tflops"] / pk["tensor"],
-            "forward": {"launch_ms": m["fw_ms"], "algorithmic_bytes": m["bytes_fw"], "achieved_gbs": m["fw_gbs"], "frac_of_hbm_peak": m["fw_gbs"] / pk["hbm"]},
-            "backward": {"launch_ms": m["bw_ms"], "algorithmic_bytes": m["bytes_bw"], "achieved_gbs": m["bw_gbs"], "frac_of_hbm_peak": m["bw_gbs"] / pk["hbm"]},
+            "forward": {"launch_ms": m["fw_ms"], "algorithmic_bytes": m["bytes_fw"], "achieved_gbs": m["fw_gbs"], "frac_of_hbm_peak": m["fw_gbs"] / pk["hbm"],
+                        "traffic": m["traffic"]["fw"]},
+            "backward": {"launch_ms": m["bw_ms"], "algorithmic_bytes": m["bytes_bw"], "achieved_gbs": m["bw_gbs"], "frac_of_hbm_peak": m["bw_gbs"] / pk["hbm"],
+                         "traffic": m["traffic"]["bw"]},
             "tokens_per_s": m["tokens"] / (m["ms_per_step"] * 1e-3), "peak_source": pk["src"]}
 
 
@@ -464,16 +489,17 @@ def run_mlstm(args):
         ms, e2e_ms = float(t[0].item()), float(t[1].item())
     if rank == 0:
         pk = m["peaks"]
+        traffic = m["traffic"]
         value = m["flops"] * world / (ms * 1e-3) / 1e12
         line = {"metric": "mlstm_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic", "config": mlstm_config_dict(args, world),
                 "tokens_per_s": m["tokens"] * world / (ms * 1e-3), "frac_of_bf16_peak": value / world / pk["tensor"],
                 "roofline": {"kernel": "mlstm backward", "bound": "hbm", "achieved": m["bw_gbs"], "peak": pk["hbm"], "unit": "GB/s",
-                             "frac": m["bw_gbs"] / pk["hbm"], "traffic": None, "peak_source": pk["src"],
+                             "frac": m["bw_gbs"] / pk["hbm"], "traffic": traffic["bw"], "peak_source": pk["src"],
                              "algorithmic_bytes": m["bytes_bw"], "launch_ms": m["bw_ms"],
                              "forward": {"achieved": m["fw_gbs"], "frac": m["fw_gbs"] / pk["hbm"], "algorithmic_bytes": m["bytes_fw"],
-                                         "launch_ms": m["fw_ms"], "traffic": None}},
+                                         "launch_ms": m["fw_ms"], "traffic": traffic["fw"]}},
                 "e2e": {"value": m["flops"] * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": m["h2d"],
                         "d2h_bytes_per_step": m["d2h"], "ms_per_step": e2e_ms},
                 "gpu_launches": m["launches"], "clocks": clocks}
@@ -710,13 +736,16 @@ def run_lm(args):
         bw_ms = float(np.mean(bw_calls)) if bw_calls else None
         fw_ms = float(np.mean(fw_calls)) if fw_calls else None
         ff, fb = flops_fwd_bwd(B, c["heads"], T, c["dqk"], c["dhv"], 64)
+        captured = (B, c["heads"], T, c["dqk"], c["dhv"]) == (8, 8, 4096, 256, 256) and not args.recompute
         roof = {"kernel": "mlstm backward op at the model's shape (B%d H%d S%d dqk%d dv%d chunk 64, bf16 gradient I/O)" % (B, c["heads"], T, c["dqk"], c["dhv"]),
                 "bound": "hbm", "achieved": bbw / (bw_ms * 1e-3) / 1e9 if bw_ms else None, "peak": pk["hbm"], "unit": "GB/s",
-                "frac": bbw / (bw_ms * 1e-3) / 1e9 / pk["hbm"] if bw_ms else None, "traffic": None, "peak_source": pk["src"],
+                "frac": bbw / (bw_ms * 1e-3) / 1e9 / pk["hbm"] if bw_ms else None,
+                "traffic": LM_CORE_TRAFFIC["bw"] if captured else None, "peak_source": pk["src"],
                 "algorithmic_bytes": bbw, "launch_ms": bw_ms, "launches_timed": len(bw_calls),
                 "tflops": fb / (bw_ms * 1e-3) / 1e12 if bw_ms else None,
                 "forward": {"launch_ms": fw_ms, "algorithmic_bytes": bfw, "achieved": bfw / (fw_ms * 1e-3) / 1e9 if fw_ms else None,
                             "frac": bfw / (fw_ms * 1e-3) / 1e9 / pk["hbm"] if fw_ms else None, "launches_timed": len(fw_calls),
+                            "traffic": LM_CORE_TRAFFIC["fw"] if captured else None,
                             "tflops": ff / (fw_ms * 1e-3) / 1e12 if fw_ms else None}}
         sl = {k: float(np.mean(per_op[k])) * 1e3 / T for k in ("slstm_fused_time", "slstm_fused_time_bwd") if per_op.get(k)}
         sustained = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))).get("bf16_tflops_sustained", pk["tensor"]) \
@@ -1021,6 +1050,7 @@ def main():
                          "ops: the other hot-path kernels alone; hier: configs[4] hierarchical training step; cp: the layer kernel "
                          "with sequences cut over the GPUs")
     ap.add_argument("--grad-dtype", default="f32", choices=["f32", "bf16"], help="mlstm workload: width of d_ytil, dq, dk, dv")
+    ap.add_argument("--mlstm-shape", default=None, help="mlstm workload: B,H,S,d instead of configs[1] (kernel studies)")
     ap.add_argument("--recompute", action="store_true", help="backward recomputes chunk-boundary states instead of reading a saved record")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-pair", action="store_true", help="lm workload: skip the configs[1] kernel-pair measurement")
