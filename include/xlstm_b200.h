@@ -46,6 +46,14 @@ extern "C" {
 
 /* flags */
 #define XLSTM_FORCE_SIMT 1u /* use the CUDA-core kernels even where a tensor-core kernel exists */
+/* Sequences of at most 32 positions that neither take nor leave a state (the hierarchical model's word rectangles:
+ * thousands of 9-position sequences per call; no reference counterpart, its kernels take one sequence per block):
+ * the tensor-core kernels put 64 / T of them into each 64-row chunk tile, with gate scans that restart at every
+ * sequence and a block-diagonal decay mask, instead of one ragged tile per sequence. Set it on the forward call and on
+ * its backward call alike (the state record is laid out tile by tile); a call with the flag that passes a carry, asks
+ * for a state or a state gradient, or has T > 32 is refused. Ignored where the tensor-core path does not apply or the
+ * heads are not 128 x 128 (the call then runs as without the flag). Results are those of the unpacked call. */
+#define XLSTM_PACK_SHORT 2u
 
 int xlstm_version(void);
 const char* xlstm_last_error(void);

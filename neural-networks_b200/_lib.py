@@ -15,6 +15,7 @@ lib = ctypes.CDLL(LIB_PATH)
 OK, DECLINED = 0, 1
 F32, BF16 = 0, 1
 FORCE_SIMT = 1
+PACK_SHORT = 2
 
 
 class MlstmShape(ctypes.Structure):

@@ -80,6 +80,50 @@ static size_t tc_record_bytes(const xlstm_mlstm_shape* s) {
     return mlstm_tc_saved_C_bytes(bhs, num_chunks(s)) + mlstm_tc_saved_n_bytes(bhs, num_chunks(s));
 }
 
+// Packed mode of the tensor-core path (XLSTM_PACK_SHORT): sequences of at most 32 positions with no carry, 64 / T of
+// them to a 64-row chunk tile. Returns the sequences per tile, 0 when the call runs unpacked (flag absent, or a shape the
+// packed kernels do not cover), -1 when the flag is set on a call that cannot be packed by its arguments. The first
+// (B / n) * n sequences run packed; the rest, fewer than n, run unpacked on the tail of every tensor.
+static int tc_pack_count(const xlstm_mlstm_shape* s, bool any_carry_or_state) {
+    if (!(s->flags & XLSTM_PACK_SHORT) || !use_tc(s) || s->dqk != 128 || s->dhv != 128) return 0;
+    if (any_carry_or_state || s->T > 32) {
+        set_error("mlstm: XLSTM_PACK_SHORT takes sequences of at most 32 positions without carries or state outputs");
+        return -1;
+    }
+    const int n = 64 / s->T;
+    return s->B >= n ? n : 0;
+}
+static size_t tc_record_bytes_bh(int bh, int nc) { return mlstm_tc_saved_C_bytes(bh, nc) + mlstm_tc_saved_n_bytes(bh, nc); }
+template <typename T>
+static T* off(T* p, size_t bytes) { return p ? (T*)((char*)p + bytes) : p; }
+template <typename T>
+static const T* off(const T* p, size_t bytes) { return p ? (const T*)((const char*)p + bytes) : p; }
+
+// The forward arguments of sequences [b0, b0 + nb) of a call (tensor-core path: bf16 q, k, v, ytil).
+static MlstmFwArgs fw_slice(MlstmFwArgs a, int b0, int nb) {
+    const size_t rows = (size_t)b0 * a.T;
+    a.q = off(a.q, rows * a.H * a.dqk * 2); a.k = off(a.k, rows * a.H * a.dqk * 2); a.v = off(a.v, rows * a.H * a.dhv * 2);
+    a.ig = off(a.ig, rows * a.H * 4); a.fg = off(a.fg, rows * a.H * 4);
+    a.ytil = off(a.ytil, rows * a.H * a.dhv * 2);
+    a.msv = off(a.msv, rows * a.H * 4); a.psiv = off(a.psiv, rows * a.H * 4); a.qnv = off(a.qnv, rows * a.H * 4);
+    a.B = nb;
+    return a;
+}
+// ... and turned into the packed launch: nb / n tiles of n sequences each.
+static MlstmFwArgs fw_packed(MlstmFwArgs a, int n) {
+    a.seg = a.T; a.npack = n; a.B /= n; a.T *= n; a.NC = 1;
+    return a;
+}
+static int tc_fw_maybe_packed(cudaStream_t st, int n, const MlstmFwArgs& a, void* saved, void* workspace,
+                              size_t workspace_bytes) {
+    if (!n) return mlstm_fw_tc_launch(st, a, saved, workspace, workspace_bytes);
+    const int full = a.B / n * n, tail = a.B - full;
+    int rc = mlstm_fw_tc_launch(st, fw_packed(fw_slice(a, 0, full), n), saved, workspace, workspace_bytes);
+    if (rc || !tail) return rc;
+    return mlstm_fw_tc_launch(st, fw_slice(a, full, tail), off(saved, tc_record_bytes_bh(full / n * a.H, 1)), workspace,
+                              workspace_bytes);
+}
+
 extern "C" size_t xlstm_mlstm_saved_bytes(const xlstm_mlstm_shape* s) {
     if (!s || s->B <= 0 || s->H <= 0 || s->T <= 0 || s->dqk <= 0 || s->dhv <= 0 || s->L <= 0) return 0;
     if (use_tc(s)) return tc_record_bytes(s);
@@ -113,7 +157,11 @@ extern "C" int xlstm_mlstm_fw(void* stream, const xlstm_mlstm_shape* s, const vo
     a.oC = out_C; a.on = out_n; a.om = out_m;
     a.B = s->B; a.H = s->H; a.T = s->T; a.dqk = s->dqk; a.dhv = s->dhv; a.L = eff_L(s); a.NC = num_chunks(s);
     a.states_only = 0;
-    if (use_tc(s)) return mlstm_fw_tc_launch((cudaStream_t)stream, a, saved, workspace, workspace_bytes);
+    if (use_tc(s)) {
+        const int npk = tc_pack_count(s, a.cC || a.oC);
+        if (npk < 0) return XLSTM_ERR_ARG;
+        return tc_fw_maybe_packed((cudaStream_t)stream, npk, a, saved, workspace, workspace_bytes);
+    }
     return mlstm_fw_simt_launch((cudaStream_t)stream, a, s->dtype);
 }
 
@@ -151,6 +199,9 @@ extern "C" int xlstm_mlstm_bw(void* stream, const xlstm_mlstm_shape* s, const vo
     if (use_tc(s)) {
         char* ws = (char*)workspace;
         size_t ws_left = workspace ? workspace_bytes : 0;
+        const int npk = tc_pack_count(s, carry_C || carry_dC || out_dC);
+        if (npk < 0) return XLSTM_ERR_ARG;
+        const int full = npk ? s->B / npk * npk : 0, tail = s->B - full;
         if (!saved) {
             // recompute the chunk-boundary states (bf16 record) into the workspace with the forward's state-only pass
             size_t need = xlstm_mlstm_bw_workspace_bytes(s, 0);
@@ -163,7 +214,7 @@ extern "C" int xlstm_mlstm_bw(void* stream, const xlstm_mlstm_shape* s, const vo
             f.q = q; f.k = k; f.v = v; f.ig = ig; f.fg = fg; f.cC = carry_C; f.cn = carry_n; f.cm = carry_m;
             f.B = s->B; f.H = s->H; f.T = s->T; f.dqk = s->dqk; f.dhv = s->dhv; f.L = eff_L(s); f.NC = num_chunks(s);
             f.states_only = 1;
-            rc = mlstm_fw_tc_launch(st, f, workspace, nullptr, 0);
+            rc = tc_fw_maybe_packed(st, npk, f, workspace, nullptr, 0);
             if (rc) return rc;
             saved = workspace;
             ws += tc_record_bytes(s);
@@ -174,7 +225,26 @@ extern "C" int xlstm_mlstm_bw(void* stream, const xlstm_mlstm_shape* s, const vo
         a.qnv = qnv; a.dytil = d_ytil; a.cdC = carry_dC; a.cdn = carry_dn;
         a.dq = dq; a.dk = dk; a.dv = dv; a.dig = dig; a.dfg = dfg; a.odC = out_dC; a.odn = out_dn;
         a.B = s->B; a.H = s->H; a.T = s->T; a.dqk = s->dqk; a.dhv = s->dhv; a.L = eff_L(s); a.NC = num_chunks(s);
-        return mlstm_bw_tc_launch(st, a, saved, s->gdtype, ws, ws_left);
+        if (!npk) return mlstm_bw_tc_launch(st, a, saved, s->gdtype, ws, ws_left);
+        // packed: the first `full` sequences npk to a tile, then the few that are left as they are
+        const size_t gw = s->gdtype == XLSTM_BF16 ? 2 : 4;
+        auto slice = [&](int b0, int nb) {
+            MlstmBwArgs x = a;
+            const size_t rows = (size_t)b0 * a.T, hq = (size_t)a.H * a.dqk, hv = (size_t)a.H * a.dhv;
+            x.q = off(a.q, rows * hq * 2); x.k = off(a.k, rows * hq * 2); x.v = off(a.v, rows * hv * 2);
+            x.ig = off(a.ig, rows * a.H * 4); x.fg = off(a.fg, rows * a.H * 4);
+            x.ytil = off(a.ytil, rows * hv * 2); x.dytil = off(a.dytil, rows * hv * gw);
+            x.msv = off(a.msv, rows * a.H * 4); x.psiv = off(a.psiv, rows * a.H * 4); x.qnv = off(a.qnv, rows * a.H * 4);
+            x.dq = off(a.dq, rows * hq * gw); x.dk = off(a.dk, rows * hq * gw); x.dv = off(a.dv, rows * hv * gw);
+            x.dig = off(a.dig, rows * a.H * 4); x.dfg = off(a.dfg, rows * a.H * 4);
+            x.B = nb;
+            return x;
+        };
+        MlstmBwArgs pk = slice(0, full);
+        pk.seg = a.T; pk.npack = npk; pk.B = full / npk; pk.T = a.T * npk; pk.NC = 1;
+        rc = mlstm_bw_tc_launch(st, pk, saved, s->gdtype, ws, ws_left);
+        if (rc || !tail) return rc;
+        return mlstm_bw_tc_launch(st, slice(full, tail), off(saved, tc_record_bytes_bh(full / npk * a.H, 1)), s->gdtype, ws, ws_left);
     }
     const float *sC, *sn;
     if (saved) {

@@ -14,6 +14,9 @@ struct MlstmFwArgs {
     float *oC, *on, *om;        // state after the last position (may be null)
     int B, H, T, dqk, dhv, L, NC;
     int states_only;            // 1: walk the state recurrence only (recompute pass of the backward)
+    // tensor-core path, packed mode (0 = off): T = npack * seg positions hold npack independent sequences of seg
+    // positions each (seg <= 32, one chunk, no carry, no state out); msv / psiv / qnv stay [sequence][head][seg]
+    int seg, npack;
 };
 
 struct MlstmBwArgs {
@@ -29,6 +32,7 @@ struct MlstmBwArgs {
     float *dig, *dfg;
     float *odC, *odn;
     int B, H, T, dqk, dhv, L, NC;
+    int seg, npack;             // packed mode of the tensor-core path, as in MlstmFwArgs
 };
 
 int mlstm_fw_simt_launch(cudaStream_t st, const MlstmFwArgs& a, int dtype);

@@ -72,8 +72,16 @@ struct Params {
     int nq, nv;
     const float* dotv;  // [B*H][T] dy_t . ytil_t over the whole head (nv > 1; else the CTA forms it itself)
     size_t qk_plane, v_plane, g_plane;
+    // Packed mode (seg > 0), as in the forward kernel: npack independent sequences of seg positions per tile, one chunk,
+    // no carry: segmented scans, block-diagonal decay mask, zero state; msv / psiv / qnv in [sequence][head][seg] order.
+    int seg, npack;
     int* status;      // device status word (first bounded wait that ran out)
 };
+
+// Index of position t0 + t of (b, h) in msv / psiv / qnv (and dotv).
+__device__ __forceinline__ size_t vec_index(const Params& p, int b, int h, int bh, int pos) {
+    return p.seg ? ((size_t)(b * p.npack + pos / p.seg) * p.H + h) * p.seg + pos % p.seg : (size_t)bh * p.T + pos;
+}
 
 static constexpr int kVecFloats = 3 * L + D;
 struct Smem {
@@ -188,7 +196,7 @@ __device__ __forceinline__ void gates_fetch(const Params& p, int b, int h, int b
             r->fr[t] = INFINITY;   // log_sigmoid(+inf) = 0: positions past a ragged end leave fc unchanged
             r->iv[t] = -INFINITY;
         }
-        cp_async4(&r->mt[t], p.msv + (size_t)bh * p.T + t0 + min(t, Lc - 1));
+        cp_async4(&r->mt[t], p.msv + vec_index(p, b, h, bh, t0 + min(t, Lc - 1)));
     }
     if (lane == 0) {
         if (ch == 0) {
@@ -199,18 +207,13 @@ __device__ __forceinline__ void gates_fetch(const Params& p, int b, int h, int b
     }
 }
 // Control warp: gate vectors of a chunk from its staged raw inputs.
-__device__ __forceinline__ void gates_compute(const GateRawS* r, Gates* G) {
+__device__ __forceinline__ void gates_compute(const GateRawS* r, Gates* G, int seg) {
     const int lane = threadIdx.x & 31;
     const float fr[2] = {r->fr[lane], r->fr[lane + 32]}, iv[2] = {r->iv[lane], r->iv[lane + 32]};
     const float mt[2] = {r->mt[lane], r->mt[lane + 32]};
     const float m_prev = r->m_prev;
     float fc0 = log_sigmoid(fr[0]), fc1 = log_sigmoid(fr[1]);
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        float y0 = __shfl_up_sync(0xffffffffu, fc0, o), y1 = __shfl_up_sync(0xffffffffu, fc1, o);
-        if (lane >= o) { fc0 += y0; fc1 += y1; }
-    }
-    fc1 += __shfl_sync(0xffffffffu, fc0, 31);
+    seg_prefix64<false>(fc0, fc1, lane, seg);
     const float fcL = __shfl_sync(0xffffffffu, fc1, 31);
     const float mL = __shfl_sync(0xffffffffu, mt[1], 31);
     float fc[2] = {fc0, fc1};
@@ -220,11 +223,11 @@ __device__ __forceinline__ void gates_compute(const GateRawS* r, Gates* G) {
         G->rowt[t] = fc[e] - mt[e];
         G->colt[t] = iv[e] - fc[e];
         G->b[t] = expf(fc[e] + m_prev - mt[e]);
-        G->a[t] = expf(fcL - fc[e] + iv[e] - mL);
+        G->a[t] = seg ? 0.f : expf(fcL - fc[e] + iv[e] - mL);  // packed: no state crosses the tile
         G->fg[t] = fr[e];
         G->emm[t] = expf(-mt[e]);
     }
-    if (lane == 0) G->g = expf(fcL + m_prev - mL);
+    if (lane == 0) G->g = seg ? 0.f : expf(fcL + m_prev - mL);
 }
 // Control warp: start the asynchronous copy of a chunk's psi, qn (64 each) and entering normaliser n (128)
 // straight into their shared-memory slot [psi 64 | qn 64 | n 128].
@@ -233,7 +236,7 @@ __device__ __forceinline__ void vec_fetch(const Params& p, int bh, int sbh, int 
     const int t0 = ch * L, Lc = min(L, p.T - t0);
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-        const size_t o = (size_t)bh * p.T + t0 + min(lane + 32 * e, Lc - 1);
+        const size_t o = vec_index(p, bh / p.H, bh % p.H, bh, t0 + min(lane + 32 * e, Lc - 1));
         cp_async4(dst + lane + 32 * e, p.psiv + o);
         cp_async4(dst + L + lane + 32 * e, p.qnv + o);
         if (p.dotv) cp_async4(dst + 2 * L + D + lane + 32 * e, p.dotv + o);
@@ -394,7 +397,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
         cp_async_commit();
         cp_async_wait_all();
         __syncwarp();
-        gates_compute(&GR[(p.NC - 1) & 1], &G[(p.NC - 1) & 1]);
+        gates_compute(&GR[(p.NC - 1) & 1], &G[(p.NC - 1) & 1], p.seg);
         if (p.NC > 1) { gates_fetch(p, b, h, bh, p.NC - 2, &GR[(p.NC - 2) & 1]); cp_async_commit(); }
     } else {
         prefetch_dy(p.NC - 1);
@@ -577,6 +580,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
                 // branch-free and on all lanes (lanes 16-31 hold no rows of an M = 64 tile; their values are not stored):
                 // the causal mask goes into the exponent's argument, exp(-inf) = 0
                 const float rt = Gc->rowt[srow], dq_t = sdqn[srow];
+                const int jmin = seg_first(srow, p.seg);  // packed mode: the row's own sequence only
 #pragma unroll
                 for (int i4 = 0; i4 < 4; ++i4) {
                     const float4 c4 = *reinterpret_cast<const float4*>(Gc->colt + 16 * cq + 4 * i4);
@@ -584,7 +588,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int i = 4 * i4 + e, j = 16 * cq + i;
-                        const float dbar = __expf((j <= srow) ? rt + cc[e] : -INFINITY);
+                        const float dbar = __expf((j <= srow && j >= jmin) ? rt + cc[e] : -INFINITY);
                         s[i] *= dbar;
                         dd[i] = dbar * (dd[i] + dq_t);
                     }
@@ -620,7 +624,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             if (ch > 0) {
                 cp_async_wait_all();  // raw gates of chunk ch-1, fetched during the previous chunk
                 __syncwarp();
-                gates_compute(&GR[(ch - 1) & 1], &G[(ch - 1) & 1]);
+                gates_compute(&GR[(ch - 1) & 1], &G[(ch - 1) & 1], p.seg);
                 vec_fetch(p, bh, sbh, ch - 1, svec + ((ch - 1) & 1) * kVecFloats);
                 if (ch > 1) gates_fetch(p, b, h, bh, ch - 2, &GR[ch & 1]);
                 cp_async_commit();
@@ -734,13 +738,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             }
             // suffix sums over the 64 positions
             float s0 = dF[0], s1 = dF[1];
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                float y0 = __shfl_down_sync(0xffffffffu, s0, o), y1 = __shfl_down_sync(0xffffffffu, s1, o);
-                if (lane + o < 32) { s0 += y0; s1 += y1; }
-            }
-            const float tot1 = __shfl_sync(0xffffffffu, s1, 0);
-            s0 += tot1;
+            seg_suffix64(s0, s1, lane, p.seg);
             const float tot = __shfl_sync(0xffffffffu, s0, 0);
             const float run = *srun;
             float sf[2] = {s0, s1};
@@ -921,6 +919,11 @@ int mlstm_bw_tc_launch(cudaStream_t st, const MlstmBwArgs& a, const void* saved,
     p.ig = a.ig; p.fg = a.fg; p.cm = a.cm; p.ytil = (const bf16*)a.ytil; p.msv = a.msv; p.psiv = a.psiv; p.qnv = a.qnv;
     p.dy = a.dytil; p.cdC = a.cdC; p.cdn = a.cdn; p.dq = a.dq; p.dk = a.dk; p.dv = a.dv; p.dig = a.dig; p.dfg = a.dfg;
     p.odC = a.odC; p.odn = a.odn; p.B = a.B; p.H = a.H; p.T = a.T; p.NC = a.NC; p.gbf16 = gbf;
+    p.seg = a.seg; p.npack = a.npack;
+    if (a.seg && (nsub != 1 || a.NC != 1 || a.T != a.seg * a.npack || a.T > L || a.seg > 32 || a.cm || a.cdC || a.odC)) {
+        set_error("mlstm_bw: packed mode takes 128-wide heads, npack * seg <= 64 positions per tile, seg <= 32 and no carries");
+        return XLSTM_ERR_ARG;
+    }
     p.status = tc_status_ptr();
     if (!p.status) { set_error("mlstm_bw: cannot resolve the device status word"); return XLSTM_ERR_CUDA; }
     if (nsub == 1) return gbf ? bw_launch_kernel<bf16, bf16, false>(st, p, BH) : bw_launch_kernel<float, float, false>(st, p, BH);

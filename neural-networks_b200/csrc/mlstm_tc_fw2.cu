@@ -66,6 +66,11 @@ struct Params {
     float *oC, *on, *om;
     int B, H, T, NC;
     int states_only;  // 1: the state recurrence only (no S, no outputs)
+    // Packed mode (seg > 0): a "sequence" of this launch is npack independent sequences of seg <= 32 positions each laid
+    // end to end (T = npack * seg <= 64: one chunk), none with a carry. Gate scans restart at every multiple of seg, the
+    // decay mask is block-diagonal, the state stays zero, and msv / psiv / qnv keep the caller's [sequence][head][seg]
+    // layout. A 9-position sequence then costs a seventh of a chunk tile instead of a whole one.
+    int seg, npack;
     int* status;
 };
 
@@ -127,20 +132,11 @@ __device__ __forceinline__ float gates_compute(const Params& p, int b, int h, in
             iv[e] = p.ig[gi];
         }
     }
+    const int seg = p.seg;  // packed mode: every sequence of the tile starts from the empty state (m_prev = 0 here)
     float fc0 = log_sigmoid(fr[0]), fc1 = log_sigmoid(fr[1]);
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        float y0 = __shfl_up_sync(0xffffffffu, fc0, o), y1 = __shfl_up_sync(0xffffffffu, fc1, o);
-        if (lane >= o) { fc0 += y0; fc1 += y1; }
-    }
-    fc1 += __shfl_sync(0xffffffffu, fc0, 31);
+    seg_prefix64<false>(fc0, fc1, lane, seg);
     float u0 = iv[0] - fc0, u1 = iv[1] - fc1;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        float y0 = __shfl_up_sync(0xffffffffu, u0, o), y1 = __shfl_up_sync(0xffffffffu, u1, o);
-        if (lane >= o) { u0 = fmaxf(u0, y0); u1 = fmaxf(u1, y1); }
-    }
-    u1 = fmaxf(u1, __shfl_sync(0xffffffffu, u0, 31));
+    seg_prefix64<true>(u0, u1, lane, seg);
     const float m0 = fc0 + fmaxf(m_prev, u0), m1 = fc1 + fmaxf(m_prev, u1);
     const float fcL = __shfl_sync(0xffffffffu, fc1, 31), mL = __shfl_sync(0xffffffffu, m1, 31);
     const float fc[2] = {fc0, fc1}, mt[2] = {m0, m1};
@@ -151,9 +147,9 @@ __device__ __forceinline__ float gates_compute(const Params& p, int b, int h, in
         G->colt[t] = iv[e] - fc[e];
         G->m[t] = mt[e];
         G->b[t] = expf(fc[e] + m_prev - mt[e]);
-        G->a[t] = expf(fcL - fc[e] + iv[e] - mL);
+        G->a[t] = seg ? 0.f : expf(fcL - fc[e] + iv[e] - mL);  // packed: no state leaves the tile
     }
-    if (lane == 0) G->g = expf(fcL + m_prev - mL);
+    if (lane == 0) G->g = seg ? 0.f : expf(fcL + m_prev - mL);
     return mL;
 }
 
@@ -363,6 +359,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
                 float rs0 = 0.f, rs1 = 0.f;
                 {
                     const float rt = Gc->rowt[row];
+                    const int jmin = seg_first(row, p.seg);  // packed mode: the row's own sequence only
 #pragma unroll
                     for (int i4 = 0; i4 < 8; ++i4) {
                         const float4 c4 = *reinterpret_cast<const float4*>(Gc->colt + 32 * half + 4 * i4);
@@ -370,7 +367,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int i = 4 * i4 + e, j = 32 * half + i;
-                            const float dbar = __expf((j <= row) ? rt + cc[e] : -INFINITY);
+                            const float dbar = __expf((j <= row && j >= jmin) ? rt + cc[e] : -INFINITY);
                             sv[i] *= dbar;
                             if (e & 1) rs1 += sv[i]; else rs0 += sv[i];
                         }
@@ -487,7 +484,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
                 const float psi = fmaxf(fabsf(qn), expf(-mt));
                 sipsi[s * L + qt] = 1.f / psi;
                 if (qt < Lc) {
-                    const size_t o = (size_t)bh * p.T + t0 + qt;
+                    const size_t o = p.seg ? ((size_t)(b * p.npack + qt / p.seg) * p.H + h) * p.seg + qt % p.seg
+                                           : (size_t)bh * p.T + t0 + qt;
                     p.msv[o] = mt; p.psiv[o] = psi; p.qnv[o] = qn;
                 }
             }
@@ -627,6 +625,11 @@ int mlstm_fw_ws_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved) {
     p.oC = a.oC; p.on = a.on; p.om = a.om;
     p.B = a.B; p.H = a.H; p.T = a.T; p.NC = a.NC;
     p.states_only = a.states_only;
+    p.seg = a.seg; p.npack = a.npack;
+    if (a.seg && (a.NC != 1 || a.T != a.seg * a.npack || a.T > L || a.seg > 32 || a.cC || a.oC)) {
+        set_error("mlstm_fw: packed mode takes npack * seg <= 64 positions per tile, seg <= 32, no carry and no state out");
+        return XLSTM_ERR_ARG;
+    }
     p.status = tc_status_ptr();
     if (!p.status) { set_error("mlstm_fw: cannot resolve the device status word"); return XLSTM_ERR_CUDA; }
     // the opt-in to large dynamic shared memory is a per-device function attribute: one flag per device

@@ -236,5 +236,36 @@ __device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
     return __bfloat1622float2(t);
 }
 
+// ---- scans over the 64 positions of a chunk tile, two per lane (t = lane and lane + 32) ---------------------------
+// `seg` > 0: the tile holds several short sequences of `seg` positions each (packed mode) and every scan restarts at a
+// multiple of seg; seg = 0: one sequence, plain scans.
+__device__ __forceinline__ int seg_first(int t, int seg) { return seg > 0 ? t - t % seg : 0; }
+__device__ __forceinline__ int seg_last(int t, int seg) { return seg > 0 ? min(63, t - t % seg + seg - 1) : 63; }
+// inclusive prefix scan (sum: MAXOP = false; running maximum: MAXOP = true)
+template <bool MAXOP>
+__device__ __forceinline__ void seg_prefix64(float& v0, float& v1, int lane, int seg) {
+    const int f0 = seg_first(lane, seg), f1 = seg_first(lane + 32, seg);
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float y0 = __shfl_up_sync(0xffffffffu, v0, o), y1 = __shfl_up_sync(0xffffffffu, v1, o);
+        if (lane >= o && lane - o >= f0) v0 = MAXOP ? fmaxf(v0, y0) : v0 + y0;
+        if (lane >= o && lane + 32 - o >= f1) v1 = MAXOP ? fmaxf(v1, y1) : v1 + y1;
+    }
+    const float c = __shfl_sync(0xffffffffu, v0, 31);
+    if (f1 <= 31) v1 = MAXOP ? fmaxf(v1, c) : v1 + c;
+}
+// inclusive suffix sum
+__device__ __forceinline__ void seg_suffix64(float& v0, float& v1, int lane, int seg) {
+    const int l0 = seg_last(lane, seg), l1 = seg_last(lane + 32, seg);
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float y0 = __shfl_down_sync(0xffffffffu, v0, o), y1 = __shfl_down_sync(0xffffffffu, v1, o);
+        if (lane + o < 32 && lane + o <= l0) v0 += y0;
+        if (lane + o < 32 && lane + 32 + o <= l1) v1 += y1;
+    }
+    const float c = __shfl_sync(0xffffffffu, v1, 0);
+    if (l0 >= 32) v0 += c;
+}
+
 }  // namespace tc
 }  // namespace xl

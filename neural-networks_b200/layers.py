@@ -192,8 +192,10 @@ class MLstm:
         """residual: when given, the call returns residual + cell(x) (the block's first residual add, done inside
         the output projection's GEMM)."""
         sdt = torch.bfloat16 if self.bf16 else torch.float32
+        # short sequences that neither take nor leave a state (word rectangles): several to a chunk tile
+        pack = T <= 32 and not (self.stateful or self.sweep) and self.carry is None and self.cp is None
         self.st = ops.MlstmShape(B, self.h, T, self.dqk, self.dhv, self.chunk, sdt,
-                                 torch.bfloat16 if self.grad_bf16 else torch.float32)
+                                 torch.bfloat16 if self.grad_bf16 else torch.float32, ops.PACK_SHORT if pack else 0)
         if self.bf16:
             x = _b16(x)  # one narrowing feeds all six projections
         if self.bf16:  # bf16 q, k, v straight from the GEMM epilogue (bias and the 1/sqrt(dqk) of k folded in)

@@ -13,6 +13,7 @@ from . import _lib
 from ._lib import lib, check
 
 _DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+FORCE_SIMT, PACK_SHORT = _lib.FORCE_SIMT, _lib.PACK_SHORT  # MlstmShape flags
 
 # ---- optional per-op device timing (benchmarks): CUDA events around the calls of the named ops -----------------------
 _timing = None

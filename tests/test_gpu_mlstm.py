@@ -242,3 +242,66 @@ def test_caller_buffers_reused_across_shapes_with_stale_contents():
             got = pool[name].view(torch.float32)[:ref.numel()].view(ref.shape)
             assert torch.equal(got, ref), name
         assert xl._lib.lib.xlstm_device_status() == 0
+
+
+@pytest.mark.parametrize("B,T", [(20, 9), (14, 9), (7, 9), (130, 1), (5, 32), (19, 7), (23, 3), (64, 16), (3, 21)])
+@pytest.mark.parametrize("gdtype,save", [(torch.float32, True), (torch.bfloat16, False)])
+def test_packed_short_sequences_equal_the_unpacked_call_and_the_oracle(B, T, gdtype, save):
+    """XLSTM_PACK_SHORT: 64 // T carry-less sequences share a chunk tile (the hierarchical model's word rectangles).
+    Same arithmetic per sequence up to the summation order of the gate scans, so the packed call agrees with the
+    unpacked one to fp32 round-off (one bf16 ulp where the result is stored as bf16); both sit inside the bf16 bar of
+    the float64 oracle. Covers batch
+    sizes below, at and off a multiple of the tile's capacity (the remainder runs unpacked on the tail), T = 1 (64 to
+    a tile), T = 32 (two), T = 21 (three, with one idle row), and both ways of getting the chunk states."""
+    from gpu_util import ops, dev, host, mlstm_inputs, bf16_round, rel_to_max
+    H, d = 2, 128
+    q, k, v, ig, fg, dy = mlstm_inputs(B, H, T, d, d, seed=31 + B + T, bf16=True)
+    if gdtype == torch.bfloat16:
+        dy = bf16_round(dy)
+    dt = torch.bfloat16
+    args = (dev(q, dt), dev(k, dt), dev(v, dt), dev(ig), dev(fg))
+    out = {}
+    for name, flags in (("packed", ops.PACK_SHORT), ("plain", 0)):
+        st = ops.MlstmShape(B, H, T, d, d, 64, dt, gdtype, flags)
+        fused = ops.mlstm_fused_fw(*args, st, save_states=save, want_state=False)
+        grads = ops.mlstm_fused_bw(fused, *args, dev(dy, gdtype), st, want_dstate=False)
+        torch.cuda.synchronize()
+        out[name] = (fused, grads)
+    assert ops.lib.xlstm_device_status() == 0
+    fp, gp = out["packed"]
+    fu, gu = out["plain"]
+    # (a position's place in the tile changes the order of the gate scans' additions: last-bit differences in m)
+    for a, b, n, bar in ((fp.ytil, fu.ytil, "ytil", 2.0 ** -8), (fp.msv, fu.msv, "m", 1e-6), (fp.psiv, fu.psiv, "psi", 1e-6),
+                         (fp.qnv, fu.qnv, "qn", 1e-5)):
+        assert rel_to_max(host(a), host(b)) <= bar, n
+    for i, n in enumerate(("dq", "dk", "dv", "dig", "dfg")):
+        assert rel_to_max(host(gp[i]), host(gu[i])) <= (1e-5 if gdtype == torch.float32 else 2.0 ** -8), n
+    ofw = O.mlstm_core_fw(q, k, v, ig, fg, B, H, T, d, d, C0=None, n0=None, m0=None)
+    obw = O.mlstm_core_bw(q, k, v, ig, fg, dy, B, H, T, d, d, C0=None, n0=None, m0=None, dC_in=None, dn_in=None)
+    got = dict(ytil=host(fp.ytil), m=host(fp.msv), psi=host(fp.psiv), dq=host(gp[0]), dk=host(gp[1]), dv=host(gp[2]),
+               dig=host(gp[3]), dfg=host(gp[4]))
+    ref = dict(ofw)
+    ref.update(obw)
+    _assert_close(got, ref, TOL[torch.bfloat16], ("ytil", "m", "psi", "dq", "dk", "dv", "dig", "dfg"))
+
+
+def test_packed_flag_is_refused_with_a_carry_or_a_state_request_and_ignored_where_it_does_not_apply():
+    from gpu_util import ops, dev, mlstm_inputs
+    B, H, T, d = 8, 2, 9, 128
+    q, k, v, ig, fg, dy = mlstm_inputs(B, H, T, d, d, seed=5, bf16=True)
+    dt = torch.bfloat16
+    args = (dev(q, dt), dev(k, dt), dev(v, dt), dev(ig), dev(fg))
+    st = ops.MlstmShape(B, H, T, d, d, 64, dt, torch.float32, ops.PACK_SHORT)
+    with pytest.raises(Exception, match="PACK_SHORT"):
+        ops.mlstm_fused_fw(*args, st, want_state=True)
+    fused = ops.mlstm_fused_fw(*args, st, want_state=False)
+    with pytest.raises(Exception, match="PACK_SHORT"):
+        ops.mlstm_fused_bw(fused, *args, dev(dy), st, want_dstate=True)
+    # CUDA-core path (fp32 storage, small heads): the flag changes nothing
+    q, k, v, ig, fg, dy = mlstm_inputs(4, 2, 6, 8, 8, seed=6)
+    a32 = (dev(q), dev(k), dev(v), dev(ig), dev(fg))
+    res = []
+    for flags in (ops.PACK_SHORT, 0):
+        s32 = ops.MlstmShape(4, 2, 6, 8, 8, 64, torch.float32, torch.float32, flags)
+        res.append(ops.mlstm_fused_fw(*a32, s32, want_state=True).ytil)
+    assert torch.equal(res[0], res[1])
