@@ -65,6 +65,22 @@ __device__ __forceinline__ float log_sigmoid(float x) {
     return x - log1pf(expf(x));
 }
 
+// acc[c] += sum over the parts of partial[part][c], in a fixed order (no float atomics): eight lanes per column take the
+// parts lane, lane + 8, ... in ascending order and the eight sums are combined pairwise. One CTA per 32 columns.
+static __global__ void __launch_bounds__(256) merge_parts8(const float* __restrict__ partial, float* __restrict__ acc,
+                                                           int nparts, int cols) {
+    __shared__ float sh[8][32];
+    const int cl = threadIdx.x & 31, pl = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cl;
+    float s = 0.f;
+    if (c < cols)
+        for (int p = pl; p < nparts; p += 8) s += partial[(size_t)p * cols + c];
+    sh[pl][cl] = s;
+    __syncthreads();
+    if (pl == 0 && c < cols)
+        acc[c] += ((sh[0][cl] + sh[1][cl]) + (sh[2][cl] + sh[3][cl])) + ((sh[4][cl] + sh[5][cl]) + (sh[6][cl] + sh[7][cl]));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -222,6 +222,49 @@ __global__ void __launch_bounds__(256) embedding_scatter_add_k(const float* __re
     }
 }
 
+// The same for row widths that are a multiple of four floats and whose 16-byte pieces (at most 256) divide the CTA:
+// the CTA's threads form RL row lanes x CL column lanes; row lane r sums the run's rows r, r + RL, ... in that order with
+// four rows' loads in flight, and the RL partial rows are added in lane order. A fixed order again, and a long run (a byte
+// vocabulary: hundreds of rows per id) no longer walks its rows one dependent load after the other.
+__global__ void __launch_bounds__(256) embedding_scatter_add_v4_k(const float* __restrict__ d, const int* __restrict__ sorted_ids,
+                                                                  const int* __restrict__ order, float* __restrict__ table_g,
+                                                                  int n, int dm, int CL) {
+    __shared__ float4 part[256];
+    const int p = blockIdx.x;
+    const int id = sorted_ids[p];
+    if (p > 0 && sorted_ids[p - 1] == id) return;
+    int end = p + 1;
+    while (end < n && sorted_ids[end] == id) ++end;
+    const int RL = 256 / CL, cl = threadIdx.x % CL, rl = threadIdx.x / CL, c4n = dm / 4;
+    float4* dst = reinterpret_cast<float4*>(table_g + (size_t)id * dm);
+    for (int c0 = 0; c0 < c4n; c0 += CL) {  // CL divides c4n or exceeds it only when c4n < CL is impossible (CL <= c4n)
+        const int c4 = c0 + cl;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q = p + rl; q < end; q += 4 * RL) {
+            float4 r[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int qq = q + k * RL;
+                r[k] = qq < end ? __ldcs(reinterpret_cast<const float4*>(d + (size_t)__ldg(order + qq) * dm) + c4)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { acc.x += r[k].x; acc.y += r[k].y; acc.z += r[k].z; acc.w += r[k].w; }
+        }
+        part[threadIdx.x] = acc;
+        __syncthreads();
+        if (rl == 0) {
+            float4 t = dst[c4];
+            for (int r2 = 0; r2 < RL; ++r2) {
+                const float4 v = part[r2 * CL + cl];
+                t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+            }
+            dst[c4] = t;
+        }
+        __syncthreads();
+    }
+}
+
 // x = hi + mid + lo with three bf16 terms (RNE at each step: hi = bf16(x), mid = bf16(x - hi), lo = bf16(x - hi - mid)),
 // the operand form of the split-bf16 fp32 product; one pass instead of five casts and two subtractions.
 __global__ void __launch_bounds__(256) split3_k(const float* __restrict__ x, bf16* __restrict__ hi, bf16* __restrict__ mid,
@@ -312,13 +355,6 @@ __global__ void __launch_bounds__(128) colsum_narrow_gen_k(const T* __restrict__
         if (out) out[(size_t)r * cols + c] = __float2bfloat16_rn(v * scale);
     }
     partial[(size_t)blockIdx.y * cols + c] = acc * scale;
-}
-__global__ void colsum_parts_merge_k(const float* __restrict__ partial, float* __restrict__ acc, int nparts, int cols) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
-    float s = 0.f;
-    for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * cols + c];
-    acc[c] += s;
 }
 static int colsum_parts(int rows, int cols) {
     const int tiles = (cols + 127) / 128;
@@ -456,7 +492,13 @@ extern "C" int xlstm_embedding_scatter_add(void* stream, const float* d, const i
     XL_CHECK_ARG(d && sorted_ids && order && table_g, "embedding_scatter_add: null pointer");
     XL_CHECK_ARG(n >= 0 && dm > 0, "embedding_scatter_add: bad shape n=%d dm=%d", n, dm);
     if (n == 0) return XLSTM_OK;
-    embedding_scatter_add_k<<<(unsigned)n, 256, 0, (cudaStream_t)stream>>>(d, sorted_ids, order, table_g, n, dm);
+    // 16-byte pieces per row: the vector kernel takes them when they tile the CTA's 256 threads (64 pieces x 4 row lanes at
+    // a row of 256 floats) or are a multiple of 256
+    const int c4n = dm % 4 == 0 ? dm / 4 : 0;
+    const int CL = c4n >= 256 ? 256 : c4n;
+    const bool v4 = c4n > 0 && CL > 0 && 256 % CL == 0 && c4n % CL == 0 && !(((uintptr_t)d | (uintptr_t)table_g) & 15);
+    if (v4) embedding_scatter_add_v4_k<<<(unsigned)n, 256, 0, (cudaStream_t)stream>>>(d, sorted_ids, order, table_g, n, dm, CL);
+    else embedding_scatter_add_k<<<(unsigned)n, 256, 0, (cudaStream_t)stream>>>(d, sorted_ids, order, table_g, n, dm);
     XL_LAUNCH_OK("embedding_scatter_add");
     return XLSTM_OK;
 }
@@ -501,7 +543,7 @@ extern "C" int xlstm_colsum_narrow(void* stream, const void* x, int x_dtype, int
         else colsum_narrow_gen_k<bf16><<<grid, 128, 0, st>>>((const bf16*)x, (bf16*)out_bf16, partial, rows, cols, scale, rpp);
     }
     XL_LAUNCH_OK("colsum_narrow");
-    colsum_parts_merge_k<<<(cols + 127) / 128, 128, 0, st>>>(partial, acc, nparts, cols);
+    merge_parts8<<<(cols + 31) / 32, 256, 0, st>>>(partial, acc, nparts, cols);
     XL_LAUNCH_OK("colsum_parts_merge");
     return XLSTM_OK;
 }

@@ -158,14 +158,6 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) rmsnorm_bw_vec(
     for (int c = threadIdx.x; c < group; c += blockDim.x) prow[c] = sacc[c];
 }
 
-// dgamma[c] += sum over parts (ascending) of partial[part][c]
-__global__ void colsum_merge(const float* __restrict__ partial, float* __restrict__ dgamma, int nparts, int F) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= F) return;
-    float s = 0.f;
-    for (int p = 0; p < nparts; ++p) s += partial[(long long)p * F + c];
-    dgamma[c] += s;
-}
 
 // ---- generic path: any group size -------------------------------------------------------
 template <typename XT, typename YT>
@@ -330,7 +322,7 @@ static int rmsnorm_bw_run(cudaStream_t st, const float* dy, const XT* x, const f
         colsum_mul_gen<XT><<<grid, 128, 0, st>>>(dy, x, inv_rms, partial, rows, F, group, rpp);
         XL_LAUNCH_OK("colsum_mul_gen");
     }
-    colsum_merge<<<(F + 127) / 128, 128, 0, st>>>(partial, dgamma, nparts, F);
+    merge_parts8<<<(F + 31) / 32, 256, 0, st>>>(partial, dgamma, nparts, F);
     XL_LAUNCH_OK("colsum_merge");
     return XLSTM_OK;
 }

@@ -160,6 +160,39 @@ def test_embedding_scatter_add_is_exact_and_repeatable():
     assert np.array_equal(outs[0], want)
 
 
+@pytest.mark.parametrize("dm,vocab", [(256, 7), (128, 3), (1024, 5), (2048, 40)])
+def test_embedding_scatter_add_wide_rows_fixed_lane_order(dm, vocab):
+    """Rows that are a whole number of 16-byte pieces tiling the CTA: 256 / min(dm / 4, 256) row lanes each sum every
+    RL-th row of an id's run in position order and the lane sums are added in lane order: a fixed order, reproduced here
+    in float32, so the result is exact and repeatable (a byte vocabulary: runs of hundreds of rows)."""
+    from gpu_util import ops
+    r = np.random.default_rng(dm)
+    n = 2500
+    ids = r.integers(0, vocab, n)
+    d = r.standard_normal((n, dm)).astype(np.float32)
+    g0 = r.standard_normal((vocab, dm)).astype(np.float32)
+    RL = 256 // min(dm // 4, 256)
+    want = g0.copy()
+    for i in range(vocab):
+        rows = np.nonzero(ids == i)[0]
+        parts = []
+        for lane in range(RL):
+            acc = np.zeros(dm, np.float32)
+            for p in rows[lane::RL]:
+                acc += d[p]
+            parts.append(acc)
+        if len(rows):
+            for acc in parts:
+                want[i] += acc
+    outs = []
+    for _ in range(2):
+        g = torch.tensor(g0, device="cuda")
+        ops.embedding_scatter_add(g, torch.tensor(ids, device="cuda"), torch.tensor(d, device="cuda"))
+        outs.append(g.cpu().numpy())
+    assert np.array_equal(outs[0], outs[1])
+    assert np.array_equal(outs[0], want)
+
+
 @pytest.mark.parametrize("wd", [0.0, 0.01])
 def test_adamw_single_and_batched(wd):
     from gpu_util import ops, dev, host, rel_to_max
