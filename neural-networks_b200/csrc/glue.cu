@@ -203,6 +203,17 @@ __global__ void __launch_bounds__(256) ogate_bw_k(const float* __restrict__ d_hc
     }
 }
 
+// First position after p whose id differs from `id` (the ids are sorted: a binary search, not a walk along a run that a
+// byte vocabulary makes hundreds of positions long).
+__device__ __forceinline__ int run_end(const int* __restrict__ sorted_ids, int p, int n, int id) {
+    int lo = p + 1, hi = n;  // the answer is in [lo, hi]
+    while (lo < hi) {
+        const int mid = lo + (hi - lo) / 2;
+        if (__ldg(sorted_ids + mid) == id) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
 // table_g[id] += sum of the rows of d that carry token id, summed in ascending position order so the result
 // does not depend on scheduling (no float atomics). `sorted_ids` are the token ids sorted stably and `order`
 // the positions in that order; CTA p works only when p starts a run of equal ids, and then owns that row.
@@ -212,8 +223,7 @@ __global__ void __launch_bounds__(256) embedding_scatter_add_k(const float* __re
     const int p = blockIdx.x;
     const int id = sorted_ids[p];
     if (p > 0 && sorted_ids[p - 1] == id) return;
-    int end = p + 1;
-    while (end < n && sorted_ids[end] == id) ++end;
+    const int end = run_end(sorted_ids, p, n, id);
     float* dst = table_g + (size_t)id * dm;
     for (int c = threadIdx.x; c < dm; c += 256) {
         float acc = dst[c];
@@ -233,8 +243,7 @@ __global__ void __launch_bounds__(256) embedding_scatter_add_v4_k(const float* _
     const int p = blockIdx.x;
     const int id = sorted_ids[p];
     if (p > 0 && sorted_ids[p - 1] == id) return;
-    int end = p + 1;
-    while (end < n && sorted_ids[end] == id) ++end;
+    const int end = run_end(sorted_ids, p, n, id);
     const int RL = 256 / CL, cl = threadIdx.x % CL, rl = threadIdx.x / CL, c4n = dm / 4;
     float4* dst = reinterpret_cast<float4*>(table_g + (size_t)id * dm);
     for (int c0 = 0; c0 < c4n; c0 += CL) {  // CL divides c4n or exceeds it only when c4n < CL is impossible (CL <= c4n)
