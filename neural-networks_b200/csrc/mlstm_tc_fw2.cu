@@ -117,6 +117,7 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
 
 // Gate vectors of one chunk by one warp (two positions per lane): fc = cumsum(log sigmoid f),
 // m_t = fc_t + max(m_prev, max_{j<=t}(i_j - fc_j)). Returns m of the chunk's last position.
+template <bool PACKED>
 __device__ __forceinline__ float gates_compute(const Params& p, int b, int h, int ch, float m_prev, Gates* G) {
     const int lane = threadIdx.x & 31;
     const int t0 = ch * L, Lc = min(L, p.T - t0);
@@ -132,7 +133,7 @@ __device__ __forceinline__ float gates_compute(const Params& p, int b, int h, in
             iv[e] = p.ig[gi];
         }
     }
-    const int seg = p.seg;  // packed mode: every sequence of the tile starts from the empty state (m_prev = 0 here)
+    const int seg = PACKED ? p.seg : 0;  // packed mode: every sequence of the tile starts from the empty state (m_prev = 0 here)
     float fc0 = log_sigmoid(fr[0]), fc1 = log_sigmoid(fr[1]);
     seg_prefix64<false>(fc0, fc1, lane, seg);
     float u0 = iv[0] - fc0, u1 = iv[1] - fc1;
@@ -183,6 +184,9 @@ __device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.
         break;                                                                                    \
     }
 
+// PACKED: the instantiation that packed launches use; the plain one carries none of their index arithmetic (the extra
+// compare per element of the decay mask alone cost the forward 6 %).
+template <bool PACKED>
 __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant__ Params p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -233,7 +237,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
                     tma_load_3d(base + 2 * kTileBytes + cbx * kBoxBytes, &p.tmv, &bars[kFull + s], col0 + 64 * cbx, c * L, b);
                 }
             }
-            m_prev = gates_compute(p, b, h, c, m_prev, &G[c & 3]);
+            m_prev = gates_compute<PACKED>(p, b, h, c, m_prev, &G[c & 3]);
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars[kGates + (c & 3)]);
         }
@@ -359,7 +363,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
                 float rs0 = 0.f, rs1 = 0.f;
                 {
                     const float rt = Gc->rowt[row];
-                    const int jmin = seg_first(row, p.seg);  // packed mode: the row's own sequence only
+                    const int jmin = PACKED ? seg_first(row, p.seg) : 0;  // packed mode: the row's own sequence only
 #pragma unroll
                     for (int i4 = 0; i4 < 8; ++i4) {
                         const float4 c4 = *reinterpret_cast<const float4*>(Gc->colt + 32 * half + 4 * i4);
@@ -367,7 +371,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int i = 4 * i4 + e, j = 32 * half + i;
-                            const float dbar = __expf((j <= row && j >= jmin) ? rt + cc[e] : -INFINITY);
+                            const float dbar = __expf((j <= row && (!PACKED || j >= jmin)) ? rt + cc[e] : -INFINITY);
                             sv[i] *= dbar;
                             if (e & 1) rs1 += sv[i]; else rs0 += sv[i];
                         }
@@ -484,7 +488,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_fw_ws(const __grid_constant
                 const float psi = fmaxf(fabsf(qn), expf(-mt));
                 sipsi[s * L + qt] = 1.f / psi;
                 if (qt < Lc) {
-                    const size_t o = p.seg ? ((size_t)(b * p.npack + qt / p.seg) * p.H + h) * p.seg + qt % p.seg
+                    const size_t o = PACKED ? ((size_t)(b * p.npack + qt / p.seg) * p.H + h) * p.seg + qt % p.seg
                                            : (size_t)bh * p.T + t0 + qt;
                     p.msv[o] = mt; p.psiv[o] = psi; p.qnv[o] = qn;
                 }
@@ -638,10 +642,12 @@ int mlstm_fw_ws_launch(cudaStream_t st, const MlstmFwArgs& a, void* saved) {
     int dev = 0;
     XL_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
-        XL_CUDA(cudaFuncSetAttribute(mlstm_fw_ws, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        XL_CUDA(cudaFuncSetAttribute(mlstm_fw_ws<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        XL_CUDA(cudaFuncSetAttribute(mlstm_fw_ws<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
-    mlstm_fw_ws<<<a.B * a.H, kThreads, smem, st>>>(p);
+    if (a.seg) mlstm_fw_ws<true><<<a.B * a.H, kThreads, smem, st>>>(p);
+    else mlstm_fw_ws<false><<<a.B * a.H, kThreads, smem, st>>>(p);
     XL_LAUNCH_OK("mlstm_fw_ws");
     return XLSTM_OK;
 }
