@@ -326,6 +326,16 @@ __global__ void __launch_bounds__(256) colsum_narrow_k(const T* __restrict__ x, 
     if (c0 < cols) {
         const size_t c4 = (size_t)c0 / 4, row4 = (size_t)cols / 4;
         int r = r0 + rl;
+        for (; r + 24 < r1; r += 32) {  // four rows in flight (summed in the same order as the loops below)
+            float4 v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = ld4(x, (size_t)(r + 8 * k) * row4 + c4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                acc.x += v[k].x; acc.y += v[k].y; acc.z += v[k].z; acc.w += v[k].w;
+                if (out) st4(out, (size_t)(r + 8 * k) * row4 + c4, make_float4(v[k].x * scale, v[k].y * scale, v[k].z * scale, v[k].w * scale));
+            }
+        }
         for (; r + 8 < r1; r += 16) {  // two rows in flight
             const float4 v0 = ld4(x, (size_t)r * row4 + c4), v1 = ld4(x, (size_t)(r + 8) * row4 + c4);
             acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
