@@ -79,8 +79,9 @@ struct Params {
 };
 
 // Index of position t0 + t of (b, h) in msv / psiv / qnv (and dotv).
-__device__ __forceinline__ size_t vec_index(const Params& p, int b, int h, int bh, int pos) {
-    return p.seg ? ((size_t)(b * p.npack + pos / p.seg) * p.H + h) * p.seg + pos % p.seg : (size_t)bh * p.T + pos;
+// (`seg` is the kernel's segment length: the compile-time 0 of the plain instantiations removes the packed arithmetic.)
+__device__ __forceinline__ size_t vec_index(const Params& p, int b, int h, int bh, int pos, int seg) {
+    return seg ? ((size_t)(b * p.npack + pos / seg) * p.H + h) * seg + pos % seg : (size_t)bh * p.T + pos;
 }
 
 static constexpr int kVecFloats = 3 * L + D;
@@ -182,7 +183,7 @@ struct GateRawS {
     float pad[3];
 };
 // Control warp: start the asynchronous copy of a chunk's raw gate inputs (two positions per lane).
-__device__ __forceinline__ void gates_fetch(const Params& p, int b, int h, int bh, int ch, GateRawS* r) {
+__device__ __forceinline__ void gates_fetch(const Params& p, int b, int h, int bh, int ch, GateRawS* r, int seg) {
     const int lane = threadIdx.x & 31;
     const int t0 = ch * L, Lc = min(L, p.T - t0);
 #pragma unroll
@@ -196,7 +197,7 @@ __device__ __forceinline__ void gates_fetch(const Params& p, int b, int h, int b
             r->fr[t] = INFINITY;   // log_sigmoid(+inf) = 0: positions past a ragged end leave fc unchanged
             r->iv[t] = -INFINITY;
         }
-        cp_async4(&r->mt[t], p.msv + vec_index(p, b, h, bh, t0 + min(t, Lc - 1)));
+        cp_async4(&r->mt[t], p.msv + vec_index(p, b, h, bh, t0 + min(t, Lc - 1), seg));
     }
     if (lane == 0) {
         if (ch == 0) {
@@ -231,12 +232,12 @@ __device__ __forceinline__ void gates_compute(const GateRawS* r, Gates* G, int s
 }
 // Control warp: start the asynchronous copy of a chunk's psi, qn (64 each) and entering normaliser n (128)
 // straight into their shared-memory slot [psi 64 | qn 64 | n 128].
-__device__ __forceinline__ void vec_fetch(const Params& p, int bh, int sbh, int ch, float* dst) {
+__device__ __forceinline__ void vec_fetch(const Params& p, int bh, int sbh, int ch, float* dst, int seg) {
     const int lane = threadIdx.x & 31;
     const int t0 = ch * L, Lc = min(L, p.T - t0);
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-        const size_t o = vec_index(p, bh / p.H, bh % p.H, bh, t0 + min(lane + 32 * e, Lc - 1));
+        const size_t o = vec_index(p, bh / p.H, bh % p.H, bh, t0 + min(lane + 32 * e, Lc - 1), seg);
         cp_async4(dst + lane + 32 * e, p.psiv + o);
         cp_async4(dst + L + lane + 32 * e, p.qnv + o);
         if (p.dotv) cp_async4(dst + 2 * L + D + lane + 32 * e, p.dotv + o);
@@ -282,8 +283,11 @@ __device__ __forceinline__ int butterfly_index(int lane) {
 
 // GT: type of the upstream gradient dy; OT: type the gradients are written in (fp32 for sub-head partials).
 // WIDE: heads split into sub-heads; the 128 x 128 instantiation folds all of that indexing away.
-template <typename GT, typename OT, bool WIDE>
+// PACKED: the instantiation packed launches use; in the others the segment length is the constant 0 and the segmented
+// scans, the mask's second test and the vector index arithmetic fold away (left in, they cost the plain kernel 3 %).
+template <typename GT, typename OT, bool WIDE, bool PACKED>
 __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant__ Params p) {
+    const int seg = PACKED ? p.seg : 0;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -392,13 +396,13 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
     // ---- prologue -------------------------------------------------------------------------------
     if (is_ctrl) {
         if (lane == 0) { issue_qk(p.NC - 1, 0); issue_v_ck(p.NC - 1); }
-        gates_fetch(p, b, h, bh, p.NC - 1, &GR[(p.NC - 1) & 1]);
-        vec_fetch(p, bh, sbh, p.NC - 1, svec + ((p.NC - 1) & 1) * kVecFloats);
+        gates_fetch(p, b, h, bh, p.NC - 1, &GR[(p.NC - 1) & 1], seg);
+        vec_fetch(p, bh, sbh, p.NC - 1, svec + ((p.NC - 1) & 1) * kVecFloats, seg);
         cp_async_commit();
         cp_async_wait_all();
         __syncwarp();
-        gates_compute(&GR[(p.NC - 1) & 1], &G[(p.NC - 1) & 1], p.seg);
-        if (p.NC > 1) { gates_fetch(p, b, h, bh, p.NC - 2, &GR[(p.NC - 2) & 1]); cp_async_commit(); }
+        gates_compute(&GR[(p.NC - 1) & 1], &G[(p.NC - 1) & 1], seg);
+        if (p.NC > 1) { gates_fetch(p, b, h, bh, p.NC - 2, &GR[(p.NC - 2) & 1], seg); cp_async_commit(); }
     } else {
         prefetch_dy(p.NC - 1);
         // carry term of the forget-gate gradient: <dC_in, C_end> + dn_in . n_end
@@ -580,7 +584,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
                 // branch-free and on all lanes (lanes 16-31 hold no rows of an M = 64 tile; their values are not stored):
                 // the causal mask goes into the exponent's argument, exp(-inf) = 0
                 const float rt = Gc->rowt[srow], dq_t = sdqn[srow];
-                const int jmin = seg_first(srow, p.seg);  // packed mode: the row's own sequence only
+                const int jmin = seg_first(srow, seg);  // packed mode: the row's own sequence only
 #pragma unroll
                 for (int i4 = 0; i4 < 4; ++i4) {
                     const float4 c4 = *reinterpret_cast<const float4*>(Gc->colt + 16 * cq + 4 * i4);
@@ -588,7 +592,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int i = 4 * i4 + e, j = 16 * cq + i;
-                        const float dbar = __expf((j <= srow && j >= jmin) ? rt + cc[e] : -INFINITY);
+                        const float dbar = __expf((j <= srow && (!PACKED || j >= jmin)) ? rt + cc[e] : -INFINITY);
                         s[i] *= dbar;
                         dd[i] = dbar * (dd[i] + dq_t);
                     }
@@ -624,9 +628,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             if (ch > 0) {
                 cp_async_wait_all();  // raw gates of chunk ch-1, fetched during the previous chunk
                 __syncwarp();
-                gates_compute(&GR[(ch - 1) & 1], &G[(ch - 1) & 1], p.seg);
-                vec_fetch(p, bh, sbh, ch - 1, svec + ((ch - 1) & 1) * kVecFloats);
-                if (ch > 1) gates_fetch(p, b, h, bh, ch - 2, &GR[ch & 1]);
+                gates_compute(&GR[(ch - 1) & 1], &G[(ch - 1) & 1], seg);
+                vec_fetch(p, bh, sbh, ch - 1, svec + ((ch - 1) & 1) * kVecFloats, seg);
+                if (ch > 1) gates_fetch(p, b, h, bh, ch - 2, &GR[ch & 1], seg);
                 cp_async_commit();
             }
         } else {
@@ -738,7 +742,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlstm_bw_tc(const __grid_constant
             }
             // suffix sums over the 64 positions
             float s0 = dF[0], s1 = dF[1];
-            seg_suffix64(s0, s1, lane, p.seg);
+            seg_suffix64(s0, s1, lane, seg);
             const float tot = __shfl_sync(0xffffffffu, s0, 0);
             const float run = *srun;
             float sf[2] = {s0, s1};
@@ -878,7 +882,7 @@ size_t mlstm_tc_bw_workspace_bytes(int B, int H, int T, int dqk, int dhv) {
     return bw_planes(B, H, T, dqk, dhv).total;
 }
 
-template <typename GT, typename OT, bool WIDE>
+template <typename GT, typename OT, bool WIDE, bool PACKED = false>
 static int bw_launch_kernel(cudaStream_t st, const bw::Params& p, int ctas) {
     using namespace bw;
     // the opt-in to large dynamic shared memory is a per-device function attribute: one flag per device and instantiation
@@ -887,10 +891,10 @@ static int bw_launch_kernel(cudaStream_t st, const bw::Params& p, int ctas) {
     int dev = 0;
     XL_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
-        XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<GT, OT, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        XL_CUDA(cudaFuncSetAttribute(mlstm_bw_tc<GT, OT, WIDE, PACKED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
     }
-    mlstm_bw_tc<GT, OT, WIDE><<<ctas, kThreads, smem, st>>>(p);
+    mlstm_bw_tc<GT, OT, WIDE, PACKED><<<ctas, kThreads, smem, st>>>(p);
     XL_LAUNCH_OK("mlstm_bw_tc");
     return XLSTM_OK;
 }
@@ -926,6 +930,7 @@ int mlstm_bw_tc_launch(cudaStream_t st, const MlstmBwArgs& a, const void* saved,
     }
     p.status = tc_status_ptr();
     if (!p.status) { set_error("mlstm_bw: cannot resolve the device status word"); return XLSTM_ERR_CUDA; }
+    if (nsub == 1 && a.seg) return gbf ? bw_launch_kernel<bf16, bf16, false, true>(st, p, BH) : bw_launch_kernel<float, float, false, true>(st, p, BH);
     if (nsub == 1) return gbf ? bw_launch_kernel<bf16, bf16, false>(st, p, BH) : bw_launch_kernel<float, float, false>(st, p, BH);
 
     // wide heads: fp32 partial planes in the workspace, summed into the caller's buffers afterwards
