@@ -817,6 +817,15 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_grid_ps(SlstmArgs a, GridSm
     const bool own = tid < B * UPC;
     if (own && T > 0) fetch(tid, T - 1, pre);
     const size_t slab = (size_t)B * dhd;  // one CTA's partials for one step
+    // One output column per thread where the head's width is the CTA's thread count and the CTA owns 16 units (64 delta
+    // rows): the column's 64 weights stay in registers, the thread walks all rows itself and stores its sums straight to
+    // the exchange buffer: no k-slice partials in shared memory, no pass that adds them, one block barrier fewer.
+    const bool wcol_on = BG % 4 == 0 && NOUT == kThreads && K == 64;
+    float wcol[64];
+    if (wcol_on) {
+#pragma unroll
+        for (int k = 0; k < 64; ++k) wcol[k] = Ws[(size_t)k * NOUT + tid];
+    }
     bool ok = true;
     for (int t = T - 1; t >= 0 && ok; --t) {
         float* xw = xch + ((size_t)((t & 1) * NH + hd) * G) * slab;  // this step's partials of the head, [G][B][dhd]
@@ -855,10 +864,33 @@ __global__ void __launch_bounds__(kThreads) slstm_bw_grid_ps(SlstmArgs a, GridSm
                 xin[(size_t)(3 * UPC + ul) * BG + b] = c.dob;
             }
             __syncthreads();
+            const int nb = min(BG, B - b0);
+            if (BG % 4 == 0 && wcol_on) {
+                float2 acc2[(BG % 4 == 0 ? BG : 4) / 2];  // batch pairs: the staged row gives them as natural register pairs
+#pragma unroll
+                for (int i = 0; i < BG / 2; ++i) acc2[i] = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int k = 0; k < 64; ++k) {
+                    const float2 ww = make_float2(wcol[k], wcol[k]);
+#pragma unroll
+                    for (int b4 = 0; b4 < BG / 4; ++b4) {
+                        const float4 x = *reinterpret_cast<const float4*>(xin + (size_t)k * BG + 4 * b4);
+                        acc2[2 * b4] = __ffma2_rn(ww, make_float2(x.x, x.y), acc2[2 * b4]);
+                        acc2[2 * b4 + 1] = __ffma2_rn(ww, make_float2(x.z, x.w), acc2[2 * b4 + 1]);
+                    }
+                }
+                float* dstc = xw + (size_t)cr * slab + (size_t)b0 * dhd + tid;
+#pragma unroll
+                for (int i = 0; i < BG / 2; ++i) {
+                    if (2 * i < nb) __stcg(dstc + (size_t)(2 * i) * dhd, acc2[i].x);
+                    if (2 * i + 1 < nb) __stcg(dstc + (size_t)(2 * i + 1) * dhd, acc2[i].y);
+                }
+                __syncthreads();
+                continue;
+            }
             matvec<BG, 4>(Ws, xin, part, K, NOUT, a.KS);
             __syncthreads();
             // sum the k-slices and publish this CTA's partial dh for every unit of the head
-            const int nb = min(BG, B - b0);
             for (int e = tid; e < nb * (NOUT / 4); e += kThreads) {
                 const int b = e / (NOUT / 4), u4 = e % (NOUT / 4);
                 float4 acc = *reinterpret_cast<const float4*>(part + (size_t)b * NOUT + 4 * u4);
